@@ -1,0 +1,287 @@
+// Reference-kernel harness: TEST INFRASTRUCTURE ONLY, never linked into the product.
+//
+// Compiled against the reference's own kernel headers where they lie (passed with -I at build
+// time; nothing of the reference is copied into this repository), it launches each reference
+// training kernel with ONE warp on tiny seeded problems and dumps the resulting factors and
+// statistics.  The cuRAND state is seeded with a fixed value and a probe kernel records the
+// chunk start positions the training kernel will draw, so a CPU replay can follow exactly the
+// same sequence of updates.  The outputs become golden vectors for the CPU oracle.
+//
+// usage: ref_harness <harness_in.bin> <harness_out.bin>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <cstdint>
+#include <cmath>
+#include <map>
+#include <string>
+#include <vector>
+#include <iostream>
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <curand_kernel.h>
+
+#include "common.h"
+#include "common_struct.h"
+#include "reduce_kernel.h"
+#include "sgd_kernel.h"
+#include "sgd_kernel_k64.h"
+#include "mascot_sgd_kernel.h"
+#include "mascot_sgd_kernel_k64.h"
+#include "mpt_sgd_kernel.h"
+#include "mpt_sgd_kernel_k64.h"
+#include "muppet_sgd_kernel.h"
+#include "muppet_sgd_kernel_k64.h"
+#include "afp_sgd_kernel.h"
+#include "afp_sgd_kernel_k64.h"
+#include "rmse.h"
+
+#define CK(x) do { cudaError_t e_ = (x); if (e_ != cudaSuccess) { \
+    fprintf(stderr, "CUDA error %s at %s:%d\n", cudaGetErrorString(e_), __FILE__, __LINE__); exit(2); } } while (0)
+
+struct Entry { uint32_t dtype; std::vector<char> data; uint64_t n; };
+typedef std::map<std::string, Entry> Bundle;
+static const size_t kDtSize[] = {4, 4, 4, 2, 1, 8};
+
+static Bundle read_bundle(const char* path) {
+    Bundle b;
+    FILE* f = fopen(path, "rb");
+    if (!f) { fprintf(stderr, "cannot open %s\n", path); exit(2); }
+    char magic[4]; uint32_t count;
+    if (fread(magic, 1, 4, f) != 4 || memcmp(magic, "MSCB", 4) || fread(&count, 4, 1, f) != 1) exit(2);
+    for (uint32_t e = 0; e < count; e++) {
+        char name[48]; uint32_t hdr[2]; uint64_t n;
+        if (fread(name, 1, 48, f) != 48 || fread(hdr, 4, 2, f) != 2 || fread(&n, 8, 1, f) != 1) exit(2);
+        Entry en; en.dtype = hdr[0]; en.n = n;
+        size_t nb = n * kDtSize[hdr[0]];
+        en.data.resize(nb);
+        if (nb && fread(en.data.data(), 1, nb, f) != nb) exit(2);
+        fseek(f, (long)((8 - nb % 8) % 8), SEEK_CUR);
+        b[std::string(name)] = en;
+    }
+    fclose(f);
+    return b;
+}
+
+static void put(Bundle& b, const std::string& name, uint32_t dtype, const void* p, uint64_t n) {
+    Entry en; en.dtype = dtype; en.n = n;
+    en.data.assign((const char*)p, (const char*)p + n * kDtSize[dtype]);
+    b[name] = en;
+}
+
+static void write_bundle(const char* path, const Bundle& b) {
+    FILE* f = fopen(path, "wb");
+    if (!f) { fprintf(stderr, "cannot write %s\n", path); exit(2); }
+    uint32_t count = (uint32_t)b.size();
+    fwrite("MSCB", 1, 4, f); fwrite(&count, 4, 1, f);
+    for (auto& kv : b) {
+        char name[48]; memset(name, 0, 48); strncpy(name, kv.first.c_str(), 47);
+        uint32_t hdr[2] = {kv.second.dtype, 0};
+        fwrite(name, 1, 48, f); fwrite(hdr, 4, 2, f); fwrite(&kv.second.n, 8, 1, f);
+        size_t nb = kv.second.data.size();
+        if (nb) fwrite(kv.second.data.data(), 1, nb, f);
+        char pad[8] = {0}; fwrite(pad, 1, (8 - nb % 8) % 8, f);
+    }
+    fclose(f);
+}
+
+template <typename T> static const T* get(const Bundle& b, const std::string& name, uint64_t* n = nullptr) {
+    auto it = b.find(name);
+    if (it == b.end()) { fprintf(stderr, "missing entry %s\n", name.c_str()); exit(2); }
+    if (n) *n = it->second.n;
+    return (const T*)it->second.data.data();
+}
+
+__global__ void seed_state(curandState* st, int seed) { curand_init(seed, 0, 0, &st[0]); }
+
+// Draw the chunk starts exactly the way every reference training kernel does, on a COPY of the state.
+__global__ void probe_starts(const curandState* st, unsigned int nnz, int count, unsigned int* out) {
+    curandState s = st[0];
+    for (int c = 0; c < count; c++) {
+        unsigned int origin = (unsigned int)(curand_uniform(&s) * nnz);
+        out[c] = origin % nnz;
+    }
+}
+
+template <typename T> static T* to_dev(const T* h, size_t n) {
+    T* d; CK(cudaMalloc(&d, sizeof(T) * (n ? n : 1)));
+    if (n) CK(cudaMemcpy(d, h, sizeof(T) * n, cudaMemcpyHostToDevice));
+    return d;
+}
+
+int main(int argc, char** argv) {
+    if (argc < 3) { fprintf(stderr, "usage: %s in.bin out.bin\n", argv[0]); return 2; }
+    Bundle in = read_bundle(argv[1]);
+    Bundle out;
+    uint64_t ncs; const char* cs = get<char>(in, "cases", &ncs);
+    std::string all(cs, cs + ncs);
+    std::vector<std::string> cases;
+    size_t pos = 0;
+    while (pos <= all.size()) {
+        size_t nl = all.find('\n', pos);
+        if (nl == std::string::npos) nl = all.size();
+        if (nl > pos) cases.push_back(all.substr(pos, nl - pos));
+        pos = nl + 1;
+    }
+
+    for (auto& name : cases) {
+        const int* meta = get<int>(in, name + ".meta");
+        const float* hyper = get<float>(in, name + ".hyper");
+        int kind = meta[0], k = meta[1], n_users = meta[2], n_items = meta[3], nnz = meta[4];
+        int update_count = meta[5], vec = meta[6], first_sample = meta[7], seed = meta[8], extra0 = meta[9];
+        float lr = hyper[0], lam = hyper[1];
+        const Node* R = (const Node*)get<uint32_t>(in, name + ".R");
+        const float* P = get<float>(in, name + ".P");
+        const float* Q = get<float>(in, name + ".Q");
+        size_t np = (size_t)n_users * k, nq = (size_t)n_items * k;
+        Node* dR = to_dev(R, nnz);
+        std::vector<float> Pout(np), Qout(nq);
+        printf("case %-22s kind %d k %d users %d items %d nnz %d\n", name.c_str(), kind, k, n_users, n_items, nnz);
+
+        if (kind == 6) {  // test RMSE
+            float* dP = to_dev(P, np); float* dQ = to_dev(Q, nq);
+            unsigned int groups = (unsigned int)ceil(nnz / (float)512);
+            unsigned int iter_num = (unsigned int)ceil(nnz / (float)(512 * groups));
+            float* dE; CK(cudaMalloc(&dE, sizeof(float) * groups));
+            if (k == 128) get_test_rmse_coalesced_k128<<<groups, 512>>>(dR, dP, dQ, dE, iter_num, 32, nnz, k);
+            else get_test_rmse_coalesced_k64<<<groups, 512>>>(dR, dP, dQ, dE, iter_num, 32, nnz, k);
+            CK(cudaDeviceSynchronize());
+            std::vector<float> e(groups);
+            CK(cudaMemcpy(e.data(), dE, sizeof(float) * groups, cudaMemcpyDeviceToHost));
+            float sum = 0; for (unsigned int g = 0; g < groups; g++) sum += e[g];
+            float rmse = sqrt(sum / (double)nnz);
+            put(out, name + ".group_err", 0, e.data(), groups);
+            put(out, name + ".rmse", 0, &rmse, 1);
+            cudaFree(dP); cudaFree(dQ); cudaFree(dE); cudaFree(dR);
+            continue;
+        }
+
+        curandState* dState; CK(cudaMalloc(&dState, sizeof(curandState)));
+        seed_state<<<1, 1>>>(dState, seed);
+        unsigned int* dStarts; CK(cudaMalloc(&dStarts, sizeof(unsigned int) * update_count));
+        probe_starts<<<1, 1>>>(dState, nnz, update_count, dStarts);
+        CK(cudaDeviceSynchronize());
+        std::vector<unsigned int> starts(update_count);
+        CK(cudaMemcpy(starts.data(), dStarts, sizeof(unsigned int) * update_count, cudaMemcpyDeviceToHost));
+        put(out, name + ".start_ids", 1, starts.data(), update_count);
+
+        if (kind == 1) {  // MASCOT: grouped fp16/fp32 arenas
+            uint64_t ug, ig;
+            const unsigned int* uend = get<unsigned int>(in, name + ".uend", &ug);
+            const unsigned int* iend = get<unsigned int>(in, name + ".iend", &ig);
+            const unsigned char* uprec = get<unsigned char>(in, name + ".uprec");
+            const unsigned char* iprec = get<unsigned char>(in, name + ".iprec");
+            auto build = [&](const float* M, const unsigned int* end, const unsigned char* prec, int groups,
+                             std::vector<void*>& ptrs) {
+                int start = 0;
+                for (int g = 0; g < groups; g++) {
+                    size_t cnt = (size_t)(end[g] + 1 - start) * k;
+                    void* d;
+                    if (prec[g]) { d = to_dev(M + (size_t)start * k, cnt); }
+                    else {
+                        std::vector<__half> h(cnt);
+                        for (size_t j = 0; j < cnt; j++) h[j] = __float2half_rn(M[(size_t)start * k + j]);
+                        d = to_dev(h.data(), cnt);
+                    }
+                    ptrs.push_back(d);
+                    start = end[g] + 1;
+                }
+            };
+            std::vector<void*> up, ip;
+            build(P, uend, uprec, (int)ug, up); build(Q, iend, iprec, (int)ig, ip);
+            void** dUp = to_dev(up.data(), ug); void** dIp = to_dev(ip.data(), ig);
+            unsigned int* dUend = to_dev(uend, ug); unsigned int* dIend = to_dev(iend, ig);
+            unsigned char* dUprec = to_dev(uprec, ug); unsigned char* dIprec = to_dev(iprec, ig);
+            float *dGp, *dGq, *dNp, *dNq;
+            CK(cudaMalloc(&dGp, sizeof(float) * ug * k)); CK(cudaMemset(dGp, 0, sizeof(float) * ug * k));
+            CK(cudaMalloc(&dGq, sizeof(float) * ig * k)); CK(cudaMemset(dGq, 0, sizeof(float) * ig * k));
+            CK(cudaMalloc(&dNp, sizeof(float) * ug)); CK(cudaMalloc(&dNq, sizeof(float) * ig));
+            size_t smem = 16384;  // generous: the reference sizes this a few bytes short for > 62 groups
+            if (k == 128)
+                mascot_sgd_k128_hogwild_kernel<<<1, 32, smem>>>(dR, nnz, dUp, dIp, dState, lr, k, update_count, vec, lam,
+                    dUend, dIend, dUprec, dIprec, dGp, dGq, dNp, dNq, first_sample, (int)ug, (int)ig);
+            else
+                mascot_sgd_k64_hogwild_kernel<<<1, 32, smem>>>(dR, nnz, dUp, dIp, dState, lr, k, update_count, vec, lam,
+                    dUend, dIend, dUprec, dIprec, dGp, dGq, dNp, dNq, first_sample, (int)ug, (int)ig);
+            CK(cudaDeviceSynchronize());
+            auto fetch = [&](float* M, const unsigned int* end, const unsigned char* prec, int groups,
+                             std::vector<void*>& ptrs) {
+                int start = 0;
+                for (int g = 0; g < groups; g++) {
+                    size_t cnt = (size_t)(end[g] + 1 - start) * k;
+                    if (prec[g]) CK(cudaMemcpy(M + (size_t)start * k, ptrs[g], sizeof(float) * cnt, cudaMemcpyDeviceToHost));
+                    else {
+                        std::vector<__half> h(cnt);
+                        CK(cudaMemcpy(h.data(), ptrs[g], sizeof(__half) * cnt, cudaMemcpyDeviceToHost));
+                        for (size_t j = 0; j < cnt; j++) M[(size_t)start * k + j] = __half2float(h[j]);
+                    }
+                    start = end[g] + 1;
+                }
+            };
+            fetch(Pout.data(), uend, uprec, (int)ug, up); fetch(Qout.data(), iend, iprec, (int)ig, ip);
+            std::vector<float> gp(ug * k), gq(ig * k), nsp(ug), nsq(ig);
+            CK(cudaMemcpy(gp.data(), dGp, sizeof(float) * ug * k, cudaMemcpyDeviceToHost));
+            CK(cudaMemcpy(gq.data(), dGq, sizeof(float) * ig * k, cudaMemcpyDeviceToHost));
+            CK(cudaMemcpy(nsp.data(), dNp, sizeof(float) * ug, cudaMemcpyDeviceToHost));
+            CK(cudaMemcpy(nsq.data(), dNq, sizeof(float) * ig, cudaMemcpyDeviceToHost));
+            put(out, name + ".gsum_p", 0, gp.data(), ug * k); put(out, name + ".gsum_q", 0, gq.data(), ig * k);
+            put(out, name + ".nsum_p", 0, nsp.data(), ug); put(out, name + ".nsum_q", 0, nsq.data(), ig);
+            for (void* d : up) cudaFree(d);
+            for (void* d : ip) cudaFree(d);
+        } else if (kind == 3) {  // fp16 storage, fp32 arithmetic
+            std::vector<__half> hp(np), hq(nq);
+            for (size_t j = 0; j < np; j++) hp[j] = __float2half_rn(P[j]);
+            for (size_t j = 0; j < nq; j++) hq[j] = __float2half_rn(Q[j]);
+            __half* dP = to_dev(hp.data(), np); __half* dQ = to_dev(hq.data(), nq);
+            if (k == 128) mem_quant_sgd_k128_hogwild_kernel<<<1, 32>>>(dR, nnz, dP, dQ, dState, lr, k, 1, 0, update_count, vec, lam);
+            else mem_quant_sgd_k64_hogwild_kernel<<<1, 32>>>(dR, nnz, dP, dQ, dState, lr, k, 1, 0, update_count, vec, lam);
+            CK(cudaDeviceSynchronize());
+            CK(cudaMemcpy(hp.data(), dP, sizeof(__half) * np, cudaMemcpyDeviceToHost));
+            CK(cudaMemcpy(hq.data(), dQ, sizeof(__half) * nq, cudaMemcpyDeviceToHost));
+            for (size_t j = 0; j < np; j++) Pout[j] = __half2float(hp[j]);
+            for (size_t j = 0; j < nq; j++) Qout[j] = __half2float(hq[j]);
+            cudaFree(dP); cudaFree(dQ);
+        } else {
+            float* dP = to_dev(P, np); float* dQ = to_dev(Q, nq);
+            if (kind == 0) {
+                if (k == 128) single_sgd_k128_hogwild_kernel<<<1, 32>>>(dR, nnz, dP, dQ, dState, lr, k, update_count, vec, lam);
+                else single_sgd_k64_hogwild_kernel<<<1, 32>>>(dR, nnz, dP, dQ, dState, lr, k, update_count, vec, lam);
+            } else if (kind == 2) {
+                float scaling = 1000;
+                __half scaled_lambda = __float2half_rn(lam * scaling);
+                if (k == 128) mpt_sgd_k128_hogwild_kernel<<<1, 32>>>(dR, nnz, dP, dQ, dState, lr, k, update_count, vec, scaled_lambda, scaling);
+                else mpt_sgd_k64_hogwild_kernel<<<1, 32>>>(dR, nnz, dP, dQ, dState, lr, k, update_count, vec, scaled_lambda, scaling);
+            } else if (kind == 4) {
+                float *dSum, *dNorms;
+                CK(cudaMalloc(&dSum, sizeof(float) * k)); CK(cudaMemset(dSum, 0, sizeof(float) * k));
+                CK(cudaMalloc(&dNorms, sizeof(float)));
+                unsigned char bits = (unsigned char)extra0;
+                if (k == 128) muppet_sgd_k128_hogwild_kernel<<<1, 32>>>(dR, nnz, dP, dQ, dState, lr, k, update_count, vec, lam,
+                                                                        first_sample, dSum, dNorms, bits, bits);
+                else muppet_sgd_k64_hogwild_kernel<<<1, 32>>>(dR, nnz, dP, dQ, dState, lr, k, update_count, vec, lam,
+                                                              first_sample, dSum, dNorms, bits, bits);
+                CK(cudaDeviceSynchronize());
+                std::vector<float> s(k); float nrm;
+                CK(cudaMemcpy(s.data(), dSum, sizeof(float) * k, cudaMemcpyDeviceToHost));
+                CK(cudaMemcpy(&nrm, dNorms, sizeof(float), cudaMemcpyDeviceToHost));
+                put(out, name + ".sum_updated_val", 0, s.data(), k);
+                put(out, name + ".sum_norms", 0, &nrm, 1);
+                cudaFree(dSum); cudaFree(dNorms);
+            } else if (kind == 5) {
+                if (k == 128) afp_sgd_k128_hogwild_kernel<<<1, 32>>>(dR, nnz, dP, dQ, dState, lr, k, extra0, update_count, vec, lam);
+                else afp_sgd_k64_hogwild_kernel<<<1, 32>>>(dR, nnz, dP, dQ, dState, lr, k, extra0, update_count, vec, lam);
+            }
+            CK(cudaDeviceSynchronize());
+            CK(cudaMemcpy(Pout.data(), dP, sizeof(float) * np, cudaMemcpyDeviceToHost));
+            CK(cudaMemcpy(Qout.data(), dQ, sizeof(float) * nq, cudaMemcpyDeviceToHost));
+            cudaFree(dP); cudaFree(dQ);
+        }
+        CK(cudaGetLastError());
+        put(out, name + ".P_out", 0, Pout.data(), np);
+        put(out, name + ".Q_out", 0, Qout.data(), nq);
+        cudaFree(dR); cudaFree(dState); cudaFree(dStarts);
+    }
+    write_bundle(argv[2], out);
+    printf("wrote %s (%zu entries)\n", argv[2], out.size());
+    return 0;
+}
