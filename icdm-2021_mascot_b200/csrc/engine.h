@@ -1,0 +1,68 @@
+// Internal interface between the host control code (mascot_api.cu) and the kernels.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace mascot {
+
+// Structure-of-arrays rating stream.  u/i carry the row index in bits 0..30 and the storage
+// precision of that row in bit 31 (kPrecBit), so the hot loop needs no group lookup.
+struct Stream {
+    const float* r = nullptr;
+    const uint32_t* u = nullptr;
+    const uint32_t* i = nullptr;
+    uint64_t n = 0;
+};
+
+// Both arenas of one side exist for the whole run (rows at a fixed stride in each); a row is live
+// in exactly one of them, chosen by its group's precision.
+struct Arena {
+    __half* f16 = nullptr;
+    float* f32 = nullptr;
+};
+
+struct SampleStats {
+    const uint16_t* ugroup = nullptr;   // group of each sorted user index
+    const uint16_t* igroup = nullptr;
+    int ug = 0, ig = 0;
+    float* gsum_p = nullptr;            // [ug*K], physical element order inside each K-vector
+    float* gsum_q = nullptr;
+    float* nsum_p = nullptr;            // [ug]
+    float* nsum_q = nullptr;
+    uint64_t first_sample_pos = 0;      // stream positions >= this are sampled
+};
+
+enum TrainKind { KIND_MIXED = 0, KIND_FP32 = 1, KIND_MPT = 2, KIND_MEMQUANT = 3 };
+
+struct LaunchShape {
+    int grid = 0;
+    int block = 0;
+    size_t smem = 0;
+};
+
+// Update kernels.  `stats` == nullptr -> plain epoch.  Returns the launch shape used.
+cudaError_t launch_train(int K, TrainKind kind, const Stream& s, Arena P, Arena Q, float lr, float lam,
+                         const SampleStats* stats, bool deterministic, int grid_blocks_hint, cudaStream_t st,
+                         LaunchShape* shape);
+
+// Test RMSE over a coded SoA stream; block_err has ceil(n/512) floats.
+cudaError_t launch_rmse(int K, const Stream& t, Arena P, Arena Q, float* block_err, cudaStream_t st);
+// Test RMSE over plain fp32 rows in the reference element order and AoS ratings {r,u,i}.
+cudaError_t launch_rmse_plain(int K, const void* d_test_aos, uint64_t n, const float* P, const float* Q,
+                              float* block_err, cudaStream_t st);
+
+// Set-up / conversion kernels.
+cudaError_t launch_encode_stream(const void* d_src_aos, uint64_t n, bool shuffle, uint64_t seed,
+                                 const uint32_t* user_map, const uint32_t* item_map,
+                                 const uint8_t* uprec_row, const uint8_t* iprec_row,
+                                 float* r, uint32_t* u, uint32_t* i, cudaStream_t st);
+cudaError_t launch_recode(uint32_t* ids, uint64_t n, const uint8_t* prec_row, cudaStream_t st);
+cudaError_t launch_scatter_factors(int K, const float* src, uint32_t rows, const uint32_t* row_map,
+                                   bool round_through_half, __half* dst16, float* dst32, cudaStream_t st);
+cudaError_t launch_gather_factors(int K, Arena a, const uint8_t* prec_row, uint32_t rows,
+                                  const uint32_t* row_map, float* dst, cudaStream_t st);
+cudaError_t launch_promote_rows(int K, Arena a, uint32_t row_begin, uint32_t row_end, cudaStream_t st);
+cudaError_t launch_init_normal(float* dst, uint64_t count, uint64_t seed, uint64_t stream_id, cudaStream_t st);
+
+}  // namespace mascot

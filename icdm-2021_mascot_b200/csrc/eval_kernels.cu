@@ -1,0 +1,142 @@
+// Test-RMSE kernels.
+//
+// The reduction is the reference's, so the result is reproducible bit for bit: per rating an fp32
+// dot product (per-lane left-to-right product chain, then the 16-8-4-2-1 lane tree), the squared
+// error in fp32, a 512-entry pairwise tree per block of 512 consecutive test ratings
+// (get_test_rmse_coalesced_k128/k64, rmse.h:26-166), and a sequential float sum of the block
+// partials on the host (rmse.h:183-188).  Unlike the reference there is no device->host->device
+// round trip of the factors (mf_methods.cu:248-313, rmse.h:170-171): the kernel reads the
+// mixed-precision arenas in place.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "engine.h"
+#include "layout.cuh"
+
+namespace mascot {
+
+namespace {
+
+constexpr int kRmseBlock = 512;    // ratings per block partial (BLOCK_SIZE in rmse.h:3)
+constexpr int kRmseThreads = 256;
+
+__device__ __forceinline__ float block_tree_512(float* tmp) {
+    // tmp[j] += tmp[j+s] for s = 256 .. 1  (rmse.h:85-91 and warpReduce, rmse.h:5-24)
+    for (int s = 256; s >= 1; s >>= 1) {
+        __syncthreads();
+        for (int j = threadIdx.x; j < s; j += blockDim.x) tmp[j] = __fadd_rn(tmp[j], tmp[j + s]);
+    }
+    __syncthreads();
+    return tmp[0];
+}
+
+template <int K>
+__global__ void __launch_bounds__(kRmseThreads) rmse_kernel(const Stream t, const Arena P, const Arena Q, float* block_err) {
+    constexpr int T = K / 4;
+    __shared__ float tmp[kRmseBlock];
+    const int tl = threadIdx.x % T;
+    const int team = threadIdx.x / T;
+    constexpr int kTeams = kRmseThreads / T;
+    const unsigned mask = (T == 32) ? 0xffffffffu : (0xffffu << (16 * ((threadIdx.x >> 4) & 1)));
+    const uint64_t base = (uint64_t)blockIdx.x * kRmseBlock;
+    for (int j = team; j < kRmseBlock; j += kTeams) {
+        const uint64_t idx = base + j;
+        float err2 = 0.f;
+        if (idx < t.n) {
+            const float r = __ldg(t.r + idx);
+            const uint32_t uc = __ldg(t.u + idx), ic = __ldg(t.i + idx);
+            const uint32_t u = uc & kIdMask, i = ic & kIdMask;
+            float p[4], q[4];
+            if (uc & kPrecBit) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(P.f32 + (size_t)u * K) + tl);
+                p[0] = v.x; p[1] = v.y; p[2] = v.z; p[3] = v.w;
+            } else {
+                const uint2 v = __ldcg(reinterpret_cast<const uint2*>(P.f16 + (size_t)u * K) + tl);
+                const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
+                const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+                p[0] = lo.x; p[1] = lo.y; p[2] = hi.x; p[3] = hi.y;
+            }
+            if (ic & kPrecBit) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(Q.f32 + (size_t)i * K) + tl);
+                q[0] = v.x; q[1] = v.y; q[2] = v.z; q[3] = v.w;
+            } else {
+                const uint2 v = __ldcg(reinterpret_cast<const uint2*>(Q.f16 + (size_t)i * K) + tl);
+                const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
+                const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+                q[0] = lo.x; q[1] = lo.y; q[2] = hi.x; q[3] = hi.y;
+            }
+            float part;
+            if (K == 128) {
+                part = __fmaf_rn(p[0], q[0], __fmul_rn(p[1], q[1]));
+                part = __fmaf_rn(p[2], q[2], part);
+                part = __fmaf_rn(p[3], q[3], part);
+            } else {
+                part = __fadd_rn(__fmaf_rn(p[0], q[0], __fmul_rn(p[1], q[1])), __fmaf_rn(p[2], q[2], __fmul_rn(p[3], q[3])));
+            }
+            part = __fadd_rn(part, __shfl_xor_sync(mask, part, 1));
+#pragma unroll
+            for (int d = T / 2; d >= 2; d >>= 1) part = __fadd_rn(part, __shfl_xor_sync(mask, part, d));
+            const float e = __fsub_rn(r, part);
+            err2 = __fmul_rn(e, e);
+        }
+        if (tl == 0) tmp[j] = err2;
+    }
+    const float s = block_tree_512(tmp);
+    if (threadIdx.x == 0) block_err[blockIdx.x] = s;
+}
+
+struct NodeAos { float r; uint32_t u; uint32_t i; };
+
+// Plain fp32 rows in the reference's own element order: lane l reads elements l, l+32, ...
+template <int K>
+__global__ void __launch_bounds__(kRmseThreads) rmse_plain_kernel(const NodeAos* t, uint64_t n, const float* P, const float* Q, float* block_err) {
+    __shared__ float tmp[kRmseBlock];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr int kWarps = kRmseThreads / 32;
+    const uint64_t base = (uint64_t)blockIdx.x * kRmseBlock;
+    for (int j = warp; j < kRmseBlock; j += kWarps) {
+        const uint64_t idx = base + j;
+        float err2 = 0.f;
+        if (idx < n) {
+            const float r = __ldg(&t[idx].r);
+            const float* p = P + (size_t)__ldg(&t[idx].u) * K;
+            const float* q = Q + (size_t)__ldg(&t[idx].i) * K;
+            float part = __fmaf_rn(p[lane], q[lane], __fmul_rn(p[lane + 32], q[lane + 32]));
+            if (K == 128) {
+                part = __fmaf_rn(p[lane + 64], q[lane + 64], part);
+                part = __fmaf_rn(p[lane + 96], q[lane + 96], part);
+            }
+#pragma unroll
+            for (int d = 16; d >= 1; d >>= 1) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, d));
+            const float e = __fsub_rn(r, part);
+            err2 = __fmul_rn(e, e);
+        }
+        if (lane == 0) tmp[j] = err2;
+    }
+    const float s = block_tree_512(tmp);
+    if (threadIdx.x == 0) block_err[blockIdx.x] = s;
+}
+
+}  // namespace
+
+cudaError_t launch_rmse(int K, const Stream& t, Arena P, Arena Q, float* block_err, cudaStream_t st) {
+    if (t.n == 0) return cudaSuccess;
+    const unsigned blocks = (unsigned)((t.n + kRmseBlock - 1) / kRmseBlock);
+    if (K == 128) rmse_kernel<128><<<blocks, kRmseThreads, 0, st>>>(t, P, Q, block_err);
+    else if (K == 64) rmse_kernel<64><<<blocks, kRmseThreads, 0, st>>>(t, P, Q, block_err);
+    else return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_rmse_plain(int K, const void* d_test_aos, uint64_t n, const float* P, const float* Q,
+                              float* block_err, cudaStream_t st) {
+    if (n == 0) return cudaSuccess;
+    const unsigned blocks = (unsigned)((n + kRmseBlock - 1) / kRmseBlock);
+    const NodeAos* t = static_cast<const NodeAos*>(d_test_aos);
+    if (K == 128) rmse_plain_kernel<128><<<blocks, kRmseThreads, 0, st>>>(t, n, P, Q, block_err);
+    else if (K == 64) rmse_plain_kernel<64><<<blocks, kRmseThreads, 0, st>>>(t, n, P, Q, block_err);
+    else return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
+
+}  // namespace mascot

@@ -1,0 +1,654 @@
+// libmascot: host control code behind the C ABI of include/mascot.h.
+//
+// One handle = one GPU, one stream, one host control thread (like the reference: a single thread
+// driving the default stream with a synchronisation after each epoch, mf_methods.cu:239).  The
+// m-quantization set-up (degree sort, grouping, id maps) runs once on the host; everything per
+// epoch runs on the device and only the small group statistics travel back on check epochs.
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+#include <cuda_runtime.h>
+
+#include "../../include/mascot.h"
+#include "engine.h"
+#include "layout.cuh"
+
+using namespace mascot;
+
+struct mascot_handle {
+    mascot_config cfg;
+    int K = 0;
+    TrainKind kind = KIND_MIXED;
+    bool grouped = false;          // m-quantization / g-switching active (MASCOT variant)
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
+
+    uint32_t n_users = 0, n_items = 0;
+    uint64_t n_train = 0, n_test = 0;
+    bool have_ratings = false, have_factors = false;
+
+    // device
+    float* tr_r = nullptr; uint32_t* tr_u = nullptr; uint32_t* tr_i = nullptr;
+    float* te_r = nullptr; uint32_t* te_u = nullptr; uint32_t* te_i = nullptr;
+    Arena P, Q;
+    uint8_t* d_uprec_row = nullptr; uint8_t* d_iprec_row = nullptr;
+    uint16_t* d_ugroup = nullptr; uint16_t* d_igroup = nullptr;
+    uint32_t* d_umap = nullptr; uint32_t* d_imap = nullptr;
+    float* d_stats = nullptr;       // gsum_p | gsum_q | nsum_p | nsum_q
+    float* d_block_err = nullptr;
+    float* d_scratch = nullptr; size_t scratch_bytes = 0;
+
+    // host
+    std::vector<uint32_t> user2sorted, item2sorted, uend, iend;
+    std::vector<uint8_t> uprec, iprec;
+    std::vector<float> uerr, ierr, init_uerr, init_ierr;
+    std::vector<float> lr;
+    std::vector<float> h_stats;     // same layout as d_stats, gsum in LOGICAL element order
+    std::vector<float> h_block_err;
+    std::string err;
+};
+
+namespace {
+
+thread_local std::string g_create_error;
+
+int fail(mascot_handle* h, int code, const std::string& msg) {
+    if (h) h->err = msg; else g_create_error = msg;
+    return code;
+}
+
+#define CU(h, call)                                                                               \
+    do {                                                                                          \
+        cudaError_t e_ = (call);                                                                  \
+        if (e_ != cudaSuccess) {                                                                  \
+            char buf_[512];                                                                       \
+            snprintf(buf_, sizeof buf_, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, __LINE__); \
+            return fail(h, e_ == cudaErrorMemoryAllocation ? MASCOT_ERR_OOM : MASCOT_ERR_CUDA, buf_); \
+        }                                                                                         \
+    } while (0)
+
+template <typename T>
+cudaError_t dev_alloc(T** p, size_t count) {
+    return cudaMalloc(reinterpret_cast<void**>(p), sizeof(T) * (count ? count : 1));
+}
+
+template <typename T>
+void dev_free(T*& p) { if (p) { cudaFree(p); p = nullptr; } }
+
+void free_ratings(mascot_handle* h) {
+    dev_free(h->tr_r); dev_free(h->tr_u); dev_free(h->tr_i);
+    dev_free(h->te_r); dev_free(h->te_u); dev_free(h->te_i);
+    dev_free(h->P.f16); dev_free(h->P.f32); dev_free(h->Q.f16); dev_free(h->Q.f32);
+    dev_free(h->d_uprec_row); dev_free(h->d_iprec_row); dev_free(h->d_ugroup); dev_free(h->d_igroup);
+    dev_free(h->d_umap); dev_free(h->d_imap); dev_free(h->d_stats); dev_free(h->d_block_err);
+    h->have_ratings = h->have_factors = false;
+}
+
+// mf_methods.cu:94-97: evaluated in double, stored as float.
+float lr_at(const mascot_config& c, uint32_t e) {
+    return (float)((double)c.learning_rate / (1.0 + ((double)c.decay * std::pow((double)e, 1.5))));
+}
+
+// mf_methods.cu:168-175: first check at epoch index 5, then every `interval`, never the last epoch.
+bool is_check_epoch(const mascot_config& c, uint32_t e) {
+    const uint32_t start_idx = 5;
+    const uint32_t it = c.interval ? c.interval : 1;
+    return e >= start_idx && (e % it == start_idx % it) && (c.epoch - 1 != e);
+}
+
+// user_item_rating_histogram (preprocess_utils.h:54-99): degree histogram, then ascending sort by
+// degree, ties in ascending id order.  Returns sorted2orig and the sorted degree list.
+void degree_sort(const mascot_rating* R, uint64_t n, bool users, uint32_t n_entities,
+                 std::vector<uint32_t>& sorted2orig, std::vector<uint32_t>& orig2sorted, std::vector<uint32_t>& cnt_sorted) {
+    std::vector<uint32_t> cnt(n_entities, 0);
+    for (uint64_t j = 0; j < n; j++) cnt[users ? R[j].u : R[j].i]++;
+    uint32_t maxc = 0;
+    for (uint32_t e = 0; e < n_entities; e++) maxc = std::max(maxc, cnt[e]);
+    std::vector<uint64_t> start((size_t)maxc + 2, 0);
+    for (uint32_t e = 0; e < n_entities; e++) start[cnt[e] + 1]++;
+    for (uint32_t c = 0; c <= maxc; c++) start[c + 1] += start[c];
+    sorted2orig.resize(n_entities); orig2sorted.resize(n_entities); cnt_sorted.resize(n_entities);
+    for (uint32_t e = 0; e < n_entities; e++) {
+        const uint64_t pos = start[cnt[e]]++;
+        sorted2orig[pos] = e; orig2sorted[e] = (uint32_t)pos; cnt_sorted[pos] = cnt[e];
+    }
+}
+
+// split_group_based_equal_size_not_strict_ret_end_idx (preprocess_utils.h:101-213): target size
+// T = ceil(N / requested); walk the distinct degrees upward counting entities; close a group at the
+// last entity of a degree class once the count reaches T; always close one at the top degree.
+void make_groups(const std::vector<uint32_t>& cnt_sorted, uint32_t requested, std::vector<uint32_t>& end_idx) {
+    end_idx.clear();
+    const uint32_t n = (uint32_t)cnt_sorted.size();
+    if (!n) return;
+    const uint32_t threshold = (uint32_t)std::ceil((float)n / (float)(requested ? requested : 1));
+    const uint32_t max_cnt = cnt_sorted[n - 1];
+    uint32_t acc = 0, pos = 0, prev = 0;
+    while (pos < n) {
+        const uint32_t c = cnt_sorted[pos];
+        uint32_t last = pos;
+        while (last + 1 < n && cnt_sorted[last + 1] == c) last++;
+        if (c >= 1) {   // the reference's walk starts at degree 1 (preprocess_utils.h:139)
+            acc += last - prev + 1;
+            if (acc >= threshold) { end_idx.push_back(last); acc = 0; }
+            else if (c == max_cnt) end_idx.push_back(last);
+            prev = last + 1;
+        }
+        pos = last + 1;
+    }
+    if (end_idx.empty() || end_idx.back() != n - 1) end_idx.push_back(n - 1);   // only when every degree is 0
+}
+
+size_t stats_floats(const mascot_handle* h) {
+    return (size_t)(h->uend.size() + h->iend.size()) * (h->K + 1);
+}
+
+int upload_side_tables(mascot_handle* h, bool users) {
+    const uint32_t n = users ? h->n_users : h->n_items;
+    const std::vector<uint32_t>& end = users ? h->uend : h->iend;
+    const std::vector<uint8_t>& prec = users ? h->uprec : h->iprec;
+    std::vector<uint16_t> group(n);
+    std::vector<uint8_t> prow(n);
+    uint32_t s = 0;
+    for (size_t g = 0; g < end.size(); g++)
+        for (; s <= end[g] && s < n; s++) { group[s] = (uint16_t)g; prow[s] = prec[g]; }
+    uint16_t** dg = users ? &h->d_ugroup : &h->d_igroup;
+    uint8_t** dp = users ? &h->d_uprec_row : &h->d_iprec_row;
+    CU(h, dev_alloc(dg, n)); CU(h, dev_alloc(dp, n));
+    CU(h, cudaMemcpyAsync(*dg, group.data(), sizeof(uint16_t) * n, cudaMemcpyHostToDevice, h->stream));
+    CU(h, cudaMemcpyAsync(*dp, prow.data(), sizeof(uint8_t) * n, cudaMemcpyHostToDevice, h->stream));
+    CU(h, cudaStreamSynchronize(h->stream));
+    return MASCOT_OK;
+}
+
+int upload_and_encode(mascot_handle* h, const mascot_rating* src, uint64_t n, bool shuffle,
+                      float** r, uint32_t** u, uint32_t** i) {
+    CU(h, dev_alloc(r, n)); CU(h, dev_alloc(u, n)); CU(h, dev_alloc(i, n));
+    if (!n) return MASCOT_OK;
+    mascot_rating* tmp = nullptr;
+    CU(h, dev_alloc(&tmp, n));
+    cudaError_t e = cudaMemcpyAsync(tmp, src, sizeof(mascot_rating) * n, cudaMemcpyHostToDevice, h->stream);
+    if (e == cudaSuccess)
+        e = launch_encode_stream(tmp, n, shuffle, h->cfg.seed, h->d_umap, h->d_imap, h->d_uprec_row, h->d_iprec_row,
+                                 *r, *u, *i, h->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
+    cudaFree(tmp);
+    CU(h, e);
+    return MASCOT_OK;
+}
+
+// One group fp16 -> fp32 (precision_switching.h:12-27): widen its rows into the fp32 arena and flip
+// the per-row precision bytes; the stream ids are re-tagged afterwards by recode_side().
+int promote_group(mascot_handle* h, bool users, size_t g) {
+    const std::vector<uint32_t>& end = users ? h->uend : h->iend;
+    std::vector<uint8_t>& prec = users ? h->uprec : h->iprec;
+    uint8_t* prow = users ? h->d_uprec_row : h->d_iprec_row;
+    const uint32_t b = g ? end[g - 1] + 1 : 0, e = end[g] + 1;
+    CU(h, launch_promote_rows(h->K, users ? h->P : h->Q, b, e, h->stream));
+    CU(h, cudaMemsetAsync(prow + b, 1, e - b, h->stream));
+    prec[g] = 1;
+    return MASCOT_OK;
+}
+
+int recode_side(mascot_handle* h, bool users) {
+    const uint8_t* prow = users ? h->d_uprec_row : h->d_iprec_row;
+    CU(h, launch_recode(users ? h->tr_u : h->tr_i, h->n_train, prow, h->stream));
+    CU(h, launch_recode(users ? h->te_u : h->te_i, h->n_test, prow, h->stream));
+    return MASCOT_OK;
+}
+
+float reference_rmse_from_partials(const std::vector<float>& part, uint64_t n) {
+    float sum = 0;                                  // rmse.h:183-186: float accumulation in block order
+    for (float v : part) sum += v;
+    return (float)std::sqrt(sum / (double)n);       // rmse.h:188, returned through a float
+}
+
+}  // namespace
+
+extern "C" {
+
+int mascot_abi_info(uint32_t* abi_version, uint32_t* config_bytes, uint32_t* epoch_stats_bytes) {
+    if (abi_version) *abi_version = MASCOT_ABI_VERSION;
+    if (config_bytes) *config_bytes = (uint32_t)sizeof(mascot_config);
+    if (epoch_stats_bytes) *epoch_stats_bytes = (uint32_t)sizeof(mascot_epoch_stats);
+    return MASCOT_OK;
+}
+
+int mascot_config_default(mascot_config* cfg) {
+    if (!cfg) return MASCOT_ERR_BAD_ARG;
+    std::memset(cfg, 0, sizeof(*cfg));
+    cfg->lambda = 0.015f; cfg->learning_rate = 0.01f; cfg->decay = 0.1f; cfg->sample_ratio = 0.01f;
+    cfg->error_threshold = 0.001f; cfg->interval = 1; cfg->user_group_num = 10; cfg->item_group_num = 10;
+    cfg->k = 128; cfg->num_workers = 2048; cfg->epoch = 50; cfg->thread_block_size = 128; cfg->version = 7;
+    cfg->shuffle = 1; cfg->seed = 1; cfg->device = 0;
+    return MASCOT_OK;
+}
+
+const char* mascot_status_string(int s) {
+    switch (s) {
+        case MASCOT_OK: return "ok";
+        case MASCOT_ERR_BAD_ARG: return "bad argument";
+        case MASCOT_ERR_CUDA: return "CUDA error";
+        case MASCOT_ERR_OOM: return "out of memory";
+        case MASCOT_ERR_STATE: return "call order violated";
+        case MASCOT_ERR_NO_DEVICE: return "no usable CUDA device";
+        case MASCOT_ERR_TIMEOUT: return "timed out";
+        case MASCOT_ERR_UNSUPPORTED: return "unsupported";
+        case MASCOT_ERR_COMM: return "communication failure";
+    }
+    return "unknown status";
+}
+
+const char* mascot_last_error(const mascot_handle* h) { return h ? h->err.c_str() : g_create_error.c_str(); }
+
+int mascot_create(const mascot_config* cfg, mascot_handle** out) {
+    if (!cfg || !out) return fail(nullptr, MASCOT_ERR_BAD_ARG, "null config or output pointer");
+    *out = nullptr;
+    if (cfg->k != 64 && cfg->k != 128) return fail(nullptr, MASCOT_ERR_BAD_ARG, "k must be 64 or 128");
+    if (cfg->epoch == 0) return fail(nullptr, MASCOT_ERR_BAD_ARG, "epoch count must be positive");
+    TrainKind kind;
+    switch (cfg->version) {
+        case MASCOT_V_MASCOT: kind = KIND_MIXED; break;
+        case MASCOT_V_SGD: kind = KIND_FP32; break;
+        case MASCOT_V_MPT: kind = KIND_MPT; break;
+        case MASCOT_V_MEMQUANT: kind = KIND_MEMQUANT; break;
+        case MASCOT_V_AFP: case MASCOT_V_MUPPET:
+            return fail(nullptr, MASCOT_ERR_UNSUPPORTED, "AFP / MuPPET trainers are not implemented by this engine yet");
+        default: return fail(nullptr, MASCOT_ERR_BAD_ARG, "unknown training variant");
+    }
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev <= 0) {
+        cudaGetLastError();
+        return fail(nullptr, MASCOT_ERR_NO_DEVICE, "no CUDA device is visible; libmascot has no CPU path");
+    }
+    if (cfg->device < 0 || cfg->device >= ndev) return fail(nullptr, MASCOT_ERR_NO_DEVICE, "requested CUDA device does not exist");
+    mascot_handle* h = new (std::nothrow) mascot_handle();
+    if (!h) return fail(nullptr, MASCOT_ERR_OOM, "host allocation failed");
+    h->cfg = *cfg; h->K = (int)cfg->k; h->kind = kind; h->grouped = (cfg->version == MASCOT_V_MASCOT);
+    h->lr.resize(cfg->epoch);
+    for (uint32_t e = 0; e < cfg->epoch; e++) h->lr[e] = lr_at(*cfg, e);
+    cudaError_t e = cudaSetDevice(cfg->device);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking);
+    for (int j = 0; j < 4 && e == cudaSuccess; j++) e = cudaEventCreate(&h->ev[j]);
+    if (e != cudaSuccess) {
+        std::string msg = std::string("CUDA set-up failed: ") + cudaGetErrorString(e);
+        mascot_destroy(h);
+        return fail(nullptr, MASCOT_ERR_CUDA, msg);
+    }
+    *out = h;
+    return MASCOT_OK;
+}
+
+int mascot_destroy(mascot_handle* h) {
+    if (!h) return MASCOT_OK;
+    cudaSetDevice(h->cfg.device);
+    free_ratings(h);
+    dev_free(h->d_scratch);
+    for (auto& ev : h->ev) if (ev) cudaEventDestroy(ev);
+    if (h->stream) cudaStreamDestroy(h->stream);
+    delete h;
+    return MASCOT_OK;
+}
+
+int mascot_set_ratings(mascot_handle* h, const mascot_rating* train, uint64_t n_train,
+                       const mascot_rating* test, uint64_t n_test, uint32_t n_users, uint32_t n_items) {
+    if (!h) return MASCOT_ERR_BAD_ARG;
+    if ((!train && n_train) || (!test && n_test)) return fail(h, MASCOT_ERR_BAD_ARG, "null rating array");
+    if (!n_users || !n_items || n_users > kIdMask || n_items > kIdMask) return fail(h, MASCOT_ERR_BAD_ARG, "user/item count out of range");
+    if (n_train >= (1ull << 40)) return fail(h, MASCOT_ERR_BAD_ARG, "too many ratings");
+    for (uint64_t j = 0; j < n_train; j++)
+        if (train[j].u >= n_users || train[j].i >= n_items) return fail(h, MASCOT_ERR_BAD_ARG, "training rating with id out of range");
+    for (uint64_t j = 0; j < n_test; j++)
+        if (test[j].u >= n_users || test[j].i >= n_items) return fail(h, MASCOT_ERR_BAD_ARG, "test rating with id out of range");
+    CU(h, cudaSetDevice(h->cfg.device));
+    free_ratings(h);
+    h->n_users = n_users; h->n_items = n_items; h->n_train = n_train; h->n_test = n_test;
+
+    // --- m-quantization set-up on the host (one-off) ---
+    if (h->grouped) {
+        std::vector<uint32_t> s2o, cnt;
+        degree_sort(train, n_train, true, n_users, s2o, h->user2sorted, cnt);
+        make_groups(cnt, h->cfg.user_group_num, h->uend);
+        degree_sort(train, n_train, false, n_items, s2o, h->item2sorted, cnt);
+        make_groups(cnt, h->cfg.item_group_num, h->iend);
+        if (h->uend.size() > 65535 || h->iend.size() > 65535) return fail(h, MASCOT_ERR_BAD_ARG, "more than 65535 groups");
+        h->uprec.assign(h->uend.size(), 0); h->iprec.assign(h->iend.size(), 0);
+    } else {
+        h->user2sorted.clear(); h->item2sorted.clear();
+        h->uend.assign(1, n_users - 1); h->iend.assign(1, n_items - 1);
+        const uint8_t p = (h->kind == KIND_MEMQUANT) ? 0 : 1;
+        h->uprec.assign(1, p); h->iprec.assign(1, p);
+    }
+    h->uerr.assign(h->uend.size(), 0.f); h->ierr.assign(h->iend.size(), 0.f);
+    h->init_uerr.assign(h->uend.size(), 1.f); h->init_ierr.assign(h->iend.size(), 1.f);   // mf_methods.cu:150-151
+
+    int rc;
+    if ((rc = upload_side_tables(h, true)) != MASCOT_OK) return rc;
+    if ((rc = upload_side_tables(h, false)) != MASCOT_OK) return rc;
+    if (h->grouped) {
+        CU(h, dev_alloc(&h->d_umap, n_users)); CU(h, dev_alloc(&h->d_imap, n_items));
+        CU(h, cudaMemcpy(h->d_umap, h->user2sorted.data(), sizeof(uint32_t) * n_users, cudaMemcpyHostToDevice));
+        CU(h, cudaMemcpy(h->d_imap, h->item2sorted.data(), sizeof(uint32_t) * n_items, cudaMemcpyHostToDevice));
+    }
+
+    // --- rating streams ---
+    if ((rc = upload_and_encode(h, train, n_train, h->cfg.shuffle != 0, &h->tr_r, &h->tr_u, &h->tr_i)) != MASCOT_OK) return rc;
+    {
+        // test_set_preprocess (preprocess_utils.h:38-52) leaves the test set ordered by (user, item)
+        std::vector<mascot_rating> t(test, test + n_test);
+        std::sort(t.begin(), t.end(), [](const mascot_rating& a, const mascot_rating& b) {
+            return a.u != b.u ? a.u < b.u : a.i < b.i;
+        });
+        if ((rc = upload_and_encode(h, t.data(), n_test, false, &h->te_r, &h->te_u, &h->te_i)) != MASCOT_OK) return rc;
+    }
+
+    // --- factor arenas and statistics ---
+    const size_t pu = (size_t)n_users * h->K, qi = (size_t)n_items * h->K;
+    if (h->kind == KIND_MIXED || h->kind == KIND_MEMQUANT) { CU(h, dev_alloc(&h->P.f16, pu)); CU(h, dev_alloc(&h->Q.f16, qi)); }
+    if (h->kind != KIND_MEMQUANT) { CU(h, dev_alloc(&h->P.f32, pu)); CU(h, dev_alloc(&h->Q.f32, qi)); }
+    CU(h, dev_alloc(&h->d_stats, stats_floats(h)));
+    CU(h, cudaMemset(h->d_stats, 0, sizeof(float) * stats_floats(h)));
+    h->h_stats.assign(stats_floats(h), 0.f);
+    const size_t blocks = (size_t)((n_test + 511) / 512);
+    CU(h, dev_alloc(&h->d_block_err, blocks));
+    h->h_block_err.assign(blocks, 0.f);
+    h->have_ratings = true;
+    return MASCOT_OK;
+}
+
+static int scatter_from_device(mascot_handle* h, const float* dP, const float* dQ) {
+    const bool through_half = (h->kind == KIND_MPT);   // MPT masters start from fp16 values (mf_methods.cu:730-733)
+    CU(h, launch_scatter_factors(h->K, dP, h->n_users, h->d_umap, through_half, h->P.f16, h->P.f32, h->stream));
+    CU(h, launch_scatter_factors(h->K, dQ, h->n_items, h->d_imap, through_half, h->Q.f16, h->Q.f32, h->stream));
+    CU(h, cudaStreamSynchronize(h->stream));
+    h->have_factors = true;
+    return MASCOT_OK;
+}
+
+int mascot_set_factors(mascot_handle* h, const float* P, const float* Q) {
+    if (!h) return MASCOT_ERR_BAD_ARG;
+    if (!P || !Q) return fail(h, MASCOT_ERR_BAD_ARG, "null factor matrix");
+    if (!h->have_ratings) return fail(h, MASCOT_ERR_STATE, "mascot_set_ratings must come first");
+    CU(h, cudaSetDevice(h->cfg.device));
+    const size_t pu = (size_t)h->n_users * h->K, qi = (size_t)h->n_items * h->K;
+    float *dP = nullptr, *dQ = nullptr;
+    CU(h, dev_alloc(&dP, pu));
+    cudaError_t e = dev_alloc(&dQ, qi);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(dP, P, sizeof(float) * pu, cudaMemcpyHostToDevice, h->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(dQ, Q, sizeof(float) * qi, cudaMemcpyHostToDevice, h->stream);
+    int rc = MASCOT_OK;
+    if (e == cudaSuccess) rc = scatter_from_device(h, dP, dQ);
+    cudaFree(dP); cudaFree(dQ);
+    CU(h, e);
+    return rc;
+}
+
+int mascot_init_factors(mascot_handle* h) {
+    if (!h) return MASCOT_ERR_BAD_ARG;
+    if (!h->have_ratings) return fail(h, MASCOT_ERR_STATE, "mascot_set_ratings must come first");
+    CU(h, cudaSetDevice(h->cfg.device));
+    const size_t pu = (size_t)h->n_users * h->K, qi = (size_t)h->n_items * h->K;
+    float *dP = nullptr, *dQ = nullptr;
+    CU(h, dev_alloc(&dP, pu));
+    cudaError_t e = dev_alloc(&dQ, qi);
+    if (e == cudaSuccess) e = launch_init_normal(dP, pu, h->cfg.seed, 1, h->stream);
+    if (e == cudaSuccess) e = launch_init_normal(dQ, qi, h->cfg.seed, 2, h->stream);
+    int rc = MASCOT_OK;
+    if (e == cudaSuccess) rc = scatter_from_device(h, dP, dQ);
+    cudaFree(dP); cudaFree(dQ);
+    CU(h, e);
+    return rc;
+}
+
+int mascot_train_epoch(mascot_handle* h, uint32_t epoch, mascot_epoch_stats* out) {
+    if (!h) return MASCOT_ERR_BAD_ARG;
+    if (!h->have_ratings || !h->have_factors) return fail(h, MASCOT_ERR_STATE, "ratings and factors must be set before training");
+    CU(h, cudaSetDevice(h->cfg.device));
+    const float lr = epoch < h->lr.size() ? h->lr[epoch] : lr_at(h->cfg, epoch);
+    const bool check = h->grouped && is_check_epoch(h->cfg, epoch);
+    const int ug = (int)h->uend.size(), ig = (int)h->iend.size(), K = h->K;
+    uint32_t launches = 0, promoted_u = 0, promoted_i = 0;
+
+    Stream s; s.r = h->tr_r; s.u = h->tr_u; s.i = h->tr_i; s.n = h->n_train;
+    SampleStats st;
+    if (check) {
+        // sampled tail of the epoch (mf_methods.cu:102-103, 173-174)
+        const uint64_t sample_num = (uint64_t)((float)h->n_train * h->cfg.sample_ratio);
+        st.first_sample_pos = h->n_train - std::min<uint64_t>(sample_num, h->n_train);
+        st.ugroup = h->d_ugroup; st.igroup = h->d_igroup; st.ug = ug; st.ig = ig;
+        st.gsum_p = h->d_stats; st.gsum_q = st.gsum_p + (size_t)ug * K;
+        st.nsum_p = st.gsum_q + (size_t)ig * K; st.nsum_q = st.nsum_p + ug;
+    }
+    CU(h, cudaEventRecord(h->ev[0], h->stream));
+    if (check) CU(h, cudaMemsetAsync(h->d_stats, 0, sizeof(float) * stats_floats(h), h->stream));   // mf_methods.cu:178-182
+    CU(h, cudaEventRecord(h->ev[1], h->stream));
+    LaunchShape shape;
+    CU(h, launch_train(K, h->kind, s, h->P, h->Q, lr, h->cfg.lambda, check ? &st : nullptr,
+                       h->cfg.deterministic != 0, (int)h->cfg.grid_blocks, h->stream, &shape));
+    launches++;
+    CU(h, cudaEventRecord(h->ev[2], h->stream));
+
+    if (check) {
+        std::vector<float> raw(stats_floats(h));
+        CU(h, cudaMemcpyAsync(raw.data(), h->d_stats, sizeof(float) * raw.size(), cudaMemcpyDeviceToHost, h->stream));
+        CU(h, cudaStreamSynchronize(h->stream));
+        // gradient sums come back in physical element order; the host loop below adds squares in
+        // the reference's logical order
+        for (size_t g = 0; g < (size_t)(ug + ig); g++)
+            for (int p = 0; p < K; p++) h->h_stats[g * K + logical_of_phys(K, p)] = raw[g * K + p];
+        std::copy(raw.begin() + (size_t)(ug + ig) * K, raw.end(), h->h_stats.begin() + (size_t)(ug + ig) * K);
+        // mf_methods.cu:325-379
+        auto errors = [&](int groups, const float* gsum, const float* nsum, const std::vector<uint8_t>& prec,
+                          const std::vector<float>& initial, std::vector<float>& err) {
+            for (int g = 0; g < groups; g++) {
+                if (prec[g]) { err[g] = -1.f; continue; }
+                float num = 0.f;
+                for (int d = 0; d < K; d++) num += powf(gsum[(size_t)g * K + d], 2);
+                const float den = nsum[g];
+                err[g] = (num / den) / initial[g];
+            }
+        };
+        const float* gs_p = h->h_stats.data(); const float* gs_q = gs_p + (size_t)ug * K;
+        const float* ns_p = gs_q + (size_t)ig * K; const float* ns_q = ns_p + ug;
+        errors(ug, gs_p, ns_p, h->uprec, h->init_uerr, h->uerr);
+        errors(ig, gs_q, ns_q, h->iprec, h->init_ierr, h->ierr);
+        if (epoch == 5) { h->init_uerr = h->uerr; h->init_ierr = h->ierr; }   // mf_methods.cu:381-388
+        if (epoch > 5) {
+            // precision_switching_by_groups_grad_diversity (precision_switching.h:8-51), one way fp16 -> fp32
+            int rc;
+            for (int side = 0; side < 2; side++) {
+                const bool users = side == 0;
+                const std::vector<uint8_t>& prec = users ? h->uprec : h->iprec;
+                const std::vector<float>& err = users ? h->uerr : h->ierr;
+                uint32_t& count = users ? promoted_u : promoted_i;
+                for (size_t g = 0; g < prec.size(); g++) {
+                    if (!(err[g] > h->cfg.error_threshold) || prec[g]) continue;
+                    if ((rc = promote_group(h, users, g)) != MASCOT_OK) return rc;
+                    count++; launches++;
+                }
+                if (count) {
+                    if ((rc = recode_side(h, users)) != MASCOT_OK) return rc;
+                    launches += 2;
+                }
+            }
+        }
+    }
+    CU(h, cudaEventRecord(h->ev[3], h->stream));
+    CU(h, cudaEventSynchronize(h->ev[3]));
+    if (out) {
+        std::memset(out, 0, sizeof(*out));
+        out->updates = h->n_train; out->lr = lr; out->error_check = check ? 1 : 0;
+        out->promoted_user_groups = promoted_u; out->promoted_item_groups = promoted_i; out->kernel_launches = launches;
+        cudaEventElapsedTime(&out->kernel_ms, h->ev[1], h->ev[2]);
+        cudaEventElapsedTime(&out->total_ms, h->ev[0], h->ev[3]);
+    }
+    return MASCOT_OK;
+}
+
+int mascot_eval_rmse(mascot_handle* h, double* rmse) {
+    if (!h || !rmse) return MASCOT_ERR_BAD_ARG;
+    if (!h->have_ratings || !h->have_factors) return fail(h, MASCOT_ERR_STATE, "ratings and factors must be set before evaluation");
+    if (!h->n_test) return fail(h, MASCOT_ERR_STATE, "no test ratings were given");
+    CU(h, cudaSetDevice(h->cfg.device));
+    Stream t; t.r = h->te_r; t.u = h->te_u; t.i = h->te_i; t.n = h->n_test;
+    CU(h, launch_rmse(h->K, t, h->P, h->Q, h->d_block_err, h->stream));
+    CU(h, cudaMemcpyAsync(h->h_block_err.data(), h->d_block_err, sizeof(float) * h->h_block_err.size(), cudaMemcpyDeviceToHost, h->stream));
+    CU(h, cudaStreamSynchronize(h->stream));
+    *rmse = (double)reference_rmse_from_partials(h->h_block_err, h->n_test);
+    return MASCOT_OK;
+}
+
+int mascot_get_factors(mascot_handle* h, float* P, float* Q, int order) {
+    if (!h) return MASCOT_ERR_BAD_ARG;
+    if (!h->have_factors) return fail(h, MASCOT_ERR_STATE, "no factors yet");
+    if (order != 0 && order != 1) return fail(h, MASCOT_ERR_BAD_ARG, "order must be 0 or 1");
+    CU(h, cudaSetDevice(h->cfg.device));
+    auto one = [&](float* dst, Arena a, const uint8_t* prow, uint32_t rows, const uint32_t* map) -> int {
+        if (!dst) return MASCOT_OK;
+        float* d = nullptr;
+        CU(h, dev_alloc(&d, (size_t)rows * h->K));
+        cudaError_t e = launch_gather_factors(h->K, a, prow, rows, order == 0 ? map : nullptr, d, h->stream);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(dst, d, sizeof(float) * (size_t)rows * h->K, cudaMemcpyDeviceToHost, h->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
+        cudaFree(d);
+        CU(h, e);
+        return MASCOT_OK;
+    };
+    int rc = one(P, h->P, h->d_uprec_row, h->n_users, h->d_umap);
+    if (rc != MASCOT_OK) return rc;
+    return one(Q, h->Q, h->d_iprec_row, h->n_items, h->d_imap);
+}
+
+int mascot_get_group_info(mascot_handle* h, int side, uint32_t* n_groups, uint32_t* end_idx, uint8_t* precision, float* error) {
+    if (!h || (side != 0 && side != 1)) return MASCOT_ERR_BAD_ARG;
+    if (!h->have_ratings) return fail(h, MASCOT_ERR_STATE, "mascot_set_ratings must come first");
+    const std::vector<uint32_t>& end = side == 0 ? h->uend : h->iend;
+    const std::vector<uint8_t>& prec = side == 0 ? h->uprec : h->iprec;
+    const std::vector<float>& err = side == 0 ? h->uerr : h->ierr;
+    if (n_groups) *n_groups = (uint32_t)end.size();
+    if (end_idx) std::copy(end.begin(), end.end(), end_idx);
+    if (precision) std::copy(prec.begin(), prec.end(), precision);
+    if (error) std::copy(err.begin(), err.end(), error);
+    return MASCOT_OK;
+}
+
+int mascot_get_index_maps(mascot_handle* h, uint32_t* user2sorted, uint32_t* item2sorted) {
+    if (!h) return MASCOT_ERR_BAD_ARG;
+    if (!h->have_ratings) return fail(h, MASCOT_ERR_STATE, "mascot_set_ratings must come first");
+    if (user2sorted) {
+        if (h->grouped) std::copy(h->user2sorted.begin(), h->user2sorted.end(), user2sorted);
+        else for (uint32_t e = 0; e < h->n_users; e++) user2sorted[e] = e;
+    }
+    if (item2sorted) {
+        if (h->grouped) std::copy(h->item2sorted.begin(), h->item2sorted.end(), item2sorted);
+        else for (uint32_t e = 0; e < h->n_items; e++) item2sorted[e] = e;
+    }
+    return MASCOT_OK;
+}
+
+int mascot_promote_group(mascot_handle* h, int side, uint32_t group) {
+    if (!h || (side != 0 && side != 1)) return MASCOT_ERR_BAD_ARG;
+    if (!h->have_ratings || !h->have_factors) return fail(h, MASCOT_ERR_STATE, "ratings and factors must be set first");
+    if (!h->grouped) return fail(h, MASCOT_ERR_UNSUPPORTED, "only the MASCOT variant stores groups in switchable precision");
+    const bool users = side == 0;
+    std::vector<uint8_t>& prec = users ? h->uprec : h->iprec;
+    if (group >= prec.size()) return fail(h, MASCOT_ERR_BAD_ARG, "group index out of range");
+    if (prec[group]) return MASCOT_OK;
+    CU(h, cudaSetDevice(h->cfg.device));
+    int rc = promote_group(h, users, group);
+    if (rc == MASCOT_OK) rc = recode_side(h, users);
+    if (rc != MASCOT_OK) return rc;
+    CU(h, cudaStreamSynchronize(h->stream));
+    return MASCOT_OK;
+}
+
+int mascot_get_sample_stats(mascot_handle* h, float* grad_sum_p, float* grad_sum_q, float* norm_sum_p, float* norm_sum_q) {
+    if (!h) return MASCOT_ERR_BAD_ARG;
+    if (!h->have_ratings) return fail(h, MASCOT_ERR_STATE, "mascot_set_ratings must come first");
+    const size_t ug = h->uend.size(), ig = h->iend.size(), K = h->K;
+    const float* s = h->h_stats.data();
+    if (grad_sum_p) std::copy(s, s + ug * K, grad_sum_p);
+    if (grad_sum_q) std::copy(s + ug * K, s + (ug + ig) * K, grad_sum_q);
+    if (norm_sum_p) std::copy(s + (ug + ig) * K, s + (ug + ig) * K + ug, norm_sum_p);
+    if (norm_sum_q) std::copy(s + (ug + ig) * K + ug, s + (ug + ig) * K + ug + ig, norm_sum_q);
+    return MASCOT_OK;
+}
+
+int mascot_get_test_ratings(mascot_handle* h, mascot_rating* out, int order) {
+    if (!h || !out) return MASCOT_ERR_BAD_ARG;
+    if (!h->have_ratings) return fail(h, MASCOT_ERR_STATE, "mascot_set_ratings must come first");
+    if (order != 0 && order != 1) return fail(h, MASCOT_ERR_BAD_ARG, "order must be 0 or 1");
+    CU(h, cudaSetDevice(h->cfg.device));
+    const uint64_t n = h->n_test;
+    std::vector<float> r(n); std::vector<uint32_t> u(n), i(n);
+    CU(h, cudaMemcpy(r.data(), h->te_r, sizeof(float) * n, cudaMemcpyDeviceToHost));
+    CU(h, cudaMemcpy(u.data(), h->te_u, sizeof(uint32_t) * n, cudaMemcpyDeviceToHost));
+    CU(h, cudaMemcpy(i.data(), h->te_i, sizeof(uint32_t) * n, cudaMemcpyDeviceToHost));
+    std::vector<uint32_t> s2u, s2i;
+    if (order == 0 && h->grouped) {
+        s2u.resize(h->n_users); s2i.resize(h->n_items);
+        for (uint32_t e = 0; e < h->n_users; e++) s2u[h->user2sorted[e]] = e;
+        for (uint32_t e = 0; e < h->n_items; e++) s2i[h->item2sorted[e]] = e;
+    }
+    for (uint64_t j = 0; j < n; j++) {
+        uint32_t uu = u[j] & kIdMask, ii = i[j] & kIdMask;
+        if (!s2u.empty()) { uu = s2u[uu]; ii = s2i[ii]; }
+        out[j].r = r[j]; out[j].u = uu; out[j].i = ii;
+    }
+    return MASCOT_OK;
+}
+
+int mascot_stream_source_index(const mascot_handle* h, uint64_t pos, uint64_t* src) {
+    if (!h || !src) return MASCOT_ERR_BAD_ARG;
+    if (pos >= h->n_train) return MASCOT_ERR_BAD_ARG;
+    *src = h->cfg.shuffle ? permute_index(pos, h->n_train, h->cfg.seed) : pos;
+    return MASCOT_OK;
+}
+
+int mascot_rmse_device(const float* d_P, const float* d_Q, uint32_t k, const mascot_rating* d_test, uint64_t n_test, double* rmse) {
+    if (!d_P || !d_Q || !d_test || !rmse || !n_test) return fail(nullptr, MASCOT_ERR_BAD_ARG, "null pointer or empty test set");
+    if (k != 64 && k != 128) return fail(nullptr, MASCOT_ERR_BAD_ARG, "k must be 64 or 128");
+    const size_t blocks = (size_t)((n_test + 511) / 512);
+    float* d_err = nullptr;
+    CU(nullptr, dev_alloc(&d_err, blocks));
+    std::vector<float> part(blocks);
+    cudaError_t e = launch_rmse_plain((int)k, d_test, n_test, d_P, d_Q, d_err, nullptr);
+    if (e == cudaSuccess) e = cudaMemcpy(part.data(), d_err, sizeof(float) * blocks, cudaMemcpyDeviceToHost);
+    cudaFree(d_err);
+    CU(nullptr, e);
+    *rmse = (double)reference_rmse_from_partials(part, n_test);
+    return MASCOT_OK;
+}
+
+int mascot_rmse_host(const float* P, uint32_t n_users, const float* Q, uint32_t n_items, uint32_t k,
+                     const mascot_rating* test, uint64_t n_test, int device, double* rmse) {
+    if (!P || !Q || !test || !rmse || !n_test || !n_users || !n_items) return fail(nullptr, MASCOT_ERR_BAD_ARG, "null pointer or empty input");
+    if (k != 64 && k != 128) return fail(nullptr, MASCOT_ERR_BAD_ARG, "k must be 64 or 128");
+    for (uint64_t j = 0; j < n_test; j++)
+        if (test[j].u >= n_users || test[j].i >= n_items) return fail(nullptr, MASCOT_ERR_BAD_ARG, "test rating with id out of range");
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || device < 0 || device >= ndev) {
+        cudaGetLastError();
+        return fail(nullptr, MASCOT_ERR_NO_DEVICE, "no usable CUDA device; libmascot has no CPU path");
+    }
+    CU(nullptr, cudaSetDevice(device));
+    float *dP = nullptr, *dQ = nullptr; mascot_rating* dT = nullptr;
+    cudaError_t e = dev_alloc(&dP, (size_t)n_users * k);
+    if (e == cudaSuccess) e = dev_alloc(&dQ, (size_t)n_items * k);
+    if (e == cudaSuccess) e = dev_alloc(&dT, n_test);
+    if (e == cudaSuccess) e = cudaMemcpy(dP, P, sizeof(float) * (size_t)n_users * k, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(dQ, Q, sizeof(float) * (size_t)n_items * k, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(dT, test, sizeof(mascot_rating) * n_test, cudaMemcpyHostToDevice);
+    int rc = MASCOT_OK;
+    if (e == cudaSuccess) rc = mascot_rmse_device(dP, dQ, k, dT, n_test, rmse);
+    cudaFree(dP); cudaFree(dQ); cudaFree(dT);
+    CU(nullptr, e);
+    return rc;
+}
+
+}  // extern "C"

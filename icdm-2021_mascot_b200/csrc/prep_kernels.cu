@@ -1,0 +1,155 @@
+// Set-up and conversion kernels: stream encoding (shuffle + id remap + precision bit), factor
+// scatter/gather between the caller's fp32 row-major view and the permuted mixed-precision arenas,
+// group promotion, and factor initialisation.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "engine.h"
+#include "layout.cuh"
+
+namespace mascot {
+
+namespace {
+
+struct NodeAos { float r; uint32_t u; uint32_t i; };
+
+inline int grid_for(uint64_t n, int block) {
+    uint64_t g = (n + block - 1) / block;
+    const uint64_t cap = 148ull * 16;
+    return (int)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+// Replaces the host random_shuffle (mf_methods.cu:38-39) and the id remap
+// matrix_reconst_gpu_triplet (preprocess_utils.h:28-36): stream position j takes source rating
+// permute_index(j), ids are mapped to sorted indices and tagged with the row's storage precision.
+__global__ void encode_kernel(const NodeAos* src, uint64_t n, int shuffle, uint64_t seed,
+                              const uint32_t* umap, const uint32_t* imap,
+                              const uint8_t* uprec, const uint8_t* iprec,
+                              float* r, uint32_t* u, uint32_t* i) {
+    for (uint64_t j = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; j < n; j += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t s = shuffle ? permute_index(j, n, seed) : j;
+        const NodeAos nd = src[s];
+        uint32_t uu = umap ? umap[nd.u] : nd.u;
+        uint32_t ii = imap ? imap[nd.i] : nd.i;
+        if (uprec[uu]) uu |= kPrecBit;
+        if (iprec[ii]) ii |= kPrecBit;
+        r[j] = nd.r; u[j] = uu; i[j] = ii;
+    }
+}
+
+__global__ void recode_kernel(uint32_t* ids, uint64_t n, const uint8_t* prec_row) {
+    for (uint64_t j = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; j < n; j += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t id = ids[j] & kIdMask;
+        ids[j] = prec_row[id] ? (id | kPrecBit) : id;
+    }
+}
+
+// cpyparams2grouped_params_for_comparison_indexing (model_init.cu:30-83): caller row e goes to
+// arena row row_map[e]; here both arenas are filled so a later promotion is a plain widening.
+template <int K>
+__global__ void scatter_kernel(const float* src, uint32_t rows, const uint32_t* row_map, int through_half,
+                               __half* dst16, float* dst32) {
+    const uint64_t total = (uint64_t)rows * K;
+    for (uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t e = (uint32_t)(t / K);
+        const int d = (int)(t % K);
+        const uint32_t row = row_map ? row_map[e] : e;
+        const size_t o = (size_t)row * K + phys_of_logical(K, d);
+        const float v = src[t];
+        const __half h = __float2half_rn(v);
+        if (dst16) dst16[o] = h;
+        if (dst32) dst32[o] = through_half ? __half2float(h) : v;
+    }
+}
+
+template <int K>
+__global__ void gather_kernel(const __half* a16, const float* a32, const uint8_t* prec_row, uint32_t rows,
+                              const uint32_t* row_map, float* dst) {
+    const uint64_t total = (uint64_t)rows * K;
+    for (uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t e = (uint32_t)(t / K);
+        const int d = (int)(t % K);
+        const uint32_t row = row_map ? row_map[e] : e;
+        const size_t o = (size_t)row * K + phys_of_logical(K, d);
+        dst[t] = prec_row[row] ? a32[o] : __half2float(a16[o]);
+    }
+}
+
+// mem_cpy_fp162fp32 (precision_switching.h:1-6) without the re-allocation around it.
+__global__ void promote_kernel(const __half* a16, float* a32, uint64_t begin, uint64_t end) {
+    for (uint64_t t = begin + (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; t < end; t += (uint64_t)gridDim.x * blockDim.x)
+        a32[t] = __half2float(a16[t]);
+}
+
+__device__ __forceinline__ uint64_t splitmix64(uint64_t x) {
+    x += 0x9e3779b97f4a7c15ull;
+    x = (x ^ (x >> 30)) * 0xbf58476d1ce4e5b9ull;
+    x = (x ^ (x >> 27)) * 0x94d049bb133111ebull;
+    return x ^ (x >> 31);
+}
+
+// N(0, 0.01^2) like init_rand_feature_single (model_init.cu:19-28), from a counter-based
+// generator: element t of stream `sid` depends only on (seed, sid, t).
+__global__ void init_normal_kernel(float* dst, uint64_t count, uint64_t seed, uint64_t sid) {
+    for (uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; t < count; t += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t z = splitmix64(splitmix64(seed ^ (sid * 0xd1342543de82ef95ull)) + t);
+        const double u1 = ((double)(z >> 11) + 1.0) * (1.0 / 9007199254740993.0);   // (0,1)
+        const uint64_t z2 = splitmix64(z);
+        const double u2 = (double)(z2 >> 11) * (1.0 / 9007199254740992.0);
+        const double nrm = sqrt(-2.0 * log(u1)) * cospi(2.0 * u2);
+        dst[t] = (float)(nrm * 0.01);
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_encode_stream(const void* d_src_aos, uint64_t n, bool shuffle, uint64_t seed,
+                                 const uint32_t* user_map, const uint32_t* item_map,
+                                 const uint8_t* uprec_row, const uint8_t* iprec_row,
+                                 float* r, uint32_t* u, uint32_t* i, cudaStream_t st) {
+    if (n == 0) return cudaSuccess;
+    encode_kernel<<<grid_for(n, 256), 256, 0, st>>>(static_cast<const NodeAos*>(d_src_aos), n, shuffle ? 1 : 0, seed,
+                                                     user_map, item_map, uprec_row, iprec_row, r, u, i);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_recode(uint32_t* ids, uint64_t n, const uint8_t* prec_row, cudaStream_t st) {
+    if (n == 0) return cudaSuccess;
+    recode_kernel<<<grid_for(n, 256), 256, 0, st>>>(ids, n, prec_row);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_scatter_factors(int K, const float* src, uint32_t rows, const uint32_t* row_map,
+                                   bool round_through_half, __half* dst16, float* dst32, cudaStream_t st) {
+    if (rows == 0) return cudaSuccess;
+    const int g = grid_for((uint64_t)rows * K, 256);
+    if (K == 128) scatter_kernel<128><<<g, 256, 0, st>>>(src, rows, row_map, round_through_half ? 1 : 0, dst16, dst32);
+    else if (K == 64) scatter_kernel<64><<<g, 256, 0, st>>>(src, rows, row_map, round_through_half ? 1 : 0, dst16, dst32);
+    else return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_gather_factors(int K, Arena a, const uint8_t* prec_row, uint32_t rows,
+                                  const uint32_t* row_map, float* dst, cudaStream_t st) {
+    if (rows == 0) return cudaSuccess;
+    const int g = grid_for((uint64_t)rows * K, 256);
+    if (K == 128) gather_kernel<128><<<g, 256, 0, st>>>(a.f16, a.f32, prec_row, rows, row_map, dst);
+    else if (K == 64) gather_kernel<64><<<g, 256, 0, st>>>(a.f16, a.f32, prec_row, rows, row_map, dst);
+    else return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_promote_rows(int K, Arena a, uint32_t row_begin, uint32_t row_end, cudaStream_t st) {
+    if (row_end <= row_begin) return cudaSuccess;
+    const uint64_t b = (uint64_t)row_begin * K, e = (uint64_t)row_end * K;
+    promote_kernel<<<grid_for(e - b, 256), 256, 0, st>>>(a.f16, a.f32, b, e);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_init_normal(float* dst, uint64_t count, uint64_t seed, uint64_t stream_id, cudaStream_t st) {
+    if (count == 0) return cudaSuccess;
+    init_normal_kernel<<<grid_for(count, 256), 256, 0, st>>>(dst, count, seed, stream_id);
+    return cudaGetLastError();
+}
+
+}  // namespace mascot

@@ -1,0 +1,344 @@
+// Per-rating SGD update kernels for sm_100a.
+//
+// One "team" of T = K/4 lanes owns one rating at a time; every lane holds four consecutive
+// physical elements of the user row and of the item row (one 64-bit access for binary16 storage,
+// one 128-bit access for fp32 storage; layout.cuh explains the element permutation that makes this
+// reproduce the reference's reduction tree).  Teams walk the rating stream in chunks of T ratings,
+// grid-stride over a persistent grid: the T records of a chunk are fetched with one coalesced load
+// per field (lane j keeps rating j) one chunk ahead of use and broadcast with shuffles, so the only
+// dependent memory round trip per rating is the row gather itself.  Bit 31 of the stream ids says
+// which arena (binary16 or fp32) a row lives in, which replaces the reference's per-rating group
+// search (mascot/mascot_sgd_kernel.h:104-180) with nothing at all.
+//
+// The arithmetic of each precision case is the reference's, including the fused multiply-adds its
+// compiled kernels execute:
+//   all binary16      mascot_sgd_kernel.h:188-278     binary16 user / fp32 item  :279-342
+//   fp32 / binary16   mascot_sgd_kernel.h:343-407     all fp32                   :408-443
+//   (sgd/sgd_kernel.h:35-76 compiles to the same operations as the all-fp32 case)
+//   MPT               mpt/mpt_sgd_kernel.h:38-91      fp16 storage (-v 7)  sgd/sgd_kernel.h:110-161
+// Every operation is written with a rounding-mode intrinsic so that ptxas cannot re-associate or
+// contract anything further.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "engine.h"
+#include "layout.cuh"
+
+namespace mascot {
+
+namespace {
+
+template <int T>
+__device__ __forceinline__ float team_sum(float x, unsigned mask) {
+    x = __fadd_rn(x, __shfl_xor_sync(mask, x, 1));
+#pragma unroll
+    for (int d = T / 2; d >= 2; d >>= 1) x = __fadd_rn(x, __shfl_xor_sync(mask, x, d));
+    return x;
+}
+
+template <int T>
+__device__ __forceinline__ __half team_sum(__half x, unsigned mask) {
+    x = __hadd_rn(x, __shfl_xor_sync(mask, x, 1));
+#pragma unroll
+    for (int d = T / 2; d >= 2; d >>= 1) x = __hadd_rn(x, __shfl_xor_sync(mask, x, d));
+    return x;
+}
+
+struct H4 { __half2 a, b; };          // four binary16 values, physical order
+struct F4 { float x[4]; };
+
+__device__ __forceinline__ H4 ld_h4(const __half* base, uint32_t row, int K, int tl) {
+    const uint2 v = __ldcg(reinterpret_cast<const uint2*>(base + (size_t)row * K) + tl);
+    H4 h;
+    h.a = *reinterpret_cast<const __half2*>(&v.x);
+    h.b = *reinterpret_cast<const __half2*>(&v.y);
+    return h;
+}
+__device__ __forceinline__ void st_h4(__half* base, uint32_t row, int K, int tl, const H4& h) {
+    uint2 v;
+    v.x = *reinterpret_cast<const unsigned*>(&h.a);
+    v.y = *reinterpret_cast<const unsigned*>(&h.b);
+    __stcg(reinterpret_cast<uint2*>(base + (size_t)row * K) + tl, v);
+}
+__device__ __forceinline__ F4 ld_f4(const float* base, uint32_t row, int K, int tl) {
+    const float4 v = __ldcg(reinterpret_cast<const float4*>(base + (size_t)row * K) + tl);
+    F4 f;
+    f.x[0] = v.x; f.x[1] = v.y; f.x[2] = v.z; f.x[3] = v.w;
+    return f;
+}
+__device__ __forceinline__ void st_f4(float* base, uint32_t row, int K, int tl, const F4& f) {
+    __stcg(reinterpret_cast<float4*>(base + (size_t)row * K) + tl, make_float4(f.x[0], f.x[1], f.x[2], f.x[3]));
+}
+__device__ __forceinline__ F4 widen(const H4& h) {
+    F4 f;
+    const float2 lo = __half22float2(h.a), hi = __half22float2(h.b);
+    f.x[0] = lo.x; f.x[1] = lo.y; f.x[2] = hi.x; f.x[3] = hi.y;
+    return f;
+}
+__device__ __forceinline__ H4 narrow(const F4& f) {
+    H4 h;
+    h.a = __halves2half2(__float2half_rn(f.x[0]), __float2half_rn(f.x[1]));
+    h.b = __halves2half2(__float2half_rn(f.x[2]), __float2half_rn(f.x[3]));
+    return h;
+}
+
+// lane partial of the dot product: (fma(a0,b0,a1*b1)) + (fma(a2,b2,a3*b3))
+__device__ __forceinline__ float pair_partial(const F4& a, const F4& b) {
+    const float f01 = __fmaf_rn(a.x[0], b.x[0], __fmul_rn(a.x[1], b.x[1]));
+    const float f23 = __fmaf_rn(a.x[2], b.x[2], __fmul_rn(a.x[3], b.x[3]));
+    return __fadd_rn(f01, f23);
+}
+// lane partial of the left-to-right product chain the fp16-storage trainer and the RMSE kernel
+// use for k=128: fma(a3,b3, fma(a2,b2, fma(a0,b0, a1*b1)))
+__device__ __forceinline__ float chain_partial(const F4& a, const F4& b) {
+    float acc = __fmaf_rn(a.x[0], b.x[0], __fmul_rn(a.x[1], b.x[1]));
+    acc = __fmaf_rn(a.x[2], b.x[2], acc);
+    return __fmaf_rn(a.x[3], b.x[3], acc);
+}
+__device__ __forceinline__ __half pair_partial(const H4& p, const H4& q) {
+    const __half2 plo = __lows2half2(p.a, p.b), phi = __highs2half2(p.a, p.b);
+    const __half2 qlo = __lows2half2(q.a, q.b), qhi = __highs2half2(q.a, q.b);
+    const __half2 f = __hfma2(plo, qlo, __hmul2_rn(phi, qhi));   // (f01, f23)
+    return __hadd_rn(__low2half(f), __high2half(f));
+}
+// t = fma(e, y, -(lam*x)) element-wise
+__device__ __forceinline__ F4 grad(float e, const F4& y, float lam, const F4& x) {
+    F4 g;
+#pragma unroll
+    for (int s = 0; s < 4; s++) g.x[s] = __fmaf_rn(e, y.x[s], -__fmul_rn(lam, x.x[s]));
+    return g;
+}
+__device__ __forceinline__ H4 grad(__half2 e, const H4& y, __half2 lam, const H4& x) {
+    H4 g;
+    g.a = __hfma2(e, y.a, __hneg2(__hmul2_rn(lam, x.a)));
+    g.b = __hfma2(e, y.b, __hneg2(__hmul2_rn(lam, x.b)));
+    return g;
+}
+__device__ __forceinline__ F4 step(float lr, const F4& g, const F4& x) {
+    F4 o;
+#pragma unroll
+    for (int s = 0; s < 4; s++) o.x[s] = __fmaf_rn(lr, g.x[s], x.x[s]);
+    return o;
+}
+__device__ __forceinline__ float sumsq_partial(const F4& g) { return pair_partial(g, g); }
+
+// Accumulators of the sampled statistics: shared memory when they fit, else straight to global.
+struct StatAcc {
+    float* gs_p; float* gs_q; float* ns_p; float* ns_q;
+};
+
+template <int K, int T>
+__device__ __forceinline__ void sample_side(const F4& g, float* gsum, float* nsum, uint32_t group, int tl, unsigned mask) {
+    const float n = team_sum<T>(sumsq_partial(g), mask);
+    if (tl == 0) atomicAdd(nsum + group, n);
+    float* dst = gsum + (size_t)group * K + 4 * tl;
+#pragma unroll
+    for (int s = 0; s < 4; s++) atomicAdd(dst + s, g.x[s]);
+}
+
+struct KernelArgs {
+    Stream s;
+    Arena P, Q;
+    float lr, lam;
+    SampleStats st;
+    int stats_in_smem;
+};
+
+template <int K, int KIND, bool STATS>
+__global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
+    constexpr int T = K / 4;
+    extern __shared__ float smem[];
+    const int tl = threadIdx.x % T;
+    const unsigned mask = (T == 32) ? 0xffffffffu : (0xffffu << (16 * ((threadIdx.x >> 4) & 1)));
+    const uint64_t team = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) / T;
+    const uint64_t nteams = ((uint64_t)gridDim.x * blockDim.x) / T;
+    const uint64_t nchunks = (a.s.n + T - 1) / T;
+
+    StatAcc acc = {a.st.gsum_p, a.st.gsum_q, a.st.nsum_p, a.st.nsum_q};
+    if (STATS && a.stats_in_smem) {
+        const int total = (a.st.ug + a.st.ig) * (K + 1);
+        for (int j = threadIdx.x; j < total; j += blockDim.x) smem[j] = 0.f;
+        acc.gs_p = smem;
+        acc.gs_q = acc.gs_p + a.st.ug * K;
+        acc.ns_p = acc.gs_q + a.st.ig * K;
+        acc.ns_q = acc.ns_p + a.st.ug;
+        __syncthreads();
+    }
+
+    const float lr = a.lr, lam = a.lam;
+    const __half2 lr_h = __half2half2(__float2half_rn(lr));     // mascot_sgd_kernel.h:79-80
+    const __half2 lam_h = __half2half2(__float2half_rn(lam));
+    // MPT constants (mpt_sgd_kernel.h:15-16, mf_methods.cu:764-765)
+    const __half mpt_scale = __float2half_rn(1000.0f);
+    const __half2 mpt_lam = __half2half2(__float2half_rn(__fmul_rn(lam, 1000.0f)));
+    const float mpt_rev = __fdiv_rn(1.0f, 1000.0f);
+
+    uint64_t c = team;
+    float r_n = 0.f; uint32_t u_n = 0, i_n = 0;
+    if (c < nchunks) {
+        const uint64_t pos = c * T + tl;
+        if (pos < a.s.n) { r_n = __ldg(a.s.r + pos); u_n = __ldg(a.s.u + pos); i_n = __ldg(a.s.i + pos); }
+    }
+    for (; c < nchunks; c += nteams) {
+        const float r_l = r_n; const uint32_t u_l = u_n, i_l = i_n;
+        const uint64_t cn = c + nteams;
+        if (cn < nchunks) {
+            const uint64_t pos = cn * T + tl;
+            if (pos < a.s.n) { r_n = __ldg(a.s.r + pos); u_n = __ldg(a.s.u + pos); i_n = __ldg(a.s.i + pos); }
+        }
+        const uint64_t base = c * T;
+        const int cnt = (a.s.n - base) < (uint64_t)T ? (int)(a.s.n - base) : T;
+        for (int j = 0; j < cnt; j++) {
+            const float r = __shfl_sync(mask, r_l, j, T);
+            const uint32_t uc = __shfl_sync(mask, u_l, j, T);
+            const uint32_t ic = __shfl_sync(mask, i_l, j, T);
+            const uint32_t u = uc & kIdMask, i = ic & kIdMask;
+            const bool sampled = STATS && (base + j >= a.st.first_sample_pos);
+
+            if (KIND == KIND_FP32) {
+                const F4 p = ld_f4(a.P.f32, u, K, tl), q = ld_f4(a.Q.f32, i, K, tl);
+                const float e = __fsub_rn(r, team_sum<T>(pair_partial(p, q), mask));
+                st_f4(a.P.f32, u, K, tl, step(lr, grad(e, q, lam, p), p));
+                st_f4(a.Q.f32, i, K, tl, step(lr, grad(e, p, lam, q), q));
+            } else if (KIND == KIND_MPT) {
+                const F4 p = ld_f4(a.P.f32, u, K, tl), q = ld_f4(a.Q.f32, i, K, tl);
+                const H4 ph = narrow(p), qh = narrow(q);
+                const __half dot = team_sum<T>(pair_partial(ph, qh), mask);
+                const __half2 e = __half2half2(__hmul_rn(mpt_scale, __hsub_rn(__float2half_rn(r), dot)));
+                const F4 gp = widen(grad(e, qh, mpt_lam, ph)), gq = widen(grad(e, ph, mpt_lam, qh));
+                F4 po, qo;
+#pragma unroll
+                for (int s = 0; s < 4; s++) {
+                    po.x[s] = __fmaf_rn(lr, __fmul_rn(mpt_rev, gp.x[s]), p.x[s]);
+                    qo.x[s] = __fmaf_rn(lr, __fmul_rn(mpt_rev, gq.x[s]), q.x[s]);
+                }
+                st_f4(a.P.f32, u, K, tl, po);
+                st_f4(a.Q.f32, i, K, tl, qo);
+            } else if (KIND == KIND_MEMQUANT) {
+                const F4 p = widen(ld_h4(a.P.f16, u, K, tl)), q = widen(ld_h4(a.Q.f16, i, K, tl));
+                const float part = (K == 128) ? chain_partial(p, q) : pair_partial(p, q);
+                const float e = __fsub_rn(r, team_sum<T>(part, mask));
+                st_h4(a.P.f16, u, K, tl, narrow(step(lr, grad(e, q, lam, p), p)));
+                st_h4(a.Q.f16, i, K, tl, narrow(step(lr, grad(e, p, lam, q), q)));
+            } else {
+                const bool uf = (uc & kPrecBit) != 0, itf = (ic & kPrecBit) != 0;
+                if (!uf && !itf) {
+                    const H4 p = ld_h4(a.P.f16, u, K, tl), q = ld_h4(a.Q.f16, i, K, tl);
+                    const __half dot = team_sum<T>(pair_partial(p, q), mask);
+                    const __half2 e = __half2half2(__hsub_rn(__float2half_rn(r), dot));
+                    const H4 gp = grad(e, q, lam_h, p), gq = grad(e, p, lam_h, q);
+                    H4 po, qo;
+                    po.a = __hfma2(lr_h, gp.a, p.a); po.b = __hfma2(lr_h, gp.b, p.b);
+                    qo.a = __hfma2(lr_h, gq.a, q.a); qo.b = __hfma2(lr_h, gq.b, q.b);
+                    st_h4(a.P.f16, u, K, tl, po);
+                    st_h4(a.Q.f16, i, K, tl, qo);
+                    if (sampled) {
+                        sample_side<K, T>(widen(gp), acc.gs_p, acc.ns_p, a.st.ugroup[u], tl, mask);
+                        sample_side<K, T>(widen(gq), acc.gs_q, acc.ns_q, a.st.igroup[i], tl, mask);
+                    }
+                } else if (!uf && itf) {
+                    const F4 p = widen(ld_h4(a.P.f16, u, K, tl)), q = ld_f4(a.Q.f32, i, K, tl);
+                    const float e = __fsub_rn(r, team_sum<T>(pair_partial(p, q), mask));
+                    const F4 gp = grad(e, q, lam, p);
+                    st_h4(a.P.f16, u, K, tl, narrow(step(lr, gp, p)));
+                    st_f4(a.Q.f32, i, K, tl, step(lr, grad(e, p, lam, q), q));
+                    if (sampled) sample_side<K, T>(gp, acc.gs_p, acc.ns_p, a.st.ugroup[u], tl, mask);
+                } else if (uf && !itf) {
+                    const F4 p = ld_f4(a.P.f32, u, K, tl), q = widen(ld_h4(a.Q.f16, i, K, tl));
+                    const float e = __fsub_rn(r, team_sum<T>(pair_partial(p, q), mask));
+                    const F4 gq = grad(e, p, lam, q);
+                    st_f4(a.P.f32, u, K, tl, step(lr, grad(e, q, lam, p), p));
+                    st_h4(a.Q.f16, i, K, tl, narrow(step(lr, gq, q)));
+                    if (sampled) sample_side<K, T>(gq, acc.gs_q, acc.ns_q, a.st.igroup[i], tl, mask);
+                } else {
+                    const F4 p = ld_f4(a.P.f32, u, K, tl), q = ld_f4(a.Q.f32, i, K, tl);
+                    const float e = __fsub_rn(r, team_sum<T>(pair_partial(p, q), mask));
+                    st_f4(a.P.f32, u, K, tl, step(lr, grad(e, q, lam, p), p));
+                    st_f4(a.Q.f32, i, K, tl, step(lr, grad(e, p, lam, q), q));
+                }
+            }
+        }
+    }
+
+    if (STATS && a.stats_in_smem) {
+        __syncthreads();
+        const int nvec = (a.st.ug + a.st.ig) * K;
+        for (int j = threadIdx.x; j < nvec; j += blockDim.x) {
+            const float v = smem[j];
+            if (v != 0.f) atomicAdd((j < a.st.ug * K) ? a.st.gsum_p + j : a.st.gsum_q + (j - a.st.ug * K), v);
+        }
+        for (int j = threadIdx.x; j < a.st.ug + a.st.ig; j += blockDim.x) {
+            const float v = smem[nvec + j];
+            if (v != 0.f) atomicAdd((j < a.st.ug) ? a.st.nsum_p + j : a.st.nsum_q + (j - a.st.ug), v);
+        }
+    }
+}
+
+int sm_count() {
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    }
+    return sms;
+}
+
+template <int K, int KIND, bool STATS>
+cudaError_t launch_one(const KernelArgs& args, bool deterministic, int grid_hint, cudaStream_t st, LaunchShape* shape) {
+    auto kern = train_kernel<K, KIND, STATS>;
+    KernelArgs a = args;
+    int block = deterministic ? K / 4 : 256;
+    size_t smem = 0;
+    a.stats_in_smem = 0;
+    if (STATS) {
+        const size_t want = (size_t)(a.st.ug + a.st.ig) * (K + 1) * sizeof(float);
+        if (want <= 200 * 1024) {
+            smem = want;
+            a.stats_in_smem = 1;
+            if (smem > 48 * 1024) {
+                cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                if (e != cudaSuccess) return e;
+            }
+        }
+    }
+    int grid = 1;
+    if (!deterministic) {
+        int per_sm = 0;
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, block, smem);
+        if (e != cudaSuccess) return e;
+        if (per_sm < 1) per_sm = 1;
+        grid = grid_hint > 0 ? grid_hint : per_sm * sm_count();
+    }
+    kern<<<grid, block, smem, st>>>(a);
+    if (shape) { shape->grid = grid; shape->block = block; shape->smem = smem; }
+    return cudaGetLastError();
+}
+
+template <int K>
+cudaError_t launch_k(TrainKind kind, const KernelArgs& a, bool stats, bool det, int hint, cudaStream_t st, LaunchShape* sh) {
+    switch (kind) {
+        case KIND_MIXED:
+            return stats ? launch_one<K, KIND_MIXED, true>(a, det, hint, st, sh) : launch_one<K, KIND_MIXED, false>(a, det, hint, st, sh);
+        case KIND_FP32: return launch_one<K, KIND_FP32, false>(a, det, hint, st, sh);
+        case KIND_MPT: return launch_one<K, KIND_MPT, false>(a, det, hint, st, sh);
+        case KIND_MEMQUANT: return launch_one<K, KIND_MEMQUANT, false>(a, det, hint, st, sh);
+    }
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+cudaError_t launch_train(int K, TrainKind kind, const Stream& s, Arena P, Arena Q, float lr, float lam,
+                         const SampleStats* stats, bool deterministic, int grid_blocks_hint, cudaStream_t st,
+                         LaunchShape* shape) {
+    KernelArgs a;
+    a.s = s; a.P = P; a.Q = Q; a.lr = lr; a.lam = lam; a.stats_in_smem = 0;
+    if (stats) a.st = *stats;
+    if (s.n == 0) { if (shape) *shape = LaunchShape(); return cudaSuccess; }
+    if (K == 128) return launch_k<128>(kind, a, stats != nullptr, deterministic, grid_blocks_hint, st, shape);
+    if (K == 64) return launch_k<64>(kind, a, stats != nullptr, deterministic, grid_blocks_hint, st, shape);
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace mascot

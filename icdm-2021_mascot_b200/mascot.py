@@ -1,0 +1,224 @@
+"""ctypes binding of libmascot.so - the thin Python face of the C ABI in include/mascot.h.
+
+Used by the tests, the benchmark and the smoke test; the production host code is the C++
+command line (cli/quantized_mf.cpp, cli/test_mf.cpp).  There is no fallback: if the shared library
+is missing or no CUDA device is usable, calls raise.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libmascot.so")
+
+RATING = np.dtype([("r", np.float32), ("u", np.uint32), ("i", np.uint32)])
+
+V_MASCOT, V_AFP, V_MUPPET, V_MPT, V_SGD, V_MEMQUANT = 1, 2, 3, 4, 5, 7
+
+OK, ERR_BAD_ARG, ERR_CUDA, ERR_OOM, ERR_STATE, ERR_NO_DEVICE, ERR_TIMEOUT, ERR_UNSUPPORTED, ERR_COMM = \
+    0, -1, -2, -3, -4, -5, -6, -7, -8
+
+EXPORTS = [
+    "mascot_abi_info", "mascot_config_default", "mascot_create", "mascot_destroy", "mascot_last_error", "mascot_status_string",
+    "mascot_set_ratings", "mascot_init_factors", "mascot_set_factors", "mascot_train_epoch", "mascot_eval_rmse",
+    "mascot_get_factors", "mascot_get_group_info", "mascot_get_index_maps", "mascot_get_sample_stats",
+    "mascot_get_test_ratings", "mascot_promote_group", "mascot_stream_source_index", "mascot_rmse_host", "mascot_rmse_device",
+]
+
+
+class Config(C.Structure):
+    _fields_ = [
+        ("lambda_", C.c_float), ("learning_rate", C.c_float), ("decay", C.c_float), ("sample_ratio", C.c_float),
+        ("error_threshold", C.c_float), ("interval", C.c_uint32), ("user_group_num", C.c_uint32),
+        ("item_group_num", C.c_uint32), ("k", C.c_uint32), ("num_workers", C.c_uint32), ("epoch", C.c_uint32),
+        ("thread_block_size", C.c_uint32), ("version", C.c_uint32), ("is_yahoo", C.c_uint32),
+        ("deterministic", C.c_uint32), ("shuffle", C.c_uint32), ("seed", C.c_uint64), ("device", C.c_int32),
+        ("grid_blocks", C.c_uint32), ("reserved", C.c_uint32 * 6),
+    ]
+
+
+class EpochStats(C.Structure):
+    _fields_ = [
+        ("updates", C.c_uint64), ("lr", C.c_float), ("kernel_ms", C.c_float), ("total_ms", C.c_float),
+        ("error_check", C.c_uint32), ("promoted_user_groups", C.c_uint32), ("promoted_item_groups", C.c_uint32),
+        ("kernel_launches", C.c_uint32),
+    ]
+
+
+class MascotError(RuntimeError):
+    def __init__(self, status, message):
+        super().__init__(f"libmascot status {status}: {message}")
+        self.status = status
+
+
+_lib = None
+
+
+def load():
+    """dlopen libmascot.so (raises if it has not been built)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise OSError(f"{LIB_PATH} is missing - run `python icdm-2021_mascot_b200/build.py`")
+        L = C.CDLL(LIB_PATH)
+        L.mascot_last_error.restype = C.c_char_p
+        L.mascot_last_error.argtypes = [C.c_void_p]
+        L.mascot_status_string.restype = C.c_char_p
+        L.mascot_status_string.argtypes = [C.c_int]
+        ver, csz, ssz = C.c_uint32(), C.c_uint32(), C.c_uint32()
+        L.mascot_abi_info(C.byref(ver), C.byref(csz), C.byref(ssz))
+        if (csz.value, ssz.value) != (C.sizeof(Config), C.sizeof(EpochStats)):
+            raise OSError(f"libmascot ABI mismatch: library structs are {csz.value}/{ssz.value} bytes, "
+                          f"binding expects {C.sizeof(Config)}/{C.sizeof(EpochStats)}")
+        _lib = L
+    return _lib
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def default_config(**overrides):
+    cfg = Config()
+    load().mascot_config_default(C.byref(cfg))
+    for key, val in overrides.items():
+        setattr(cfg, "lambda_" if key in ("lambda", "lam") else key, val)
+    return cfg
+
+
+def as_ratings(a):
+    a = np.ascontiguousarray(a)
+    if a.dtype != RATING:
+        a = a.reshape(-1, 3).astype(np.uint32, copy=False).view(RATING).reshape(-1)
+    return a
+
+
+def make_ratings(u, i, r):
+    out = np.empty(len(r), RATING)
+    out["u"], out["i"], out["r"] = u, i, r
+    return out
+
+
+class Engine:
+    """One libmascot handle."""
+
+    def __init__(self, cfg):
+        self._lib = load()
+        self.cfg = cfg
+        self._h = C.c_void_p()
+        rc = self._lib.mascot_create(C.byref(cfg), C.byref(self._h))
+        if rc != OK:
+            raise MascotError(rc, self._lib.mascot_last_error(None).decode())
+        self.k = int(cfg.k)
+        self.n_users = self.n_items = 0
+        self.n_train = self.n_test = 0
+
+    def _check(self, rc):
+        if rc != OK:
+            raise MascotError(rc, self._lib.mascot_last_error(self._h).decode())
+
+    def close(self):
+        if self._h:
+            self._lib.mascot_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def set_ratings(self, train, test, n_users, n_items):
+        train, test = as_ratings(train), as_ratings(test)
+        self._check(self._lib.mascot_set_ratings(self._h, _ptr(train), C.c_uint64(train.size), _ptr(test),
+                                                 C.c_uint64(test.size), C.c_uint32(n_users), C.c_uint32(n_items)))
+        self.n_users, self.n_items, self.n_train, self.n_test = n_users, n_items, train.size, test.size
+
+    def set_ratings_raw(self, train_ptr, n_train, test_ptr, n_test, n_users, n_items):
+        """Same call with raw host addresses (e.g. pinned buffers owned by the caller)."""
+        self._check(self._lib.mascot_set_ratings(self._h, C.c_void_p(train_ptr), C.c_uint64(n_train), C.c_void_p(test_ptr),
+                                                 C.c_uint64(n_test), C.c_uint32(n_users), C.c_uint32(n_items)))
+        self.n_users, self.n_items, self.n_train, self.n_test = n_users, n_items, n_train, n_test
+
+    def init_factors(self):
+        self._check(self._lib.mascot_init_factors(self._h))
+
+    def set_factors(self, P, Q):
+        P = np.ascontiguousarray(P, np.float32)
+        Q = np.ascontiguousarray(Q, np.float32)
+        assert P.size == self.n_users * self.k and Q.size == self.n_items * self.k
+        self._check(self._lib.mascot_set_factors(self._h, _ptr(P), _ptr(Q)))
+
+    def train_epoch(self, epoch):
+        st = EpochStats()
+        self._check(self._lib.mascot_train_epoch(self._h, C.c_uint32(epoch), C.byref(st)))
+        return st
+
+    def eval_rmse(self):
+        v = C.c_double()
+        self._check(self._lib.mascot_eval_rmse(self._h, C.byref(v)))
+        return v.value
+
+    def get_factors(self, order=0):
+        P = np.empty((self.n_users, self.k), np.float32)
+        Q = np.empty((self.n_items, self.k), np.float32)
+        self._check(self._lib.mascot_get_factors(self._h, _ptr(P), _ptr(Q), C.c_int(order)))
+        return P, Q
+
+    def group_info(self, side):
+        n = C.c_uint32()
+        self._check(self._lib.mascot_get_group_info(self._h, C.c_int(side), C.byref(n), None, None, None))
+        end = np.empty(n.value, np.uint32)
+        prec = np.empty(n.value, np.uint8)
+        err = np.empty(n.value, np.float32)
+        self._check(self._lib.mascot_get_group_info(self._h, C.c_int(side), C.byref(n), _ptr(end), _ptr(prec), _ptr(err)))
+        return end, prec, err
+
+    def promote_group(self, side, group):
+        self._check(self._lib.mascot_promote_group(self._h, C.c_int(side), C.c_uint32(group)))
+
+    def index_maps(self):
+        u = np.empty(self.n_users, np.uint32)
+        i = np.empty(self.n_items, np.uint32)
+        self._check(self._lib.mascot_get_index_maps(self._h, _ptr(u), _ptr(i)))
+        return u, i
+
+    def sample_stats(self):
+        ug, ig = len(self.group_info(0)[0]), len(self.group_info(1)[0])
+        gp = np.empty(ug * self.k, np.float32)
+        gq = np.empty(ig * self.k, np.float32)
+        np_ = np.empty(ug, np.float32)
+        nq = np.empty(ig, np.float32)
+        self._check(self._lib.mascot_get_sample_stats(self._h, _ptr(gp), _ptr(gq), _ptr(np_), _ptr(nq)))
+        return gp, gq, np_, nq
+
+    def test_ratings(self, order=1):
+        out = np.empty(self.n_test, RATING)
+        self._check(self._lib.mascot_get_test_ratings(self._h, _ptr(out), C.c_int(order)))
+        return out
+
+    def stream_source_index(self, pos):
+        v = C.c_uint64()
+        self._check(self._lib.mascot_stream_source_index(self._h, C.c_uint64(pos), C.byref(v)))
+        return v.value
+
+
+def rmse_host(P, Q, test, k, device=0):
+    """Handle-free evaluation of fp32 factors on host buffers (the test_mf path)."""
+    L = load()
+    P = np.ascontiguousarray(P, np.float32)
+    Q = np.ascontiguousarray(Q, np.float32)
+    test = as_ratings(test)
+    v = C.c_double()
+    rc = L.mascot_rmse_host(_ptr(P), C.c_uint32(P.size // k), _ptr(Q), C.c_uint32(Q.size // k), C.c_uint32(k),
+                            _ptr(test), C.c_uint64(test.size), C.c_int(device), C.byref(v))
+    if rc != OK:
+        raise MascotError(rc, L.mascot_last_error(None).decode())
+    return v.value

@@ -1,0 +1,191 @@
+/* libmascot - C ABI of the B200-native MASCOT training engine.
+ *
+ * The reference (Yujaeseo/ICDM-2021_MASCOT) has no FFI: its hot path sits behind the eight
+ * `void X_training_mf(Mf_info*, SGD*)` trainers (mf_methods.h:4-11), `init_model_*`
+ * (model_init.h:5-10) and `gpu_test_rmse` (rmse.h:168).  This header is what a binding of that
+ * path would call instead.  Conventions:
+ *   - every function returns an int status (MASCOT_OK == 0, negative on failure) instead of the
+ *     reference's print-and-exit `gpuErr` (common.h:3-11); nothing throws or exits;
+ *   - plain pointers and sizes only; the caller owns every host buffer it passes, the library owns
+ *     all device memory of a handle until mascot_destroy();
+ *   - one host control thread per handle, as in the reference (one thread, synchronous epochs);
+ *   - factor matrices cross this boundary as fp32, row-major, k consecutive elements per row, in the
+ *     caller's id space - the internal storage precision and element order never leak out;
+ *   - there is no CPU fallback: without a usable CUDA device every call fails with
+ *     MASCOT_ERR_CUDA / MASCOT_ERR_NO_DEVICE.
+ */
+#ifndef MASCOT_H
+#define MASCOT_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MASCOT_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define MASCOT_API __attribute__((visibility("default")))
+#else
+#define MASCOT_API
+#endif
+
+enum {
+    MASCOT_OK = 0,
+    MASCOT_ERR_BAD_ARG = -1,      /* null pointer, k not in {64,128}, unknown variant, id out of range ... */
+    MASCOT_ERR_CUDA = -2,         /* a CUDA runtime call failed; see mascot_last_error() */
+    MASCOT_ERR_OOM = -3,          /* host or device allocation failed */
+    MASCOT_ERR_STATE = -4,        /* call order violated (e.g. training before ratings were set) */
+    MASCOT_ERR_NO_DEVICE = -5,    /* no CUDA device / requested device absent */
+    MASCOT_ERR_TIMEOUT = -6,      /* a bounded wait (multi-GPU exchange) ran out */
+    MASCOT_ERR_UNSUPPORTED = -7,  /* valid request the engine does not implement */
+    MASCOT_ERR_COMM = -8          /* NCCL / peer communication failure */
+};
+
+/* Training variants, numbered like the reference's `-v` flag (main.cu:152-162). */
+enum {
+    MASCOT_V_MASCOT = 1,    /* mascot_training_mf            mf_methods.cu:36-434   */
+    MASCOT_V_AFP = 2,       /* adaptive_fixed_point_training mf_methods.cu:436-527  */
+    MASCOT_V_MUPPET = 3,    /* muppet_training_mf            mf_methods.cu:529-711  */
+    MASCOT_V_MPT = 4,       /* mixed_precision_training_mf   mf_methods.cu:713-818  */
+    MASCOT_V_SGD = 5,       /* training_single_mf            mf_methods.cu:820-924  */
+    MASCOT_V_MEMQUANT = 7   /* training_mem_quant_mf         mf_methods.cu:1303-1394 */
+};
+
+/* One rating; same 12-byte record as the reference's `Node` (common_struct.h:8-12). */
+typedef struct mascot_rating {
+    float r;
+    uint32_t u;
+    uint32_t i;
+} mascot_rating;
+
+/* Mirrors `Parameter` (common_struct.h:19-35) plus `Mf_info::version` / `is_yahoo`
+ * (common_struct.h:85-86); the trailing fields are additive extensions. */
+typedef struct mascot_config {
+    float lambda;                /* -b   regularisation            default 0.015 (main.cu:19)  */
+    float learning_rate;         /* -a                             default 0.01                */
+    float decay;                 /* -d                             default 0.1                 */
+    float sample_ratio;          /* -s / -r  sampled tail          default 0.01                */
+    float error_threshold;       /* -e   promote when error > e    default 0.001               */
+    uint32_t interval;           /* -it  epochs between checks     default 1                   */
+    uint32_t user_group_num;     /* -ug  requested user groups     default 10                  */
+    uint32_t item_group_num;     /* -ig  requested item groups     default 10                  */
+    uint32_t k;                  /* -k   64 or 128                 default 128                 */
+    uint32_t num_workers;        /* -wg  accepted for CLI parity; a hint only (persistent grid) */
+    uint32_t epoch;              /* -l   number of epochs          default 50                  */
+    uint32_t thread_block_size;  /* -bl  accepted for CLI parity; a hint only                   */
+    uint32_t version;            /* -v   one of MASCOT_V_*         default 7 in the reference  */
+    uint32_t is_yahoo;           /* MuPPET starts at 12 bits when set (mf_methods.cu:600-601)  */
+    /* ---- extensions ---- */
+    uint32_t deterministic;      /* 1: a single team of lanes walks the stream in order; bit-exact
+                                       against a sequential host replay of the same rule         */
+    uint32_t shuffle;            /* 1: apply the seeded permutation to the training stream
+                                       (the reference shuffles with srand(time(0)), mf_methods.cu:38-39) */
+    uint64_t seed;               /* seeds the stream permutation and mascot_init_factors()      */
+    int32_t device;              /* CUDA device ordinal                                         */
+    uint32_t grid_blocks;        /* 0: engine chooses a persistent grid from the SM count        */
+    uint32_t reserved[6];
+} mascot_config;
+
+typedef struct mascot_epoch_stats {
+    uint64_t updates;            /* ratings processed by this epoch's update kernel             */
+    float lr;                    /* learning rate used (schedule mf_methods.cu:94-97)           */
+    float kernel_ms;             /* update kernel, CUDA-event time on the engine's stream       */
+    float total_ms;              /* update + statistics + promotion, CUDA-event time            */
+    uint32_t error_check;        /* 1 when group errors were computed this epoch                */
+    uint32_t promoted_user_groups;
+    uint32_t promoted_item_groups;
+    uint32_t kernel_launches;    /* kernels launched by this call                               */
+} mascot_epoch_stats;
+
+typedef struct mascot_handle mascot_handle;
+
+/* ABI self-description for bindings: version and the byte sizes of the two public structs. */
+MASCOT_API int mascot_abi_info(uint32_t* abi_version, uint32_t* config_bytes, uint32_t* epoch_stats_bytes);
+
+/* Fill `cfg` with the reference CLI defaults (main.cu:19-32); extensions: shuffle=1, seed=1. */
+MASCOT_API int mascot_config_default(mascot_config* cfg);
+
+/* Create an engine on cfg->device.  Replaces the argument plumbing of main.cu:134-148. */
+MASCOT_API int mascot_create(const mascot_config* cfg, mascot_handle** out);
+MASCOT_API int mascot_destroy(mascot_handle* h);
+
+/* Message of the last failure on this handle (or of the last failed mascot_create when h is NULL). */
+MASCOT_API const char* mascot_last_error(const mascot_handle* h);
+MASCOT_API const char* mascot_status_string(int status);
+
+/* Hand over the training and test ratings (host memory, ids already compact in [0,n_users) x
+ * [0,n_items), the id space produced by read_training_dataset, io_utils.h:93-106).  Uploads them,
+ * and for MASCOT_V_MASCOT runs the m-quantization set-up: degree histogram, ascending sort,
+ * grouping, id -> sorted-index remap (user_item_rating_histogram / split_group_... /
+ * matrix_reconstruction, preprocess_utils.h:54-255; host shuffle mf_methods.cu:38-42). */
+MASCOT_API int mascot_set_ratings(mascot_handle* h, const mascot_rating* train, uint64_t n_train,
+                       const mascot_rating* test, uint64_t n_test, uint32_t n_users, uint32_t n_items);
+
+/* N(0, 0.01^2) factors from a counter-based generator seeded with cfg.seed (init_model_single /
+ * init_model_half, model_init.cu:114-173; the reference seeds cuRAND with clock()). */
+MASCOT_API int mascot_init_factors(mascot_handle* h);
+/* Caller-provided factors, fp32 [n_users][k] and [n_items][k] in compact-id order.  For fp16-stored
+ * variants they are converted with round-to-nearest-even (model_init.cu:51-54). */
+MASCOT_API int mascot_set_factors(mascot_handle* h, const float* P, const float* Q);
+
+/* One epoch = one pass of the update kernel over the training stream with lr_schedule[epoch]; for
+ * MASCOT_V_MASCOT also the sampled group-error statistics on check epochs and the precision
+ * switching that follows (epoch body of mf_methods.cu:168-397; precision_switching.h:8-51).
+ * `stats` may be NULL. */
+MASCOT_API int mascot_train_epoch(mascot_handle* h, uint32_t epoch, mascot_epoch_stats* stats);
+
+/* Test RMSE of the current factors, reduced exactly like gpu_test_rmse (rmse.h:168-189): fp32 dot
+ * products, 512-rating block trees, float sum of the block partials, sqrt(sum / n). */
+MASCOT_API int mascot_eval_rmse(mascot_handle* h, double* rmse);
+
+/* Copy the factors out as fp32.  order 0: compact-id rows (what save_trained_model writes,
+ * io_utils.h:242-303); order 1: sorted-index rows (save_trained_model_reconst, io_utils.h:305-332;
+ * identical to order 0 for variants without m-quantization). */
+MASCOT_API int mascot_get_factors(mascot_handle* h, float* P, float* Q, int order);
+
+/* Group tables of one side (0 users, 1 items): number of groups, inclusive end index of each group
+ * in sorted-index space, storage precision (0 fp16, 1 fp32) and the last normalised group error
+ * (-1 for groups already in fp32).  Any output pointer may be NULL.  Arrays need room for the
+ * requested group count of the config. */
+MASCOT_API int mascot_get_group_info(mascot_handle* h, int side, uint32_t* n_groups, uint32_t* end_idx,
+                          uint8_t* precision, float* error);
+
+/* Extension: switch one fp16 group of the MASCOT variant to fp32 storage now - the action
+ * precision_switching_by_groups_grad_diversity (precision_switching.h:8-51) takes for a group whose
+ * error exceeds the threshold.  One way; a no-op for a group that is already fp32. */
+MASCOT_API int mascot_promote_group(mascot_handle* h, int side, uint32_t group);
+
+/* id -> sorted-index maps built by the m-quantization set-up (matrix_reconstruction,
+ * preprocess_utils.h:215-240); identity for other variants.  Either pointer may be NULL. */
+MASCOT_API int mascot_get_index_maps(mascot_handle* h, uint32_t* user2sorted, uint32_t* item2sorted);
+
+/* Sampled statistics of the last check epoch (grad_sum_norm_{p,q} [groups*k] and per-group sum of
+ * squared gradient norms; mascot_sgd_kernel.h:240-277, 448-456).  Pointers may be NULL. */
+MASCOT_API int mascot_get_sample_stats(mascot_handle* h, float* grad_sum_p, float* grad_sum_q,
+                            float* norm_sum_p, float* norm_sum_q);
+
+/* The test set in the id space of `order` (1: sorted-index, what save_reconst_testset writes,
+ * io_utils.h:374-405), sorted like test_set_preprocess (preprocess_utils.h:38-52) leaves it. */
+MASCOT_API int mascot_get_test_ratings(mascot_handle* h, mascot_rating* out, int order);
+
+/* Position in the caller's training array of the rating that the engine processes at stream
+ * position `pos` (identity when shuffle == 0).  Lets a host replay follow the same order. */
+MASCOT_API int mascot_stream_source_index(const mascot_handle* h, uint64_t pos, uint64_t* src);
+
+/* ---- handle-free evaluation: the `gpu_test_rmse` used by test_mf (test_mf/test.cu:56-72) ---- */
+
+/* Host buffers in, RMSE out: fp32 P [n_users][k], Q [n_items][k], test ratings with plain row
+ * indices.  Copies to the device, evaluates, frees. */
+MASCOT_API int mascot_rmse_host(const float* P, uint32_t n_users, const float* Q, uint32_t n_items, uint32_t k,
+                     const mascot_rating* test, uint64_t n_test, int device, double* rmse);
+/* Same evaluation on buffers already on the current device (fp32 rows in the reference's element
+ * order).  Allocates its block-partial scratch with cudaMalloc and frees it before returning. */
+MASCOT_API int mascot_rmse_device(const float* d_P, const float* d_Q, uint32_t k, const mascot_rating* d_test,
+                       uint64_t n_test, double* rmse);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MASCOT_H */

@@ -176,15 +176,16 @@ int mo_grouping(const uint32_t* cnt_sorted, uint32_t n_entities, uint32_t reques
     uint32_t max_cnt = cnt_sorted[n_entities - 1];
     int groups = 0;
     uint32_t acc = 0;
-    uint32_t pos = 0;
+    uint32_t pos = 0, prev = 0;
     while (pos < n_entities) {
         uint32_t c = cnt_sorted[pos];
         uint32_t last = pos;
         while (last + 1 < n_entities && cnt_sorted[last + 1] == c) last++;
         if (c >= 1) {   /* the reference's walk starts at degree 1 (preprocess_utils.h:139) */
-            acc += last - pos + 1;
+            acc += last - prev + 1;
             if (acc >= threshold) { end_idx[groups++] = last; acc = 0; }
             else if (c == max_cnt) end_idx[groups++] = last;
+            prev = last + 1;
         }
         pos = last + 1;
     }
