@@ -41,7 +41,7 @@ struct mascot_handle {
     uint32_t* d_umap = nullptr; uint32_t* d_imap = nullptr;
     float* d_stats = nullptr;       // gsum_p | gsum_q | nsum_p | nsum_q
     float* d_block_err = nullptr;
-    float* d_scratch = nullptr; size_t scratch_bytes = 0;
+    void* d_scratch = nullptr; size_t scratch_bytes = 0;   // staging for mascot_reload_train
 
     // host
     std::vector<uint32_t> user2sorted, item2sorted, uend, iend;
@@ -50,6 +50,8 @@ struct mascot_handle {
     std::vector<float> lr;
     std::vector<float> h_stats;     // same layout as d_stats, gsum in LOGICAL element order
     std::vector<float> h_block_err;
+    std::vector<uint64_t> udeg_sum, ideg_sum;   // ratings per group (training set), for byte accounting
+    uint64_t n_train_accounted = 0;
     std::string err;
 };
 
@@ -142,6 +144,29 @@ void make_groups(const std::vector<uint32_t>& cnt_sorted, uint32_t requested, st
         pos = last + 1;
     }
     if (end_idx.empty() || end_idx.back() != n - 1) end_idx.push_back(n - 1);   // only when every degree is 0
+}
+
+void group_degree_sums(const std::vector<uint32_t>& cnt_sorted, const std::vector<uint32_t>& end, std::vector<uint64_t>& out) {
+    out.assign(end.size(), 0);
+    uint32_t s = 0;
+    for (size_t g = 0; g < end.size(); g++)
+        for (; s <= end[g] && s < cnt_sorted.size(); s++) out[g] += cnt_sorted[s];
+}
+
+// bytes the update rule moves per epoch: every rating reads and writes k elements on each side
+uint64_t algorithmic_bytes(const mascot_handle* h) {
+    double per_side[2] = {0, 0};
+    for (int side = 0; side < 2; side++) {
+        const std::vector<uint64_t>& deg = side == 0 ? h->udeg_sum : h->ideg_sum;
+        const std::vector<uint8_t>& prec = side == 0 ? h->uprec : h->iprec;
+        for (size_t g = 0; g < deg.size(); g++) {
+            // MPT / AFP / MuPPET keep fp32 masters; fp16-stored groups move 2 bytes per element
+            per_side[side] += (double)deg[g] * (prec[g] ? 4.0 : 2.0);
+        }
+    }
+    double total = 2.0 * h->K * (per_side[0] + per_side[1]);
+    if (h->n_train_accounted && h->n_train != h->n_train_accounted) total *= (double)h->n_train / (double)h->n_train_accounted;
+    return (uint64_t)total;
 }
 
 size_t stats_floats(const mascot_handle* h) {
@@ -314,8 +339,10 @@ int mascot_set_ratings(mascot_handle* h, const mascot_rating* train, uint64_t n_
         std::vector<uint32_t> s2o, cnt;
         degree_sort(train, n_train, true, n_users, s2o, h->user2sorted, cnt);
         make_groups(cnt, h->cfg.user_group_num, h->uend);
+        group_degree_sums(cnt, h->uend, h->udeg_sum);
         degree_sort(train, n_train, false, n_items, s2o, h->item2sorted, cnt);
         make_groups(cnt, h->cfg.item_group_num, h->iend);
+        group_degree_sums(cnt, h->iend, h->ideg_sum);
         if (h->uend.size() > 65535 || h->iend.size() > 65535) return fail(h, MASCOT_ERR_BAD_ARG, "more than 65535 groups");
         h->uprec.assign(h->uend.size(), 0); h->iprec.assign(h->iend.size(), 0);
     } else {
@@ -323,7 +350,9 @@ int mascot_set_ratings(mascot_handle* h, const mascot_rating* train, uint64_t n_
         h->uend.assign(1, n_users - 1); h->iend.assign(1, n_items - 1);
         const uint8_t p = (h->kind == KIND_MEMQUANT) ? 0 : 1;
         h->uprec.assign(1, p); h->iprec.assign(1, p);
+        h->udeg_sum.assign(1, n_train); h->ideg_sum.assign(1, n_train);
     }
+    h->n_train_accounted = n_train;
     h->uerr.assign(h->uend.size(), 0.f); h->ierr.assign(h->iend.size(), 0.f);
     h->init_uerr.assign(h->uend.size(), 1.f); h->init_ierr.assign(h->iend.size(), 1.f);   // mf_methods.cu:150-151
 
@@ -341,7 +370,7 @@ int mascot_set_ratings(mascot_handle* h, const mascot_rating* train, uint64_t n_
     {
         // test_set_preprocess (preprocess_utils.h:38-52) leaves the test set ordered by (user, item)
         std::vector<mascot_rating> t(test, test + n_test);
-        std::sort(t.begin(), t.end(), [](const mascot_rating& a, const mascot_rating& b) {
+        std::stable_sort(t.begin(), t.end(), [](const mascot_rating& a, const mascot_rating& b) {
             return a.u != b.u ? a.u < b.u : a.i < b.i;
         });
         if ((rc = upload_and_encode(h, t.data(), n_test, false, &h->te_r, &h->te_u, &h->te_i)) != MASCOT_OK) return rc;
@@ -358,6 +387,30 @@ int mascot_set_ratings(mascot_handle* h, const mascot_rating* train, uint64_t n_
     CU(h, dev_alloc(&h->d_block_err, blocks));
     h->h_block_err.assign(blocks, 0.f);
     h->have_ratings = true;
+    return MASCOT_OK;
+}
+
+int mascot_reload_train(mascot_handle* h, const mascot_rating* train, uint64_t n_train) {
+    if (!h) return MASCOT_ERR_BAD_ARG;
+    if (!train && n_train) return fail(h, MASCOT_ERR_BAD_ARG, "null rating array");
+    if (!h->have_ratings) return fail(h, MASCOT_ERR_STATE, "mascot_set_ratings must come first");
+    CU(h, cudaSetDevice(h->cfg.device));
+    if (n_train != h->n_train) {
+        dev_free(h->tr_r); dev_free(h->tr_u); dev_free(h->tr_i);
+        CU(h, dev_alloc(&h->tr_r, n_train)); CU(h, dev_alloc(&h->tr_u, n_train)); CU(h, dev_alloc(&h->tr_i, n_train));
+        h->n_train = n_train;
+    }
+    if (!n_train) return MASCOT_OK;
+    const size_t bytes = sizeof(mascot_rating) * n_train;
+    if (h->scratch_bytes < bytes) {
+        dev_free(h->d_scratch); h->scratch_bytes = 0;
+        CU(h, cudaMalloc(&h->d_scratch, bytes));
+        h->scratch_bytes = bytes;
+    }
+    CU(h, cudaMemcpyAsync(h->d_scratch, train, bytes, cudaMemcpyHostToDevice, h->stream));
+    CU(h, launch_encode_stream(h->d_scratch, n_train, h->cfg.shuffle != 0, h->cfg.seed, h->d_umap, h->d_imap,
+                               h->d_uprec_row, h->d_iprec_row, h->tr_r, h->tr_u, h->tr_i, h->stream));
+    CU(h, cudaStreamSynchronize(h->stream));
     return MASCOT_OK;
 }
 
@@ -424,6 +477,7 @@ int mascot_train_epoch(mascot_handle* h, uint32_t epoch, mascot_epoch_stats* out
         st.gsum_p = h->d_stats; st.gsum_q = st.gsum_p + (size_t)ug * K;
         st.nsum_p = st.gsum_q + (size_t)ig * K; st.nsum_q = st.nsum_p + ug;
     }
+    const uint64_t bytes_this_epoch = algorithmic_bytes(h);    // with the precisions the kernel is about to see
     CU(h, cudaEventRecord(h->ev[0], h->stream));
     if (check) CU(h, cudaMemsetAsync(h->d_stats, 0, sizeof(float) * stats_floats(h), h->stream));   // mf_methods.cu:178-182
     CU(h, cudaEventRecord(h->ev[1], h->stream));
@@ -484,6 +538,7 @@ int mascot_train_epoch(mascot_handle* h, uint32_t epoch, mascot_epoch_stats* out
         std::memset(out, 0, sizeof(*out));
         out->updates = h->n_train; out->lr = lr; out->error_check = check ? 1 : 0;
         out->promoted_user_groups = promoted_u; out->promoted_item_groups = promoted_i; out->kernel_launches = launches;
+        out->algorithmic_bytes = bytes_this_epoch;
         cudaEventElapsedTime(&out->kernel_ms, h->ev[1], h->ev[2]);
         cudaEventElapsedTime(&out->total_ms, h->ev[0], h->ev[3]);
     }

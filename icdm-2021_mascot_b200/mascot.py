@@ -23,7 +23,7 @@ EXPORTS = [
     "mascot_abi_info", "mascot_config_default", "mascot_create", "mascot_destroy", "mascot_last_error", "mascot_status_string",
     "mascot_set_ratings", "mascot_init_factors", "mascot_set_factors", "mascot_train_epoch", "mascot_eval_rmse",
     "mascot_get_factors", "mascot_get_group_info", "mascot_get_index_maps", "mascot_get_sample_stats",
-    "mascot_get_test_ratings", "mascot_promote_group", "mascot_stream_source_index", "mascot_rmse_host", "mascot_rmse_device",
+    "mascot_get_test_ratings", "mascot_promote_group", "mascot_reload_train", "mascot_stream_source_index", "mascot_rmse_host", "mascot_rmse_device",
 ]
 
 
@@ -42,7 +42,7 @@ class EpochStats(C.Structure):
     _fields_ = [
         ("updates", C.c_uint64), ("lr", C.c_float), ("kernel_ms", C.c_float), ("total_ms", C.c_float),
         ("error_check", C.c_uint32), ("promoted_user_groups", C.c_uint32), ("promoted_item_groups", C.c_uint32),
-        ("kernel_launches", C.c_uint32),
+        ("kernel_launches", C.c_uint32), ("algorithmic_bytes", C.c_uint64),
     ]
 
 
@@ -146,6 +146,15 @@ class Engine:
         self._check(self._lib.mascot_set_ratings(self._h, C.c_void_p(train_ptr), C.c_uint64(n_train), C.c_void_p(test_ptr),
                                                  C.c_uint64(n_test), C.c_uint32(n_users), C.c_uint32(n_items)))
         self.n_users, self.n_items, self.n_train, self.n_test = n_users, n_items, n_train, n_test
+
+    def reload_train_raw(self, train_ptr, n_train):
+        """Replace the training stream from a raw host address (the per-step input path)."""
+        self._check(self._lib.mascot_reload_train(self._h, C.c_void_p(train_ptr), C.c_uint64(n_train)))
+        self.n_train = n_train
+
+    def reload_train(self, train):
+        train = as_ratings(train)
+        self.reload_train_raw(train.ctypes.data, train.size)
 
     def init_factors(self):
         self._check(self._lib.mascot_init_factors(self._h))

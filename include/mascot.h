@@ -97,6 +97,9 @@ typedef struct mascot_epoch_stats {
     uint32_t promoted_user_groups;
     uint32_t promoted_item_groups;
     uint32_t kernel_launches;    /* kernels launched by this call                               */
+    uint64_t algorithmic_bytes;  /* factor bytes the update rule reads + writes this epoch:
+                                    sum over ratings of 2*k*(bytes per user element + bytes per
+                                    item element), 2 for fp16 storage and 4 for fp32            */
 } mascot_epoch_stats;
 
 typedef struct mascot_handle mascot_handle;
@@ -122,6 +125,12 @@ MASCOT_API const char* mascot_status_string(int status);
  * matrix_reconstruction, preprocess_utils.h:54-255; host shuffle mf_methods.cu:38-42). */
 MASCOT_API int mascot_set_ratings(mascot_handle* h, const mascot_rating* train, uint64_t n_train,
                        const mascot_rating* test, uint64_t n_test, uint32_t n_users, uint32_t n_items);
+
+/* Extension: replace the training stream by `train` (host memory, same id space and same
+ * n_users / n_items as the last mascot_set_ratings) without redoing the set-up: one host->device
+ * copy plus the encode kernel.  This is the per-step input path of an out-of-core / end-to-end
+ * epoch.  The ids are not validated again. */
+MASCOT_API int mascot_reload_train(mascot_handle* h, const mascot_rating* train, uint64_t n_train);
 
 /* N(0, 0.01^2) factors from a counter-based generator seeded with cfg.seed (init_model_single /
  * init_model_half, model_init.cu:114-173; the reference seeds cuRAND with clock()). */

@@ -41,3 +41,9 @@ def random_problem(rng, n_users, n_items, n, k, scale=0.1, grid=None):
     P = (rng.standard_normal((n_users, k)) * scale).astype(np.float32)
     Q = (rng.standard_normal((n_items, k)) * scale).astype(np.float32)
     return R, P, Q
+
+
+def sort_like_reference(test):
+    """Order of test_set_preprocess (preprocess_utils.h:38-52): by user, then item; equal pairs keep
+    the caller's order (the engine uses a stable sort)."""
+    return test[np.lexsort((test["i"], test["u"]))]

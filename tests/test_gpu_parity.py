@@ -7,7 +7,7 @@ import ctypes as C
 import numpy as np
 import pytest
 
-from helpers import assert_bit_equal, golden_case, random_problem
+from helpers import assert_bit_equal, golden_case, random_problem, sort_like_reference
 
 pytestmark = pytest.mark.gpu
 KS = (128, 64)
@@ -134,7 +134,7 @@ def test_deterministic_epochs_bit_exact(mascot, oracle, k, version):
     assert_bit_equal(Pg, Po, "P")
     assert_bit_equal(Qg, Qo, "Q")
     # test RMSE, reduced exactly like the reference
-    ts = np.sort(test, order=["u", "i"])
+    ts = sort_like_reference(test)
     want, _ = oracle.rmse_literal(k, ts, Po, Qo, rules)
     got = eng.eval_rmse()
     assert_bit_equal(np.float32(got), np.float32(want), "rmse")
@@ -231,7 +231,7 @@ def test_mascot_training_with_switching_bit_exact(mascot, oracle, k):
         assert_bit_equal(Qg, Qo, f"epoch {e} Q")
     assert promoted_any, "the case is meant to exercise threshold-driven switching"
     # evaluation straight from the mixed-precision arenas
-    ts = np.sort(test, order=["u", "i"]); ts_s = ts.copy(); ts_s["u"] = u2s[ts["u"]]; ts_s["i"] = i2s[ts["i"]]
+    ts = sort_like_reference(test); ts_s = ts.copy(); ts_s["u"] = u2s[ts["u"]]; ts_s["i"] = i2s[ts["i"]]
     want, _ = oracle.rmse_literal(k, ts_s, Po, Qo, rules)
     assert_bit_equal(np.float32(eng.eval_rmse()), np.float32(want), "rmse")
     got_test = eng.test_ratings(1)
