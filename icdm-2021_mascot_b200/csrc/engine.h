@@ -65,4 +65,7 @@ cudaError_t launch_gather_factors(int K, Arena a, const uint8_t* prec_row, uint3
 cudaError_t launch_promote_rows(int K, Arena a, uint32_t row_begin, uint32_t row_end, cudaStream_t st);
 cudaError_t launch_init_normal(float* dst, uint64_t count, uint64_t seed, uint64_t stream_id, cudaStream_t st);
 
+// Records the message returned by mascot_last_error(NULL) for handle-free entry points.
+void set_global_error(const char* msg);
+
 }  // namespace mascot

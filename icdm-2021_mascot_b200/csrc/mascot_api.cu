@@ -59,6 +59,12 @@ namespace {
 
 thread_local std::string g_create_error;
 
+}  // namespace
+
+void mascot::set_global_error(const char* msg) { g_create_error = msg ? msg : ""; }
+
+namespace {
+
 int fail(mascot_handle* h, int code, const std::string& msg) {
     if (h) h->err = msg; else g_create_error = msg;
     return code;

@@ -260,10 +260,13 @@ def test_full_grid_on_conflict_free_ratings_bit_exact(mascot, oracle, k, version
     eng.set_ratings(R, R[:100], n, n)
     eng.set_factors(P, Q)
     # every entity has degree 1, so each side is a single group: promoting it switches the whole side
-    if version in ("mascot_fh", "mascot_ff"):
-        eng.promote_group(0, 0)
-    if version in ("mascot_hf", "mascot_ff"):
-        eng.promote_group(1, 0)
+    model = None
+    if version != "sgd":
+        model, u2s, i2s = mascot_oracle_model(oracle, eng, k, P, Q)
+        if version in ("mascot_fh", "mascot_ff"):
+            eng.promote_group(0, 0); model.promote("u", 0)
+        if version in ("mascot_hf", "mascot_ff"):
+            eng.promote_group(1, 0); model.promote("i", 0)
     st = eng.train_epoch(0)
     assert st.updates == n
     rules = oracle.rules_reference()
@@ -272,7 +275,6 @@ def test_full_grid_on_conflict_free_ratings_bit_exact(mascot, oracle, k, version
         oracle.sgd_run(k, R, None, Po, Qo, 0.01, 0.05, rules)
         Pg, Qg = eng.get_factors(0)
     else:
-        model, u2s, i2s = mascot_oracle_model(oracle, eng, k, P, Q)
         Rs = R.copy(); Rs["u"] = u2s[R["u"]]; Rs["i"] = i2s[R["i"]]
         model.run(Rs, None, 0.01, 0.05, rules)
         Po, Qo = model.factors()
