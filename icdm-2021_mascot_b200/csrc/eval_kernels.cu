@@ -10,6 +10,10 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <cmath>
+#include <cstdio>
+
+#include "../../include/mascot.h"
 #include "engine.h"
 #include "layout.cuh"
 
@@ -140,3 +144,76 @@ cudaError_t launch_rmse_plain(int K, const void* d_test_aos, uint64_t n, const f
 }
 
 }  // namespace mascot
+
+// ---------------------------------------------------------------------------------------------
+// Evaluation without any allocation.
+//
+// Some callers must not allocate device memory at call time: an evaluation hook that runs between
+// training steps of a host program which has handed the whole GPU to its own memory pool (a
+// cudaMalloc there can fail or fragment the pool), a serving loop that cannot afford the implicit
+// device-wide synchronisation of cudaMalloc/cudaFree, or a process working inside a memory budget
+// that was fixed at start-up.  For them the per-block partial sums live in the fixed array below
+// instead of a cudaMalloc'ed buffer.  Every GPU that loads this library holds the array (256 KiB)
+// until the process exits.
+// ---------------------------------------------------------------------------------------------
+namespace mascot {
+namespace {
+
+constexpr uint64_t kStaticMaxBlocks = 1u << 16;                       // 65,536 partials = 256 KiB
+constexpr uint64_t kStaticMaxRatings = kStaticMaxBlocks * kRmseBlock; // 33,554,432 test ratings
+constexpr int kMaxDevices = 64;
+
+static __device__ __align__(256) float g_static_block_err[kStaticMaxBlocks];
+
+// In host code the name above is only a stand-in for the symbol, not an address a kernel can use:
+// the device address is looked up once per device (with that device current) and cached here.
+float* g_static_block_err_addr[kMaxDevices] = {nullptr};
+float g_static_host_partials[kStaticMaxBlocks];
+
+}  // namespace
+}  // namespace mascot
+
+extern "C" int mascot_rmse_device_noalloc(const float* d_P, const float* d_Q, uint32_t k, const mascot_rating* d_test,
+                                          uint64_t n_test, double* rmse) {
+    using namespace mascot;
+    char msg[256];
+    if (!d_P || !d_Q || !d_test || !rmse || !n_test) { set_global_error("null pointer or empty test set"); return MASCOT_ERR_BAD_ARG; }
+    if (k != 64 && k != 128) { set_global_error("k must be 64 or 128"); return MASCOT_ERR_BAD_ARG; }
+    if (n_test > kStaticMaxRatings) {
+        snprintf(msg, sizeof msg, "mascot_rmse_device_noalloc handles at most %llu test ratings per call (got %llu); "
+                 "use mascot_rmse_device for larger sets", (unsigned long long)kStaticMaxRatings, (unsigned long long)n_test);
+        set_global_error(msg);
+        return MASCOT_ERR_BAD_ARG;
+    }
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        set_global_error("no current CUDA device (or device ordinal beyond 63)");
+        return MASCOT_ERR_NO_DEVICE;
+    }
+    if (!g_static_block_err_addr[dev]) {
+        // first call on this device: resolve the symbol's device address
+        float* addr = nullptr;
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&addr), g_static_block_err);
+        if (e != cudaSuccess || !addr) {
+            snprintf(msg, sizeof msg, "cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+            set_global_error(msg);
+            return MASCOT_ERR_CUDA;
+        }
+        g_static_block_err_addr[dev] = addr;
+    }
+    float* d_err = g_static_block_err_addr[dev];
+    const size_t blocks = (size_t)((n_test + kRmseBlock - 1) / kRmseBlock);
+    // every one of the `blocks` partials is overwritten by its block, so nothing has to be cleared
+    e = launch_rmse_plain((int)k, d_test, n_test, d_P, d_Q, d_err, nullptr);
+    if (e == cudaSuccess) e = cudaMemcpy(g_static_host_partials, d_err, sizeof(float) * blocks, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) {
+        snprintf(msg, sizeof msg, "evaluation failed: %s", cudaGetErrorString(e));
+        set_global_error(msg);
+        return MASCOT_ERR_CUDA;
+    }
+    float sum = 0;                                   // same float accumulation order as mascot_rmse_device
+    for (size_t b = 0; b < blocks; b++) sum += g_static_host_partials[b];
+    *rmse = (double)(float)std::sqrt(sum / (double)n_test);
+    return MASCOT_OK;
+}

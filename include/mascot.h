@@ -194,6 +194,22 @@ MASCOT_API int mascot_rmse_host(const float* P, uint32_t n_users, const float* Q
 MASCOT_API int mascot_rmse_device(const float* d_P, const float* d_Q, uint32_t k, const mascot_rating* d_test,
                        uint64_t n_test, double* rmse);
 
+/* No counterpart in the reference.  The same evaluation as mascot_rmse_device for callers that
+ * must not allocate device memory when they call: it performs no cudaMalloc / cudaFree and calls no
+ * allocating library routine; the block partials go to a fixed 256 KiB array in device memory that
+ * every GPU loading libmascot holds until the process exits.
+ *   - limit: at most 33,554,432 test ratings per call (65,536 blocks of 512); larger sets are
+ *     rejected with MASCOT_ERR_BAD_ARG and a message naming the limit;
+ *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress, with
+ *     that device current); make that first call before any stream capture begins;
+ *   - all calls share the one array (and one host staging buffer) and it keeps the previous call's
+ *     contents; each call overwrites every entry it reads, so nothing needs clearing, but two calls
+ *     that overlap in time - from different threads or on different streams of one GPU - race;
+ *   - inputs and output exactly as mascot_rmse_device: device pointers on the current device, fp32
+ *     rows in the reference element order, RMSE written to host memory. */
+MASCOT_API int mascot_rmse_device_noalloc(const float* d_P, const float* d_Q, uint32_t k, const mascot_rating* d_test,
+                                          uint64_t n_test, double* rmse);
+
 #ifdef __cplusplus
 }
 #endif
