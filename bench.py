@@ -177,6 +177,8 @@ def main():
     ap.add_argument("--scale", type=float, default=1.0, help="shrink the workload (debugging only)")
     ap.add_argument("--seed", type=int, default=4)
     ap.add_argument("--cpu-sample", type=int, default=4_000_000)
+    ap.add_argument("--item-zipf", type=float, default=None, help="experiment knob: override the item popularity exponent")
+    ap.add_argument("--grid-blocks", type=int, default=0, help="experiment knob: persistent grid size (0 = engine default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -190,6 +192,8 @@ def main():
     cfg = S.CONFIGS[args.workload]
     if args.scale != 1.0:
         cfg = S.scaled(cfg, args.scale)
+    if args.item_zipf is not None:
+        cfg = dict(cfg, item_deg=("zipf", args.item_zipf))
     args.workload_desc = (f"{args.workload}: MASCOT -v {cfg['version']} k={cfg['k']}, {cfg['users']}x{cfg['items']}, "
                           f"{cfg['n_train']} train ratings, ug=ig=100 s=0.05 it=2 e=20")
 
@@ -212,7 +216,7 @@ def main():
     torch.cuda.empty_cache()
     n_train, n_test = train_t.shape[0], test_t.shape[0]
 
-    ecfg = engine_config(M, cfg, device=local_rank, seed=args.seed)
+    ecfg = engine_config(M, cfg, device=local_rank, seed=args.seed, grid_blocks=args.grid_blocks)
     eng = M.Engine(ecfg)
     eng.set_ratings_raw(train_t.data_ptr(), n_train, test_t.data_ptr(), n_test, cfg["users"], cfg["items"])
     eng.init_factors()

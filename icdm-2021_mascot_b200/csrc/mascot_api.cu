@@ -34,6 +34,7 @@ struct mascot_handle {
 
     // device
     float* tr_r = nullptr; uint32_t* tr_u = nullptr; uint32_t* tr_i = nullptr;
+    uint32_t* tr_src = nullptr;     // source position of each stream entry (when n_train < 2^32)
     float* te_r = nullptr; uint32_t* te_u = nullptr; uint32_t* te_i = nullptr;
     Arena P, Q;
     uint8_t* d_uprec_row = nullptr; uint8_t* d_iprec_row = nullptr;
@@ -89,7 +90,7 @@ template <typename T>
 void dev_free(T*& p) { if (p) { cudaFree(p); p = nullptr; } }
 
 void free_ratings(mascot_handle* h) {
-    dev_free(h->tr_r); dev_free(h->tr_u); dev_free(h->tr_i);
+    dev_free(h->tr_r); dev_free(h->tr_u); dev_free(h->tr_i); dev_free(h->tr_src);
     dev_free(h->te_r); dev_free(h->te_u); dev_free(h->te_i);
     dev_free(h->P.f16); dev_free(h->P.f32); dev_free(h->Q.f16); dev_free(h->Q.f32);
     dev_free(h->d_uprec_row); dev_free(h->d_iprec_row); dev_free(h->d_ugroup); dev_free(h->d_igroup);
@@ -198,15 +199,16 @@ int upload_side_tables(mascot_handle* h, bool users) {
 }
 
 int upload_and_encode(mascot_handle* h, const mascot_rating* src, uint64_t n, bool shuffle,
-                      float** r, uint32_t** u, uint32_t** i) {
+                      float** r, uint32_t** u, uint32_t** i, uint32_t** src_idx) {
     CU(h, dev_alloc(r, n)); CU(h, dev_alloc(u, n)); CU(h, dev_alloc(i, n));
+    if (src_idx && n < (1ull << 32)) CU(h, dev_alloc(src_idx, n));
     if (!n) return MASCOT_OK;
     mascot_rating* tmp = nullptr;
     CU(h, dev_alloc(&tmp, n));
     cudaError_t e = cudaMemcpyAsync(tmp, src, sizeof(mascot_rating) * n, cudaMemcpyHostToDevice, h->stream);
     if (e == cudaSuccess)
         e = launch_encode_stream(tmp, n, shuffle, h->cfg.seed, h->d_umap, h->d_imap, h->d_uprec_row, h->d_iprec_row,
-                                 *r, *u, *i, h->stream);
+                                 h->n_items, *r, *u, *i, src_idx ? *src_idx : nullptr, h->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
     cudaFree(tmp);
     CU(h, e);
@@ -372,14 +374,14 @@ int mascot_set_ratings(mascot_handle* h, const mascot_rating* train, uint64_t n_
     }
 
     // --- rating streams ---
-    if ((rc = upload_and_encode(h, train, n_train, h->cfg.shuffle != 0, &h->tr_r, &h->tr_u, &h->tr_i)) != MASCOT_OK) return rc;
+    if ((rc = upload_and_encode(h, train, n_train, h->cfg.shuffle != 0, &h->tr_r, &h->tr_u, &h->tr_i, &h->tr_src)) != MASCOT_OK) return rc;
     {
         // test_set_preprocess (preprocess_utils.h:38-52) leaves the test set ordered by (user, item)
         std::vector<mascot_rating> t(test, test + n_test);
         std::stable_sort(t.begin(), t.end(), [](const mascot_rating& a, const mascot_rating& b) {
             return a.u != b.u ? a.u < b.u : a.i < b.i;
         });
-        if ((rc = upload_and_encode(h, t.data(), n_test, false, &h->te_r, &h->te_u, &h->te_i)) != MASCOT_OK) return rc;
+        if ((rc = upload_and_encode(h, t.data(), n_test, false, &h->te_r, &h->te_u, &h->te_i, nullptr)) != MASCOT_OK) return rc;
     }
 
     // --- factor arenas and statistics ---
@@ -402,8 +404,9 @@ int mascot_reload_train(mascot_handle* h, const mascot_rating* train, uint64_t n
     if (!h->have_ratings) return fail(h, MASCOT_ERR_STATE, "mascot_set_ratings must come first");
     CU(h, cudaSetDevice(h->cfg.device));
     if (n_train != h->n_train) {
-        dev_free(h->tr_r); dev_free(h->tr_u); dev_free(h->tr_i);
+        dev_free(h->tr_r); dev_free(h->tr_u); dev_free(h->tr_i); dev_free(h->tr_src);
         CU(h, dev_alloc(&h->tr_r, n_train)); CU(h, dev_alloc(&h->tr_u, n_train)); CU(h, dev_alloc(&h->tr_i, n_train));
+        if (n_train < (1ull << 32)) CU(h, dev_alloc(&h->tr_src, n_train));
         h->n_train = n_train;
     }
     if (!n_train) return MASCOT_OK;
@@ -415,7 +418,7 @@ int mascot_reload_train(mascot_handle* h, const mascot_rating* train, uint64_t n
     }
     CU(h, cudaMemcpyAsync(h->d_scratch, train, bytes, cudaMemcpyHostToDevice, h->stream));
     CU(h, launch_encode_stream(h->d_scratch, n_train, h->cfg.shuffle != 0, h->cfg.seed, h->d_umap, h->d_imap,
-                               h->d_uprec_row, h->d_iprec_row, h->tr_r, h->tr_u, h->tr_i, h->stream));
+                               h->d_uprec_row, h->d_iprec_row, h->n_items, h->tr_r, h->tr_u, h->tr_i, h->tr_src, h->stream));
     CU(h, cudaStreamSynchronize(h->stream));
     return MASCOT_OK;
 }
@@ -666,8 +669,22 @@ int mascot_get_test_ratings(mascot_handle* h, mascot_rating* out, int order) {
 
 int mascot_stream_source_index(const mascot_handle* h, uint64_t pos, uint64_t* src) {
     if (!h || !src) return MASCOT_ERR_BAD_ARG;
-    if (pos >= h->n_train) return MASCOT_ERR_BAD_ARG;
-    *src = h->cfg.shuffle ? permute_index(pos, h->n_train, h->cfg.seed) : pos;
+    if (!h->have_ratings || pos >= h->n_train) return MASCOT_ERR_BAD_ARG;
+    if (!h->cfg.shuffle) { *src = pos; return MASCOT_OK; }
+    if (!h->tr_src) return MASCOT_ERR_UNSUPPORTED;       // streams of 2^32 ratings or more keep no map
+    uint32_t v = 0;
+    if (cudaSetDevice(h->cfg.device) != cudaSuccess ||
+        cudaMemcpy(&v, h->tr_src + pos, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return MASCOT_ERR_CUDA;
+    *src = v;
+    return MASCOT_OK;
+}
+
+int mascot_get_stream_order(mascot_handle* h, uint32_t* src_out) {
+    if (!h || !src_out) return MASCOT_ERR_BAD_ARG;
+    if (!h->have_ratings) return fail(h, MASCOT_ERR_STATE, "mascot_set_ratings must come first");
+    if (!h->tr_src) return fail(h, MASCOT_ERR_UNSUPPORTED, "streams of 2^32 ratings or more keep no order map");
+    CU(h, cudaSetDevice(h->cfg.device));
+    CU(h, cudaMemcpy(src_out, h->tr_src, sizeof(uint32_t) * h->n_train, cudaMemcpyDeviceToHost));
     return MASCOT_OK;
 }
 

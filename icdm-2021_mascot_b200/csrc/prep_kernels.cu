@@ -4,6 +4,8 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <cub/block/block_radix_sort.cuh>
+
 #include "engine.h"
 #include "layout.cuh"
 
@@ -25,7 +27,7 @@ inline int grid_for(uint64_t n, int block) {
 __global__ void encode_kernel(const NodeAos* src, uint64_t n, int shuffle, uint64_t seed,
                               const uint32_t* umap, const uint32_t* imap,
                               const uint8_t* uprec, const uint8_t* iprec,
-                              float* r, uint32_t* u, uint32_t* i) {
+                              float* r, uint32_t* u, uint32_t* i, uint32_t* src_out) {
     for (uint64_t j = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; j < n; j += (uint64_t)gridDim.x * blockDim.x) {
         const uint64_t s = shuffle ? permute_index(j, n, seed) : j;
         const NodeAos nd = src[s];
@@ -34,6 +36,59 @@ __global__ void encode_kernel(const NodeAos* src, uint64_t n, int shuffle, uint6
         if (uprec[uu]) uu |= kPrecBit;
         if (iprec[ii]) ii |= kPrecBit;
         r[j] = nd.r; u[j] = uu; i[j] = ii;
+        if (src_out) src_out[j] = (uint32_t)s;
+    }
+}
+
+// Locality-aware variant used when the stream is shuffled: after the seeded permutation the stream is
+// cut into windows of kWindow consecutive positions and each window is stably sorted by item row.
+// Ratings of a popular item then sit next to each other, and the update kernel keeps that item's
+// row in registers for the whole run instead of reading and writing it once per rating - which is
+// what bounds throughput on skewed data (every update of the most popular item otherwise goes
+// through the same L2 lines).  Order inside a window carries no meaning for SGD; across windows the
+// stream stays randomly ordered.  src_out records which source rating landed at each position.
+constexpr int kSortThreads = 256;
+constexpr int kSortItemsPerThread = 16;
+constexpr int kWindow = kSortThreads * kSortItemsPerThread;
+
+__global__ void __launch_bounds__(kSortThreads) encode_sorted_kernel(
+        const NodeAos* src, uint64_t n, uint64_t seed, const uint32_t* umap, const uint32_t* imap,
+        const uint8_t* uprec, const uint8_t* iprec, int key_bits,
+        float* r, uint32_t* u, uint32_t* i, uint32_t* src_out) {
+    typedef cub::BlockRadixSort<uint32_t, kSortThreads, kSortItemsPerThread, uint32_t> Sort;
+    __shared__ typename Sort::TempStorage temp;
+    const uint64_t windows = (n + kWindow - 1) / kWindow;
+    for (uint64_t w = blockIdx.x; w < windows; w += gridDim.x) {
+        const uint64_t base = w * kWindow;
+        uint32_t keys[kSortItemsPerThread], vals[kSortItemsPerThread];
+#pragma unroll
+        for (int t = 0; t < kSortItemsPerThread; t++) {
+            const uint32_t local = threadIdx.x * kSortItemsPerThread + t;
+            const uint64_t pos = base + local;
+            uint32_t key = 0xffffffffu >> (32 - key_bits);      // padding sorts last
+            if (pos < n) {
+                const uint32_t it = src[permute_index(pos, n, seed)].i;
+                key = imap ? imap[it] : it;
+            }
+            keys[t] = key;
+            vals[t] = local;
+        }
+        Sort(temp).Sort(keys, vals, 0, key_bits);
+        __syncthreads();
+#pragma unroll
+        for (int t = 0; t < kSortItemsPerThread; t++) {
+            const uint64_t out = base + threadIdx.x * kSortItemsPerThread + t;
+            if (out < n) {
+                const uint64_t s = permute_index(base + vals[t], n, seed);
+                const NodeAos nd = src[s];
+                uint32_t uu = umap ? umap[nd.u] : nd.u;
+                uint32_t ii = keys[t];
+                if (uprec[uu]) uu |= kPrecBit;
+                if (iprec[ii]) ii |= kPrecBit;
+                r[out] = nd.r; u[out] = uu; i[out] = ii;
+                if (src_out) src_out[out] = (uint32_t)s;
+            }
+        }
     }
 }
 
@@ -105,11 +160,21 @@ __global__ void init_normal_kernel(float* dst, uint64_t count, uint64_t seed, ui
 
 cudaError_t launch_encode_stream(const void* d_src_aos, uint64_t n, bool shuffle, uint64_t seed,
                                  const uint32_t* user_map, const uint32_t* item_map,
-                                 const uint8_t* uprec_row, const uint8_t* iprec_row,
-                                 float* r, uint32_t* u, uint32_t* i, cudaStream_t st) {
+                                 const uint8_t* uprec_row, const uint8_t* iprec_row, uint32_t n_items,
+                                 float* r, uint32_t* u, uint32_t* i, uint32_t* src_out, cudaStream_t st) {
     if (n == 0) return cudaSuccess;
-    encode_kernel<<<grid_for(n, 256), 256, 0, st>>>(static_cast<const NodeAos*>(d_src_aos), n, shuffle ? 1 : 0, seed,
-                                                     user_map, item_map, uprec_row, iprec_row, r, u, i);
+    const NodeAos* src = static_cast<const NodeAos*>(d_src_aos);
+    if (shuffle) {
+        int key_bits = 1;
+        while (key_bits < 31 && (1ull << key_bits) < (uint64_t)n_items + 1) key_bits++;
+        const uint64_t windows = (n + kWindow - 1) / kWindow;
+        const int grid = (int)(windows < 148 * 8 ? windows : 148 * 8);
+        encode_sorted_kernel<<<grid, kSortThreads, 0, st>>>(src, n, seed, user_map, item_map, uprec_row, iprec_row,
+                                                             key_bits, r, u, i, src_out);
+    } else {
+        encode_kernel<<<grid_for(n, 256), 256, 0, st>>>(src, n, 0, seed, user_map, item_map, uprec_row, iprec_row,
+                                                         r, u, i, src_out);
+    }
     return cudaGetLastError();
 }
 

@@ -69,6 +69,27 @@ __device__ __forceinline__ F4 ld_f4(const float* base, uint32_t row, int K, int 
 __device__ __forceinline__ void st_f4(float* base, uint32_t row, int K, int tl, const F4& f) {
     __stcg(reinterpret_cast<float4*>(base + (size_t)row * K) + tl, make_float4(f.x[0], f.x[1], f.x[2], f.x[3]));
 }
+// Raw fetch of a user row: 16 bytes per lane for fp32 storage, 8 (in .x/.y) for binary16 storage.
+template <int KIND>
+__device__ __forceinline__ uint4 ld_row_raw(const Arena& A, uint32_t code, int K, int tl) {
+    const uint32_t row = code & kIdMask;
+    const bool f32 = (KIND == KIND_MIXED) ? ((code & kPrecBit) != 0) : (KIND == KIND_FP32 || KIND == KIND_MPT);
+    if (f32) return __ldcg(reinterpret_cast<const uint4*>(A.f32 + (size_t)row * K) + tl);
+    const uint2 v = __ldcg(reinterpret_cast<const uint2*>(A.f16 + (size_t)row * K) + tl);
+    return make_uint4(v.x, v.y, 0u, 0u);
+}
+__device__ __forceinline__ F4 raw_f4(const uint4& v) {
+    F4 f;
+    f.x[0] = __uint_as_float(v.x); f.x[1] = __uint_as_float(v.y); f.x[2] = __uint_as_float(v.z); f.x[3] = __uint_as_float(v.w);
+    return f;
+}
+__device__ __forceinline__ H4 raw_h4(const uint4& v) {
+    H4 h;
+    h.a = *reinterpret_cast<const __half2*>(&v.x);
+    h.b = *reinterpret_cast<const __half2*>(&v.y);
+    return h;
+}
+
 __device__ __forceinline__ F4 widen(const H4& h) {
     F4 f;
     const float2 lo = __half22float2(h.a), hi = __half22float2(h.b);
@@ -80,6 +101,14 @@ __device__ __forceinline__ H4 narrow(const F4& f) {
     h.a = __halves2half2(__float2half_rn(f.x[0]), __float2half_rn(f.x[1]));
     h.b = __halves2half2(__float2half_rn(f.x[2]), __float2half_rn(f.x[3]));
     return h;
+}
+
+// Write a cached item row back to the arena its precision selects.
+template <int KIND>
+__device__ __forceinline__ void st_item(const Arena& Q, uint32_t code, int K, int tl, const H4& qh, const F4& qf) {
+    const uint32_t row = code & kIdMask;
+    const bool f32 = (KIND == KIND_MIXED) ? ((code & kPrecBit) != 0) : (KIND == KIND_FP32 || KIND == KIND_MPT);
+    if (f32) st_f4(Q.f32, row, K, tl, qf); else st_h4(Q.f16, row, K, tl, qh);
 }
 
 // lane partial of the dot product: (fma(a0,b0,a1*b1)) + (fma(a2,b2,a3*b3))
@@ -173,6 +202,10 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
     const __half2 mpt_lam = __half2half2(__float2half_rn(__fmul_rn(lam, 1000.0f)));
     const float mpt_rev = __fdiv_rn(1.0f, 1000.0f);
 
+    // storage precision of each side: fixed by the trainer, or per row (bit 31) for the mixed one
+    constexpr bool kUserF32Fixed = (KIND == KIND_FP32 || KIND == KIND_MPT);
+    constexpr bool kItemF32Fixed = kUserF32Fixed;
+
     uint64_t c = team;
     float r_n = 0.f; uint32_t u_n = 0, i_n = 0;
     if (c < nchunks) {
@@ -188,76 +221,97 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
         }
         const uint64_t base = c * T;
         const int cnt = (a.s.n - base) < (uint64_t)T ? (int)(a.s.n - base) : T;
+
+        // The item row of a run of equal items stays in registers (qh or qf, by its precision) and is
+        // written back when the item changes or the chunk ends; within one team this is exactly the
+        // sequential semantics, because nothing else of this team touches that row in between.
+        uint32_t cur_ic = 0xffffffffu;          // no row cached (a real id never has all bits set)
+        H4 qh; F4 qf;
+        qh.a = qh.b = __half2half2(__ushort_as_half(0));
+        qf.x[0] = qf.x[1] = qf.x[2] = qf.x[3] = 0.f;
+
+        // user row of the first rating, fetched raw (low 8 bytes used for binary16 rows)
+        uint32_t uc = __shfl_sync(mask, u_l, 0, T);
+        uint4 p_raw = ld_row_raw<KIND>(a.P, uc, K, tl);
         for (int j = 0; j < cnt; j++) {
             const float r = __shfl_sync(mask, r_l, j, T);
-            const uint32_t uc = __shfl_sync(mask, u_l, j, T);
             const uint32_t ic = __shfl_sync(mask, i_l, j, T);
             const uint32_t u = uc & kIdMask, i = ic & kIdMask;
+            const bool uf = (KIND == KIND_MIXED) ? ((uc & kPrecBit) != 0) : kUserF32Fixed;
+            const bool itf = (KIND == KIND_MIXED) ? ((ic & kPrecBit) != 0) : kItemF32Fixed;
             const bool sampled = STATS && (base + j >= a.st.first_sample_pos);
 
-            if (KIND == KIND_FP32) {
-                const F4 p = ld_f4(a.P.f32, u, K, tl), q = ld_f4(a.Q.f32, i, K, tl);
-                const float e = __fsub_rn(r, team_sum<T>(pair_partial(p, q), mask));
-                st_f4(a.P.f32, u, K, tl, step(lr, grad(e, q, lam, p), p));
-                st_f4(a.Q.f32, i, K, tl, step(lr, grad(e, p, lam, q), q));
-            } else if (KIND == KIND_MPT) {
-                const F4 p = ld_f4(a.P.f32, u, K, tl), q = ld_f4(a.Q.f32, i, K, tl);
-                const H4 ph = narrow(p), qh = narrow(q);
-                const __half dot = team_sum<T>(pair_partial(ph, qh), mask);
+            if (ic != cur_ic) {
+                if (cur_ic != 0xffffffffu) st_item<KIND>(a.Q, cur_ic, K, tl, qh, qf);
+                cur_ic = ic;
+                if (itf) qf = ld_f4(a.Q.f32, i, K, tl); else qh = ld_h4(a.Q.f16, i, K, tl);
+            }
+            // prefetch the next rating's user row while this one is processed; a repeated user is
+            // re-read after the store below so that it sees this update
+            const uint4 p_cur = p_raw;
+            uint32_t uc_next = uc;
+            bool refetch = false;
+            if (j + 1 < cnt) {
+                uc_next = __shfl_sync(mask, u_l, j + 1, T);
+                if (uc_next != uc) p_raw = ld_row_raw<KIND>(a.P, uc_next, K, tl); else refetch = true;
+            }
+
+            if (KIND == KIND_MPT) {
+                const F4 p = raw_f4(p_cur);
+                const H4 ph = narrow(p), qhh = narrow(qf);
+                const __half dot = team_sum<T>(pair_partial(ph, qhh), mask);
                 const __half2 e = __half2half2(__hmul_rn(mpt_scale, __hsub_rn(__float2half_rn(r), dot)));
-                const F4 gp = widen(grad(e, qh, mpt_lam, ph)), gq = widen(grad(e, ph, mpt_lam, qh));
-                F4 po, qo;
+                const F4 gp = widen(grad(e, qhh, mpt_lam, ph)), gq = widen(grad(e, ph, mpt_lam, qhh));
+                F4 po;
 #pragma unroll
                 for (int s = 0; s < 4; s++) {
                     po.x[s] = __fmaf_rn(lr, __fmul_rn(mpt_rev, gp.x[s]), p.x[s]);
-                    qo.x[s] = __fmaf_rn(lr, __fmul_rn(mpt_rev, gq.x[s]), q.x[s]);
+                    qf.x[s] = __fmaf_rn(lr, __fmul_rn(mpt_rev, gq.x[s]), qf.x[s]);
                 }
                 st_f4(a.P.f32, u, K, tl, po);
-                st_f4(a.Q.f32, i, K, tl, qo);
             } else if (KIND == KIND_MEMQUANT) {
-                const F4 p = widen(ld_h4(a.P.f16, u, K, tl)), q = widen(ld_h4(a.Q.f16, i, K, tl));
+                const F4 p = widen(raw_h4(p_cur)), q = widen(qh);
                 const float part = (K == 128) ? chain_partial(p, q) : pair_partial(p, q);
                 const float e = __fsub_rn(r, team_sum<T>(part, mask));
                 st_h4(a.P.f16, u, K, tl, narrow(step(lr, grad(e, q, lam, p), p)));
-                st_h4(a.Q.f16, i, K, tl, narrow(step(lr, grad(e, p, lam, q), q)));
-            } else {
-                const bool uf = (uc & kPrecBit) != 0, itf = (ic & kPrecBit) != 0;
-                if (!uf && !itf) {
-                    const H4 p = ld_h4(a.P.f16, u, K, tl), q = ld_h4(a.Q.f16, i, K, tl);
-                    const __half dot = team_sum<T>(pair_partial(p, q), mask);
-                    const __half2 e = __half2half2(__hsub_rn(__float2half_rn(r), dot));
-                    const H4 gp = grad(e, q, lam_h, p), gq = grad(e, p, lam_h, q);
-                    H4 po, qo;
-                    po.a = __hfma2(lr_h, gp.a, p.a); po.b = __hfma2(lr_h, gp.b, p.b);
-                    qo.a = __hfma2(lr_h, gq.a, q.a); qo.b = __hfma2(lr_h, gq.b, q.b);
-                    st_h4(a.P.f16, u, K, tl, po);
-                    st_h4(a.Q.f16, i, K, tl, qo);
-                    if (sampled) {
-                        sample_side<K, T>(widen(gp), acc.gs_p, acc.ns_p, a.st.ugroup[u], tl, mask);
-                        sample_side<K, T>(widen(gq), acc.gs_q, acc.ns_q, a.st.igroup[i], tl, mask);
-                    }
-                } else if (!uf && itf) {
-                    const F4 p = widen(ld_h4(a.P.f16, u, K, tl)), q = ld_f4(a.Q.f32, i, K, tl);
-                    const float e = __fsub_rn(r, team_sum<T>(pair_partial(p, q), mask));
-                    const F4 gp = grad(e, q, lam, p);
-                    st_h4(a.P.f16, u, K, tl, narrow(step(lr, gp, p)));
-                    st_f4(a.Q.f32, i, K, tl, step(lr, grad(e, p, lam, q), q));
-                    if (sampled) sample_side<K, T>(gp, acc.gs_p, acc.ns_p, a.st.ugroup[u], tl, mask);
-                } else if (uf && !itf) {
-                    const F4 p = ld_f4(a.P.f32, u, K, tl), q = widen(ld_h4(a.Q.f16, i, K, tl));
-                    const float e = __fsub_rn(r, team_sum<T>(pair_partial(p, q), mask));
-                    const F4 gq = grad(e, p, lam, q);
-                    st_f4(a.P.f32, u, K, tl, step(lr, grad(e, q, lam, p), p));
-                    st_h4(a.Q.f16, i, K, tl, narrow(step(lr, gq, q)));
-                    if (sampled) sample_side<K, T>(gq, acc.gs_q, acc.ns_q, a.st.igroup[i], tl, mask);
-                } else {
-                    const F4 p = ld_f4(a.P.f32, u, K, tl), q = ld_f4(a.Q.f32, i, K, tl);
-                    const float e = __fsub_rn(r, team_sum<T>(pair_partial(p, q), mask));
-                    st_f4(a.P.f32, u, K, tl, step(lr, grad(e, q, lam, p), p));
-                    st_f4(a.Q.f32, i, K, tl, step(lr, grad(e, p, lam, q), q));
+                qh = narrow(step(lr, grad(e, p, lam, q), q));
+            } else if (!uf && !itf) {
+                const H4 p = raw_h4(p_cur);
+                const __half dot = team_sum<T>(pair_partial(p, qh), mask);
+                const __half2 e = __half2half2(__hsub_rn(__float2half_rn(r), dot));
+                const H4 gp = grad(e, qh, lam_h, p), gq = grad(e, p, lam_h, qh);
+                H4 po;
+                po.a = __hfma2(lr_h, gp.a, p.a); po.b = __hfma2(lr_h, gp.b, p.b);
+                qh.a = __hfma2(lr_h, gq.a, qh.a); qh.b = __hfma2(lr_h, gq.b, qh.b);
+                st_h4(a.P.f16, u, K, tl, po);
+                if (sampled) {
+                    sample_side<K, T>(widen(gp), acc.gs_p, acc.ns_p, a.st.ugroup[u], tl, mask);
+                    sample_side<K, T>(widen(gq), acc.gs_q, acc.ns_q, a.st.igroup[i], tl, mask);
                 }
+            } else if (!uf && itf) {
+                const F4 p = widen(raw_h4(p_cur));
+                const float e = __fsub_rn(r, team_sum<T>(pair_partial(p, qf), mask));
+                const F4 gp = grad(e, qf, lam, p);
+                st_h4(a.P.f16, u, K, tl, narrow(step(lr, gp, p)));
+                qf = step(lr, grad(e, p, lam, qf), qf);
+                if (sampled) sample_side<K, T>(gp, acc.gs_p, acc.ns_p, a.st.ugroup[u], tl, mask);
+            } else if (uf && !itf) {
+                const F4 p = raw_f4(p_cur), q = widen(qh);
+                const float e = __fsub_rn(r, team_sum<T>(pair_partial(p, q), mask));
+                const F4 gq = grad(e, p, lam, q);
+                st_f4(a.P.f32, u, K, tl, step(lr, grad(e, q, lam, p), p));
+                qh = narrow(step(lr, gq, q));
+                if (sampled) sample_side<K, T>(gq, acc.gs_q, acc.ns_q, a.st.igroup[i], tl, mask);
+            } else {
+                const F4 p = raw_f4(p_cur);
+                const float e = __fsub_rn(r, team_sum<T>(pair_partial(p, qf), mask));
+                st_f4(a.P.f32, u, K, tl, step(lr, grad(e, qf, lam, p), p));
+                qf = step(lr, grad(e, p, lam, qf), qf);
             }
+            if (refetch) p_raw = ld_row_raw<KIND>(a.P, uc_next, K, tl);
+            uc = uc_next;
         }
+        if (cur_ic != 0xffffffffu) st_item<KIND>(a.Q, cur_ic, K, tl, qh, qf);
     }
 
     if (STATS && a.stats_in_smem) {

@@ -23,7 +23,7 @@ EXPORTS = [
     "mascot_abi_info", "mascot_config_default", "mascot_create", "mascot_destroy", "mascot_last_error", "mascot_status_string",
     "mascot_set_ratings", "mascot_init_factors", "mascot_set_factors", "mascot_train_epoch", "mascot_eval_rmse",
     "mascot_get_factors", "mascot_get_group_info", "mascot_get_index_maps", "mascot_get_sample_stats",
-    "mascot_get_test_ratings", "mascot_promote_group", "mascot_reload_train", "mascot_stream_source_index", "mascot_rmse_host", "mascot_rmse_device", "mascot_rmse_device_noalloc",
+    "mascot_get_test_ratings", "mascot_promote_group", "mascot_reload_train", "mascot_stream_source_index", "mascot_get_stream_order", "mascot_rmse_host", "mascot_rmse_device", "mascot_rmse_device_noalloc",
 ]
 
 
@@ -211,6 +211,11 @@ class Engine:
     def test_ratings(self, order=1):
         out = np.empty(self.n_test, RATING)
         self._check(self._lib.mascot_get_test_ratings(self._h, _ptr(out), C.c_int(order)))
+        return out
+
+    def stream_order(self):
+        out = np.empty(self.n_train, np.uint32)
+        self._check(self._lib.mascot_get_stream_order(self._h, _ptr(out)))
         return out
 
     def stream_source_index(self, pos):

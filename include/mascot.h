@@ -80,8 +80,9 @@ typedef struct mascot_config {
     /* ---- extensions ---- */
     uint32_t deterministic;      /* 1: a single team of lanes walks the stream in order; bit-exact
                                        against a sequential host replay of the same rule         */
-    uint32_t shuffle;            /* 1: apply the seeded permutation to the training stream
-                                       (the reference shuffles with srand(time(0)), mf_methods.cu:38-39) */
+    uint32_t shuffle;            /* 1: seeded permutation of the training stream (the reference shuffles with
+                                       srand(time(0)), mf_methods.cu:38-39), then item-sorted windows of
+                                       4096 ratings; 0: the caller's order, untouched                  */
     uint64_t seed;               /* seeds the stream permutation and mascot_init_factors()      */
     int32_t device;              /* CUDA device ordinal                                         */
     uint32_t grid_blocks;        /* 0: engine chooses a persistent grid from the SM count        */
@@ -180,8 +181,12 @@ MASCOT_API int mascot_get_sample_stats(mascot_handle* h, float* grad_sum_p, floa
 MASCOT_API int mascot_get_test_ratings(mascot_handle* h, mascot_rating* out, int order);
 
 /* Position in the caller's training array of the rating that the engine processes at stream
- * position `pos` (identity when shuffle == 0).  Lets a host replay follow the same order. */
+ * position `pos` (identity when shuffle == 0).  With shuffle == 1 the stream is the seeded
+ * permutation of the caller's array, cut into windows of 4096 positions that are each sorted by
+ * item so that equal items are neighbours.  Lets a host replay follow exactly the same order. */
 MASCOT_API int mascot_stream_source_index(const mascot_handle* h, uint64_t pos, uint64_t* src);
+/* The whole order at once: src_out[pos] for pos in [0, n_train). */
+MASCOT_API int mascot_get_stream_order(mascot_handle* h, uint32_t* src_out);
 
 /* ---- handle-free evaluation: the `gpu_test_rmse` used by test_mf (test_mf/test.cu:56-72) ---- */
 

@@ -291,8 +291,11 @@ def test_seeded_shuffle_is_a_permutation_and_is_followed(mascot, oracle):
     eng = make_engine(mascot, mascot.V_SGD, k, shuffle=1, seed=1234)
     eng.set_ratings(R, R[:10], n_users, n_items)
     eng.set_factors(P, Q)
-    order = np.array([eng.stream_source_index(j) for j in range(n)])
+    order = eng.stream_order().astype(np.int64)
+    assert [eng.stream_source_index(j) for j in (0, 1, 77, n - 1)] == [order[0], order[1], order[77], order[n - 1]]
     assert sorted(order.tolist()) == list(range(n)) and (order != np.arange(n)).any()
+    items = R["i"][order]
+    assert (np.diff(items.astype(np.int64)) >= 0).all(), "one window (n < 4096): equal items are neighbours"
     eng.train_epoch(0)
     Po, Qo = P.copy(), Q.copy()
     oracle.sgd_run(k, R, order.astype(np.uint32), Po, Qo, 0.01, 0.05, oracle.rules_reference())
