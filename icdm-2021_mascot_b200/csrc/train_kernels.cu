@@ -171,10 +171,97 @@ struct KernelArgs {
     float lr, lam;
     SampleStats st;
     int stats_in_smem;
+    int deterministic;
 };
 
+// ---------------------------------------------------------------------------------------------
+// Fast path for k = 128 when every row of a 32-rating chunk is stored in binary16 (the common case
+// of the MASCOT variant): the warp splits into two half-warps, each walking 16 of the chunk's
+// ratings on its own, so every instruction serves two ratings and a row is one 128-bit access per
+// lane.  Lane m of a half-warp holds physical elements 8m..8m+7 = the four elements of reference
+// lane m followed by the four of reference lane m+16; adding the two lane partials is the
+// reference's shfl_down-16 step and xor 8,4,2,1 inside the half-warp finishes the same tree, so
+// the arithmetic is bit-identical to the 32-lane path.  The two half-warps are independent workers
+// (like two warps of the reference), hence this path is not used in deterministic mode.
+// ---------------------------------------------------------------------------------------------
+struct H8 { __half2 v[4]; };
+
+__device__ __forceinline__ H8 raw_h8(const uint4& x) {
+    H8 h;
+    h.v[0] = *reinterpret_cast<const __half2*>(&x.x); h.v[1] = *reinterpret_cast<const __half2*>(&x.y);
+    h.v[2] = *reinterpret_cast<const __half2*>(&x.z); h.v[3] = *reinterpret_cast<const __half2*>(&x.w);
+    return h;
+}
+__device__ __forceinline__ uint4 h8_raw(const H8& h) {
+    uint4 x;
+    x.x = *reinterpret_cast<const unsigned*>(&h.v[0]); x.y = *reinterpret_cast<const unsigned*>(&h.v[1]);
+    x.z = *reinterpret_cast<const unsigned*>(&h.v[2]); x.w = *reinterpret_cast<const unsigned*>(&h.v[3]);
+    return x;
+}
+
+__device__ __forceinline__ void chunk_all_half_k128(const KernelArgs& a, float r_l, uint32_t u_l, uint32_t i_l, int cnt,
+                                                    __half2 lr_h, __half2 lam_h) {
+    constexpr int K = 128;
+    const unsigned full = 0xffffffffu;
+    const int lane = threadIdx.x & 31;
+    const int m = lane & 15;                     // lane inside the half-warp
+    const int half_id = lane >> 4;
+    const int my_cnt = min(max(cnt - 16 * half_id, 0), 16);
+    const int max_cnt = min(cnt, 16);            // half-warp 0 always has at least as many ratings
+
+    uint32_t cur_i = 0xffffffffu;
+    H8 q;
+    q.v[0] = q.v[1] = q.v[2] = q.v[3] = __half2half2(__ushort_as_half(0));
+    uint32_t u = __shfl_sync(full, u_l, 0, 16);
+    uint4 p_raw = make_uint4(0u, 0u, 0u, 0u);
+    if (my_cnt > 0) p_raw = __ldcg(reinterpret_cast<const uint4*>(a.P.f16 + (size_t)u * K) + m);
+    for (int j = 0; j < max_cnt; j++) {
+        const bool on = j < my_cnt;
+        const float r = __shfl_sync(full, r_l, j, 16);
+        const uint32_t i = __shfl_sync(full, i_l, j, 16);
+        const int jn = (j + 1 < 16) ? j + 1 : j;
+        const uint32_t u_next = __shfl_sync(full, u_l, jn, 16);
+        if (on && i != cur_i) {
+            if (cur_i != 0xffffffffu) __stcg(reinterpret_cast<uint4*>(a.Q.f16 + (size_t)cur_i * K) + m, h8_raw(q));
+            cur_i = i;
+            q = raw_h8(__ldcg(reinterpret_cast<const uint4*>(a.Q.f16 + (size_t)i * K) + m));
+        }
+        const H8 p = raw_h8(p_raw);
+        const bool more = on && (j + 1 < my_cnt);
+        const bool refetch = more && (u_next == u);
+        if (more && !refetch) p_raw = __ldcg(reinterpret_cast<const uint4*>(a.P.f16 + (size_t)u_next * K) + m);
+
+        // lane partials of reference lanes m and m+16, then the shfl_down-16 step
+        const __half2 fa = __hfma2(__lows2half2(p.v[0], p.v[1]), __lows2half2(q.v[0], q.v[1]),
+                                   __hmul2_rn(__highs2half2(p.v[0], p.v[1]), __highs2half2(q.v[0], q.v[1])));
+        const __half2 fb = __hfma2(__lows2half2(p.v[2], p.v[3]), __lows2half2(q.v[2], q.v[3]),
+                                   __hmul2_rn(__highs2half2(p.v[2], p.v[3]), __highs2half2(q.v[2], q.v[3])));
+        const __half2 t = __hadd2_rn(__lows2half2(fa, fb), __highs2half2(fa, fb));
+        __half x = __hadd_rn(__low2half(t), __high2half(t));
+#pragma unroll
+        for (int d = 8; d >= 1; d >>= 1) x = __hadd_rn(x, __shfl_xor_sync(full, x, d));
+        const __half2 e = __half2half2(__hsub_rn(__float2half_rn(r), x));
+        H8 po;
+#pragma unroll
+        for (int s = 0; s < 4; s++) {
+            const __half2 gp = __hfma2(e, q.v[s], __hneg2(__hmul2_rn(lam_h, p.v[s])));
+            const __half2 gq = __hfma2(e, p.v[s], __hneg2(__hmul2_rn(lam_h, q.v[s])));
+            po.v[s] = __hfma2(lr_h, gp, p.v[s]);
+            if (on) q.v[s] = __hfma2(lr_h, gq, q.v[s]);
+        }
+        if (on) __stcg(reinterpret_cast<uint4*>(a.P.f16 + (size_t)u * K) + m, h8_raw(po));
+        if (refetch) p_raw = __ldcg(reinterpret_cast<const uint4*>(a.P.f16 + (size_t)u_next * K) + m);
+        u = u_next;
+    }
+    if (cur_i != 0xffffffffu) __stcg(reinterpret_cast<uint4*>(a.Q.f16 + (size_t)cur_i * K) + m, h8_raw(q));
+}
+
+#ifndef MASCOT_TRAIN_MIN_BLOCKS
+#define MASCOT_TRAIN_MIN_BLOCKS 4
+#endif
+
 template <int K, int KIND, bool STATS>
-__global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
+__global__ void __launch_bounds__(256, MASCOT_TRAIN_MIN_BLOCKS) train_kernel(const KernelArgs a) {
     constexpr int T = K / 4;
     extern __shared__ float smem[];
     const int tl = threadIdx.x % T;
@@ -221,6 +308,15 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
         }
         const uint64_t base = c * T;
         const int cnt = (a.s.n - base) < (uint64_t)T ? (int)(a.s.n - base) : T;
+
+        if (K == 128 && KIND == KIND_MIXED && !a.deterministic) {
+            const bool any_f32 = __ballot_sync(0xffffffffu, ((u_l | i_l) & kPrecBit) != 0) != 0;
+            const bool has_samples = STATS && (base + T > a.st.first_sample_pos);
+            if (!any_f32 && !has_samples) {
+                chunk_all_half_k128(a, r_l, u_l, i_l, cnt, lr_h, lam_h);
+                continue;
+            }
+        }
 
         // The item row of a run of equal items stays in registers (qh or qf, by its precision) and is
         // written back when the item changes or the chunk ends; within one team this is exactly the
@@ -342,6 +438,7 @@ template <int K, int KIND, bool STATS>
 cudaError_t launch_one(const KernelArgs& args, bool deterministic, int grid_hint, cudaStream_t st, LaunchShape* shape) {
     auto kern = train_kernel<K, KIND, STATS>;
     KernelArgs a = args;
+    a.deterministic = deterministic ? 1 : 0;
     int block = deterministic ? K / 4 : 256;
     size_t smem = 0;
     a.stats_in_smem = 0;
@@ -387,7 +484,7 @@ cudaError_t launch_train(int K, TrainKind kind, const Stream& s, Arena P, Arena 
                          const SampleStats* stats, bool deterministic, int grid_blocks_hint, cudaStream_t st,
                          LaunchShape* shape) {
     KernelArgs a;
-    a.s = s; a.P = P; a.Q = Q; a.lr = lr; a.lam = lam; a.stats_in_smem = 0;
+    a.s = s; a.P = P; a.Q = Q; a.lr = lr; a.lam = lam; a.stats_in_smem = 0; a.deterministic = 0;
     if (stats) a.st = *stats;
     if (s.n == 0) { if (shape) *shape = LaunchShape(); return cudaSuccess; }
     if (K == 128) return launch_k<128>(kind, a, stats != nullptr, deterministic, grid_blocks_hint, st, shape);

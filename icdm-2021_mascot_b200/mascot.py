@@ -10,7 +10,7 @@ import os
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libmascot.so")
+LIB_PATH = os.environ.get("MASCOT_LIB_PATH", os.path.join(HERE, "libmascot.so"))
 
 RATING = np.dtype([("r", np.float32), ("u", np.uint32), ("i", np.uint32)])
 
