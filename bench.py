@@ -178,7 +178,7 @@ def main():
     ap.add_argument("--seed", type=int, default=4)
     ap.add_argument("--cpu-sample", type=int, default=4_000_000)
     ap.add_argument("--item-zipf", type=float, default=None, help="experiment knob: override the item popularity exponent")
-    ap.add_argument("--grid-blocks", type=int, default=0, help="experiment knob: persistent grid size (0 = engine default)")
+    ap.add_argument("--workers", type=int, default=0, help="concurrent sequential workers (-wg); 0 = the configuration's value")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -216,7 +216,8 @@ def main():
     torch.cuda.empty_cache()
     n_train, n_test = train_t.shape[0], test_t.shape[0]
 
-    ecfg = engine_config(M, cfg, device=local_rank, seed=args.seed, grid_blocks=args.grid_blocks)
+    extra = {"num_workers": args.workers} if args.workers else {}
+    ecfg = engine_config(M, cfg, device=local_rank, seed=args.seed, **extra)
     eng = M.Engine(ecfg)
     eng.set_ratings_raw(train_t.data_ptr(), n_train, test_t.data_ptr(), n_test, cfg["users"], cfg["items"])
     eng.init_factors()

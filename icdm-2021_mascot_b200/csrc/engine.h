@@ -39,11 +39,14 @@ struct LaunchShape {
     int grid = 0;
     int block = 0;
     size_t smem = 0;
+    unsigned workers = 0;   // concurrent sequential workers the launch provides
 };
 
-// Update kernels.  `stats` == nullptr -> plain epoch.  Returns the launch shape used.
+// Update kernels.  `stats` == nullptr -> plain epoch.  `workers` = requested number of concurrent
+// sequential workers (1 = fully sequential); `any_f32_rows` tells the mixed-precision trainer whether
+// any group has been promoted (otherwise every row is binary16).  Returns the launch shape used.
 cudaError_t launch_train(int K, TrainKind kind, const Stream& s, Arena P, Arena Q, float lr, float lam,
-                         const SampleStats* stats, bool deterministic, int grid_blocks_hint, cudaStream_t st,
+                         const SampleStats* stats, bool any_f32_rows, unsigned workers, cudaStream_t st,
                          LaunchShape* shape);
 
 // Test RMSE over a coded SoA stream; block_err has ceil(n/512) floats.

@@ -491,8 +491,11 @@ int mascot_train_epoch(mascot_handle* h, uint32_t epoch, mascot_epoch_stats* out
     if (check) CU(h, cudaMemsetAsync(h->d_stats, 0, sizeof(float) * stats_floats(h), h->stream));   // mf_methods.cu:178-182
     CU(h, cudaEventRecord(h->ev[1], h->stream));
     LaunchShape shape;
-    CU(h, launch_train(K, h->kind, s, h->P, h->Q, lr, h->cfg.lambda, check ? &st : nullptr,
-                       h->cfg.deterministic != 0, (int)h->cfg.grid_blocks, h->stream, &shape));
+    const unsigned workers = h->cfg.deterministic ? 1u : (h->cfg.num_workers ? h->cfg.num_workers : 2048u);
+    bool any_f32 = false;
+    for (uint8_t p : h->uprec) any_f32 |= p != 0;
+    for (uint8_t p : h->iprec) any_f32 |= p != 0;
+    CU(h, launch_train(K, h->kind, s, h->P, h->Q, lr, h->cfg.lambda, check ? &st : nullptr, any_f32, workers, h->stream, &shape));
     launches++;
     CU(h, cudaEventRecord(h->ev[2], h->stream));
 
@@ -548,6 +551,7 @@ int mascot_train_epoch(mascot_handle* h, uint32_t epoch, mascot_epoch_stats* out
         out->updates = h->n_train; out->lr = lr; out->error_check = check ? 1 : 0;
         out->promoted_user_groups = promoted_u; out->promoted_item_groups = promoted_i; out->kernel_launches = launches;
         out->algorithmic_bytes = bytes_this_epoch;
+        out->workers = shape.workers;
         cudaEventElapsedTime(&out->kernel_ms, h->ev[1], h->ev[2]);
         cudaEventElapsedTime(&out->total_ms, h->ev[0], h->ev[3]);
     }

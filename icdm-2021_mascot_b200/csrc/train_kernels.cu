@@ -1,23 +1,31 @@
 // Per-rating SGD update kernels for sm_100a.
 //
-// One "team" of T = K/4 lanes owns one rating at a time; every lane holds four consecutive
-// physical elements of the user row and of the item row (one 64-bit access for binary16 storage,
-// one 128-bit access for fp32 storage; layout.cuh explains the element permutation that makes this
-// reproduce the reference's reduction tree).  Teams walk the rating stream in chunks of T ratings,
-// grid-stride over a persistent grid: the T records of a chunk are fetched with one coalesced load
-// per field (lane j keeps rating j) one chunk ahead of use and broadcast with shuffles, so the only
-// dependent memory round trip per rating is the row gather itself.  Bit 31 of the stream ids says
-// which arena (binary16 or fp32) a row lives in, which replaces the reference's per-rating group
-// search (mascot/mascot_sgd_kernel.h:104-180) with nothing at all.
+// WORKERS.  The reference runs `-wg` warps, each applying one rating at a time; the number of such
+// sequential workers decides how many updates of a popular row are lost to races, i.e. how fast the
+// model converges per epoch.  This engine keeps that meaning of `-wg` - a worker is a group of
+// K/8 lanes (16 for k=128, 8 for k=64; two or four workers per warp) that applies its ratings
+// strictly one after the other - and gets its speed from making each worker fast instead of adding
+// workers: every lane holds eight consecutive physical elements of a row (one 128-bit access for
+// binary16 storage, two for fp32), the rating records of a chunk are fetched coalesced one chunk
+// ahead, user rows are prefetched up to eight ratings ahead into a register ring, the row of an
+// item that repeats (the stream is item-sorted inside shuffle windows) stays in registers for the
+// whole run, and the next run's item row is prefetched when a run starts.  In the steady state a
+// worker waits for nothing but its own dot-product reduction.
 //
-// The arithmetic of each precision case is the reference's, including the fused multiply-adds its
-// compiled kernels execute:
-//   all binary16      mascot_sgd_kernel.h:188-278     binary16 user / fp32 item  :279-342
-//   fp32 / binary16   mascot_sgd_kernel.h:343-407     all fp32                   :408-443
+// ELEMENT ORDER.  layout.cuh stores rows permuted so that lane m of a worker holds the elements of
+// reference lanes m and m+16 (k=128) or m, m+16, m+8, m+24 (k=64).  With pair products
+// f_j = fma(a_2j, b_2j, a_2j+1 * b_2j+1) the lane partial (f_0 + f_1) + (f_2 + f_3) and a xor
+// butterfly over the worker's lanes add exactly the pairs that the reference's per-lane sum and
+// shfl_down 16-8-4-2-1 tree add, so results are bit-identical to the reference kernels:
+//   all binary16      mascot/mascot_sgd_kernel.h:188-278     binary16 user / fp32 item  :279-342
+//   fp32 / binary16   mascot/mascot_sgd_kernel.h:343-407     all fp32                   :408-443
 //   (sgd/sgd_kernel.h:35-76 compiles to the same operations as the all-fp32 case)
-//   MPT               mpt/mpt_sgd_kernel.h:38-91      fp16 storage (-v 7)  sgd/sgd_kernel.h:110-161
-// Every operation is written with a rounding-mode intrinsic so that ptxas cannot re-associate or
-// contract anything further.
+//   MPT               mpt/mpt_sgd_kernel.h:38-91              fp16 storage (-v 7)  sgd/sgd_kernel.h:110-161
+// including the fused multiply-adds the compiled reference executes.  Every operation is written
+// with a rounding-mode intrinsic so that ptxas cannot contract or re-associate anything further.
+//
+// Bit 31 of a stream id says which arena (binary16 or fp32) the row lives in, which replaces the
+// reference's per-rating group search (mascot_sgd_kernel.h:104-180).
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
@@ -28,141 +36,179 @@ namespace mascot {
 
 namespace {
 
-template <int T>
-__device__ __forceinline__ float team_sum(float x, unsigned mask) {
-    x = __fadd_rn(x, __shfl_xor_sync(mask, x, 1));
+constexpr uint32_t kNoRow = 0xffffffffu;     // never a valid stream id
+
+struct V8h { __half2 v[4]; };                // eight binary16 values, physical order
+struct V8f { float x[8]; };
+
+// How the rows of a launch are stored.  Known on the host, so the common cases carry no
+// per-rating precision test and no unused registers.
+enum RowMode { ROWS_HALF = 0, ROWS_F32 = 1, ROWS_DYN = 2 };
+
+// A lane's slice of a row as fetched: 16 bytes for binary16 storage, 32 bytes for fp32 storage.
+template <int MODE> struct Raw { uint4 a, b; };
+template <> struct Raw<ROWS_HALF> { uint4 a; };
+
+__device__ __forceinline__ V8h v8h_of(const uint4& a) {
+    V8h h;
+    h.v[0] = *reinterpret_cast<const __half2*>(&a.x); h.v[1] = *reinterpret_cast<const __half2*>(&a.y);
+    h.v[2] = *reinterpret_cast<const __half2*>(&a.z); h.v[3] = *reinterpret_cast<const __half2*>(&a.w);
+    return h;
+}
+__device__ __forceinline__ V8f v8f_of(const uint4& a, const uint4& b) {
+    V8f f;
+    f.x[0] = __uint_as_float(a.x); f.x[1] = __uint_as_float(a.y); f.x[2] = __uint_as_float(a.z); f.x[3] = __uint_as_float(a.w);
+    f.x[4] = __uint_as_float(b.x); f.x[5] = __uint_as_float(b.y); f.x[6] = __uint_as_float(b.z); f.x[7] = __uint_as_float(b.w);
+    return f;
+}
+template <int MODE> __device__ __forceinline__ V8h as_v8h(const Raw<MODE>& r) { return v8h_of(r.a); }
+template <int MODE> __device__ __forceinline__ V8f as_v8f(const Raw<MODE>& r) {
+    if constexpr (MODE != ROWS_HALF) return v8f_of(r.a, r.b); else return v8f_of(r.a, r.a);   // fp32 rows never occur in ROWS_HALF
+}
+
+template <int MODE> __device__ __forceinline__ void put(Raw<MODE>& r, const V8h& h) {
+    r.a.x = *reinterpret_cast<const unsigned*>(&h.v[0]); r.a.y = *reinterpret_cast<const unsigned*>(&h.v[1]);
+    r.a.z = *reinterpret_cast<const unsigned*>(&h.v[2]); r.a.w = *reinterpret_cast<const unsigned*>(&h.v[3]);
+}
+template <int MODE> __device__ __forceinline__ void put(Raw<MODE>& r, const V8f& f) {
+    if constexpr (MODE != ROWS_HALF) {
+        r.a = make_uint4(__float_as_uint(f.x[0]), __float_as_uint(f.x[1]), __float_as_uint(f.x[2]), __float_as_uint(f.x[3]));
+        r.b = make_uint4(__float_as_uint(f.x[4]), __float_as_uint(f.x[5]), __float_as_uint(f.x[6]), __float_as_uint(f.x[7]));
+    }
+}
+
+__device__ __forceinline__ V8f widen(const V8h& h) {
+    V8f f;
 #pragma unroll
-    for (int d = T / 2; d >= 2; d >>= 1) x = __fadd_rn(x, __shfl_xor_sync(mask, x, d));
+    for (int s = 0; s < 4; s++) { const float2 t = __half22float2(h.v[s]); f.x[2 * s] = t.x; f.x[2 * s + 1] = t.y; }
+    return f;
+}
+__device__ __forceinline__ V8h narrow(const V8f& f) {
+    V8h h;
+#pragma unroll
+    for (int s = 0; s < 4; s++) h.v[s] = __halves2half2(__float2half_rn(f.x[2 * s]), __float2half_rn(f.x[2 * s + 1]));
+    return h;
+}
+
+// Is the row behind this stream id stored in fp32?
+template <int MODE> __device__ __forceinline__ bool is_f32(uint32_t code) {
+    return MODE == ROWS_F32 || (MODE == ROWS_DYN && (code & kPrecBit));
+}
+
+// Row slice of lane m: L2-only loads/stores (rows are shared between SMs and never reused from L1).
+template <int K, int MODE>
+__device__ __forceinline__ Raw<MODE> ld_row(const Arena& A, uint32_t code, int m) {
+    const uint32_t row = code & kIdMask;
+    Raw<MODE> r;
+    if (is_f32<MODE>(code)) {
+        const uint4* p = reinterpret_cast<const uint4*>(A.f32 + (size_t)row * K) + 2 * m;
+        r.a = __ldcg(p);
+        if constexpr (MODE != ROWS_HALF) r.b = __ldcg(p + 1);
+    } else {
+        r.a = __ldcg(reinterpret_cast<const uint4*>(A.f16 + (size_t)row * K) + m);
+    }
+    return r;
+}
+template <int K, int MODE>
+__device__ __forceinline__ void st_row(const Arena& A, uint32_t code, int m, const Raw<MODE>& r) {
+    const uint32_t row = code & kIdMask;
+    if (is_f32<MODE>(code)) {
+        uint4* p = reinterpret_cast<uint4*>(A.f32 + (size_t)row * K) + 2 * m;
+        __stcg(p, r.a);
+        if constexpr (MODE != ROWS_HALF) __stcg(p + 1, r.b);
+    } else {
+        __stcg(reinterpret_cast<uint4*>(A.f16 + (size_t)row * K) + m, r.a);
+    }
+}
+
+// ---- lane partials -------------------------------------------------------------------------
+// (f_0 + f_1) + (f_2 + f_3) with f_j = fma(a_2j, b_2j, a_2j+1 * b_2j+1)
+__device__ __forceinline__ float pair_partial(const V8f& a, const V8f& b) {
+    float f[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) f[j] = __fmaf_rn(a.x[2 * j], b.x[2 * j], __fmul_rn(a.x[2 * j + 1], b.x[2 * j + 1]));
+    return __fadd_rn(__fadd_rn(f[0], f[1]), __fadd_rn(f[2], f[3]));
+}
+__device__ __forceinline__ __half pair_partial(const V8h& p, const V8h& q) {
+    const __half2 f01 = __hfma2(__lows2half2(p.v[0], p.v[1]), __lows2half2(q.v[0], q.v[1]),
+                                __hmul2_rn(__highs2half2(p.v[0], p.v[1]), __highs2half2(q.v[0], q.v[1])));
+    const __half2 f23 = __hfma2(__lows2half2(p.v[2], p.v[3]), __lows2half2(q.v[2], q.v[3]),
+                                __hmul2_rn(__highs2half2(p.v[2], p.v[3]), __highs2half2(q.v[2], q.v[3])));
+    const __half2 t = __hadd2_rn(__lows2half2(f01, f23), __highs2half2(f01, f23));   // (f0+f1, f2+f3)
+    return __hadd_rn(__low2half(t), __high2half(t));
+}
+// k=128 only: the left-to-right product chain of a reference lane over its four elements,
+// fma(a3,b3, fma(a2,b2, fma(a0,b0, a1*b1))), for the two reference lanes this lane holds
+// (fp16-storage trainer sgd/sgd_kernel.h:124, RMSE rmse.h:75).
+__device__ __forceinline__ float chain_partial_k128(const V8f& a, const V8f& b) {
+    float c[2];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        float acc = __fmaf_rn(a.x[4 * h], b.x[4 * h], __fmul_rn(a.x[4 * h + 1], b.x[4 * h + 1]));
+        acc = __fmaf_rn(a.x[4 * h + 2], b.x[4 * h + 2], acc);
+        c[h] = __fmaf_rn(a.x[4 * h + 3], b.x[4 * h + 3], acc);
+    }
+    return __fadd_rn(c[0], c[1]);
+}
+
+template <int TS>
+__device__ __forceinline__ float worker_sum(float x, unsigned wmask) {
+#pragma unroll
+    for (int d = TS / 2; d >= 1; d >>= 1) x = __fadd_rn(x, __shfl_xor_sync(wmask, x, d));
+    return x;
+}
+template <int TS>
+__device__ __forceinline__ __half worker_sum(__half x, unsigned wmask) {
+#pragma unroll
+    for (int d = TS / 2; d >= 1; d >>= 1) x = __hadd_rn(x, __shfl_xor_sync(wmask, x, d));
     return x;
 }
 
-template <int T>
-__device__ __forceinline__ __half team_sum(__half x, unsigned mask) {
-    x = __hadd_rn(x, __shfl_xor_sync(mask, x, 1));
+// t = fma(e, y, -(lam*x)) and x' = fma(lr, t, x), element-wise
+__device__ __forceinline__ V8f grad(float e, const V8f& y, float lam, const V8f& x) {
+    V8f g;
 #pragma unroll
-    for (int d = T / 2; d >= 2; d >>= 1) x = __hadd_rn(x, __shfl_xor_sync(mask, x, d));
-    return x;
-}
-
-struct H4 { __half2 a, b; };          // four binary16 values, physical order
-struct F4 { float x[4]; };
-
-__device__ __forceinline__ H4 ld_h4(const __half* base, uint32_t row, int K, int tl) {
-    const uint2 v = __ldcg(reinterpret_cast<const uint2*>(base + (size_t)row * K) + tl);
-    H4 h;
-    h.a = *reinterpret_cast<const __half2*>(&v.x);
-    h.b = *reinterpret_cast<const __half2*>(&v.y);
-    return h;
-}
-__device__ __forceinline__ void st_h4(__half* base, uint32_t row, int K, int tl, const H4& h) {
-    uint2 v;
-    v.x = *reinterpret_cast<const unsigned*>(&h.a);
-    v.y = *reinterpret_cast<const unsigned*>(&h.b);
-    __stcg(reinterpret_cast<uint2*>(base + (size_t)row * K) + tl, v);
-}
-__device__ __forceinline__ F4 ld_f4(const float* base, uint32_t row, int K, int tl) {
-    const float4 v = __ldcg(reinterpret_cast<const float4*>(base + (size_t)row * K) + tl);
-    F4 f;
-    f.x[0] = v.x; f.x[1] = v.y; f.x[2] = v.z; f.x[3] = v.w;
-    return f;
-}
-__device__ __forceinline__ void st_f4(float* base, uint32_t row, int K, int tl, const F4& f) {
-    __stcg(reinterpret_cast<float4*>(base + (size_t)row * K) + tl, make_float4(f.x[0], f.x[1], f.x[2], f.x[3]));
-}
-// Raw fetch of a user row: 16 bytes per lane for fp32 storage, 8 (in .x/.y) for binary16 storage.
-template <int KIND>
-__device__ __forceinline__ uint4 ld_row_raw(const Arena& A, uint32_t code, int K, int tl) {
-    const uint32_t row = code & kIdMask;
-    const bool f32 = (KIND == KIND_MIXED) ? ((code & kPrecBit) != 0) : (KIND == KIND_FP32 || KIND == KIND_MPT);
-    if (f32) return __ldcg(reinterpret_cast<const uint4*>(A.f32 + (size_t)row * K) + tl);
-    const uint2 v = __ldcg(reinterpret_cast<const uint2*>(A.f16 + (size_t)row * K) + tl);
-    return make_uint4(v.x, v.y, 0u, 0u);
-}
-__device__ __forceinline__ F4 raw_f4(const uint4& v) {
-    F4 f;
-    f.x[0] = __uint_as_float(v.x); f.x[1] = __uint_as_float(v.y); f.x[2] = __uint_as_float(v.z); f.x[3] = __uint_as_float(v.w);
-    return f;
-}
-__device__ __forceinline__ H4 raw_h4(const uint4& v) {
-    H4 h;
-    h.a = *reinterpret_cast<const __half2*>(&v.x);
-    h.b = *reinterpret_cast<const __half2*>(&v.y);
-    return h;
-}
-
-__device__ __forceinline__ F4 widen(const H4& h) {
-    F4 f;
-    const float2 lo = __half22float2(h.a), hi = __half22float2(h.b);
-    f.x[0] = lo.x; f.x[1] = lo.y; f.x[2] = hi.x; f.x[3] = hi.y;
-    return f;
-}
-__device__ __forceinline__ H4 narrow(const F4& f) {
-    H4 h;
-    h.a = __halves2half2(__float2half_rn(f.x[0]), __float2half_rn(f.x[1]));
-    h.b = __halves2half2(__float2half_rn(f.x[2]), __float2half_rn(f.x[3]));
-    return h;
-}
-
-// Write a cached item row back to the arena its precision selects.
-template <int KIND>
-__device__ __forceinline__ void st_item(const Arena& Q, uint32_t code, int K, int tl, const H4& qh, const F4& qf) {
-    const uint32_t row = code & kIdMask;
-    const bool f32 = (KIND == KIND_MIXED) ? ((code & kPrecBit) != 0) : (KIND == KIND_FP32 || KIND == KIND_MPT);
-    if (f32) st_f4(Q.f32, row, K, tl, qf); else st_h4(Q.f16, row, K, tl, qh);
-}
-
-// lane partial of the dot product: (fma(a0,b0,a1*b1)) + (fma(a2,b2,a3*b3))
-__device__ __forceinline__ float pair_partial(const F4& a, const F4& b) {
-    const float f01 = __fmaf_rn(a.x[0], b.x[0], __fmul_rn(a.x[1], b.x[1]));
-    const float f23 = __fmaf_rn(a.x[2], b.x[2], __fmul_rn(a.x[3], b.x[3]));
-    return __fadd_rn(f01, f23);
-}
-// lane partial of the left-to-right product chain the fp16-storage trainer and the RMSE kernel
-// use for k=128: fma(a3,b3, fma(a2,b2, fma(a0,b0, a1*b1)))
-__device__ __forceinline__ float chain_partial(const F4& a, const F4& b) {
-    float acc = __fmaf_rn(a.x[0], b.x[0], __fmul_rn(a.x[1], b.x[1]));
-    acc = __fmaf_rn(a.x[2], b.x[2], acc);
-    return __fmaf_rn(a.x[3], b.x[3], acc);
-}
-__device__ __forceinline__ __half pair_partial(const H4& p, const H4& q) {
-    const __half2 plo = __lows2half2(p.a, p.b), phi = __highs2half2(p.a, p.b);
-    const __half2 qlo = __lows2half2(q.a, q.b), qhi = __highs2half2(q.a, q.b);
-    const __half2 f = __hfma2(plo, qlo, __hmul2_rn(phi, qhi));   // (f01, f23)
-    return __hadd_rn(__low2half(f), __high2half(f));
-}
-// t = fma(e, y, -(lam*x)) element-wise
-__device__ __forceinline__ F4 grad(float e, const F4& y, float lam, const F4& x) {
-    F4 g;
-#pragma unroll
-    for (int s = 0; s < 4; s++) g.x[s] = __fmaf_rn(e, y.x[s], -__fmul_rn(lam, x.x[s]));
+    for (int s = 0; s < 8; s++) g.x[s] = __fmaf_rn(e, y.x[s], -__fmul_rn(lam, x.x[s]));
     return g;
 }
-__device__ __forceinline__ H4 grad(__half2 e, const H4& y, __half2 lam, const H4& x) {
-    H4 g;
-    g.a = __hfma2(e, y.a, __hneg2(__hmul2_rn(lam, x.a)));
-    g.b = __hfma2(e, y.b, __hneg2(__hmul2_rn(lam, x.b)));
+__device__ __forceinline__ V8h grad(__half2 e, const V8h& y, __half2 lam, const V8h& x) {
+    V8h g;
+#pragma unroll
+    for (int s = 0; s < 4; s++) g.v[s] = __hfma2(e, y.v[s], __hneg2(__hmul2_rn(lam, x.v[s])));
     return g;
 }
-__device__ __forceinline__ F4 step(float lr, const F4& g, const F4& x) {
-    F4 o;
+__device__ __forceinline__ V8f step(float lr, const V8f& g, const V8f& x) {
+    V8f o;
 #pragma unroll
-    for (int s = 0; s < 4; s++) o.x[s] = __fmaf_rn(lr, g.x[s], x.x[s]);
+    for (int s = 0; s < 8; s++) o.x[s] = __fmaf_rn(lr, g.x[s], x.x[s]);
     return o;
 }
-__device__ __forceinline__ float sumsq_partial(const F4& g) { return pair_partial(g, g); }
+__device__ __forceinline__ V8h step(__half2 lr, const V8h& g, const V8h& x) {
+    V8h o;
+#pragma unroll
+    for (int s = 0; s < 4; s++) o.v[s] = __hfma2(lr, g.v[s], x.v[s]);
+    return o;
+}
 
-// Accumulators of the sampled statistics: shared memory when they fit, else straight to global.
-struct StatAcc {
-    float* gs_p; float* gs_q; float* ns_p; float* ns_q;
+struct Consts {
+    float lr, lam;
+    __half2 lr_h, lam_h;          // mascot_sgd_kernel.h:79-80
+    __half mpt_scale;             // mpt_sgd_kernel.h:15-16
+    __half2 mpt_lam;              // mf_methods.cu:764-765
+    float mpt_rev;
 };
 
-template <int K, int T>
-__device__ __forceinline__ void sample_side(const F4& g, float* gsum, float* nsum, uint32_t group, int tl, unsigned mask) {
-    const float n = team_sum<T>(sumsq_partial(g), mask);
-    if (tl == 0) atomicAdd(nsum + group, n);
-    float* dst = gsum + (size_t)group * K + 4 * tl;
+struct StatAcc { float* gs_p; float* gs_q; float* ns_p; float* ns_q; };
+
+// Sampled statistics of one side (mascot_sgd_kernel.h:240-277): sum of squared gradient elements
+// (same pair/tree order as the dot product) and the element-wise gradient sum of the row's group.
+template <int K, int TS>
+__device__ __forceinline__ void sample_side(const V8f& g, float* gsum, float* nsum, uint32_t group, int m, unsigned wmask) {
+    const float n = worker_sum<TS>(pair_partial(g, g), wmask);
+    if (m == 0) atomicAdd(nsum + group, n);
+    float* dst = gsum + (size_t)group * K + 8 * m;
 #pragma unroll
-    for (int s = 0; s < 4; s++) atomicAdd(dst + s, g.x[s]);
+    for (int s = 0; s < 8; s++) atomicAdd(dst + s, g.x[s]);
 }
 
 struct KernelArgs {
@@ -171,104 +217,86 @@ struct KernelArgs {
     float lr, lam;
     SampleStats st;
     int stats_in_smem;
-    int deterministic;
+    unsigned workers;             // concurrent sequential workers actually used
 };
 
-// ---------------------------------------------------------------------------------------------
-// Fast path for k = 128 when every row of a 32-rating chunk is stored in binary16 (the common case
-// of the MASCOT variant): the warp splits into two half-warps, each walking 16 of the chunk's
-// ratings on its own, so every instruction serves two ratings and a row is one 128-bit access per
-// lane.  Lane m of a half-warp holds physical elements 8m..8m+7 = the four elements of reference
-// lane m followed by the four of reference lane m+16; adding the two lane partials is the
-// reference's shfl_down-16 step and xor 8,4,2,1 inside the half-warp finishes the same tree, so
-// the arithmetic is bit-identical to the 32-lane path.  The two half-warps are independent workers
-// (like two warps of the reference), hence this path is not used in deterministic mode.
-// ---------------------------------------------------------------------------------------------
-struct H8 { __half2 v[4]; };
-
-__device__ __forceinline__ H8 raw_h8(const uint4& x) {
-    H8 h;
-    h.v[0] = *reinterpret_cast<const __half2*>(&x.x); h.v[1] = *reinterpret_cast<const __half2*>(&x.y);
-    h.v[2] = *reinterpret_cast<const __half2*>(&x.z); h.v[3] = *reinterpret_cast<const __half2*>(&x.w);
-    return h;
-}
-__device__ __forceinline__ uint4 h8_raw(const H8& h) {
-    uint4 x;
-    x.x = *reinterpret_cast<const unsigned*>(&h.v[0]); x.y = *reinterpret_cast<const unsigned*>(&h.v[1]);
-    x.z = *reinterpret_cast<const unsigned*>(&h.v[2]); x.w = *reinterpret_cast<const unsigned*>(&h.v[3]);
-    return x;
-}
-
-__device__ __forceinline__ void chunk_all_half_k128(const KernelArgs& a, float r_l, uint32_t u_l, uint32_t i_l, int cnt,
-                                                    __half2 lr_h, __half2 lam_h) {
-    constexpr int K = 128;
-    const unsigned full = 0xffffffffu;
-    const int lane = threadIdx.x & 31;
-    const int m = lane & 15;                     // lane inside the half-warp
-    const int half_id = lane >> 4;
-    const int my_cnt = min(max(cnt - 16 * half_id, 0), 16);
-    const int max_cnt = min(cnt, 16);            // half-warp 0 always has at least as many ratings
-
-    uint32_t cur_i = 0xffffffffu;
-    H8 q;
-    q.v[0] = q.v[1] = q.v[2] = q.v[3] = __half2half2(__ushort_as_half(0));
-    uint32_t u = __shfl_sync(full, u_l, 0, 16);
-    uint4 p_raw = make_uint4(0u, 0u, 0u, 0u);
-    if (my_cnt > 0) p_raw = __ldcg(reinterpret_cast<const uint4*>(a.P.f16 + (size_t)u * K) + m);
-    for (int j = 0; j < max_cnt; j++) {
-        const bool on = j < my_cnt;
-        const float r = __shfl_sync(full, r_l, j, 16);
-        const uint32_t i = __shfl_sync(full, i_l, j, 16);
-        const int jn = (j + 1 < 16) ? j + 1 : j;
-        const uint32_t u_next = __shfl_sync(full, u_l, jn, 16);
-        if (on && i != cur_i) {
-            if (cur_i != 0xffffffffu) __stcg(reinterpret_cast<uint4*>(a.Q.f16 + (size_t)cur_i * K) + m, h8_raw(q));
-            cur_i = i;
-            q = raw_h8(__ldcg(reinterpret_cast<const uint4*>(a.Q.f16 + (size_t)i * K) + m));
-        }
-        const H8 p = raw_h8(p_raw);
-        const bool more = on && (j + 1 < my_cnt);
-        const bool refetch = more && (u_next == u);
-        if (more && !refetch) p_raw = __ldcg(reinterpret_cast<const uint4*>(a.P.f16 + (size_t)u_next * K) + m);
-
-        // lane partials of reference lanes m and m+16, then the shfl_down-16 step
-        const __half2 fa = __hfma2(__lows2half2(p.v[0], p.v[1]), __lows2half2(q.v[0], q.v[1]),
-                                   __hmul2_rn(__highs2half2(p.v[0], p.v[1]), __highs2half2(q.v[0], q.v[1])));
-        const __half2 fb = __hfma2(__lows2half2(p.v[2], p.v[3]), __lows2half2(q.v[2], q.v[3]),
-                                   __hmul2_rn(__highs2half2(p.v[2], p.v[3]), __highs2half2(q.v[2], q.v[3])));
-        const __half2 t = __hadd2_rn(__lows2half2(fa, fb), __highs2half2(fa, fb));
-        __half x = __hadd_rn(__low2half(t), __high2half(t));
+// One update.  p_raw / q_raw are the row slices in their storage precision; both are replaced by the
+// updated values.  Statistics go to `acc` when the rating is sampled.
+template <int K, int KIND, int MODE, bool STATS>
+__device__ __forceinline__ void update_one(const Consts& c, float r, uint32_t uc, uint32_t ic, Raw<MODE>& p_raw, Raw<MODE>& q_raw,
+                                           bool sampled, const StatAcc& acc, const SampleStats& st, int m, unsigned wmask) {
+    constexpr int TS = K / 8;
+    if constexpr (KIND == KIND_MPT) {
+        const V8f p = as_v8f(p_raw), q = as_v8f(q_raw);
+        const V8h ph = narrow(p), qh = narrow(q);
+        const __half dot = worker_sum<TS>(pair_partial(ph, qh), wmask);
+        const __half2 e = __half2half2(__hmul_rn(c.mpt_scale, __hsub_rn(__float2half_rn(r), dot)));
+        const V8f gp = widen(grad(e, qh, c.mpt_lam, ph)), gq = widen(grad(e, ph, c.mpt_lam, qh));
+        V8f po, qo;
 #pragma unroll
-        for (int d = 8; d >= 1; d >>= 1) x = __hadd_rn(x, __shfl_xor_sync(full, x, d));
-        const __half2 e = __half2half2(__hsub_rn(__float2half_rn(r), x));
-        H8 po;
-#pragma unroll
-        for (int s = 0; s < 4; s++) {
-            const __half2 gp = __hfma2(e, q.v[s], __hneg2(__hmul2_rn(lam_h, p.v[s])));
-            const __half2 gq = __hfma2(e, p.v[s], __hneg2(__hmul2_rn(lam_h, q.v[s])));
-            po.v[s] = __hfma2(lr_h, gp, p.v[s]);
-            if (on) q.v[s] = __hfma2(lr_h, gq, q.v[s]);
+        for (int s = 0; s < 8; s++) {
+            po.x[s] = __fmaf_rn(c.lr, __fmul_rn(c.mpt_rev, gp.x[s]), p.x[s]);
+            qo.x[s] = __fmaf_rn(c.lr, __fmul_rn(c.mpt_rev, gq.x[s]), q.x[s]);
         }
-        if (on) __stcg(reinterpret_cast<uint4*>(a.P.f16 + (size_t)u * K) + m, h8_raw(po));
-        if (refetch) p_raw = __ldcg(reinterpret_cast<const uint4*>(a.P.f16 + (size_t)u_next * K) + m);
-        u = u_next;
+        put(p_raw, po); put(q_raw, qo);
+    } else if constexpr (KIND == KIND_MEMQUANT) {
+        const V8f p = widen(as_v8h(p_raw)), q = widen(as_v8h(q_raw));
+        const float part = (K == 128) ? chain_partial_k128(p, q) : pair_partial(p, q);
+        const float e = __fsub_rn(r, worker_sum<TS>(part, wmask));
+        put(p_raw, narrow(step(c.lr, grad(e, q, c.lam, p), p)));
+        put(q_raw, narrow(step(c.lr, grad(e, p, c.lam, q), q)));
+    } else {
+        const bool uf = is_f32<MODE>(uc), itf = is_f32<MODE>(ic);
+        if (!uf && !itf) {
+            const V8h p = as_v8h(p_raw), q = as_v8h(q_raw);
+            const __half dot = worker_sum<TS>(pair_partial(p, q), wmask);
+            const __half2 e = __half2half2(__hsub_rn(__float2half_rn(r), dot));
+            const V8h gp = grad(e, q, c.lam_h, p), gq = grad(e, p, c.lam_h, q);
+            put(p_raw, step(c.lr_h, gp, p));
+            put(q_raw, step(c.lr_h, gq, q));
+            if (STATS && sampled) {
+                sample_side<K, TS>(widen(gp), acc.gs_p, acc.ns_p, st.ugroup[uc & kIdMask], m, wmask);
+                sample_side<K, TS>(widen(gq), acc.gs_q, acc.ns_q, st.igroup[ic & kIdMask], m, wmask);
+            }
+        } else if constexpr (MODE != ROWS_HALF) {
+            const V8f p = uf ? as_v8f(p_raw) : widen(as_v8h(p_raw));
+            const V8f q = itf ? as_v8f(q_raw) : widen(as_v8h(q_raw));
+            const float e = __fsub_rn(r, worker_sum<TS>(pair_partial(p, q), wmask));
+            const V8f gp = grad(e, q, c.lam, p), gq = grad(e, p, c.lam, q);
+            const V8f po = step(c.lr, gp, p), qo = step(c.lr, gq, q);
+            if (uf) put(p_raw, po); else put(p_raw, narrow(po));
+            if (itf) put(q_raw, qo); else put(q_raw, narrow(qo));
+            if (STATS && sampled) {
+                if (!uf) sample_side<K, TS>(gp, acc.gs_p, acc.ns_p, st.ugroup[uc & kIdMask], m, wmask);
+                if (!itf) sample_side<K, TS>(gq, acc.gs_q, acc.ns_q, st.igroup[ic & kIdMask], m, wmask);
+            }
+        }
     }
-    if (cur_i != 0xffffffffu) __stcg(reinterpret_cast<uint4*>(a.Q.f16 + (size_t)cur_i * K) + m, h8_raw(q));
 }
 
-#ifndef MASCOT_TRAIN_MIN_BLOCKS
-#define MASCOT_TRAIN_MIN_BLOCKS 4
-#endif
+// The records of one chunk (TS ratings), one per lane of the worker.
+struct Chunk {
+    float r; uint32_t u, i;
+    int cnt;            // valid ratings in the chunk (0: no chunk)
+    unsigned dup;       // bit j: the user of rating j also occurs among the D ratings before it
+    uint64_t base;      // stream position of its first rating
+};
 
-template <int K, int KIND, bool STATS>
-__global__ void __launch_bounds__(256, MASCOT_TRAIN_MIN_BLOCKS) train_kernel(const KernelArgs a) {
-    constexpr int T = K / 4;
+// DEEP: user-row prefetch depth 8 (binary16 rows) / 4 (fp32 or mixed rows), for launches with few
+// workers per SM, where each worker must hide memory latency on its own.  Otherwise depth 2, which
+// keeps the register count low enough for many resident workers.
+template <int K, int KIND, int MODE, bool STATS, bool DEEP>
+__global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
+    constexpr int TS = K / 8;                      // lanes per worker = ratings per chunk
+    constexpr int D = DEEP ? (MODE == ROWS_HALF ? 8 : 4) : 2;
+    static_assert(TS % D == 0, "the prefetch ring must divide the chunk");
     extern __shared__ float smem[];
-    const int tl = threadIdx.x % T;
-    const unsigned mask = (T == 32) ? 0xffffffffu : (0xffffu << (16 * ((threadIdx.x >> 4) & 1)));
-    const uint64_t team = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) / T;
-    const uint64_t nteams = ((uint64_t)gridDim.x * blockDim.x) / T;
-    const uint64_t nchunks = (a.s.n + T - 1) / T;
+    const int lane = threadIdx.x & 31;
+    const int m = lane % TS;
+    const unsigned wmask = (TS == 32) ? 0xffffffffu : (((1u << TS) - 1u) << (lane - m));
+    const uint64_t worker = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) / TS;
+    const uint64_t W = a.workers;
+    const uint64_t nchunks = (a.s.n + TS - 1) / TS;
 
     StatAcc acc = {a.st.gsum_p, a.st.gsum_q, a.st.nsum_p, a.st.nsum_q};
     if (STATS && a.stats_in_smem) {
@@ -281,133 +309,131 @@ __global__ void __launch_bounds__(256, MASCOT_TRAIN_MIN_BLOCKS) train_kernel(con
         __syncthreads();
     }
 
-    const float lr = a.lr, lam = a.lam;
-    const __half2 lr_h = __half2half2(__float2half_rn(lr));     // mascot_sgd_kernel.h:79-80
-    const __half2 lam_h = __half2half2(__float2half_rn(lam));
-    // MPT constants (mpt_sgd_kernel.h:15-16, mf_methods.cu:764-765)
-    const __half mpt_scale = __float2half_rn(1000.0f);
-    const __half2 mpt_lam = __half2half2(__float2half_rn(__fmul_rn(lam, 1000.0f)));
-    const float mpt_rev = __fdiv_rn(1.0f, 1000.0f);
+    Consts c;
+    c.lr = a.lr; c.lam = a.lam;
+    c.lr_h = __half2half2(__float2half_rn(a.lr));
+    c.lam_h = __half2half2(__float2half_rn(a.lam));
+    c.mpt_scale = __float2half_rn(1000.0f);
+    c.mpt_lam = __half2half2(__float2half_rn(__fmul_rn(a.lam, 1000.0f)));
+    c.mpt_rev = __fdiv_rn(1.0f, 1000.0f);
+    // only the mixed-precision mode reads the precision bit of an id
+    constexpr uint32_t kKeep = (MODE == ROWS_DYN) ? 0xffffffffu : kIdMask;
 
-    // storage precision of each side: fixed by the trainer, or per row (bit 31) for the mixed one
-    constexpr bool kUserF32Fixed = (KIND == KIND_FP32 || KIND == KIND_MPT);
-    constexpr bool kItemF32Fixed = kUserF32Fixed;
-
-    uint64_t c = team;
-    float r_n = 0.f; uint32_t u_n = 0, i_n = 0;
-    if (c < nchunks) {
-        const uint64_t pos = c * T + tl;
-        if (pos < a.s.n) { r_n = __ldg(a.s.r + pos); u_n = __ldg(a.s.u + pos); i_n = __ldg(a.s.i + pos); }
-    }
-    for (; c < nchunks; c += nteams) {
-        const float r_l = r_n; const uint32_t u_l = u_n, i_l = i_n;
-        const uint64_t cn = c + nteams;
-        if (cn < nchunks) {
-            const uint64_t pos = cn * T + tl;
-            if (pos < a.s.n) { r_n = __ldg(a.s.r + pos); u_n = __ldg(a.s.u + pos); i_n = __ldg(a.s.i + pos); }
-        }
-        const uint64_t base = c * T;
-        const int cnt = (a.s.n - base) < (uint64_t)T ? (int)(a.s.n - base) : T;
-
-        if (K == 128 && KIND == KIND_MIXED && !a.deterministic) {
-            const bool any_f32 = __ballot_sync(0xffffffffu, ((u_l | i_l) & kPrecBit) != 0) != 0;
-            const bool has_samples = STATS && (base + T > a.st.first_sample_pos);
-            if (!any_f32 && !has_samples) {
-                chunk_all_half_k128(a, r_l, u_l, i_l, cnt, lr_h, lam_h);
-                continue;
+    // Loads chunk `ci` and marks the ratings whose user repeats within the D ratings before them
+    // (those rows cannot be prefetched: they must be read after the earlier update is stored).
+    auto load_chunk = [&](uint64_t ci, const Chunk& before) {
+        Chunk k; k.r = 0.f; k.u = kNoRow; k.i = 0; k.cnt = 0; k.dup = 0; k.base = 0;
+        if (ci < nchunks) {
+            k.base = ci * TS;
+            const uint64_t left = a.s.n - k.base;
+            k.cnt = left < (uint64_t)TS ? (int)left : TS;
+            if (m < k.cnt) {
+                k.r = __ldg(a.s.r + k.base + m);
+                k.u = __ldg(a.s.u + k.base + m) & kKeep;
+                k.i = __ldg(a.s.i + k.base + m) & kKeep;
             }
-        }
-
-        // The item row of a run of equal items stays in registers (qh or qf, by its precision) and is
-        // written back when the item changes or the chunk ends; within one team this is exactly the
-        // sequential semantics, because nothing else of this team touches that row in between.
-        uint32_t cur_ic = 0xffffffffu;          // no row cached (a real id never has all bits set)
-        H4 qh; F4 qf;
-        qh.a = qh.b = __half2half2(__ushort_as_half(0));
-        qf.x[0] = qf.x[1] = qf.x[2] = qf.x[3] = 0.f;
-
-        // user row of the first rating, fetched raw (low 8 bytes used for binary16 rows)
-        uint32_t uc = __shfl_sync(mask, u_l, 0, T);
-        uint4 p_raw = ld_row_raw<KIND>(a.P, uc, K, tl);
-        for (int j = 0; j < cnt; j++) {
-            const float r = __shfl_sync(mask, r_l, j, T);
-            const uint32_t ic = __shfl_sync(mask, i_l, j, T);
-            const uint32_t u = uc & kIdMask, i = ic & kIdMask;
-            const bool uf = (KIND == KIND_MIXED) ? ((uc & kPrecBit) != 0) : kUserF32Fixed;
-            const bool itf = (KIND == KIND_MIXED) ? ((ic & kPrecBit) != 0) : kItemF32Fixed;
-            const bool sampled = STATS && (base + j >= a.st.first_sample_pos);
-
-            if (ic != cur_ic) {
-                if (cur_ic != 0xffffffffu) st_item<KIND>(a.Q, cur_ic, K, tl, qh, qf);
-                cur_ic = ic;
-                if (itf) qf = ld_f4(a.Q.f32, i, K, tl); else qh = ld_h4(a.Q.f16, i, K, tl);
-            }
-            // prefetch the next rating's user row while this one is processed; a repeated user is
-            // re-read after the store below so that it sees this update
-            const uint4 p_cur = p_raw;
-            uint32_t uc_next = uc;
-            bool refetch = false;
-            if (j + 1 < cnt) {
-                uc_next = __shfl_sync(mask, u_l, j + 1, T);
-                if (uc_next != uc) p_raw = ld_row_raw<KIND>(a.P, uc_next, K, tl); else refetch = true;
-            }
-
-            if (KIND == KIND_MPT) {
-                const F4 p = raw_f4(p_cur);
-                const H4 ph = narrow(p), qhh = narrow(qf);
-                const __half dot = team_sum<T>(pair_partial(ph, qhh), mask);
-                const __half2 e = __half2half2(__hmul_rn(mpt_scale, __hsub_rn(__float2half_rn(r), dot)));
-                const F4 gp = widen(grad(e, qhh, mpt_lam, ph)), gq = widen(grad(e, ph, mpt_lam, qhh));
-                F4 po;
+            bool mine = false;
 #pragma unroll
-                for (int s = 0; s < 4; s++) {
-                    po.x[s] = __fmaf_rn(lr, __fmul_rn(mpt_rev, gp.x[s]), p.x[s]);
-                    qf.x[s] = __fmaf_rn(lr, __fmul_rn(mpt_rev, gq.x[s]), qf.x[s]);
-                }
-                st_f4(a.P.f32, u, K, tl, po);
-            } else if (KIND == KIND_MEMQUANT) {
-                const F4 p = widen(raw_h4(p_cur)), q = widen(qh);
-                const float part = (K == 128) ? chain_partial(p, q) : pair_partial(p, q);
-                const float e = __fsub_rn(r, team_sum<T>(part, mask));
-                st_h4(a.P.f16, u, K, tl, narrow(step(lr, grad(e, q, lam, p), p)));
-                qh = narrow(step(lr, grad(e, p, lam, q), q));
-            } else if (!uf && !itf) {
-                const H4 p = raw_h4(p_cur);
-                const __half dot = team_sum<T>(pair_partial(p, qh), mask);
-                const __half2 e = __half2half2(__hsub_rn(__float2half_rn(r), dot));
-                const H4 gp = grad(e, qh, lam_h, p), gq = grad(e, p, lam_h, qh);
-                H4 po;
-                po.a = __hfma2(lr_h, gp.a, p.a); po.b = __hfma2(lr_h, gp.b, p.b);
-                qh.a = __hfma2(lr_h, gq.a, qh.a); qh.b = __hfma2(lr_h, gq.b, qh.b);
-                st_h4(a.P.f16, u, K, tl, po);
-                if (sampled) {
-                    sample_side<K, T>(widen(gp), acc.gs_p, acc.ns_p, a.st.ugroup[u], tl, mask);
-                    sample_side<K, T>(widen(gq), acc.gs_q, acc.ns_q, a.st.igroup[i], tl, mask);
-                }
-            } else if (!uf && itf) {
-                const F4 p = widen(raw_h4(p_cur));
-                const float e = __fsub_rn(r, team_sum<T>(pair_partial(p, qf), mask));
-                const F4 gp = grad(e, qf, lam, p);
-                st_h4(a.P.f16, u, K, tl, narrow(step(lr, gp, p)));
-                qf = step(lr, grad(e, p, lam, qf), qf);
-                if (sampled) sample_side<K, T>(gp, acc.gs_p, acc.ns_p, a.st.ugroup[u], tl, mask);
-            } else if (uf && !itf) {
-                const F4 p = raw_f4(p_cur), q = widen(qh);
-                const float e = __fsub_rn(r, team_sum<T>(pair_partial(p, q), mask));
-                const F4 gq = grad(e, p, lam, q);
-                st_f4(a.P.f32, u, K, tl, step(lr, grad(e, q, lam, p), p));
-                qh = narrow(step(lr, gq, q));
-                if (sampled) sample_side<K, T>(gq, acc.gs_q, acc.ns_q, a.st.igroup[i], tl, mask);
-            } else {
-                const F4 p = raw_f4(p_cur);
-                const float e = __fsub_rn(r, team_sum<T>(pair_partial(p, qf), mask));
-                st_f4(a.P.f32, u, K, tl, step(lr, grad(e, qf, lam, p), p));
-                qf = step(lr, grad(e, p, lam, qf), qf);
+            for (int d = 1; d <= D; d++) {
+                const int src = (m - d) & (TS - 1);
+                const uint32_t here = __shfl_sync(wmask, k.u, src, TS);
+                const uint32_t prev = __shfl_sync(wmask, before.u, src, TS);
+                mine |= ((m >= d) ? here : prev) == k.u;
             }
-            if (refetch) p_raw = ld_row_raw<KIND>(a.P, uc_next, K, tl);
-            uc = uc_next;
+            k.dup = __ballot_sync(wmask, mine && m < k.cnt) >> (lane - m);
         }
-        if (cur_ic != 0xffffffffu) st_item<KIND>(a.Q, cur_ic, K, tl, qh, qf);
+        return k;
+    };
+
+    if (worker < W) {
+        uint64_t ci = worker;
+        Chunk none; none.r = 0.f; none.u = kNoRow; none.i = 0; none.cnt = 0; none.dup = 0; none.base = 0;
+        Chunk cur = load_chunk(ci, none);
+        Chunk nxt = load_chunk(ci + W, cur);
+
+        Raw<MODE> ring[D];             // slot j % D: prefetched user row of rating j of the current chunk
+        unsigned stale = 0;            // bit t: slot t was not prefetched and is read at use
+        bool primed = false;           // the ring holds the first D rows of `cur`
+
+        // item row of the current run, and the prefetched row of the run after it
+        uint32_t cur_ic = kNoRow, nxt_ic = kNoRow;
+        Raw<MODE> q, qn;
+
+        // switches the cached item row when the item changes; `j` is the rating's index in `cur`
+        auto item_row = [&](uint32_t ic, int j) {
+            if (ic != cur_ic) {
+                if (cur_ic != kNoRow) st_row<K, MODE>(a.Q, cur_ic, m, q);
+                if (ic == nxt_ic) q = qn; else q = ld_row<K, MODE>(a.Q, ic, m);
+                cur_ic = ic;
+                // prefetch the row of the next run: first different item later in this chunk, else
+                // the first item of the worker's next chunk
+                const unsigned later = __ballot_sync(wmask, cur.i != ic && m > j && m < cur.cnt) >> (lane - m);
+                uint32_t cand = kNoRow;
+                if (later) cand = __shfl_sync(wmask, cur.i, __ffs(later) - 1, TS);
+                else if (nxt.cnt > 0) cand = __shfl_sync(wmask, nxt.i, 0, TS);
+                if (cand != kNoRow && cand != ic) { qn = ld_row<K, MODE>(a.Q, cand, m); nxt_ic = cand; }
+            }
+        };
+
+        while (cur.cnt > 0) {
+            if (cur.cnt == TS) {
+                // ---- full chunk: software-pipelined ----
+                if (!primed) {
+                    stale = 0;
+#pragma unroll
+                    for (int t = 0; t < D; t++) {
+                        const uint32_t ut = __shfl_sync(wmask, cur.u, t, TS);
+                        if ((cur.dup >> t) & 1u) stale |= 1u << t; else ring[t] = ld_row<K, MODE>(a.P, ut, m);
+                    }
+                }
+                const bool next_full = (nxt.cnt == TS);
+#pragma unroll 1
+                for (int jb = 0; jb < TS; jb += D) {
+#pragma unroll
+                    for (int t = 0; t < D; t++) {
+                        const int j = jb + t;
+                        const float r = __shfl_sync(wmask, cur.r, j, TS);
+                        const uint32_t uc = __shfl_sync(wmask, cur.u, j, TS);
+                        const uint32_t ic = __shfl_sync(wmask, cur.i, j, TS);
+                        const bool sampled = STATS && (cur.base + j >= a.st.first_sample_pos);
+                        item_row(ic, j);
+                        Raw<MODE> p = ring[t];
+                        if (stale & (1u << t)) { p = ld_row<K, MODE>(a.P, uc, m); stale &= ~(1u << t); }
+                        // refill the slot with the row of the rating D ahead
+                        const int x = j + D;
+                        if (x < TS) {
+                            const uint32_t ux = __shfl_sync(wmask, cur.u, x, TS);
+                            if ((cur.dup >> x) & 1u) stale |= 1u << t; else ring[t] = ld_row<K, MODE>(a.P, ux, m);
+                        } else if (next_full) {
+                            const uint32_t ux = __shfl_sync(wmask, nxt.u, x - TS, TS);
+                            if ((nxt.dup >> (x - TS)) & 1u) stale |= 1u << t; else ring[t] = ld_row<K, MODE>(a.P, ux, m);
+                        }
+                        update_one<K, KIND, MODE, STATS>(c, r, uc, ic, p, q, sampled, acc, a.st, m, wmask);
+                        st_row<K, MODE>(a.P, uc, m, p);
+                    }
+                }
+                primed = next_full;
+            } else {
+                // ---- ragged last chunk: plain sequential ----
+                for (int j = 0; j < cur.cnt; j++) {
+                    const float r = __shfl_sync(wmask, cur.r, j, TS);
+                    const uint32_t uc = __shfl_sync(wmask, cur.u, j, TS);
+                    const uint32_t ic = __shfl_sync(wmask, cur.i, j, TS);
+                    const bool sampled = STATS && (cur.base + j >= a.st.first_sample_pos);
+                    item_row(ic, j);
+                    Raw<MODE> p = ld_row<K, MODE>(a.P, uc, m);
+                    update_one<K, KIND, MODE, STATS>(c, r, uc, ic, p, q, sampled, acc, a.st, m, wmask);
+                    st_row<K, MODE>(a.P, uc, m, p);
+                }
+                primed = false;
+            }
+            ci += W;
+            const Chunk done = cur;
+            cur = nxt;
+            nxt = load_chunk(ci + W, cur);
+            (void)done;
+        }
+        if (cur_ic != kNoRow) st_row<K, MODE>(a.Q, cur_ic, m, q);
     }
 
     if (STATS && a.stats_in_smem) {
@@ -434,17 +460,33 @@ int sm_count() {
     return sms;
 }
 
-template <int K, int KIND, bool STATS>
-cudaError_t launch_one(const KernelArgs& args, bool deterministic, int grid_hint, cudaStream_t st, LaunchShape* shape) {
-    auto kern = train_kernel<K, KIND, STATS>;
+template <int K, int KIND, int MODE, bool STATS>
+cudaError_t launch_one(const KernelArgs& args, unsigned workers, cudaStream_t st, LaunchShape* shape) {
+    constexpr int TS = K / 8;
+    constexpr int kPerWarp = 32 / TS;
     KernelArgs a = args;
-    a.deterministic = deterministic ? 1 : 0;
-    int block = deterministic ? K / 4 : 256;
+    // Spread the workers evenly: the same number of warps on every SM, in blocks of at most 8 warps.
+    if (workers < 1) workers = 1;
+    const unsigned warps = (workers + kPerWarp - 1) / kPerWarp;
+    int grid, block;
+    unsigned per_sm = warps;
+    if (warps <= 8) {
+        grid = 1; block = (int)(32 * warps);
+    } else {
+        const unsigned sms = (unsigned)sm_count();
+        per_sm = (warps + sms - 1) / sms;
+        const unsigned blocks_per_sm = (per_sm + 7) / 8;
+        const unsigned warps_per_block = (per_sm + blocks_per_sm - 1) / blocks_per_sm;
+        grid = (int)(sms * blocks_per_sm);
+        block = (int)(32 * warps_per_block);
+    }
+    const bool deep = per_sm <= 12;
+    auto kern = deep ? train_kernel<K, KIND, MODE, STATS, true> : train_kernel<K, KIND, MODE, STATS, false>;
     size_t smem = 0;
     a.stats_in_smem = 0;
     if (STATS) {
         const size_t want = (size_t)(a.st.ug + a.st.ig) * (K + 1) * sizeof(float);
-        if (want <= 200 * 1024) {
+        if (want <= 100 * 1024) {
             smem = want;
             a.stats_in_smem = 1;
             if (smem > 48 * 1024) {
@@ -453,27 +495,26 @@ cudaError_t launch_one(const KernelArgs& args, bool deterministic, int grid_hint
             }
         }
     }
-    int grid = 1;
-    if (!deterministic) {
-        int per_sm = 0;
-        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, block, smem);
-        if (e != cudaSuccess) return e;
-        if (per_sm < 1) per_sm = 1;
-        grid = grid_hint > 0 ? grid_hint : per_sm * sm_count();
-    }
+    const unsigned capacity = (unsigned)grid * (unsigned)(block / 32) * kPerWarp;
+    // a single block (deterministic runs, tiny worker counts) uses exactly the requested workers
+    a.workers = (grid == 1) ? workers : capacity;
     kern<<<grid, block, smem, st>>>(a);
-    if (shape) { shape->grid = grid; shape->block = block; shape->smem = smem; }
+    if (shape) { shape->grid = grid; shape->block = block; shape->smem = smem; shape->workers = a.workers; }
     return cudaGetLastError();
 }
 
 template <int K>
-cudaError_t launch_k(TrainKind kind, const KernelArgs& a, bool stats, bool det, int hint, cudaStream_t st, LaunchShape* sh) {
+cudaError_t launch_k(TrainKind kind, const KernelArgs& a, bool stats, bool any_f32, unsigned workers, cudaStream_t st, LaunchShape* sh) {
     switch (kind) {
         case KIND_MIXED:
-            return stats ? launch_one<K, KIND_MIXED, true>(a, det, hint, st, sh) : launch_one<K, KIND_MIXED, false>(a, det, hint, st, sh);
-        case KIND_FP32: return launch_one<K, KIND_FP32, false>(a, det, hint, st, sh);
-        case KIND_MPT: return launch_one<K, KIND_MPT, false>(a, det, hint, st, sh);
-        case KIND_MEMQUANT: return launch_one<K, KIND_MEMQUANT, false>(a, det, hint, st, sh);
+            if (any_f32)
+                return stats ? launch_one<K, KIND_MIXED, ROWS_DYN, true>(a, workers, st, sh)
+                             : launch_one<K, KIND_MIXED, ROWS_DYN, false>(a, workers, st, sh);
+            return stats ? launch_one<K, KIND_MIXED, ROWS_HALF, true>(a, workers, st, sh)
+                         : launch_one<K, KIND_MIXED, ROWS_HALF, false>(a, workers, st, sh);
+        case KIND_FP32: return launch_one<K, KIND_FP32, ROWS_F32, false>(a, workers, st, sh);
+        case KIND_MPT: return launch_one<K, KIND_MPT, ROWS_F32, false>(a, workers, st, sh);
+        case KIND_MEMQUANT: return launch_one<K, KIND_MEMQUANT, ROWS_HALF, false>(a, workers, st, sh);
     }
     return cudaErrorInvalidValue;
 }
@@ -481,14 +522,13 @@ cudaError_t launch_k(TrainKind kind, const KernelArgs& a, bool stats, bool det, 
 }  // namespace
 
 cudaError_t launch_train(int K, TrainKind kind, const Stream& s, Arena P, Arena Q, float lr, float lam,
-                         const SampleStats* stats, bool deterministic, int grid_blocks_hint, cudaStream_t st,
-                         LaunchShape* shape) {
+                         const SampleStats* stats, bool any_f32_rows, unsigned workers, cudaStream_t st, LaunchShape* shape) {
     KernelArgs a;
-    a.s = s; a.P = P; a.Q = Q; a.lr = lr; a.lam = lam; a.stats_in_smem = 0; a.deterministic = 0;
+    a.s = s; a.P = P; a.Q = Q; a.lr = lr; a.lam = lam; a.stats_in_smem = 0; a.workers = workers;
     if (stats) a.st = *stats;
     if (s.n == 0) { if (shape) *shape = LaunchShape(); return cudaSuccess; }
-    if (K == 128) return launch_k<128>(kind, a, stats != nullptr, deterministic, grid_blocks_hint, st, shape);
-    if (K == 64) return launch_k<64>(kind, a, stats != nullptr, deterministic, grid_blocks_hint, st, shape);
+    if (K == 128) return launch_k<128>(kind, a, stats != nullptr, any_f32_rows, workers, st, shape);
+    if (K == 64) return launch_k<64>(kind, a, stats != nullptr, any_f32_rows, workers, st, shape);
     return cudaErrorInvalidValue;
 }
 

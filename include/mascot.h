@@ -72,21 +72,23 @@ typedef struct mascot_config {
     uint32_t user_group_num;     /* -ug  requested user groups     default 10                  */
     uint32_t item_group_num;     /* -ig  requested item groups     default 10                  */
     uint32_t k;                  /* -k   64 or 128                 default 128                 */
-    uint32_t num_workers;        /* -wg  accepted for CLI parity; a hint only (persistent grid) */
+    uint32_t num_workers;        /* -wg  number of concurrent sequential workers (the reference's warps):
+                                       fewer workers lose fewer updates of popular rows to races and
+                                       converge faster per epoch, more workers run faster; rounded up
+                                       to fill every SM evenly                     default 2048        */
     uint32_t epoch;              /* -l   number of epochs          default 50                  */
-    uint32_t thread_block_size;  /* -bl  accepted for CLI parity; a hint only                   */
+    uint32_t thread_block_size;  /* -bl  accepted for CLI parity, not used (blocks are sized per SM) */
     uint32_t version;            /* -v   one of MASCOT_V_*         default 7 in the reference  */
     uint32_t is_yahoo;           /* MuPPET starts at 12 bits when set (mf_methods.cu:600-601)  */
     /* ---- extensions ---- */
-    uint32_t deterministic;      /* 1: a single team of lanes walks the stream in order; bit-exact
-                                       against a sequential host replay of the same rule         */
+    uint32_t deterministic;      /* 1: a single worker walks the stream in order; bit-exact against
+                                       a sequential host replay of the same rule                  */
     uint32_t shuffle;            /* 1: seeded permutation of the training stream (the reference shuffles with
                                        srand(time(0)), mf_methods.cu:38-39), then item-sorted windows of
                                        4096 ratings; 0: the caller's order, untouched                  */
     uint64_t seed;               /* seeds the stream permutation and mascot_init_factors()      */
     int32_t device;              /* CUDA device ordinal                                         */
-    uint32_t grid_blocks;        /* 0: engine chooses a persistent grid from the SM count        */
-    uint32_t reserved[6];
+    uint32_t reserved[7];
 } mascot_config;
 
 typedef struct mascot_epoch_stats {
@@ -98,6 +100,8 @@ typedef struct mascot_epoch_stats {
     uint32_t promoted_user_groups;
     uint32_t promoted_item_groups;
     uint32_t kernel_launches;    /* kernels launched by this call                               */
+    uint32_t workers;            /* concurrent sequential workers the update kernel ran with    */
+    uint32_t reserved0;
     uint64_t algorithmic_bytes;  /* factor bytes the update rule reads + writes this epoch:
                                     sum over ratings of 2*k*(bytes per user element + bytes per
                                     item element), 2 for fp16 storage and 4 for fp32            */
