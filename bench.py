@@ -237,6 +237,7 @@ def main():
     launches = 0
     alg_bytes = 0
     checks = 0
+    per_epoch = []
     for _ in range(args.steps):
         st = eng.train_epoch(epoch)
         epoch += 1
@@ -245,6 +246,7 @@ def main():
         launches += st.kernel_launches
         alg_bytes += st.algorithmic_bytes
         checks += st.error_check
+        per_epoch.append((round(st.kernel_ms, 2), int(st.error_check)))
     torch.cuda.synchronize()
     wall_ms = (time.perf_counter() - t0) * 1e3
     rmse_after = eng.eval_rmse()
@@ -288,7 +290,8 @@ def main():
         "scaling": "strong", "vs_baseline": None, "dtype": "f16+f32", "data": "synthetic",
         "config": {"workload": args.workload_desc, "l2": "inputs larger than L2 (1.2 GB rating stream + 123 MB user factors per epoch)",
                    "check_epochs_in_timed_region": checks, "kernel_ms_per_step": kern_ms / args.steps,
-                   "wall_ms_per_step": wall_ms / args.steps, "rmse_before": rmse_before, "rmse_after": rmse_after},
+                   "wall_ms_per_step": wall_ms / args.steps, "rmse_before": rmse_before, "rmse_after": rmse_after,
+                   "kernel_ms_and_check_flag_per_step": per_epoch, "workers": int(st.workers)},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": traffic, "peak_kind": f"of {peak_kind}",
                      "algorithmic_bytes_per_launch": alg_bytes / args.steps},

@@ -44,10 +44,11 @@ struct LaunchShape {
 
 // Update kernels.  `stats` == nullptr -> plain epoch.  `workers` = requested number of concurrent
 // sequential workers (1 = fully sequential); `any_f32_rows` tells the mixed-precision trainer whether
-// any group has been promoted (otherwise every row is binary16).  Returns the launch shape used.
+// any group has been promoted (otherwise every row is binary16); `work_counter` is 8 bytes of device
+// scratch the launch resets and uses to hand out chunks.  Returns the launch shape used.
 cudaError_t launch_train(int K, TrainKind kind, const Stream& s, Arena P, Arena Q, float lr, float lam,
-                         const SampleStats* stats, bool any_f32_rows, unsigned workers, cudaStream_t st,
-                         LaunchShape* shape);
+                         const SampleStats* stats, bool any_f32_rows, unsigned workers,
+                         unsigned long long* work_counter, cudaStream_t st, LaunchShape* shape);
 
 // Test RMSE over a coded SoA stream; block_err has ceil(n/512) floats.
 cudaError_t launch_rmse(int K, const Stream& t, Arena P, Arena Q, float* block_err, cudaStream_t st);

@@ -42,6 +42,7 @@ struct mascot_handle {
     uint32_t* d_umap = nullptr; uint32_t* d_imap = nullptr;
     float* d_stats = nullptr;       // gsum_p | gsum_q | nsum_p | nsum_q
     float* d_block_err = nullptr;
+    unsigned long long* d_work_counter = nullptr;
     void* d_scratch = nullptr; size_t scratch_bytes = 0;   // staging for mascot_reload_train
 
     // host
@@ -308,6 +309,7 @@ int mascot_create(const mascot_config* cfg, mascot_handle** out) {
     cudaError_t e = cudaSetDevice(cfg->device);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking);
     for (int j = 0; j < 4 && e == cudaSuccess; j++) e = cudaEventCreate(&h->ev[j]);
+    if (e == cudaSuccess) e = dev_alloc(&h->d_work_counter, 1);
     if (e != cudaSuccess) {
         std::string msg = std::string("CUDA set-up failed: ") + cudaGetErrorString(e);
         mascot_destroy(h);
@@ -321,7 +323,7 @@ int mascot_destroy(mascot_handle* h) {
     if (!h) return MASCOT_OK;
     cudaSetDevice(h->cfg.device);
     free_ratings(h);
-    dev_free(h->d_scratch);
+    dev_free(h->d_scratch); dev_free(h->d_work_counter);
     for (auto& ev : h->ev) if (ev) cudaEventDestroy(ev);
     if (h->stream) cudaStreamDestroy(h->stream);
     delete h;
@@ -495,7 +497,8 @@ int mascot_train_epoch(mascot_handle* h, uint32_t epoch, mascot_epoch_stats* out
     bool any_f32 = false;
     for (uint8_t p : h->uprec) any_f32 |= p != 0;
     for (uint8_t p : h->iprec) any_f32 |= p != 0;
-    CU(h, launch_train(K, h->kind, s, h->P, h->Q, lr, h->cfg.lambda, check ? &st : nullptr, any_f32, workers, h->stream, &shape));
+    CU(h, launch_train(K, h->kind, s, h->P, h->Q, lr, h->cfg.lambda, check ? &st : nullptr, any_f32, workers,
+                       h->d_work_counter, h->stream, &shape));
     launches++;
     CU(h, cudaEventRecord(h->ev[2], h->stream));
 

@@ -198,17 +198,20 @@ struct Consts {
     float mpt_rev;
 };
 
-struct StatAcc { float* gs_p; float* gs_q; float* ns_p; float* ns_q; };
+// Sampled statistics (mascot_sgd_kernel.h:240-277): per group the element-wise sum of the gradients
+// and the sum of their squared norms.  They go to global memory as 128-bit fire-and-forget
+// reductions.  The reference adds every rating's gradient with scalar atomics in no particular
+// order; here the user side does the same per rating, while the item side - whose ratings arrive in
+// runs of the same group, because shuffle windows are item-sorted - is summed in registers over a run
+// of equal item groups and flushed once per run, which removes the contention on popular items.
+struct Sample {
+    V8f gp, gq;
+    bool user, item;      // which sides of this rating contribute (binary16-stored rows only)
+};
 
-// Sampled statistics of one side (mascot_sgd_kernel.h:240-277): sum of squared gradient elements
-// (same pair/tree order as the dot product) and the element-wise gradient sum of the row's group.
-template <int K, int TS>
-__device__ __forceinline__ void sample_side(const V8f& g, float* gsum, float* nsum, uint32_t group, int m, unsigned wmask) {
-    const float n = worker_sum<TS>(pair_partial(g, g), wmask);
-    if (m == 0) atomicAdd(nsum + group, n);
-    float* dst = gsum + (size_t)group * K + 8 * m;
-#pragma unroll
-    for (int s = 0; s < 8; s++) atomicAdd(dst + s, g.x[s]);
+__device__ __forceinline__ void red_add8(float* dst, const V8f& g) {
+    atomicAdd(reinterpret_cast<float4*>(dst), make_float4(g.x[0], g.x[1], g.x[2], g.x[3]));
+    atomicAdd(reinterpret_cast<float4*>(dst) + 1, make_float4(g.x[4], g.x[5], g.x[6], g.x[7]));
 }
 
 struct KernelArgs {
@@ -216,16 +219,19 @@ struct KernelArgs {
     Arena P, Q;
     float lr, lam;
     SampleStats st;
-    int stats_in_smem;
-    unsigned workers;             // concurrent sequential workers actually used
+    unsigned workers;             // concurrent sequential workers actually launched
+    unsigned long long* next_chunk;   // work counter, zero at launch: chunks beyond the first two per
+                                      // worker are handed out dynamically, so the launch never depends on
+                                      // every block being resident at the same time
 };
 
 // One update.  p_raw / q_raw are the row slices in their storage precision; both are replaced by the
 // updated values.  Statistics go to `acc` when the rating is sampled.
 template <int K, int KIND, int MODE, bool STATS>
 __device__ __forceinline__ void update_one(const Consts& c, float r, uint32_t uc, uint32_t ic, Raw<MODE>& p_raw, Raw<MODE>& q_raw,
-                                           bool sampled, const StatAcc& acc, const SampleStats& st, int m, unsigned wmask) {
+                                           bool sampled, Sample& smp, unsigned wmask) {
     constexpr int TS = K / 8;
+    if (STATS) { smp.user = false; smp.item = false; }
     if constexpr (KIND == KIND_MPT) {
         const V8f p = as_v8f(p_raw), q = as_v8f(q_raw);
         const V8h ph = narrow(p), qh = narrow(q);
@@ -254,10 +260,7 @@ __device__ __forceinline__ void update_one(const Consts& c, float r, uint32_t uc
             const V8h gp = grad(e, q, c.lam_h, p), gq = grad(e, p, c.lam_h, q);
             put(p_raw, step(c.lr_h, gp, p));
             put(q_raw, step(c.lr_h, gq, q));
-            if (STATS && sampled) {
-                sample_side<K, TS>(widen(gp), acc.gs_p, acc.ns_p, st.ugroup[uc & kIdMask], m, wmask);
-                sample_side<K, TS>(widen(gq), acc.gs_q, acc.ns_q, st.igroup[ic & kIdMask], m, wmask);
-            }
+            if (STATS && sampled) { smp.gp = widen(gp); smp.gq = widen(gq); smp.user = true; smp.item = true; }
         } else if constexpr (MODE != ROWS_HALF) {
             const V8f p = uf ? as_v8f(p_raw) : widen(as_v8h(p_raw));
             const V8f q = itf ? as_v8f(q_raw) : widen(as_v8h(q_raw));
@@ -266,10 +269,7 @@ __device__ __forceinline__ void update_one(const Consts& c, float r, uint32_t uc
             const V8f po = step(c.lr, gp, p), qo = step(c.lr, gq, q);
             if (uf) put(p_raw, po); else put(p_raw, narrow(po));
             if (itf) put(q_raw, qo); else put(q_raw, narrow(qo));
-            if (STATS && sampled) {
-                if (!uf) sample_side<K, TS>(gp, acc.gs_p, acc.ns_p, st.ugroup[uc & kIdMask], m, wmask);
-                if (!itf) sample_side<K, TS>(gq, acc.gs_q, acc.ns_q, st.igroup[ic & kIdMask], m, wmask);
-            }
+            if (STATS && sampled) { smp.gp = gp; smp.gq = gq; smp.user = !uf; smp.item = !itf; }
         }
     }
 }
@@ -290,24 +290,12 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
     constexpr int TS = K / 8;                      // lanes per worker = ratings per chunk
     constexpr int D = DEEP ? (MODE == ROWS_HALF ? 8 : 4) : 2;
     static_assert(TS % D == 0, "the prefetch ring must divide the chunk");
-    extern __shared__ float smem[];
     const int lane = threadIdx.x & 31;
     const int m = lane % TS;
     const unsigned wmask = (TS == 32) ? 0xffffffffu : (((1u << TS) - 1u) << (lane - m));
     const uint64_t worker = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) / TS;
     const uint64_t W = a.workers;
     const uint64_t nchunks = (a.s.n + TS - 1) / TS;
-
-    StatAcc acc = {a.st.gsum_p, a.st.gsum_q, a.st.nsum_p, a.st.nsum_q};
-    if (STATS && a.stats_in_smem) {
-        const int total = (a.st.ug + a.st.ig) * (K + 1);
-        for (int j = threadIdx.x; j < total; j += blockDim.x) smem[j] = 0.f;
-        acc.gs_p = smem;
-        acc.gs_q = acc.gs_p + a.st.ug * K;
-        acc.ns_p = acc.gs_q + a.st.ig * K;
-        acc.ns_q = acc.ns_p + a.st.ug;
-        __syncthreads();
-    }
 
     Consts c;
     c.lr = a.lr; c.lam = a.lam;
@@ -345,11 +333,20 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
         return k;
     };
 
+    // chunk ids: worker, worker + W, then 2W + (ticket from the shared counter)
+    auto take_chunk = [&]() -> uint64_t {
+        unsigned long long t = 0;
+        if (m == 0) t = atomicAdd(a.next_chunk, 1ull);
+        const unsigned lo = __shfl_sync(wmask, (unsigned)t, 0, TS), hi = __shfl_sync(wmask, (unsigned)(t >> 32), 0, TS);
+        return 2 * W + (((uint64_t)hi << 32) | lo);
+    };
+
     if (worker < W) {
         uint64_t ci = worker;
         Chunk none; none.r = 0.f; none.u = kNoRow; none.i = 0; none.cnt = 0; none.dup = 0; none.base = 0;
         Chunk cur = load_chunk(ci, none);
         Chunk nxt = load_chunk(ci + W, cur);
+        (void)ci;
 
         Raw<MODE> ring[D];             // slot j % D: prefetched user row of rating j of the current chunk
         unsigned stale = 0;            // bit t: slot t was not prefetched and is read at use
@@ -359,12 +356,46 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
         uint32_t cur_ic = kNoRow, nxt_ic = kNoRow;
         Raw<MODE> q, qn;
 
+        // item-side statistics of the current run of equal item groups
+        V8f gq_acc; float nq_acc = 0.f; uint32_t acc_group = kNoRow;
+#pragma unroll
+        for (int t = 0; t < 8; t++) gq_acc.x[t] = 0.f;
+        auto flush_item_stats = [&]() {
+            if (acc_group != kNoRow) {
+                red_add8(a.st.gsum_q + (size_t)acc_group * K + 8 * m, gq_acc);
+                if (m == 0) atomicAdd(a.st.nsum_q + acc_group, nq_acc);
+            }
+        };
+        auto record = [&](const Sample& smp, uint32_t uc, uint32_t ic) {
+            if (smp.user) {
+                const uint32_t g = a.st.ugroup[uc & kIdMask];
+                const float n = worker_sum<TS>(pair_partial(smp.gp, smp.gp), wmask);
+                red_add8(a.st.gsum_p + (size_t)g * K + 8 * m, smp.gp);
+                if (m == 0) atomicAdd(a.st.nsum_p + g, n);
+            }
+            if (smp.item) {
+                const uint32_t g = a.st.igroup[ic & kIdMask];
+                const float n = worker_sum<TS>(pair_partial(smp.gq, smp.gq), wmask);
+                if (g != acc_group) {
+                    flush_item_stats();
+                    acc_group = g; nq_acc = 0.f;
+#pragma unroll
+                    for (int t = 0; t < 8; t++) gq_acc.x[t] = 0.f;
+                }
+#pragma unroll
+                for (int t = 0; t < 8; t++) gq_acc.x[t] = __fadd_rn(gq_acc.x[t], smp.gq.x[t]);
+                nq_acc = __fadd_rn(nq_acc, n);
+            }
+        };
+        Sample smp;
+
         // switches the cached item row when the item changes; `j` is the rating's index in `cur`
         auto item_row = [&](uint32_t ic, int j) {
             if (ic != cur_ic) {
                 if (cur_ic != kNoRow) st_row<K, MODE>(a.Q, cur_ic, m, q);
                 if (ic == nxt_ic) q = qn; else q = ld_row<K, MODE>(a.Q, ic, m);
                 cur_ic = ic;
+                nxt_ic = kNoRow;               // a prefetched row is used at most once, right after its fetch
                 // prefetch the row of the next run: first different item later in this chunk, else
                 // the first item of the worker's next chunk
                 const unsigned later = __ballot_sync(wmask, cur.i != ic && m > j && m < cur.cnt) >> (lane - m);
@@ -408,8 +439,9 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
                             const uint32_t ux = __shfl_sync(wmask, nxt.u, x - TS, TS);
                             if ((nxt.dup >> (x - TS)) & 1u) stale |= 1u << t; else ring[t] = ld_row<K, MODE>(a.P, ux, m);
                         }
-                        update_one<K, KIND, MODE, STATS>(c, r, uc, ic, p, q, sampled, acc, a.st, m, wmask);
+                        update_one<K, KIND, MODE, STATS>(c, r, uc, ic, p, q, sampled, smp, wmask);
                         st_row<K, MODE>(a.P, uc, m, p);
+                        if (STATS && sampled) record(smp, uc, ic);
                     }
                 }
                 primed = next_full;
@@ -422,31 +454,17 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
                     const bool sampled = STATS && (cur.base + j >= a.st.first_sample_pos);
                     item_row(ic, j);
                     Raw<MODE> p = ld_row<K, MODE>(a.P, uc, m);
-                    update_one<K, KIND, MODE, STATS>(c, r, uc, ic, p, q, sampled, acc, a.st, m, wmask);
+                    update_one<K, KIND, MODE, STATS>(c, r, uc, ic, p, q, sampled, smp, wmask);
                     st_row<K, MODE>(a.P, uc, m, p);
+                    if (STATS && sampled) record(smp, uc, ic);
                 }
                 primed = false;
             }
-            ci += W;
-            const Chunk done = cur;
             cur = nxt;
-            nxt = load_chunk(ci + W, cur);
-            (void)done;
+            nxt = (cur.cnt > 0) ? load_chunk(take_chunk(), cur) : none;
         }
         if (cur_ic != kNoRow) st_row<K, MODE>(a.Q, cur_ic, m, q);
-    }
-
-    if (STATS && a.stats_in_smem) {
-        __syncthreads();
-        const int nvec = (a.st.ug + a.st.ig) * K;
-        for (int j = threadIdx.x; j < nvec; j += blockDim.x) {
-            const float v = smem[j];
-            if (v != 0.f) atomicAdd((j < a.st.ug * K) ? a.st.gsum_p + j : a.st.gsum_q + (j - a.st.ug * K), v);
-        }
-        for (int j = threadIdx.x; j < a.st.ug + a.st.ig; j += blockDim.x) {
-            const float v = smem[nvec + j];
-            if (v != 0.f) atomicAdd((j < a.st.ug) ? a.st.nsum_p + j : a.st.nsum_q + (j - a.st.ug), v);
-        }
+        if (STATS) flush_item_stats();
     }
 }
 
@@ -482,19 +500,7 @@ cudaError_t launch_one(const KernelArgs& args, unsigned workers, cudaStream_t st
     }
     const bool deep = per_sm <= 12;
     auto kern = deep ? train_kernel<K, KIND, MODE, STATS, true> : train_kernel<K, KIND, MODE, STATS, false>;
-    size_t smem = 0;
-    a.stats_in_smem = 0;
-    if (STATS) {
-        const size_t want = (size_t)(a.st.ug + a.st.ig) * (K + 1) * sizeof(float);
-        if (want <= 100 * 1024) {
-            smem = want;
-            a.stats_in_smem = 1;
-            if (smem > 48 * 1024) {
-                cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-                if (e != cudaSuccess) return e;
-            }
-        }
-    }
+    const size_t smem = 0;
     const unsigned capacity = (unsigned)grid * (unsigned)(block / 32) * kPerWarp;
     // a single block (deterministic runs, tiny worker counts) uses exactly the requested workers
     a.workers = (grid == 1) ? workers : capacity;
@@ -522,11 +528,14 @@ cudaError_t launch_k(TrainKind kind, const KernelArgs& a, bool stats, bool any_f
 }  // namespace
 
 cudaError_t launch_train(int K, TrainKind kind, const Stream& s, Arena P, Arena Q, float lr, float lam,
-                         const SampleStats* stats, bool any_f32_rows, unsigned workers, cudaStream_t st, LaunchShape* shape) {
+                         const SampleStats* stats, bool any_f32_rows, unsigned workers, unsigned long long* work_counter,
+                         cudaStream_t st, LaunchShape* shape) {
     KernelArgs a;
-    a.s = s; a.P = P; a.Q = Q; a.lr = lr; a.lam = lam; a.stats_in_smem = 0; a.workers = workers;
+    a.s = s; a.P = P; a.Q = Q; a.lr = lr; a.lam = lam; a.workers = workers; a.next_chunk = work_counter;
     if (stats) a.st = *stats;
     if (s.n == 0) { if (shape) *shape = LaunchShape(); return cudaSuccess; }
+    cudaError_t e0 = cudaMemsetAsync(work_counter, 0, sizeof(unsigned long long), st);
+    if (e0 != cudaSuccess) return e0;
     if (K == 128) return launch_k<128>(kind, a, stats != nullptr, any_f32_rows, workers, st, shape);
     if (K == 64) return launch_k<64>(kind, a, stats != nullptr, any_f32_rows, workers, st, shape);
     return cudaErrorInvalidValue;

@@ -372,18 +372,44 @@ void mo_mascot_run(int k, const mo_node* R, const uint32_t* seq, uint64_t nseq,
                    uint16_t* P16, float* P32, const uint8_t* uprec_row, const uint32_t* ugroup,
                    uint16_t* Q16, float* Q32, const uint8_t* iprec_row, const uint32_t* igroup,
                    float lr, float lam, uint64_t first_sample_pos,
-                   float* gsum_p, float* gsum_q, float* nsum_p, float* nsum_q, const mo_rules* rules) {
+                   float* gsum_p, float* gsum_q, float* nsum_p, float* nsum_q, int item_stats_by_run,
+                   const mo_rules* rules) {
     uint16_t lr_h = mo_f2h(lr), lam_h = mo_f2h(lam);   /* mascot_sgd_kernel.h:79-80 */
     float dummy_vec[128]; float dummy = 0;
+    /* item side of a run of equal item groups, when summed per run (see mascot_oracle.h) */
+    float run_g[128]; float run_n = 0; int64_t run_group = -1;
     for (uint64_t t = 0; t < nseq; t++) {
         const mo_node* n = &R[seq ? seq[t] : t];
         int sampled = (t >= first_sample_pos) && gsum_p;
         uint32_t gu = ugroup ? ugroup[n->u] : 0, gi = igroup ? igroup[n->i] : 0;
-        mascot_update(k, P16 + (size_t)n->u * k, P32 + (size_t)n->u * k, uprec_row[n->u],
-                      Q16 + (size_t)n->i * k, Q32 + (size_t)n->i * k, iprec_row[n->i],
-                      n->r, lr, lam, lr_h, lam_h, sampled,
-                      sampled ? gsum_p + (size_t)gu * k : dummy_vec, sampled ? gsum_q + (size_t)gi * k : dummy_vec,
-                      sampled ? nsum_p + gu : &dummy, sampled ? nsum_q + gi : &dummy, rules);
+        if (sampled && item_stats_by_run) {
+            float gq[128]; float nq = 0;
+            memset(gq, 0, sizeof gq);
+            mascot_update(k, P16 + (size_t)n->u * k, P32 + (size_t)n->u * k, uprec_row[n->u],
+                          Q16 + (size_t)n->i * k, Q32 + (size_t)n->i * k, iprec_row[n->i],
+                          n->r, lr, lam, lr_h, lam_h, 1, gsum_p + (size_t)gu * k, gq, nsum_p + gu, &nq, rules);
+            if (!iprec_row[n->i]) {
+                if ((int64_t)gi != run_group) {
+                    if (run_group >= 0) {
+                        for (int d = 0; d < k; d++) gsum_q[(size_t)run_group * k + d] += run_g[d];
+                        nsum_q[run_group] += run_n;
+                    }
+                    run_group = gi; run_n = 0; memset(run_g, 0, sizeof run_g);
+                }
+                for (int d = 0; d < k; d++) run_g[d] += gq[d];
+                run_n += nq;
+            }
+        } else {
+            mascot_update(k, P16 + (size_t)n->u * k, P32 + (size_t)n->u * k, uprec_row[n->u],
+                          Q16 + (size_t)n->i * k, Q32 + (size_t)n->i * k, iprec_row[n->i],
+                          n->r, lr, lam, lr_h, lam_h, sampled,
+                          sampled ? gsum_p + (size_t)gu * k : dummy_vec, sampled ? gsum_q + (size_t)gi * k : dummy_vec,
+                          sampled ? nsum_p + gu : &dummy, sampled ? nsum_q + gi : &dummy, rules);
+        }
+    }
+    if (run_group >= 0) {
+        for (int d = 0; d < k; d++) gsum_q[(size_t)run_group * k + d] += run_g[d];
+        nsum_q[run_group] += run_n;
     }
 }
 

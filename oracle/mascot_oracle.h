@@ -65,14 +65,20 @@ int mo_grouping(const uint32_t* cnt_sorted, uint32_t n_entities, uint32_t reques
 void mo_group_errors(const float* grad_sum, const float* norm_sum, int n_norm_parts, int groups, int k,
                      const uint8_t* prec, const float* initial_err, float* err_out);
 
-/* ---- per-rating update engines; seq[t] indexes R, processed sequentially ---- */
+/* ---- per-rating update engines; seq[t] indexes R, processed sequentially ----
+ * Sampled statistics: the reference adds each sampled rating's gradient to the per-group sums with
+ * unordered atomics, so the order of that floating-point sum is not defined by the reference.  With
+ * item_stats_by_run == 0 the sums grow rating by rating (what one reference warp does, and what the
+ * golden vectors hold); with 1 the item side is first summed over each run of consecutive sampled
+ * ratings whose items fall in the same group and then added once (what the engine does). */
 void mo_sgd_run(int k, const mo_node* R, const uint32_t* seq, uint64_t nseq, float* P, float* Q,
                 float lr, float lam, const mo_rules* rules);
 void mo_mascot_run(int k, const mo_node* R, const uint32_t* seq, uint64_t nseq,
                    uint16_t* P16, float* P32, const uint8_t* uprec_row, const uint32_t* ugroup,
                    uint16_t* Q16, float* Q32, const uint8_t* iprec_row, const uint32_t* igroup,
                    float lr, float lam, uint64_t first_sample_pos,
-                   float* gsum_p, float* gsum_q, float* nsum_p, float* nsum_q, const mo_rules* rules);
+                   float* gsum_p, float* gsum_q, float* nsum_p, float* nsum_q, int item_stats_by_run,
+                   const mo_rules* rules);
 void mo_mpt_run(int k, const mo_node* R, const uint32_t* seq, uint64_t nseq, float* P, float* Q,
                 float lr, float lam, const mo_rules* rules);
 void mo_memquant_run(int k, const mo_node* R, const uint32_t* seq, uint64_t nseq, uint16_t* P, uint16_t* Q,

@@ -190,7 +190,7 @@ class MascotModel:
         Q = np.where(self.iprec_row[:, None] == 1, self.Q32, h2f(self.Q16))
         return P.astype(np.float32), Q.astype(np.float32)
 
-    def run(self, R, seq, lr, lam, rules, first_sample_pos=None, stats=False):
+    def run(self, R, seq, lr, lam, rules, first_sample_pos=None, stats=False, item_stats_by_run=False):
         R = as_nodes(R)
         seq = _seq(seq)
         nseq = seq.size if seq is not None else R.size
@@ -207,7 +207,7 @@ class MascotModel:
                             _p(self.P16), _p(self.P32), _p(upr), _p(self.ugroup),
                             _p(self.Q16), _p(self.Q32), _p(ipr), _p(self.igroup),
                             C.c_float(lr), C.c_float(lam), C.c_uint64(fsp),
-                            _p(gp), _p(gq), _p(np_), _p(nq), C.byref(rules))
+                            _p(gp), _p(gq), _p(np_), _p(nq), C.c_int(1 if item_stats_by_run else 0), C.byref(rules))
         return gp, gq, np_, nq
 
 

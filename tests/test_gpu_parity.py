@@ -203,7 +203,7 @@ def test_mascot_training_with_switching_bit_exact(mascot, oracle, k):
         st = eng.train_epoch(e)
         assert bool(st.error_check) == check
         stats = model.run(Rs, None, float(lrs[e]), 0.015, rules,
-                          first_sample_pos=(n - sample_num) if check else None, stats=check)
+                          first_sample_pos=(n - sample_num) if check else None, stats=check, item_stats_by_run=True)
         if check:
             got = eng.sample_stats()
             for a, b, what in zip(got, stats, ("gsum_p", "gsum_q", "nsum_p", "nsum_q")):
