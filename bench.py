@@ -179,6 +179,7 @@ def main():
     ap.add_argument("--cpu-sample", type=int, default=4_000_000)
     ap.add_argument("--item-zipf", type=float, default=None, help="experiment knob: override the item popularity exponent")
     ap.add_argument("--workers", type=int, default=0, help="concurrent sequential workers (-wg); 0 = the configuration's value")
+    ap.add_argument("--sample-ratio", type=float, default=None, help="experiment knob: override -s")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -217,6 +218,8 @@ def main():
     n_train, n_test = train_t.shape[0], test_t.shape[0]
 
     extra = {"num_workers": args.workers} if args.workers else {}
+    if args.sample_ratio is not None:
+        extra["sample_ratio"] = args.sample_ratio
     ecfg = engine_config(M, cfg, device=local_rank, seed=args.seed, **extra)
     eng = M.Engine(ecfg)
     eng.set_ratings_raw(train_t.data_ptr(), n_train, test_t.data_ptr(), n_test, cfg["users"], cfg["items"])

@@ -31,6 +31,10 @@ struct SampleStats {
     float* nsum_p = nullptr;            // [ug]
     float* nsum_q = nullptr;
     uint64_t first_sample_pos = 0;      // stream positions >= this are sampled
+    // The four arrays above are the first of `copies` private sets laid out `copy_stride` floats
+    // apart; block b adds into set b % copies, and launch_reduce_stats folds them into set 0.
+    int copies = 1;
+    size_t copy_stride = 0;
 };
 
 enum TrainKind { KIND_MIXED = 0, KIND_FP32 = 1, KIND_MPT = 2, KIND_MEMQUANT = 3 };
@@ -49,6 +53,9 @@ struct LaunchShape {
 cudaError_t launch_train(int K, TrainKind kind, const Stream& s, Arena P, Arena Q, float lr, float lam,
                          const SampleStats* stats, bool any_f32_rows, unsigned workers,
                          unsigned long long* work_counter, cudaStream_t st, LaunchShape* shape);
+
+// Folds the private statistic sets of a launch into set 0 (sets are added in index order).
+cudaError_t launch_reduce_stats(float* sets, int copies, size_t copy_stride, size_t floats_per_set, cudaStream_t st);
 
 // Test RMSE over a coded SoA stream; block_err has ceil(n/512) floats.
 cudaError_t launch_rmse(int K, const Stream& t, Arena P, Arena Q, float* block_err, cudaStream_t st);

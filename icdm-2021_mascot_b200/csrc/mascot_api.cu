@@ -40,7 +40,8 @@ struct mascot_handle {
     uint8_t* d_uprec_row = nullptr; uint8_t* d_iprec_row = nullptr;
     uint16_t* d_ugroup = nullptr; uint16_t* d_igroup = nullptr;
     uint32_t* d_umap = nullptr; uint32_t* d_imap = nullptr;
-    float* d_stats = nullptr;       // gsum_p | gsum_q | nsum_p | nsum_q
+    float* d_stats = nullptr;       // stats_copies sets of: gsum_p | gsum_q | nsum_p | nsum_q
+    int stats_copies = 1; size_t stats_stride = 0;
     float* d_block_err = nullptr;
     unsigned long long* d_work_counter = nullptr;
     void* d_scratch = nullptr; size_t scratch_bytes = 0;   // staging for mascot_reload_train
@@ -60,6 +61,7 @@ struct mascot_handle {
 namespace {
 
 thread_local std::string g_create_error;
+constexpr int kStatCopies = 256;   // private accumulator sets of the sampled statistics
 
 }  // namespace
 
@@ -390,8 +392,10 @@ int mascot_set_ratings(mascot_handle* h, const mascot_rating* train, uint64_t n_
     const size_t pu = (size_t)n_users * h->K, qi = (size_t)n_items * h->K;
     if (h->kind == KIND_MIXED || h->kind == KIND_MEMQUANT) { CU(h, dev_alloc(&h->P.f16, pu)); CU(h, dev_alloc(&h->Q.f16, qi)); }
     if (h->kind != KIND_MEMQUANT) { CU(h, dev_alloc(&h->P.f32, pu)); CU(h, dev_alloc(&h->Q.f32, qi)); }
-    CU(h, dev_alloc(&h->d_stats, stats_floats(h)));
-    CU(h, cudaMemset(h->d_stats, 0, sizeof(float) * stats_floats(h)));
+    h->stats_copies = h->cfg.deterministic ? 1 : kStatCopies;
+    h->stats_stride = (stats_floats(h) + 63) / 64 * 64;
+    CU(h, dev_alloc(&h->d_stats, h->stats_stride * h->stats_copies));
+    CU(h, cudaMemset(h->d_stats, 0, sizeof(float) * h->stats_stride * h->stats_copies));
     h->h_stats.assign(stats_floats(h), 0.f);
     const size_t blocks = (size_t)((n_test + 511) / 512);
     CU(h, dev_alloc(&h->d_block_err, blocks));
@@ -487,19 +491,40 @@ int mascot_train_epoch(mascot_handle* h, uint32_t epoch, mascot_epoch_stats* out
         st.ugroup = h->d_ugroup; st.igroup = h->d_igroup; st.ug = ug; st.ig = ig;
         st.gsum_p = h->d_stats; st.gsum_q = st.gsum_p + (size_t)ug * K;
         st.nsum_p = st.gsum_q + (size_t)ig * K; st.nsum_q = st.nsum_p + ug;
+        st.copies = h->stats_copies; st.copy_stride = h->stats_stride;
     }
     const uint64_t bytes_this_epoch = algorithmic_bytes(h);    // with the precisions the kernel is about to see
     CU(h, cudaEventRecord(h->ev[0], h->stream));
-    if (check) CU(h, cudaMemsetAsync(h->d_stats, 0, sizeof(float) * stats_floats(h), h->stream));   // mf_methods.cu:178-182
+    if (check) CU(h, cudaMemsetAsync(h->d_stats, 0, sizeof(float) * h->stats_stride * h->stats_copies, h->stream));   // mf_methods.cu:178-182
     CU(h, cudaEventRecord(h->ev[1], h->stream));
     LaunchShape shape;
     const unsigned workers = h->cfg.deterministic ? 1u : (h->cfg.num_workers ? h->cfg.num_workers : 2048u);
     bool any_f32 = false;
     for (uint8_t p : h->uprec) any_f32 |= p != 0;
     for (uint8_t p : h->iprec) any_f32 |= p != 0;
-    CU(h, launch_train(K, h->kind, s, h->P, h->Q, lr, h->cfg.lambda, check ? &st : nullptr, any_f32, workers,
-                       h->d_work_counter, h->stream, &shape));
+    if (!check) {
+        CU(h, launch_train(K, h->kind, s, h->P, h->Q, lr, h->cfg.lambda, nullptr, any_f32, workers,
+                           h->d_work_counter, h->stream, &shape));
+    } else {
+        // Check epoch: the stream up to the sampled tail runs through the plain kernel, the tail
+        // through the statistics-collecting one, so only the sampled fraction pays for the statistics.
+        const uint64_t head = st.first_sample_pos;
+        if (head > 0) {
+            Stream sa = s; sa.n = head;
+            CU(h, launch_train(K, h->kind, sa, h->P, h->Q, lr, h->cfg.lambda, nullptr, any_f32, workers,
+                               h->d_work_counter, h->stream, &shape));
+            launches++;
+        }
+        Stream sb; sb.r = s.r + head; sb.u = s.u + head; sb.i = s.i + head; sb.n = s.n - head;
+        st.first_sample_pos = 0;
+        CU(h, launch_train(K, h->kind, sb, h->P, h->Q, lr, h->cfg.lambda, &st, any_f32, workers,
+                           h->d_work_counter, h->stream, &shape));
+    }
     launches++;
+    if (check && h->stats_copies > 1) {
+        CU(h, launch_reduce_stats(h->d_stats, h->stats_copies, h->stats_stride, stats_floats(h), h->stream));
+        launches++;
+    }
     CU(h, cudaEventRecord(h->ev[2], h->stream));
 
     if (check) {

@@ -360,18 +360,22 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
         V8f gq_acc; float nq_acc = 0.f; uint32_t acc_group = kNoRow;
 #pragma unroll
         for (int t = 0; t < 8; t++) gq_acc.x[t] = 0.f;
+        // this block's private set of accumulators (fewer workers per address, less serialisation)
+        const size_t my_set = STATS ? (size_t)(blockIdx.x % (unsigned)a.st.copies) * a.st.copy_stride : 0;
+        float* const gsum_p = a.st.gsum_p + my_set; float* const gsum_q = a.st.gsum_q + my_set;
+        float* const nsum_p = a.st.nsum_p + my_set; float* const nsum_q = a.st.nsum_q + my_set;
         auto flush_item_stats = [&]() {
             if (acc_group != kNoRow) {
-                red_add8(a.st.gsum_q + (size_t)acc_group * K + 8 * m, gq_acc);
-                if (m == 0) atomicAdd(a.st.nsum_q + acc_group, nq_acc);
+                red_add8(gsum_q + (size_t)acc_group * K + 8 * m, gq_acc);
+                if (m == 0) atomicAdd(nsum_q + acc_group, nq_acc);
             }
         };
         auto record = [&](const Sample& smp, uint32_t uc, uint32_t ic) {
             if (smp.user) {
                 const uint32_t g = a.st.ugroup[uc & kIdMask];
                 const float n = worker_sum<TS>(pair_partial(smp.gp, smp.gp), wmask);
-                red_add8(a.st.gsum_p + (size_t)g * K + 8 * m, smp.gp);
-                if (m == 0) atomicAdd(a.st.nsum_p + g, n);
+                red_add8(gsum_p + (size_t)g * K + 8 * m, smp.gp);
+                if (m == 0) atomicAdd(nsum_p + g, n);
             }
             if (smp.item) {
                 const uint32_t g = a.st.igroup[ic & kIdMask];
@@ -468,6 +472,14 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
     }
 }
 
+__global__ void reduce_stats_kernel(float* sets, int copies, size_t stride, size_t n) {
+    for (size_t j = (size_t)blockIdx.x * blockDim.x + threadIdx.x; j < n; j += (size_t)gridDim.x * blockDim.x) {
+        float acc = sets[j];
+        for (int c = 1; c < copies; c++) acc = __fadd_rn(acc, sets[(size_t)c * stride + j]);
+        sets[j] = acc;
+    }
+}
+
 int sm_count() {
     static int sms = 0;
     if (!sms) {
@@ -526,6 +538,13 @@ cudaError_t launch_k(TrainKind kind, const KernelArgs& a, bool stats, bool any_f
 }
 
 }  // namespace
+
+cudaError_t launch_reduce_stats(float* sets, int copies, size_t copy_stride, size_t floats_per_set, cudaStream_t st) {
+    if (copies <= 1 || floats_per_set == 0) return cudaSuccess;
+    const int grid = (int)((floats_per_set + 255) / 256);
+    reduce_stats_kernel<<<grid, 256, 0, st>>>(sets, copies, copy_stride, floats_per_set);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_train(int K, TrainKind kind, const Stream& s, Arena P, Arena Q, float lr, float lam,
                          const SampleStats* stats, bool any_f32_rows, unsigned workers, unsigned long long* work_counter,
