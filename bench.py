@@ -178,7 +178,7 @@ def main():
     ap.add_argument("--seed", type=int, default=4)
     ap.add_argument("--cpu-sample", type=int, default=4_000_000)
     ap.add_argument("--item-zipf", type=float, default=None, help="experiment knob: override the item popularity exponent")
-    ap.add_argument("--workers", type=int, default=0, help="concurrent sequential workers (-wg); 0 = the configuration's value")
+    ap.add_argument("--workers", type=int, default=0, help="concurrent sequential workers (-wg); 0 = the engine's automatic choice")
     ap.add_argument("--sample-ratio", type=float, default=None, help="experiment knob: override -s")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")

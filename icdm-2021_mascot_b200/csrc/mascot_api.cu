@@ -498,7 +498,12 @@ int mascot_train_epoch(mascot_handle* h, uint32_t epoch, mascot_epoch_stats* out
     if (check) CU(h, cudaMemsetAsync(h->d_stats, 0, sizeof(float) * h->stats_stride * h->stats_copies, h->stream));   // mf_methods.cu:178-182
     CU(h, cudaEventRecord(h->ev[1], h->stream));
     LaunchShape shape;
-    const unsigned workers = h->cfg.deterministic ? 1u : (h->cfg.num_workers ? h->cfg.num_workers : 2048u);
+    // -wg 0 = automatic: one worker per 8192 ratings of the epoch keeps the sequential depth per
+    // worker - and with it the convergence per epoch - at the level of the reference's tuned runs;
+    // the launch caps the count at what the GPU can keep resident.
+    unsigned workers = h->cfg.num_workers;
+    if (h->cfg.deterministic) workers = 1u;
+    else if (workers == 0) workers = (unsigned)std::min<uint64_t>(std::max<uint64_t>(h->n_train / 8192, 512), 1u << 20);
     bool any_f32 = false;
     for (uint8_t p : h->uprec) any_f32 |= p != 0;
     for (uint8_t p : h->iprec) any_f32 |= p != 0;

@@ -307,9 +307,12 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
     // only the mixed-precision mode reads the precision bit of an id
     constexpr uint32_t kKeep = (MODE == ROWS_DYN) ? 0xffffffffu : kIdMask;
 
-    // Loads chunk `ci` and marks the ratings whose user repeats within the D ratings before them
-    // (those rows cannot be prefetched: they must be read after the earlier update is stored).
-    auto load_chunk = [&](uint64_t ci, const Chunk& before) {
+    // Chunk pipeline, four stages deep so that no stage waits for the one before it:
+    //   ticket (atomic on the work counter) -> record loads -> repeat marking -> use.
+    // fetch_chunk only issues the loads; mark_repeats, run one chunk later when the data has
+    // arrived, flags the ratings whose user also occurs among the D ratings before them (those rows
+    // cannot be prefetched: they must be read after the earlier update has been stored).
+    auto fetch_chunk = [&](uint64_t ci) {
         Chunk k; k.r = 0.f; k.u = kNoRow; k.i = 0; k.cnt = 0; k.dup = 0; k.base = 0;
         if (ci < nchunks) {
             k.base = ci * TS;
@@ -320,6 +323,11 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
                 k.u = __ldg(a.s.u + k.base + m) & kKeep;
                 k.i = __ldg(a.s.i + k.base + m) & kKeep;
             }
+        }
+        return k;
+    };
+    auto mark_repeats = [&](Chunk& k, const Chunk& before) {
+        if (k.cnt > 0) {
             bool mine = false;
 #pragma unroll
             for (int d = 1; d <= D; d++) {
@@ -330,23 +338,26 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
             }
             k.dup = __ballot_sync(wmask, mine && m < k.cnt) >> (lane - m);
         }
-        return k;
     };
-
-    // chunk ids: worker, worker + W, then 2W + (ticket from the shared counter)
-    auto take_chunk = [&]() -> uint64_t {
-        unsigned long long t = 0;
-        if (m == 0) t = atomicAdd(a.next_chunk, 1ull);
+    // chunk ids: worker, worker + W, then 2W + (ticket from the shared counter); a ticket is
+    // requested one chunk before it is needed and stays in lane 0 until then
+    auto request_ticket = [&]() -> unsigned long long {
+        return (m == 0) ? atomicAdd(a.next_chunk, 1ull) : 0ull;
+    };
+    auto ticket_chunk = [&](unsigned long long t) -> uint64_t {
         const unsigned lo = __shfl_sync(wmask, (unsigned)t, 0, TS), hi = __shfl_sync(wmask, (unsigned)(t >> 32), 0, TS);
         return 2 * W + (((uint64_t)hi << 32) | lo);
     };
 
     if (worker < W) {
-        uint64_t ci = worker;
         Chunk none; none.r = 0.f; none.u = kNoRow; none.i = 0; none.cnt = 0; none.dup = 0; none.base = 0;
-        Chunk cur = load_chunk(ci, none);
-        Chunk nxt = load_chunk(ci + W, cur);
-        (void)ci;
+        Chunk cur = fetch_chunk(worker);
+        Chunk nxt = fetch_chunk(worker + W);
+        unsigned long long ticket = request_ticket();
+        Chunk nn = fetch_chunk(ticket_chunk(ticket));        // only this very first ticket is waited for
+        ticket = request_ticket();
+        mark_repeats(cur, none);
+        mark_repeats(nxt, cur);
 
         Raw<MODE> ring[D];             // slot j % D: prefetched user row of rating j of the current chunk
         unsigned stale = 0;            // bit t: slot t was not prefetched and is read at use
@@ -465,7 +476,10 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
                 primed = false;
             }
             cur = nxt;
-            nxt = (cur.cnt > 0) ? load_chunk(take_chunk(), cur) : none;
+            nxt = nn;
+            mark_repeats(nxt, cur);
+            nn = (nxt.cnt > 0) ? fetch_chunk(ticket_chunk(ticket)) : none;
+            if (nn.cnt > 0) ticket = request_ticket();
         }
         if (cur_ic != kNoRow) st_row<K, MODE>(a.Q, cur_ic, m, q);
         if (STATS) flush_item_stats();
@@ -497,6 +511,9 @@ cudaError_t launch_one(const KernelArgs& args, unsigned workers, cudaStream_t st
     KernelArgs a = args;
     // Spread the workers evenly: the same number of warps on every SM, in blocks of at most 8 warps.
     if (workers < 1) workers = 1;
+    // more workers than can be resident at once (64 warps per SM) only add launch overhead
+    const unsigned resident_cap = (unsigned)sm_count() * 64u * kPerWarp;
+    if (workers > resident_cap) workers = resident_cap;
     const unsigned warps = (workers + kPerWarp - 1) / kPerWarp;
     int grid, block;
     unsigned per_sm = warps;

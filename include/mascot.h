@@ -75,7 +75,9 @@ typedef struct mascot_config {
     uint32_t num_workers;        /* -wg  number of concurrent sequential workers (the reference's warps):
                                        fewer workers lose fewer updates of popular rows to races and
                                        converge faster per epoch, more workers run faster; rounded up
-                                       to fill every SM evenly                     default 2048        */
+                                       to fill every SM evenly; 0 = automatic (one per 8192 training
+                                       ratings, at least 512, at most what the GPU keeps resident)
+                                                                                   default 2048        */
     uint32_t epoch;              /* -l   number of epochs          default 50                  */
     uint32_t thread_block_size;  /* -bl  accepted for CLI parity, not used (blocks are sized per SM) */
     uint32_t version;            /* -v   one of MASCOT_V_*         default 7 in the reference  */
