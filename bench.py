@@ -167,6 +167,70 @@ def cpu_baseline_sample(S, cfg, seed, budget_s=15.0):
             "sample": f"{reps} passes over the first {n} ratings of the workload, {threads} host threads, Hogwild"}
 
 
+def run_sharded(args, S, M, cfg, rank, world, local_rank):
+    """N > 1: one process per GPU, users pinned per rank, item blocks rotating (multi.py)."""
+    import torch
+    import torch.distributed as dist
+    MU = _load("mascot_multi", os.path.join(PKG, "multi.py"))
+    dev = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", device_id=dev)
+    train_t, test_t = S.generate_cuda(cfg, seed=args.seed, device=f"cuda:{local_rank}")     # same seed: same data on every rank
+    torch.cuda.synchronize(); torch.cuda.empty_cache()
+    train = train_t.numpy().view(np.uint32).reshape(-1, 3).view(M.RATING).reshape(-1)
+    test = test_t.numpy().view(np.uint32).reshape(-1, 3).view(M.RATING).reshape(-1)
+    n_train = int(train.size)
+    plan = MU.make_plan(train["u"], train["i"], cfg["users"], cfg["items"], world)
+    extra = {"num_workers": args.workers} if args.workers else {}
+    ecfg = engine_config(M, cfg, device=local_rank, seed=args.seed, **extra)
+    shard = MU.EngineShard(M, ecfg, plan, rank, train, test, cfg["users"], cfg["items"])
+    shard.engine.init_factors()                        # same seed: identical factors on every rank
+    del train, test, train_t, test_t
+    epoch = 0
+    for _ in range(args.warmup):
+        MU.train_epoch(dist, shard, rank, world, epoch, comm_device=dev); epoch += 1
+    MU.gather_item_factors(dist, shard, world)
+    rmse_before = MU.global_rmse(dist, shard, world, comm_device=dev)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    dist.barrier(); torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    sent = 0
+    for _ in range(args.steps):
+        b, _pr = MU.train_epoch(dist, shard, rank, world, epoch, comm_device=dev); epoch += 1
+        sent += b
+    shard.sync(); torch.cuda.synchronize()
+    mine_ms = (time.perf_counter() - t0) * 1e3
+    dist.barrier()
+    t = torch.tensor([mine_ms], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    loc = torch.tensor([float(shard.n_local)], dtype=torch.float64, device=dev)
+    mx = loc.clone(); dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+    MU.gather_item_factors(dist, shard, world)
+    rmse_after = MU.global_rmse(dist, shard, world, comm_device=dev)
+    sampler.stop_flag.set(); sampler.join(timeout=3)
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        value = n_train * args.steps / (total_ms * 1e-3)
+        achieved = value * 2 * cfg["k"] * 4 / 1e9            # all-fp16 rows: 2*k*(2+2) bytes per update
+        line = {
+            "metric": "rating updates/sec (k=128)", "value": value, "unit": "updates/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16+f32", "data": "synthetic",
+            "config": {"workload": args.workload_desc, "parallelism": f"users pinned on {world} GPUs, {world} item blocks rotating by NCCL send/recv",
+                       "l2": "inputs larger than L2", "rmse_before": rmse_before, "rmse_after": rmse_after,
+                       "item_block_rows": plan.block_rows, "max_ratings_on_one_rank": int(mx.item()),
+                       "nvlink_bytes_sent_per_rank_per_step": sent / max(args.steps, 1), "timing": "wall clock between barrier+synchronize, max over ranks"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak * world, "unit": "GB/s", "frac": achieved / (peak * world),
+                         "traffic": None, "peak_kind": f"of {peak_kind} (x{world} GPUs)"},
+            "clocks": sampler.summary(), "gpu_launches": args.steps * world * 2, "e2e": None,
+        }
+        print(json.dumps(line), flush=True)
+    shard.close()
+    dist.destroy_process_group()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -208,10 +272,9 @@ def main():
     M.load()   # fails loudly when the CUDA library is missing
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: libmascot has no CPU path")
-    if world > 1:
-        raise SystemExit("multi-GPU launch is handled by bench_multi (not wired yet)")
     torch.cuda.set_device(local_rank)
-
+    if world > 1:
+        return run_sharded(args, S, M, cfg, rank, world, local_rank)
     train_t, test_t = S.generate_cuda(cfg, seed=args.seed, device=f"cuda:{local_rank}")
     torch.cuda.synchronize()
     torch.cuda.empty_cache()

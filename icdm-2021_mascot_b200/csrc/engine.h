@@ -67,7 +67,8 @@ cudaError_t launch_rmse_plain(int K, const void* d_test_aos, uint64_t n, const f
 cudaError_t launch_encode_stream(const void* d_src_aos, uint64_t n, bool shuffle, uint64_t seed,
                                  const uint32_t* user_map, const uint32_t* item_map,
                                  const uint8_t* uprec_row, const uint8_t* iprec_row, uint32_t n_items,
-                                 float* r, uint32_t* u, uint32_t* i, uint32_t* src_out, cudaStream_t st);
+                                 float* r, uint32_t* u, uint32_t* i, uint32_t* src_out, uint32_t src_base,
+                                 cudaStream_t st);
 cudaError_t launch_recode(uint32_t* ids, uint64_t n, const uint8_t* prec_row, cudaStream_t st);
 cudaError_t launch_scatter_factors(int K, const float* src, uint32_t rows, const uint32_t* row_map,
                                    bool round_through_half, __half* dst16, float* dst32, cudaStream_t st);

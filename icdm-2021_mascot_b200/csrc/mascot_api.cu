@@ -54,6 +54,7 @@ struct mascot_handle {
     std::vector<float> h_stats;     // same layout as d_stats, gsum in LOGICAL element order
     std::vector<float> h_block_err;
     std::vector<uint64_t> udeg_sum, ideg_sum;   // ratings per group (training set), for byte accounting
+    std::vector<uint64_t> seg_off;              // training stream segments: [seg_off[s], seg_off[s+1])
     uint64_t n_train_accounted = 0;
     std::string err;
 };
@@ -114,11 +115,13 @@ bool is_check_epoch(const mascot_config& c, uint32_t e) {
 }
 
 // user_item_rating_histogram (preprocess_utils.h:54-99): degree histogram, then ascending sort by
-// degree, ties in ascending id order.  Returns sorted2orig and the sorted degree list.
-void degree_sort(const mascot_rating* R, uint64_t n, bool users, uint32_t n_entities,
+// degree, ties in ascending id order.  Returns sorted2orig and the sorted degree list.  A shard of a
+// larger data set passes the global degrees so that every shard builds the same index space.
+void degree_sort(const mascot_rating* R, uint64_t n, bool users, uint32_t n_entities, const uint32_t* given_degree,
                  std::vector<uint32_t>& sorted2orig, std::vector<uint32_t>& orig2sorted, std::vector<uint32_t>& cnt_sorted) {
     std::vector<uint32_t> cnt(n_entities, 0);
-    for (uint64_t j = 0; j < n; j++) cnt[users ? R[j].u : R[j].i]++;
+    if (given_degree) cnt.assign(given_degree, given_degree + n_entities);   // degrees of the whole data set (sharded runs)
+    else for (uint64_t j = 0; j < n; j++) cnt[users ? R[j].u : R[j].i]++;
     uint32_t maxc = 0;
     for (uint32_t e = 0; e < n_entities; e++) maxc = std::max(maxc, cnt[e]);
     std::vector<uint64_t> start((size_t)maxc + 2, 0);
@@ -154,13 +157,6 @@ void make_groups(const std::vector<uint32_t>& cnt_sorted, uint32_t requested, st
         pos = last + 1;
     }
     if (end_idx.empty() || end_idx.back() != n - 1) end_idx.push_back(n - 1);   // only when every degree is 0
-}
-
-void group_degree_sums(const std::vector<uint32_t>& cnt_sorted, const std::vector<uint32_t>& end, std::vector<uint64_t>& out) {
-    out.assign(end.size(), 0);
-    uint32_t s = 0;
-    for (size_t g = 0; g < end.size(); g++)
-        for (; s <= end[g] && s < cnt_sorted.size(); s++) out[g] += cnt_sorted[s];
 }
 
 // bytes the update rule moves per epoch: every rating reads and writes k elements on each side
@@ -201,7 +197,21 @@ int upload_side_tables(mascot_handle* h, bool users) {
     return MASCOT_OK;
 }
 
-int upload_and_encode(mascot_handle* h, const mascot_rating* src, uint64_t n, bool shuffle,
+// Encodes an uploaded rating array into the structure-of-arrays stream, segment by segment: the
+// seeded permutation and the item-sorted windows never cross a segment boundary.
+cudaError_t encode_segments(mascot_handle* h, const mascot_rating* d_src, const std::vector<uint64_t>& seg, bool shuffle,
+                            float* r, uint32_t* u, uint32_t* i, uint32_t* src_idx) {
+    for (size_t sgm = 0; sgm + 1 < seg.size(); sgm++) {
+        const uint64_t off = seg[sgm], n = seg[sgm + 1] - off;
+        cudaError_t e = launch_encode_stream(d_src + off, n, shuffle, h->cfg.seed + 0x9e3779b97f4a7c15ull * sgm, h->d_umap, h->d_imap,
+                                             h->d_uprec_row, h->d_iprec_row, h->n_items, r + off, u + off, i + off,
+                                             src_idx ? src_idx + off : nullptr, (uint32_t)off, h->stream);
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
+}
+
+int upload_and_encode(mascot_handle* h, const mascot_rating* src, uint64_t n, const std::vector<uint64_t>& seg, bool shuffle,
                       float** r, uint32_t** u, uint32_t** i, uint32_t** src_idx) {
     CU(h, dev_alloc(r, n)); CU(h, dev_alloc(u, n)); CU(h, dev_alloc(i, n));
     if (src_idx && n < (1ull << 32)) CU(h, dev_alloc(src_idx, n));
@@ -209,9 +219,7 @@ int upload_and_encode(mascot_handle* h, const mascot_rating* src, uint64_t n, bo
     mascot_rating* tmp = nullptr;
     CU(h, dev_alloc(&tmp, n));
     cudaError_t e = cudaMemcpyAsync(tmp, src, sizeof(mascot_rating) * n, cudaMemcpyHostToDevice, h->stream);
-    if (e == cudaSuccess)
-        e = launch_encode_stream(tmp, n, shuffle, h->cfg.seed, h->d_umap, h->d_imap, h->d_uprec_row, h->d_iprec_row,
-                                 h->n_items, *r, *u, *i, src_idx ? *src_idx : nullptr, h->stream);
+    if (e == cudaSuccess) e = encode_segments(h, tmp, seg, shuffle, *r, *u, *i, src_idx ? *src_idx : nullptr);
     if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
     cudaFree(tmp);
     CU(h, e);
@@ -334,10 +342,25 @@ int mascot_destroy(mascot_handle* h) {
 
 int mascot_set_ratings(mascot_handle* h, const mascot_rating* train, uint64_t n_train,
                        const mascot_rating* test, uint64_t n_test, uint32_t n_users, uint32_t n_items) {
+    return mascot_set_ratings_sharded(h, train, n_train, nullptr, 1, test, n_test, n_users, n_items, nullptr, nullptr);
+}
+
+int mascot_set_ratings_sharded(mascot_handle* h, const mascot_rating* train, uint64_t n_train,
+                               const uint64_t* segment_offsets, uint32_t n_segments,
+                               const mascot_rating* test, uint64_t n_test, uint32_t n_users, uint32_t n_items,
+                               const uint32_t* user_degree, const uint32_t* item_degree) {
     if (!h) return MASCOT_ERR_BAD_ARG;
     if ((!train && n_train) || (!test && n_test)) return fail(h, MASCOT_ERR_BAD_ARG, "null rating array");
     if (!n_users || !n_items || n_users > kIdMask || n_items > kIdMask) return fail(h, MASCOT_ERR_BAD_ARG, "user/item count out of range");
     if (n_train >= (1ull << 40)) return fail(h, MASCOT_ERR_BAD_ARG, "too many ratings");
+    if (n_segments == 0 || (n_segments > 1 && !segment_offsets)) return fail(h, MASCOT_ERR_BAD_ARG, "bad segment table");
+    if ((user_degree == nullptr) != (item_degree == nullptr)) return fail(h, MASCOT_ERR_BAD_ARG, "give both degree tables or none");
+    std::vector<uint64_t> seg(n_segments + 1);
+    if (segment_offsets) {
+        for (uint32_t j = 0; j <= n_segments; j++) seg[j] = segment_offsets[j];
+        if (seg[0] != 0 || seg[n_segments] != n_train) return fail(h, MASCOT_ERR_BAD_ARG, "segment offsets must run from 0 to n_train");
+        for (uint32_t j = 0; j < n_segments; j++) if (seg[j] > seg[j + 1]) return fail(h, MASCOT_ERR_BAD_ARG, "segment offsets must not decrease");
+    } else { seg[0] = 0; seg[1] = n_train; }
     for (uint64_t j = 0; j < n_train; j++)
         if (train[j].u >= n_users || train[j].i >= n_items) return fail(h, MASCOT_ERR_BAD_ARG, "training rating with id out of range");
     for (uint64_t j = 0; j < n_test; j++)
@@ -345,18 +368,26 @@ int mascot_set_ratings(mascot_handle* h, const mascot_rating* train, uint64_t n_
     CU(h, cudaSetDevice(h->cfg.device));
     free_ratings(h);
     h->n_users = n_users; h->n_items = n_items; h->n_train = n_train; h->n_test = n_test;
+    h->seg_off = seg;
 
     // --- m-quantization set-up on the host (one-off) ---
     if (h->grouped) {
         std::vector<uint32_t> s2o, cnt;
-        degree_sort(train, n_train, true, n_users, s2o, h->user2sorted, cnt);
+        degree_sort(train, n_train, true, n_users, user_degree, s2o, h->user2sorted, cnt);
         make_groups(cnt, h->cfg.user_group_num, h->uend);
-        group_degree_sums(cnt, h->uend, h->udeg_sum);
-        degree_sort(train, n_train, false, n_items, s2o, h->item2sorted, cnt);
+        degree_sort(train, n_train, false, n_items, item_degree, s2o, h->item2sorted, cnt);
         make_groups(cnt, h->cfg.item_group_num, h->iend);
-        group_degree_sums(cnt, h->iend, h->ideg_sum);
         if (h->uend.size() > 65535 || h->iend.size() > 65535) return fail(h, MASCOT_ERR_BAD_ARG, "more than 65535 groups");
         h->uprec.assign(h->uend.size(), 0); h->iprec.assign(h->iend.size(), 0);
+        // ratings of THIS engine's stream per group (byte accounting)
+        std::vector<uint32_t> ug_of(n_users), ig_of(n_items);
+        { uint32_t p = 0; for (size_t g = 0; g < h->uend.size(); g++) for (; p <= h->uend[g] && p < n_users; p++) ug_of[p] = (uint32_t)g; }
+        { uint32_t p = 0; for (size_t g = 0; g < h->iend.size(); g++) for (; p <= h->iend[g] && p < n_items; p++) ig_of[p] = (uint32_t)g; }
+        h->udeg_sum.assign(h->uend.size(), 0); h->ideg_sum.assign(h->iend.size(), 0);
+        for (uint64_t j = 0; j < n_train; j++) {
+            h->udeg_sum[ug_of[h->user2sorted[train[j].u]]]++;
+            h->ideg_sum[ig_of[h->item2sorted[train[j].i]]]++;
+        }
     } else {
         h->user2sorted.clear(); h->item2sorted.clear();
         h->uend.assign(1, n_users - 1); h->iend.assign(1, n_items - 1);
@@ -378,14 +409,15 @@ int mascot_set_ratings(mascot_handle* h, const mascot_rating* train, uint64_t n_
     }
 
     // --- rating streams ---
-    if ((rc = upload_and_encode(h, train, n_train, h->cfg.shuffle != 0, &h->tr_r, &h->tr_u, &h->tr_i, &h->tr_src)) != MASCOT_OK) return rc;
+    if ((rc = upload_and_encode(h, train, n_train, seg, h->cfg.shuffle != 0, &h->tr_r, &h->tr_u, &h->tr_i, &h->tr_src)) != MASCOT_OK) return rc;
     {
         // test_set_preprocess (preprocess_utils.h:38-52) leaves the test set ordered by (user, item)
         std::vector<mascot_rating> t(test, test + n_test);
         std::stable_sort(t.begin(), t.end(), [](const mascot_rating& a, const mascot_rating& b) {
             return a.u != b.u ? a.u < b.u : a.i < b.i;
         });
-        if ((rc = upload_and_encode(h, t.data(), n_test, false, &h->te_r, &h->te_u, &h->te_i, nullptr)) != MASCOT_OK) return rc;
+        const std::vector<uint64_t> whole = {0, n_test};
+        if ((rc = upload_and_encode(h, t.data(), n_test, whole, false, &h->te_r, &h->te_u, &h->te_i, nullptr)) != MASCOT_OK) return rc;
     }
 
     // --- factor arenas and statistics ---
@@ -414,6 +446,7 @@ int mascot_reload_train(mascot_handle* h, const mascot_rating* train, uint64_t n
         CU(h, dev_alloc(&h->tr_r, n_train)); CU(h, dev_alloc(&h->tr_u, n_train)); CU(h, dev_alloc(&h->tr_i, n_train));
         if (n_train < (1ull << 32)) CU(h, dev_alloc(&h->tr_src, n_train));
         h->n_train = n_train;
+        h->seg_off.assign({0, n_train});           // a stream of another length is one segment
     }
     if (!n_train) return MASCOT_OK;
     const size_t bytes = sizeof(mascot_rating) * n_train;
@@ -423,8 +456,8 @@ int mascot_reload_train(mascot_handle* h, const mascot_rating* train, uint64_t n
         h->scratch_bytes = bytes;
     }
     CU(h, cudaMemcpyAsync(h->d_scratch, train, bytes, cudaMemcpyHostToDevice, h->stream));
-    CU(h, launch_encode_stream(h->d_scratch, n_train, h->cfg.shuffle != 0, h->cfg.seed, h->d_umap, h->d_imap,
-                               h->d_uprec_row, h->d_iprec_row, h->n_items, h->tr_r, h->tr_u, h->tr_i, h->tr_src, h->stream));
+    CU(h, encode_segments(h, static_cast<const mascot_rating*>(h->d_scratch), h->seg_off, h->cfg.shuffle != 0,
+                          h->tr_r, h->tr_u, h->tr_i, h->tr_src));
     CU(h, cudaStreamSynchronize(h->stream));
     return MASCOT_OK;
 }
@@ -473,109 +506,212 @@ int mascot_init_factors(mascot_handle* h) {
     return rc;
 }
 
+}  // extern "C"
+
+namespace {
+
+unsigned worker_count(const mascot_handle* h, uint64_t n) {
+    // -wg 0 = automatic: one worker per 8192 ratings keeps the sequential depth per worker - and with
+    // it the convergence per epoch - at the level of the reference's tuned runs; the launch caps the
+    // count at what the GPU can keep resident.
+    if (h->cfg.deterministic) return 1u;
+    if (h->cfg.num_workers) return h->cfg.num_workers;
+    return (unsigned)std::min<uint64_t>(std::max<uint64_t>(n / 8192, 512), 1u << 20);
+}
+
+SampleStats stats_view(mascot_handle* h) {
+    const int ug = (int)h->uend.size(), ig = (int)h->iend.size(), K = h->K;
+    SampleStats st;
+    st.ugroup = h->d_ugroup; st.igroup = h->d_igroup; st.ug = ug; st.ig = ig;
+    st.gsum_p = h->d_stats; st.gsum_q = st.gsum_p + (size_t)ug * K;
+    st.nsum_p = st.gsum_q + (size_t)ig * K; st.nsum_q = st.nsum_p + ug;
+    st.copies = h->stats_copies; st.copy_stride = h->stats_stride;
+    st.first_sample_pos = 0;
+    return st;
+}
+
+// Runs the update kernel over stream positions [begin, end).  With `collect`, the last
+// sample_ratio of the range (mf_methods.cu:102-103, 173-174) goes through the statistics kernel -
+// a second launch, so that only the sampled fraction pays for the statistics.
+int train_range(mascot_handle* h, float lr, uint64_t begin, uint64_t end, bool collect, LaunchShape* shape, uint32_t* launches) {
+    if (end <= begin) return MASCOT_OK;
+    const uint64_t n = end - begin;
+    bool any_f32 = false;
+    for (uint8_t p : h->uprec) any_f32 |= p != 0;
+    for (uint8_t p : h->iprec) any_f32 |= p != 0;
+    const unsigned workers = worker_count(h, n);
+    Stream s; s.r = h->tr_r + begin; s.u = h->tr_u + begin; s.i = h->tr_i + begin; s.n = n;
+    uint64_t head = n;
+    if (collect) {
+        const uint64_t sample_num = (uint64_t)((float)n * h->cfg.sample_ratio);
+        head = n - std::min<uint64_t>(sample_num, n);
+    }
+    if (head > 0) {
+        Stream sa = s; sa.n = head;
+        CU(h, launch_train(h->K, h->kind, sa, h->P, h->Q, lr, h->cfg.lambda, nullptr, any_f32, workers,
+                           h->d_work_counter, h->stream, shape));
+        (*launches)++;
+    }
+    if (head < n) {
+        Stream sb; sb.r = s.r + head; sb.u = s.u + head; sb.i = s.i + head; sb.n = n - head;
+        const SampleStats st = stats_view(h);
+        CU(h, launch_train(h->K, h->kind, sb, h->P, h->Q, lr, h->cfg.lambda, &st, any_f32, workers,
+                           h->d_work_counter, h->stream, shape));
+        (*launches)++;
+    }
+    return MASCOT_OK;
+}
+
+// Folds the private accumulator sets and brings the sums to the host in LOGICAL element order.
+int fetch_stats(mascot_handle* h, uint32_t* launches) {
+    const int ug = (int)h->uend.size(), ig = (int)h->iend.size(), K = h->K;
+    if (h->stats_copies > 1) {
+        CU(h, launch_reduce_stats(h->d_stats, h->stats_copies, h->stats_stride, stats_floats(h), h->stream));
+        if (launches) (*launches)++;
+    }
+    std::vector<float> raw(stats_floats(h));
+    CU(h, cudaMemcpyAsync(raw.data(), h->d_stats, sizeof(float) * raw.size(), cudaMemcpyDeviceToHost, h->stream));
+    CU(h, cudaStreamSynchronize(h->stream));
+    for (size_t g = 0; g < (size_t)(ug + ig); g++)
+        for (int p = 0; p < K; p++) h->h_stats[g * K + logical_of_phys(K, p)] = raw[g * K + p];
+    std::copy(raw.begin() + (size_t)(ug + ig) * K, raw.end(), h->h_stats.begin() + (size_t)(ug + ig) * K);
+    return MASCOT_OK;
+}
+
+// Group errors from the sums in h->h_stats and the switching that follows (mf_methods.cu:325-393,
+// precision_switching.h:8-51).
+int apply_stats(mascot_handle* h, uint32_t epoch, uint32_t* promoted_u, uint32_t* promoted_i, uint32_t* launches) {
+    const int ug = (int)h->uend.size(), ig = (int)h->iend.size(), K = h->K;
+    auto errors = [&](int groups, const float* gsum, const float* nsum, const std::vector<uint8_t>& prec,
+                      const std::vector<float>& initial, std::vector<float>& err) {
+        for (int g = 0; g < groups; g++) {
+            if (prec[g]) { err[g] = -1.f; continue; }
+            float num = 0.f;
+            for (int d = 0; d < K; d++) num += powf(gsum[(size_t)g * K + d], 2);
+            const float den = nsum[g];
+            err[g] = (num / den) / initial[g];
+        }
+    };
+    const float* gs_p = h->h_stats.data(); const float* gs_q = gs_p + (size_t)ug * K;
+    const float* ns_p = gs_q + (size_t)ig * K; const float* ns_q = ns_p + ug;
+    errors(ug, gs_p, ns_p, h->uprec, h->init_uerr, h->uerr);
+    errors(ig, gs_q, ns_q, h->iprec, h->init_ierr, h->ierr);
+    if (epoch == 5) { h->init_uerr = h->uerr; h->init_ierr = h->ierr; }   // mf_methods.cu:381-388
+    if (epoch > 5) {
+        int rc;
+        for (int side = 0; side < 2; side++) {
+            const bool users = side == 0;
+            const std::vector<uint8_t>& prec = users ? h->uprec : h->iprec;
+            const std::vector<float>& err = users ? h->uerr : h->ierr;
+            uint32_t& count = users ? *promoted_u : *promoted_i;
+            for (size_t g = 0; g < prec.size(); g++) {
+                if (!(err[g] > h->cfg.error_threshold) || prec[g]) continue;
+                if ((rc = promote_group(h, users, g)) != MASCOT_OK) return rc;
+                count++; if (launches) (*launches)++;
+            }
+            if (count) {
+                if ((rc = recode_side(h, users)) != MASCOT_OK) return rc;
+                if (launches) (*launches) += 2;
+            }
+        }
+    }
+    return MASCOT_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int mascot_is_check_epoch(const mascot_handle* h, uint32_t epoch) {
+    return (h && h->grouped && is_check_epoch(h->cfg, epoch)) ? 1 : 0;
+}
+
+int mascot_stats_begin(mascot_handle* h) {
+    if (!h) return MASCOT_ERR_BAD_ARG;
+    if (!h->have_ratings) return fail(h, MASCOT_ERR_STATE, "mascot_set_ratings must come first");
+    CU(h, cudaSetDevice(h->cfg.device));
+    CU(h, cudaMemsetAsync(h->d_stats, 0, sizeof(float) * h->stats_stride * h->stats_copies, h->stream));   // mf_methods.cu:178-182
+    return MASCOT_OK;
+}
+
+int mascot_train_segment(mascot_handle* h, uint32_t epoch, uint32_t segment, uint32_t collect_stats, mascot_epoch_stats* out) {
+    if (!h) return MASCOT_ERR_BAD_ARG;
+    if (!h->have_ratings || !h->have_factors) return fail(h, MASCOT_ERR_STATE, "ratings and factors must be set before training");
+    if (segment + 1 >= h->seg_off.size()) return fail(h, MASCOT_ERR_BAD_ARG, "segment index out of range");
+    CU(h, cudaSetDevice(h->cfg.device));
+    const float lr = epoch < h->lr.size() ? h->lr[epoch] : lr_at(h->cfg, epoch);
+    LaunchShape shape; uint32_t launches = 0;
+    CU(h, cudaEventRecord(h->ev[0], h->stream));
+    const int rc = train_range(h, lr, h->seg_off[segment], h->seg_off[segment + 1], collect_stats && h->grouped, &shape, &launches);
+    if (rc != MASCOT_OK) return rc;
+    CU(h, cudaEventRecord(h->ev[3], h->stream));
+    if (out) {
+        CU(h, cudaEventSynchronize(h->ev[3]));
+        std::memset(out, 0, sizeof(*out));
+        out->updates = h->seg_off[segment + 1] - h->seg_off[segment]; out->lr = lr; out->kernel_launches = launches;
+        out->workers = shape.workers; out->error_check = (collect_stats && h->grouped) ? 1 : 0;
+        cudaEventElapsedTime(&out->kernel_ms, h->ev[0], h->ev[3]);
+        out->total_ms = out->kernel_ms;
+    }
+    return MASCOT_OK;
+}
+
+int mascot_stats_fetch(mascot_handle* h, float* grad_sum_p, float* grad_sum_q, float* norm_sum_p, float* norm_sum_q) {
+    if (!h) return MASCOT_ERR_BAD_ARG;
+    if (!h->have_ratings) return fail(h, MASCOT_ERR_STATE, "mascot_set_ratings must come first");
+    CU(h, cudaSetDevice(h->cfg.device));
+    const int rc = fetch_stats(h, nullptr);
+    if (rc != MASCOT_OK) return rc;
+    return mascot_get_sample_stats(h, grad_sum_p, grad_sum_q, norm_sum_p, norm_sum_q);
+}
+
+int mascot_stats_apply(mascot_handle* h, uint32_t epoch, const float* grad_sum_p, const float* grad_sum_q,
+                       const float* norm_sum_p, const float* norm_sum_q, uint32_t* promoted_user_groups, uint32_t* promoted_item_groups) {
+    if (!h || !grad_sum_p || !grad_sum_q || !norm_sum_p || !norm_sum_q) return MASCOT_ERR_BAD_ARG;
+    if (!h->have_ratings || !h->have_factors) return fail(h, MASCOT_ERR_STATE, "ratings and factors must be set first");
+    CU(h, cudaSetDevice(h->cfg.device));
+    const size_t ug = h->uend.size(), ig = h->iend.size(), K = h->K;
+    float* s = h->h_stats.data();
+    std::copy(grad_sum_p, grad_sum_p + ug * K, s);
+    std::copy(grad_sum_q, grad_sum_q + ig * K, s + ug * K);
+    std::copy(norm_sum_p, norm_sum_p + ug, s + (ug + ig) * K);
+    std::copy(norm_sum_q, norm_sum_q + ig, s + (ug + ig) * K + ug);
+    uint32_t pu = 0, pi = 0;
+    const int rc = apply_stats(h, epoch, &pu, &pi, nullptr);
+    if (rc != MASCOT_OK) return rc;
+    CU(h, cudaStreamSynchronize(h->stream));
+    if (promoted_user_groups) *promoted_user_groups = pu;
+    if (promoted_item_groups) *promoted_item_groups = pi;
+    return MASCOT_OK;
+}
+
 int mascot_train_epoch(mascot_handle* h, uint32_t epoch, mascot_epoch_stats* out) {
     if (!h) return MASCOT_ERR_BAD_ARG;
     if (!h->have_ratings || !h->have_factors) return fail(h, MASCOT_ERR_STATE, "ratings and factors must be set before training");
     CU(h, cudaSetDevice(h->cfg.device));
     const float lr = epoch < h->lr.size() ? h->lr[epoch] : lr_at(h->cfg, epoch);
     const bool check = h->grouped && is_check_epoch(h->cfg, epoch);
-    const int ug = (int)h->uend.size(), ig = (int)h->iend.size(), K = h->K;
     uint32_t launches = 0, promoted_u = 0, promoted_i = 0;
-
-    Stream s; s.r = h->tr_r; s.u = h->tr_u; s.i = h->tr_i; s.n = h->n_train;
-    SampleStats st;
-    if (check) {
-        // sampled tail of the epoch (mf_methods.cu:102-103, 173-174)
-        const uint64_t sample_num = (uint64_t)((float)h->n_train * h->cfg.sample_ratio);
-        st.first_sample_pos = h->n_train - std::min<uint64_t>(sample_num, h->n_train);
-        st.ugroup = h->d_ugroup; st.igroup = h->d_igroup; st.ug = ug; st.ig = ig;
-        st.gsum_p = h->d_stats; st.gsum_q = st.gsum_p + (size_t)ug * K;
-        st.nsum_p = st.gsum_q + (size_t)ig * K; st.nsum_q = st.nsum_p + ug;
-        st.copies = h->stats_copies; st.copy_stride = h->stats_stride;
-    }
     const uint64_t bytes_this_epoch = algorithmic_bytes(h);    // with the precisions the kernel is about to see
     CU(h, cudaEventRecord(h->ev[0], h->stream));
     if (check) CU(h, cudaMemsetAsync(h->d_stats, 0, sizeof(float) * h->stats_stride * h->stats_copies, h->stream));   // mf_methods.cu:178-182
     CU(h, cudaEventRecord(h->ev[1], h->stream));
     LaunchShape shape;
-    // -wg 0 = automatic: one worker per 8192 ratings of the epoch keeps the sequential depth per
-    // worker - and with it the convergence per epoch - at the level of the reference's tuned runs;
-    // the launch caps the count at what the GPU can keep resident.
-    unsigned workers = h->cfg.num_workers;
-    if (h->cfg.deterministic) workers = 1u;
-    else if (workers == 0) workers = (unsigned)std::min<uint64_t>(std::max<uint64_t>(h->n_train / 8192, 512), 1u << 20);
-    bool any_f32 = false;
-    for (uint8_t p : h->uprec) any_f32 |= p != 0;
-    for (uint8_t p : h->iprec) any_f32 |= p != 0;
-    if (!check) {
-        CU(h, launch_train(K, h->kind, s, h->P, h->Q, lr, h->cfg.lambda, nullptr, any_f32, workers,
-                           h->d_work_counter, h->stream, &shape));
-    } else {
-        // Check epoch: the stream up to the sampled tail runs through the plain kernel, the tail
-        // through the statistics-collecting one, so only the sampled fraction pays for the statistics.
-        const uint64_t head = st.first_sample_pos;
-        if (head > 0) {
-            Stream sa = s; sa.n = head;
-            CU(h, launch_train(K, h->kind, sa, h->P, h->Q, lr, h->cfg.lambda, nullptr, any_f32, workers,
-                               h->d_work_counter, h->stream, &shape));
-            launches++;
-        }
-        Stream sb; sb.r = s.r + head; sb.u = s.u + head; sb.i = s.i + head; sb.n = s.n - head;
-        st.first_sample_pos = 0;
-        CU(h, launch_train(K, h->kind, sb, h->P, h->Q, lr, h->cfg.lambda, &st, any_f32, workers,
-                           h->d_work_counter, h->stream, &shape));
-    }
-    launches++;
+    int rc;
+    for (size_t sgm = 0; sgm + 1 < h->seg_off.size(); sgm++)
+        if ((rc = train_range(h, lr, h->seg_off[sgm], h->seg_off[sgm + 1], check, &shape, &launches)) != MASCOT_OK) return rc;
     if (check && h->stats_copies > 1) {
         CU(h, launch_reduce_stats(h->d_stats, h->stats_copies, h->stats_stride, stats_floats(h), h->stream));
         launches++;
     }
     CU(h, cudaEventRecord(h->ev[2], h->stream));
-
     if (check) {
-        std::vector<float> raw(stats_floats(h));
-        CU(h, cudaMemcpyAsync(raw.data(), h->d_stats, sizeof(float) * raw.size(), cudaMemcpyDeviceToHost, h->stream));
-        CU(h, cudaStreamSynchronize(h->stream));
-        // gradient sums come back in physical element order; the host loop below adds squares in
-        // the reference's logical order
-        for (size_t g = 0; g < (size_t)(ug + ig); g++)
-            for (int p = 0; p < K; p++) h->h_stats[g * K + logical_of_phys(K, p)] = raw[g * K + p];
-        std::copy(raw.begin() + (size_t)(ug + ig) * K, raw.end(), h->h_stats.begin() + (size_t)(ug + ig) * K);
-        // mf_methods.cu:325-379
-        auto errors = [&](int groups, const float* gsum, const float* nsum, const std::vector<uint8_t>& prec,
-                          const std::vector<float>& initial, std::vector<float>& err) {
-            for (int g = 0; g < groups; g++) {
-                if (prec[g]) { err[g] = -1.f; continue; }
-                float num = 0.f;
-                for (int d = 0; d < K; d++) num += powf(gsum[(size_t)g * K + d], 2);
-                const float den = nsum[g];
-                err[g] = (num / den) / initial[g];
-            }
-        };
-        const float* gs_p = h->h_stats.data(); const float* gs_q = gs_p + (size_t)ug * K;
-        const float* ns_p = gs_q + (size_t)ig * K; const float* ns_q = ns_p + ug;
-        errors(ug, gs_p, ns_p, h->uprec, h->init_uerr, h->uerr);
-        errors(ig, gs_q, ns_q, h->iprec, h->init_ierr, h->ierr);
-        if (epoch == 5) { h->init_uerr = h->uerr; h->init_ierr = h->ierr; }   // mf_methods.cu:381-388
-        if (epoch > 5) {
-            // precision_switching_by_groups_grad_diversity (precision_switching.h:8-51), one way fp16 -> fp32
-            int rc;
-            for (int side = 0; side < 2; side++) {
-                const bool users = side == 0;
-                const std::vector<uint8_t>& prec = users ? h->uprec : h->iprec;
-                const std::vector<float>& err = users ? h->uerr : h->ierr;
-                uint32_t& count = users ? promoted_u : promoted_i;
-                for (size_t g = 0; g < prec.size(); g++) {
-                    if (!(err[g] > h->cfg.error_threshold) || prec[g]) continue;
-                    if ((rc = promote_group(h, users, g)) != MASCOT_OK) return rc;
-                    count++; launches++;
-                }
-                if (count) {
-                    if ((rc = recode_side(h, users)) != MASCOT_OK) return rc;
-                    launches += 2;
-                }
-            }
-        }
+        const int saved = h->stats_copies;
+        h->stats_copies = 1;                      // already folded above, inside the timed kernel span
+        rc = fetch_stats(h, nullptr);
+        h->stats_copies = saved;
+        if (rc != MASCOT_OK) return rc;
+        if ((rc = apply_stats(h, epoch, &promoted_u, &promoted_i, &launches)) != MASCOT_OK) return rc;
     }
     CU(h, cudaEventRecord(h->ev[3], h->stream));
     CU(h, cudaEventSynchronize(h->ev[3]));
@@ -588,6 +724,42 @@ int mascot_train_epoch(mascot_handle* h, uint32_t epoch, mascot_epoch_stats* out
         cudaEventElapsedTime(&out->kernel_ms, h->ev[1], h->ev[2]);
         cudaEventElapsedTime(&out->total_ms, h->ev[0], h->ev[3]);
     }
+    return MASCOT_OK;
+}
+
+int mascot_item_rows(mascot_handle* h, uint32_t row_begin, uint32_t row_end, void** f16_ptr, uint64_t* f16_bytes,
+                     void** f32_ptr, uint64_t* f32_bytes) {
+    if (!h || row_end < row_begin) return MASCOT_ERR_BAD_ARG;
+    if (!h->have_ratings) return fail(h, MASCOT_ERR_STATE, "mascot_set_ratings must come first");
+    if (row_end > h->n_items) return fail(h, MASCOT_ERR_BAD_ARG, "item row range out of bounds");
+    const size_t b = (size_t)row_begin * h->K, n = (size_t)(row_end - row_begin) * h->K;
+    if (f16_ptr) *f16_ptr = h->Q.f16 ? (void*)(h->Q.f16 + b) : nullptr;
+    if (f16_bytes) *f16_bytes = h->Q.f16 ? n * sizeof(__half) : 0;
+    if (f32_ptr) *f32_ptr = h->Q.f32 ? (void*)(h->Q.f32 + b) : nullptr;
+    if (f32_bytes) *f32_bytes = h->Q.f32 ? n * sizeof(float) : 0;
+    return MASCOT_OK;
+}
+
+int mascot_sync(mascot_handle* h) {
+    if (!h) return MASCOT_ERR_BAD_ARG;
+    CU(h, cudaSetDevice(h->cfg.device));
+    CU(h, cudaStreamSynchronize(h->stream));
+    return MASCOT_OK;
+}
+
+int mascot_eval_sq_error(mascot_handle* h, double* sum_sq, uint64_t* count) {
+    if (!h || !sum_sq || !count) return MASCOT_ERR_BAD_ARG;
+    if (!h->have_ratings || !h->have_factors) return fail(h, MASCOT_ERR_STATE, "ratings and factors must be set before evaluation");
+    *sum_sq = 0; *count = h->n_test;
+    if (!h->n_test) return MASCOT_OK;
+    CU(h, cudaSetDevice(h->cfg.device));
+    Stream t; t.r = h->te_r; t.u = h->te_u; t.i = h->te_i; t.n = h->n_test;
+    CU(h, launch_rmse(h->K, t, h->P, h->Q, h->d_block_err, h->stream));
+    CU(h, cudaMemcpyAsync(h->h_block_err.data(), h->d_block_err, sizeof(float) * h->h_block_err.size(), cudaMemcpyDeviceToHost, h->stream));
+    CU(h, cudaStreamSynchronize(h->stream));
+    double s = 0;
+    for (float v : h->h_block_err) s += (double)v;
+    *sum_sq = s;
     return MASCOT_OK;
 }
 

@@ -27,7 +27,7 @@ inline int grid_for(uint64_t n, int block) {
 __global__ void encode_kernel(const NodeAos* src, uint64_t n, int shuffle, uint64_t seed,
                               const uint32_t* umap, const uint32_t* imap,
                               const uint8_t* uprec, const uint8_t* iprec,
-                              float* r, uint32_t* u, uint32_t* i, uint32_t* src_out) {
+                              float* r, uint32_t* u, uint32_t* i, uint32_t* src_out, uint32_t src_base) {
     for (uint64_t j = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; j < n; j += (uint64_t)gridDim.x * blockDim.x) {
         const uint64_t s = shuffle ? permute_index(j, n, seed) : j;
         const NodeAos nd = src[s];
@@ -36,7 +36,7 @@ __global__ void encode_kernel(const NodeAos* src, uint64_t n, int shuffle, uint6
         if (uprec[uu]) uu |= kPrecBit;
         if (iprec[ii]) ii |= kPrecBit;
         r[j] = nd.r; u[j] = uu; i[j] = ii;
-        if (src_out) src_out[j] = (uint32_t)s;
+        if (src_out) src_out[j] = src_base + (uint32_t)s;
     }
 }
 
@@ -54,7 +54,7 @@ constexpr int kWindow = kSortThreads * kSortItemsPerThread;
 __global__ void __launch_bounds__(kSortThreads) encode_sorted_kernel(
         const NodeAos* src, uint64_t n, uint64_t seed, const uint32_t* umap, const uint32_t* imap,
         const uint8_t* uprec, const uint8_t* iprec, int key_bits,
-        float* r, uint32_t* u, uint32_t* i, uint32_t* src_out) {
+        float* r, uint32_t* u, uint32_t* i, uint32_t* src_out, uint32_t src_base) {
     typedef cub::BlockRadixSort<uint32_t, kSortThreads, kSortItemsPerThread, uint32_t> Sort;
     __shared__ typename Sort::TempStorage temp;
     const uint64_t windows = (n + kWindow - 1) / kWindow;
@@ -86,7 +86,7 @@ __global__ void __launch_bounds__(kSortThreads) encode_sorted_kernel(
                 if (uprec[uu]) uu |= kPrecBit;
                 if (iprec[ii]) ii |= kPrecBit;
                 r[out] = nd.r; u[out] = uu; i[out] = ii;
-                if (src_out) src_out[out] = (uint32_t)s;
+                if (src_out) src_out[out] = src_base + (uint32_t)s;
             }
         }
     }
@@ -161,7 +161,8 @@ __global__ void init_normal_kernel(float* dst, uint64_t count, uint64_t seed, ui
 cudaError_t launch_encode_stream(const void* d_src_aos, uint64_t n, bool shuffle, uint64_t seed,
                                  const uint32_t* user_map, const uint32_t* item_map,
                                  const uint8_t* uprec_row, const uint8_t* iprec_row, uint32_t n_items,
-                                 float* r, uint32_t* u, uint32_t* i, uint32_t* src_out, cudaStream_t st) {
+                                 float* r, uint32_t* u, uint32_t* i, uint32_t* src_out, uint32_t src_base,
+                                 cudaStream_t st) {
     if (n == 0) return cudaSuccess;
     const NodeAos* src = static_cast<const NodeAos*>(d_src_aos);
     if (shuffle) {
@@ -170,10 +171,10 @@ cudaError_t launch_encode_stream(const void* d_src_aos, uint64_t n, bool shuffle
         const uint64_t windows = (n + kWindow - 1) / kWindow;
         const int grid = (int)(windows < 148 * 8 ? windows : 148 * 8);
         encode_sorted_kernel<<<grid, kSortThreads, 0, st>>>(src, n, seed, user_map, item_map, uprec_row, iprec_row,
-                                                             key_bits, r, u, i, src_out);
+                                                             key_bits, r, u, i, src_out, src_base);
     } else {
         encode_kernel<<<grid_for(n, 256), 256, 0, st>>>(src, n, 0, seed, user_map, item_map, uprec_row, iprec_row,
-                                                         r, u, i, src_out);
+                                                         r, u, i, src_out, src_base);
     }
     return cudaGetLastError();
 }

@@ -24,6 +24,8 @@ EXPORTS = [
     "mascot_set_ratings", "mascot_init_factors", "mascot_set_factors", "mascot_train_epoch", "mascot_eval_rmse",
     "mascot_get_factors", "mascot_get_group_info", "mascot_get_index_maps", "mascot_get_sample_stats",
     "mascot_get_test_ratings", "mascot_promote_group", "mascot_reload_train", "mascot_stream_source_index", "mascot_get_stream_order", "mascot_rmse_host", "mascot_rmse_device", "mascot_rmse_device_noalloc",
+    "mascot_set_ratings_sharded", "mascot_is_check_epoch", "mascot_stats_begin", "mascot_train_segment", "mascot_stats_fetch",
+    "mascot_stats_apply", "mascot_item_rows", "mascot_sync", "mascot_eval_sq_error",
 ]
 
 
@@ -147,6 +149,55 @@ class Engine:
         self._check(self._lib.mascot_set_ratings(self._h, C.c_void_p(train_ptr), C.c_uint64(n_train), C.c_void_p(test_ptr),
                                                  C.c_uint64(n_test), C.c_uint32(n_users), C.c_uint32(n_items)))
         self.n_users, self.n_items, self.n_train, self.n_test = n_users, n_items, n_train, n_test
+
+    # ---- sharded training building blocks ----
+    def set_ratings_sharded(self, train, segment_offsets, test, n_users, n_items, user_degree=None, item_degree=None):
+        train, test = as_ratings(train), as_ratings(test)
+        seg = np.ascontiguousarray(segment_offsets, np.uint64)
+        ud = None if user_degree is None else np.ascontiguousarray(user_degree, np.uint32)
+        idg = None if item_degree is None else np.ascontiguousarray(item_degree, np.uint32)
+        self._check(self._lib.mascot_set_ratings_sharded(self._h, _ptr(train), C.c_uint64(train.size), _ptr(seg), C.c_uint32(seg.size - 1),
+                                                         _ptr(test), C.c_uint64(test.size), C.c_uint32(n_users), C.c_uint32(n_items),
+                                                         _ptr(ud), _ptr(idg)))
+        self.n_users, self.n_items, self.n_train, self.n_test = n_users, n_items, train.size, test.size
+
+    def is_check_epoch(self, epoch):
+        return bool(self._lib.mascot_is_check_epoch(self._h, C.c_uint32(epoch)))
+
+    def stats_begin(self):
+        self._check(self._lib.mascot_stats_begin(self._h))
+
+    def train_segment(self, epoch, segment, collect_stats=False, wait=True):
+        st = EpochStats() if wait else None
+        self._check(self._lib.mascot_train_segment(self._h, C.c_uint32(epoch), C.c_uint32(segment), C.c_uint32(1 if collect_stats else 0),
+                                                   C.byref(st) if wait else None))
+        return st
+
+    def stats_fetch(self):
+        ug, ig = len(self.group_info(0)[0]), len(self.group_info(1)[0])
+        out = [np.empty(ug * self.k, np.float32), np.empty(ig * self.k, np.float32), np.empty(ug, np.float32), np.empty(ig, np.float32)]
+        self._check(self._lib.mascot_stats_fetch(self._h, *[_ptr(a) for a in out]))
+        return out
+
+    def stats_apply(self, epoch, gsum_p, gsum_q, nsum_p, nsum_q):
+        arrs = [np.ascontiguousarray(a, np.float32) for a in (gsum_p, gsum_q, nsum_p, nsum_q)]
+        pu, pi = C.c_uint32(), C.c_uint32()
+        self._check(self._lib.mascot_stats_apply(self._h, C.c_uint32(epoch), *[_ptr(a) for a in arrs], C.byref(pu), C.byref(pi)))
+        return pu.value, pi.value
+
+    def item_rows(self, row_begin, row_end):
+        p16, b16, p32, b32 = C.c_void_p(), C.c_uint64(), C.c_void_p(), C.c_uint64()
+        self._check(self._lib.mascot_item_rows(self._h, C.c_uint32(row_begin), C.c_uint32(row_end), C.byref(p16), C.byref(b16),
+                                               C.byref(p32), C.byref(b32)))
+        return (p16.value or 0, b16.value), (p32.value or 0, b32.value)
+
+    def sync(self):
+        self._check(self._lib.mascot_sync(self._h))
+
+    def eval_sq_error(self):
+        s, n = C.c_double(), C.c_uint64()
+        self._check(self._lib.mascot_eval_sq_error(self._h, C.byref(s), C.byref(n)))
+        return s.value, n.value
 
     def reload_train_raw(self, train_ptr, n_train):
         """Replace the training stream from a raw host address (the per-step input path)."""

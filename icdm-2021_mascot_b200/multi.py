@@ -1,0 +1,186 @@
+"""Sharded (multi-GPU) training on top of the libmascot building blocks: one process per GPU.
+
+Scheme (the reference is single-GPU; this has no counterpart there): the users are dealt to the
+ranks so that every rank gets the same mix of degrees, and with them their ratings and their rows of
+P; the items - in the engine's degree-sorted index space - are cut into `world` contiguous blocks of
+about equal rating count.  Sub-epoch s: rank g trains its ratings that fall into item block
+(g + s) mod world, then hands that block of Q to rank g-1 and receives block (g + s + 1) mod world
+from rank g+1.  At any time the ranks work on disjoint users AND disjoint items, so there are no
+races between GPUs, and after `world` sub-epochs every block is back home.  The only data-path
+communication is that block hand-over (point-to-point, NCCL send/recv through torch.distributed on
+GPUs); the small g-switching statistics and the RMSE partial sums are all-reduced.
+
+The schedule and the exchange are written against a tiny shard interface, so the same code drives
+libmascot engines on GPUs and a CPU stand-in in the tests.
+"""
+import numpy as np
+
+
+class Plan:
+    """Who owns which user, which item block an item belongs to, and the row range of each block."""
+
+    def __init__(self, world, user_rank, item_block, block_rows, user_degree, item_degree, item_sorted_index):
+        self.world = world
+        self.user_rank = user_rank                # [n_users] compact id -> rank
+        self.item_block = item_block              # [n_items] compact id -> block
+        self.block_rows = block_rows              # [(row_begin, row_end)] in item sorted-index space
+        self.user_degree = user_degree
+        self.item_degree = item_degree
+        self.item_sorted_index = item_sorted_index
+
+
+def make_plan(train_u, train_i, n_users, n_items, world):
+    """Degree tables of the whole training set, user dealing and item blocks."""
+    user_degree = np.bincount(train_u, minlength=n_users).astype(np.uint32)
+    item_degree = np.bincount(train_i, minlength=n_items).astype(np.uint32)
+    # same order as the engine's set-up: ascending degree, ties by ascending id
+    user_sorted = np.argsort(user_degree, kind="stable")
+    item_sorted = np.argsort(item_degree, kind="stable")
+    # deal the users out from the heaviest down, reversing direction every round (snake order), so
+    # that the rating counts of the ranks stay close even for heavy-tailed degrees
+    pos = np.arange(n_users)
+    rnd, idx = pos // world, pos % world
+    user_rank = np.empty(n_users, np.int32)
+    user_rank[user_sorted[::-1]] = np.where(rnd % 2 == 0, idx, world - 1 - idx)
+    item_sorted_index = np.empty(n_items, np.uint32)
+    item_sorted_index[item_sorted] = np.arange(n_items, dtype=np.uint32)
+    # contiguous blocks of about equal rating count (an item is never split)
+    cum = np.cumsum(item_degree[item_sorted].astype(np.int64))
+    total = int(cum[-1]) if n_items else 0
+    bounds = [0]
+    for b in range(1, world):
+        cut = int(np.searchsorted(cum, total * b / world, side="left")) + 1
+        bounds.append(min(max(cut, bounds[-1]), n_items))
+    bounds.append(n_items)
+    block_rows = [(bounds[b], bounds[b + 1]) for b in range(world)]
+    block_of_row = np.zeros(n_items, np.int32)
+    for b, (lo, hi) in enumerate(block_rows):
+        block_of_row[lo:hi] = b
+    item_block = block_of_row[item_sorted_index]
+    return Plan(world, user_rank, item_block, block_rows, user_degree, item_degree, item_sorted_index)
+
+
+def shard_ratings(plan, rank, train, test):
+    """The ratings of this rank's users, ordered into one segment per item block."""
+    mine = train[plan.user_rank[train["u"]] == rank]
+    blk = plan.item_block[mine["i"]]
+    order = np.argsort(blk, kind="stable")
+    mine = np.ascontiguousarray(mine[order])
+    counts = np.bincount(blk, minlength=plan.world)
+    seg = np.zeros(plan.world + 1, np.uint64)
+    seg[1:] = np.cumsum(counts)
+    my_test = np.ascontiguousarray(test[plan.user_rank[test["u"]] == rank])
+    return mine, seg, my_test
+
+
+def exchange_block(dist, shard, send_block, recv_block, dst, src):
+    """Hand `send_block` to rank dst and take `recv_block` from rank src (in place, both arenas)."""
+    if send_block == recv_block and dst == src:
+        return 0
+    ops, nbytes = [], 0
+    for t in shard.block_tensors(send_block):
+        ops.append(dist.P2POp(dist.isend, t, dst))
+        nbytes += t.numel() * t.element_size()
+    for t in shard.block_tensors(recv_block):
+        ops.append(dist.P2POp(dist.irecv, t, src))
+    for req in dist.batch_isend_irecv(ops):
+        req.wait()
+    return nbytes
+
+
+def train_epoch(dist, shard, rank, world, epoch, comm_device="cpu"):
+    """One epoch = `world` sub-epochs with a block rotation after each.  Returns bytes sent."""
+    import torch
+    check = shard.is_check_epoch(epoch)
+    if check:
+        shard.stats_begin()
+    sent = 0
+    for s in range(world):
+        b = (rank + s) % world
+        shard.train_segment(epoch, b, collect_stats=check)
+        shard.sync()
+        if world > 1:
+            sent += exchange_block(dist, shard, b, (rank + s + 1) % world, (rank - 1) % world, (rank + 1) % world)
+    promoted = (0, 0)
+    if check:
+        sums = [torch.from_numpy(a).to(comm_device) for a in shard.stats_fetch()]
+        if world > 1:
+            for t in sums:
+                dist.all_reduce(t)
+        promoted = shard.stats_apply(epoch, *[t.cpu().numpy() for t in sums])
+    return sent, promoted
+
+
+def gather_item_factors(dist, shard, world):
+    """After an epoch every rank holds only its home block fresh; make all of Q fresh everywhere."""
+    if world == 1:
+        return
+    for b in range(world):
+        for t in shard.block_tensors(b):
+            dist.broadcast(t, src=b)
+
+
+def global_rmse(dist, shard, world, comm_device="cpu"):
+    import torch
+    s, n = shard.eval_sq_error()
+    t = torch.tensor([s, float(n)], dtype=torch.float64, device=comm_device)
+    if world > 1:
+        dist.all_reduce(t)
+    return float(torch.sqrt(t[0] / t[1]).item()) if t[1] > 0 else float("nan")
+
+
+class _DeviceBytes:
+    """Raw device memory exposed through the CUDA array interface, so torch can wrap it without a copy."""
+
+    def __init__(self, ptr, nbytes):
+        self.__cuda_array_interface__ = {"shape": (int(nbytes),), "typestr": "|u1", "data": (int(ptr), False), "version": 2}
+
+
+class EngineShard:
+    """A libmascot engine holding one rank's shard."""
+
+    def __init__(self, M, cfg, plan, rank, train, test, n_users, n_items):
+        import torch
+        self.M, self.plan, self.rank = M, plan, rank
+        mine, seg, my_test = shard_ratings(plan, rank, train, test)
+        self.n_local = int(mine.size)
+        self.engine = M.Engine(cfg)
+        self.engine.set_ratings_sharded(mine, seg, my_test, n_users, n_items, plan.user_degree, plan.item_degree)
+        self.device = torch.device("cuda", int(cfg.device))
+        self._views = {}
+
+    def block_tensors(self, b):
+        import torch
+        if b not in self._views:
+            lo, hi = self.plan.block_rows[b]
+            views = []
+            for ptr, nbytes in self.engine.item_rows(lo, hi):
+                if ptr and nbytes:
+                    views.append(torch.as_tensor(_DeviceBytes(ptr, nbytes), device=self.device))
+            self._views[b] = views
+        return self._views[b]
+
+    def is_check_epoch(self, epoch):
+        return self.engine.is_check_epoch(epoch)
+
+    def stats_begin(self):
+        self.engine.stats_begin()
+
+    def train_segment(self, epoch, b, collect_stats=False):
+        self.engine.train_segment(epoch, b, collect_stats, wait=False)
+
+    def sync(self):
+        self.engine.sync()
+
+    def stats_fetch(self):
+        return self.engine.stats_fetch()
+
+    def stats_apply(self, epoch, *sums):
+        return self.engine.stats_apply(epoch, *sums)
+
+    def eval_sq_error(self):
+        return self.engine.eval_sq_error()
+
+    def close(self):
+        self._views.clear()
+        self.engine.close()

@@ -194,6 +194,46 @@ MASCOT_API int mascot_stream_source_index(const mascot_handle* h, uint64_t pos, 
 /* The whole order at once: src_out[pos] for pos in [0, n_train). */
 MASCOT_API int mascot_get_stream_order(mascot_handle* h, uint32_t* src_out);
 
+/* ---- building blocks for sharded (multi-GPU) training; no counterpart in the reference, which is
+ * single-GPU.  One engine per GPU holds the ratings of its own users, cut into segments by item
+ * block; the host (one process per GPU) trains a segment, passes that item block on to the next
+ * GPU and receives the following one, so that no two GPUs ever update the same row at once.  Every
+ * engine keeps full-size arenas in the same global index space, so a block is the same row range
+ * on every GPU and "passing it on" is a plain copy of that range. ---- */
+
+/* Like mascot_set_ratings, with the training ratings already ordered into `n_segments` consecutive
+ * segments (segment_offsets has n_segments + 1 entries, from 0 to n_train; NULL with n_segments == 1)
+ * and, optionally, the degrees of every user and item in the WHOLE data set, so that all shards
+ * build identical sorted-index spaces and groups.  The seeded permutation and the item-sorted
+ * windows stay inside a segment. */
+MASCOT_API int mascot_set_ratings_sharded(mascot_handle* h, const mascot_rating* train, uint64_t n_train,
+                               const uint64_t* segment_offsets, uint32_t n_segments,
+                               const mascot_rating* test, uint64_t n_test, uint32_t n_users, uint32_t n_items,
+                               const uint32_t* user_degree, const uint32_t* item_degree);
+/* 1 when `epoch` computes group errors (mf_methods.cu:168-175), else 0. */
+MASCOT_API int mascot_is_check_epoch(const mascot_handle* h, uint32_t epoch);
+/* Zero the statistic accumulators (start of a check epoch). */
+MASCOT_API int mascot_stats_begin(mascot_handle* h);
+/* Train one segment with lr_schedule[epoch]; with collect_stats != 0 the last sample_ratio of the
+ * segment adds to the statistic accumulators.  With stats == NULL the call does not wait for the
+ * kernel (use mascot_sync), so copies on other streams can overlap it. */
+MASCOT_API int mascot_train_segment(mascot_handle* h, uint32_t epoch, uint32_t segment, uint32_t collect_stats,
+                                    mascot_epoch_stats* stats);
+/* The accumulated sums of this engine, layout as in mascot_get_sample_stats. */
+MASCOT_API int mascot_stats_fetch(mascot_handle* h, float* grad_sum_p, float* grad_sum_q, float* norm_sum_p, float* norm_sum_q);
+/* Group errors and precision switching from sums the caller provides (e.g. summed over all shards). */
+MASCOT_API int mascot_stats_apply(mascot_handle* h, uint32_t epoch, const float* grad_sum_p, const float* grad_sum_q,
+                       const float* norm_sum_p, const float* norm_sum_q,
+                       uint32_t* promoted_user_groups, uint32_t* promoted_item_groups);
+/* Device addresses and byte sizes of the item rows [row_begin, row_end) (sorted-index space) in the
+ * binary16 and the fp32 arena (NULL / 0 for an arena the variant does not keep). */
+MASCOT_API int mascot_item_rows(mascot_handle* h, uint32_t row_begin, uint32_t row_end, void** f16_ptr, uint64_t* f16_bytes,
+                     void** f32_ptr, uint64_t* f32_bytes);
+/* Wait for everything queued on the engine's stream. */
+MASCOT_API int mascot_sync(mascot_handle* h);
+/* Sum of squared test errors and number of test ratings of this engine (for an RMSE over shards). */
+MASCOT_API int mascot_eval_sq_error(mascot_handle* h, double* sum_sq, uint64_t* count);
+
 /* ---- handle-free evaluation: the `gpu_test_rmse` used by test_mf (test_mf/test.cu:56-72) ---- */
 
 /* Host buffers in, RMSE out: fp32 P [n_users][k], Q [n_items][k], test ratings with plain row

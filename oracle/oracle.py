@@ -190,13 +190,16 @@ class MascotModel:
         Q = np.where(self.iprec_row[:, None] == 1, self.Q32, h2f(self.Q16))
         return P.astype(np.float32), Q.astype(np.float32)
 
-    def run(self, R, seq, lr, lam, rules, first_sample_pos=None, stats=False, item_stats_by_run=False):
+    def run(self, R, seq, lr, lam, rules, first_sample_pos=None, stats=False, item_stats_by_run=False, into=None):
+        """`into`: four existing statistic arrays to keep accumulating into (instead of fresh zeros)."""
         R = as_nodes(R)
         seq = _seq(seq)
         nseq = seq.size if seq is not None else R.size
         k = self.k
         ug, ig = len(self.uprec), len(self.iprec)
-        if stats:
+        if stats and into is not None:
+            gp, gq, np_, nq = into
+        elif stats:
             gp, gq = np.zeros(ug * k, np.float32), np.zeros(ig * k, np.float32)
             np_, nq = np.zeros(ug, np.float32), np.zeros(ig, np.float32)
         else:

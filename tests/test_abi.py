@@ -17,7 +17,7 @@ def declared_symbols():
 
 def test_header_declares_the_expected_surface():
     names = declared_symbols()
-    assert len(names) == len(set(names)) and len(names) >= 23
+    assert len(names) == len(set(names)) and len(names) >= 32
     for must in ("mascot_create", "mascot_set_ratings", "mascot_train_epoch", "mascot_eval_rmse",
                  "mascot_get_factors", "mascot_get_group_info", "mascot_destroy", "mascot_rmse_host"):
         assert must in names
