@@ -73,6 +73,14 @@ def shard_ratings(plan, rank, train, test):
     return mine, seg, my_test
 
 
+def _finish_device_work(t):
+    """NCCL work is only ordered on torch's stream; the engine runs on its own stream, so the host
+    waits for the transfer before the next kernel is launched."""
+    if t is not None and t.is_cuda:
+        import torch
+        torch.cuda.current_stream(t.device).synchronize()
+
+
 def exchange_block(dist, shard, send_block, recv_block, dst, src):
     """Hand `send_block` to rank dst and take `recv_block` from rank src (in place, both arenas)."""
     if send_block == recv_block and dst == src:
@@ -85,6 +93,7 @@ def exchange_block(dist, shard, send_block, recv_block, dst, src):
         ops.append(dist.P2POp(dist.irecv, t, src))
     for req in dist.batch_isend_irecv(ops):
         req.wait()
+    _finish_device_work(ops[0].tensor if ops else None)
     return nbytes
 
 
@@ -115,9 +124,12 @@ def gather_item_factors(dist, shard, world):
     """After an epoch every rank holds only its home block fresh; make all of Q fresh everywhere."""
     if world == 1:
         return
+    last = None
     for b in range(world):
         for t in shard.block_tensors(b):
             dist.broadcast(t, src=b)
+            last = t
+    _finish_device_work(last)
 
 
 def global_rmse(dist, shard, world, comm_device="cpu"):
