@@ -747,6 +747,12 @@ int mascot_sync(mascot_handle* h) {
     return MASCOT_OK;
 }
 
+int mascot_get_stream(mascot_handle* h, void** stream) {
+    if (!h || !stream) return MASCOT_ERR_BAD_ARG;
+    *stream = (void*)h->stream;
+    return MASCOT_OK;
+}
+
 int mascot_eval_sq_error(mascot_handle* h, double* sum_sq, uint64_t* count) {
     if (!h || !sum_sq || !count) return MASCOT_ERR_BAD_ARG;
     if (!h->have_ratings || !h->have_factors) return fail(h, MASCOT_ERR_STATE, "ratings and factors must be set before evaluation");

@@ -25,7 +25,7 @@ EXPORTS = [
     "mascot_get_factors", "mascot_get_group_info", "mascot_get_index_maps", "mascot_get_sample_stats",
     "mascot_get_test_ratings", "mascot_promote_group", "mascot_reload_train", "mascot_stream_source_index", "mascot_get_stream_order", "mascot_rmse_host", "mascot_rmse_device", "mascot_rmse_device_noalloc",
     "mascot_set_ratings_sharded", "mascot_is_check_epoch", "mascot_stats_begin", "mascot_train_segment", "mascot_stats_fetch",
-    "mascot_stats_apply", "mascot_item_rows", "mascot_sync", "mascot_eval_sq_error",
+    "mascot_stats_apply", "mascot_item_rows", "mascot_sync", "mascot_get_stream", "mascot_eval_sq_error",
 ]
 
 
@@ -193,6 +193,12 @@ class Engine:
 
     def sync(self):
         self._check(self._lib.mascot_sync(self._h))
+
+    def stream_handle(self):
+        """Address of the engine's cudaStream_t (for ordering a caller's own device work on it)."""
+        st = C.c_void_p()
+        self._check(self._lib.mascot_get_stream(self._h, C.byref(st)))
+        return st.value or 0
 
     def eval_sq_error(self):
         s, n = C.c_double(), C.c_uint64()

@@ -231,6 +231,10 @@ MASCOT_API int mascot_item_rows(mascot_handle* h, uint32_t row_begin, uint32_t r
                      void** f32_ptr, uint64_t* f32_bytes);
 /* Wait for everything queued on the engine's stream. */
 MASCOT_API int mascot_sync(mascot_handle* h);
+/* The CUDA stream (a cudaStream_t) every kernel and copy of this engine is queued on, so that a
+ * host program can order its own transfers and events against the engine's work on the device,
+ * without host-side waits.  No reference counterpart (the reference uses the default stream). */
+MASCOT_API int mascot_get_stream(mascot_handle* h, void** stream);
 /* Sum of squared test errors and number of test ratings of this engine (for an RMSE over shards). */
 MASCOT_API int mascot_eval_sq_error(mascot_handle* h, double* sum_sq, uint64_t* count);
 

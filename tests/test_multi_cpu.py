@@ -91,6 +91,10 @@ class OracleShard:
     def sync(self):
         pass
 
+    def device_order(self):
+        import contextlib
+        return contextlib.nullcontext()
+
     def stats_fetch(self):
         return [a.copy() for a in self.stats]
 
