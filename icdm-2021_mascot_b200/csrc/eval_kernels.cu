@@ -34,14 +34,32 @@ __device__ __forceinline__ float block_tree_512(float* tmp) {
     return tmp[0];
 }
 
+// A lane's eight consecutive physical elements of a row as fp32 (positions: see layout.cuh).
+__device__ __forceinline__ void load8(const Arena& A, uint32_t code, int K, int tl, float* x) {
+    const uint32_t row = code & kIdMask;
+    if (code & kPrecBit) {
+        const float4* p = reinterpret_cast<const float4*>(A.f32 + (size_t)row * K) + 2 * tl;
+        const float4 v = __ldcg(p), w = __ldcg(p + 1);
+        x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w; x[4] = w.x; x[5] = w.y; x[6] = w.z; x[7] = w.w;
+    } else {
+        const uint4 v = __ldcg(reinterpret_cast<const uint4*>(A.f16 + (size_t)row * K) + tl);
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+        const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&v.z));
+        const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&v.w));
+        x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y; x[4] = c.x; x[5] = c.y; x[6] = d.x; x[7] = d.y;
+    }
+}
+
 template <int K>
 __global__ void __launch_bounds__(kRmseThreads) rmse_kernel(const Stream t, const Arena P, const Arena Q, float* block_err) {
-    constexpr int T = K / 4;
+    constexpr int T = K / 8;                      // lanes per rating, eight elements each
     __shared__ float tmp[kRmseBlock];
     const int tl = threadIdx.x % T;
     const int team = threadIdx.x / T;
     constexpr int kTeams = kRmseThreads / T;
-    const unsigned mask = (T == 32) ? 0xffffffffu : (0xffffu << (16 * ((threadIdx.x >> 4) & 1)));
+    const int lane = threadIdx.x & 31;
+    const unsigned mask = ((1u << T) - 1u) << (lane - tl);
     const uint64_t base = (uint64_t)blockIdx.x * kRmseBlock;
     for (int j = team; j < kRmseBlock; j += kTeams) {
         const uint64_t idx = base + j;
@@ -49,37 +67,32 @@ __global__ void __launch_bounds__(kRmseThreads) rmse_kernel(const Stream t, cons
         if (idx < t.n) {
             const float r = __ldg(t.r + idx);
             const uint32_t uc = __ldg(t.u + idx), ic = __ldg(t.i + idx);
-            const uint32_t u = uc & kIdMask, i = ic & kIdMask;
-            float p[4], q[4];
-            if (uc & kPrecBit) {
-                const float4 v = __ldcg(reinterpret_cast<const float4*>(P.f32 + (size_t)u * K) + tl);
-                p[0] = v.x; p[1] = v.y; p[2] = v.z; p[3] = v.w;
-            } else {
-                const uint2 v = __ldcg(reinterpret_cast<const uint2*>(P.f16 + (size_t)u * K) + tl);
-                const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
-                const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
-                p[0] = lo.x; p[1] = lo.y; p[2] = hi.x; p[3] = hi.y;
-            }
-            if (ic & kPrecBit) {
-                const float4 v = __ldcg(reinterpret_cast<const float4*>(Q.f32 + (size_t)i * K) + tl);
-                q[0] = v.x; q[1] = v.y; q[2] = v.z; q[3] = v.w;
-            } else {
-                const uint2 v = __ldcg(reinterpret_cast<const uint2*>(Q.f16 + (size_t)i * K) + tl);
-                const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
-                const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
-                q[0] = lo.x; q[1] = lo.y; q[2] = hi.x; q[3] = hi.y;
-            }
+            float p[8], q[8];
+            load8(P, uc, K, tl, p);
+            load8(Q, ic, K, tl, q);
+            // positions 0 2 4 6 hold e0..e3, positions 1 3 5 7 hold e4..e7
             float part;
             if (K == 128) {
-                part = __fmaf_rn(p[0], q[0], __fmul_rn(p[1], q[1]));
-                part = __fmaf_rn(p[2], q[2], part);
-                part = __fmaf_rn(p[3], q[3], part);
-            } else {
-                part = __fadd_rn(__fmaf_rn(p[0], q[0], __fmul_rn(p[1], q[1])), __fmaf_rn(p[2], q[2], __fmul_rn(p[3], q[3])));
-            }
-            part = __fadd_rn(part, __shfl_xor_sync(mask, part, 1));
+                // two reference lanes (m, m+16): product chain over four elements each (rmse.h:75),
+                // their sum is the tree's 16 step
+                float c[2];
 #pragma unroll
-            for (int d = T / 2; d >= 2; d >>= 1) part = __fadd_rn(part, __shfl_xor_sync(mask, part, d));
+                for (int h = 0; h < 2; h++) {
+                    float acc = __fmaf_rn(p[h], q[h], __fmul_rn(p[2 + h], q[2 + h]));
+                    acc = __fmaf_rn(p[4 + h], q[4 + h], acc);
+                    c[h] = __fmaf_rn(p[6 + h], q[6 + h], acc);
+                }
+                part = __fadd_rn(c[0], c[1]);
+            } else {
+                // four reference lanes (m, m+16, m+8, m+24) with two elements each: 16 step, then 8 step
+                const float f0 = __fmaf_rn(p[0], q[0], __fmul_rn(p[2], q[2]));
+                const float f1 = __fmaf_rn(p[4], q[4], __fmul_rn(p[6], q[6]));
+                const float f2 = __fmaf_rn(p[1], q[1], __fmul_rn(p[3], q[3]));
+                const float f3 = __fmaf_rn(p[5], q[5], __fmul_rn(p[7], q[7]));
+                part = __fadd_rn(__fadd_rn(f0, f1), __fadd_rn(f2, f3));
+            }
+#pragma unroll
+            for (int d = T / 2; d >= 1; d >>= 1) part = __fadd_rn(part, __shfl_xor_sync(mask, part, d));
             const float e = __fsub_rn(r, part);
             err2 = __fmul_rn(e, e);
         }

@@ -1,21 +1,24 @@
-// Factor-row storage layout and the team reduction that goes with it.
+// Factor-row storage layout and the worker reduction that goes with it.
 //
 // The reference gives lane l of a warp the elements l, l+32 [, l+64, l+96] of a row, adds the
 // lane's products pairwise and then folds the 32 lane partials with shfl_down 16,8,4,2,1
 // (sgd/sgd_kernel.h:42-63, mascot/mascot_sgd_kernel.h:193-210).  Floating-point addition is
 // not associative, so a bit-exact engine has to add the same pairs in the same tree - but it need
-// not keep the strided 2/4-byte accesses.  Rows are therefore stored PERMUTED so that one 64-bit
-// (fp16) or 128-bit (fp32) access per lane fetches exactly the operands of one or two reference
-// lanes, and a xor-butterfly over a "team" of K/4 lanes reproduces the reference tree:
+// not keep the strided 2/4-byte accesses.  Rows are therefore stored PERMUTED so that lane m of a
+// "worker" of K/8 lanes owns the eight consecutive physical elements 8m..8m+7 (one 128-bit access
+// in binary16, two in fp32), which are the operands of two (k=128) or four (k=64) reference lanes:
 //
-//   K = 128, team of 32 lanes, lane t holds physical elements 4t..4t+3 =
-//            slots 0..3 of reference lane  (t>>1) + 16*(t&1)
-//   K =  64, team of 16 lanes, lane t holds physical elements 4t..4t+3 =
-//            slots 0,1 of reference lane A = (t>>1) + 8*(t&1)  followed by slots 0,1 of lane A+16
+//   K = 128:  e0..e3 = slots 0..3 of reference lane m,       e4..e7 = slots 0..3 of lane m+16
+//   K =  64:  e0,e1 = slots 0,1 of lane m,  e2,e3 = of lane m+16,  e4,e5 = of m+8,  e6,e7 = of m+24
 //
-// In both cases the lane partial is (fma(a0,b0,a1*b1)) + (fma(a2,b2,a3*b3)) - for K=64 the outer
-// add is the reference's shfl_down-16 step - and the remaining tree steps are xor 1, T/2, .., 2.
-// Addition is commutative, so after the butterfly every lane holds the reference's lane-0 value.
+// and inside the lane they are stored in the order  e0 e4 e1 e5 e2 e6 e3 e7, i.e. as the four
+// binary16 pairs (e0,e4) (e1,e5) (e2,e6) (e3,e7).  With that order two packed multiplies, two
+// packed fused multiply-adds and one packed add give (f0+f1, f2+f3) for the pair products
+// f_j = fma(e_2j, e'_2j, e_2j+1 * e'_2j+1) without moving a single half between registers; one more
+// add finishes the lane partial (f0+f1)+(f2+f3).  For k=128 that last add is the reference's
+// shfl_down-16 step, for k=64 the packed add is its 16 step and the last add its 8 step; the
+// remaining steps are a xor butterfly over the worker's lanes.  Addition is commutative, so after
+// the butterfly every lane holds the reference's lane-0 value.
 #pragma once
 #include <cstdint>
 
@@ -27,18 +30,24 @@
 
 namespace mascot {
 
+// position inside a lane's eight elements: e_s is stored at 2*(s&3) + (s>>2)
+MASCOT_HD inline int lane_pos_of_elem(int s) { return 2 * (s & 3) + (s >> 2); }
+MASCOT_HD inline int lane_elem_of_pos(int q) { return (q >> 1) + 4 * (q & 1); }
+
 // physical position of logical element e (0 <= e < K) inside a row
 MASCOT_HD inline int phys_of_logical(int K, int e) {
     const int lane = e & 31, slot = e >> 5;
-    if (K == 128) return 8 * (lane & 15) + 4 * (lane >> 4) + slot;
-    return 8 * (lane & 7) + 4 * ((lane >> 3) & 1) + 2 * ((lane >> 4) & 1) + slot;
+    int m, s;
+    if (K == 128) { m = lane & 15; s = 4 * (lane >> 4) + slot; }
+    else { m = lane & 7; s = 4 * ((lane >> 3) & 1) + 2 * ((lane >> 4) & 1) + slot; }
+    return 8 * m + lane_pos_of_elem(s);
 }
 
 // logical element stored at physical position p
 MASCOT_HD inline int logical_of_phys(int K, int p) {
-    const int t = p >> 2, s = p & 3;
-    if (K == 128) return (t >> 1) + 16 * (t & 1) + 32 * s;
-    return (t >> 1) + 8 * (t & 1) + 16 * (s >> 1) + 32 * (s & 1);
+    const int m = p >> 3, s = lane_elem_of_pos(p & 7);
+    if (K == 128) return m + 16 * (s >> 2) + 32 * (s & 3);
+    return m + 8 * (s >> 2) + 16 * ((s >> 1) & 1) + 32 * (s & 1);
 }
 
 // Seeded bijection of [0, n): a 4-round Feistel network over the next even power-of-two domain,

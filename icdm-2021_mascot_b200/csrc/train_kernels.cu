@@ -122,19 +122,20 @@ __device__ __forceinline__ void st_row(const Arena& A, uint32_t code, int m, con
 }
 
 // ---- lane partials -------------------------------------------------------------------------
-// (f_0 + f_1) + (f_2 + f_3) with f_j = fma(a_2j, b_2j, a_2j+1 * b_2j+1)
+// A lane's elements e0..e7 sit at positions 0 2 4 6 1 3 5 7 (layout.cuh), i.e. as the binary16 pairs
+// (e0,e4) (e1,e5) (e2,e6) (e3,e7).  Lane partial: (f_0 + f_1) + (f_2 + f_3) with
+// f_j = fma(e_2j, e'_2j, e_2j+1 * e'_2j+1).
 __device__ __forceinline__ float pair_partial(const V8f& a, const V8f& b) {
-    float f[4];
-#pragma unroll
-    for (int j = 0; j < 4; j++) f[j] = __fmaf_rn(a.x[2 * j], b.x[2 * j], __fmul_rn(a.x[2 * j + 1], b.x[2 * j + 1]));
-    return __fadd_rn(__fadd_rn(f[0], f[1]), __fadd_rn(f[2], f[3]));
+    const float f0 = __fmaf_rn(a.x[0], b.x[0], __fmul_rn(a.x[2], b.x[2]));
+    const float f1 = __fmaf_rn(a.x[4], b.x[4], __fmul_rn(a.x[6], b.x[6]));
+    const float f2 = __fmaf_rn(a.x[1], b.x[1], __fmul_rn(a.x[3], b.x[3]));
+    const float f3 = __fmaf_rn(a.x[5], b.x[5], __fmul_rn(a.x[7], b.x[7]));
+    return __fadd_rn(__fadd_rn(f0, f1), __fadd_rn(f2, f3));
 }
 __device__ __forceinline__ __half pair_partial(const V8h& p, const V8h& q) {
-    const __half2 f01 = __hfma2(__lows2half2(p.v[0], p.v[1]), __lows2half2(q.v[0], q.v[1]),
-                                __hmul2_rn(__highs2half2(p.v[0], p.v[1]), __highs2half2(q.v[0], q.v[1])));
-    const __half2 f23 = __hfma2(__lows2half2(p.v[2], p.v[3]), __lows2half2(q.v[2], q.v[3]),
-                                __hmul2_rn(__highs2half2(p.v[2], p.v[3]), __highs2half2(q.v[2], q.v[3])));
-    const __half2 t = __hadd2_rn(__lows2half2(f01, f23), __highs2half2(f01, f23));   // (f0+f1, f2+f3)
+    const __half2 f02 = __hfma2(p.v[0], q.v[0], __hmul2_rn(p.v[1], q.v[1]));   // (f_0, f_2)
+    const __half2 f13 = __hfma2(p.v[2], q.v[2], __hmul2_rn(p.v[3], q.v[3]));   // (f_1, f_3)
+    const __half2 t = __hadd2_rn(f02, f13);                                     // (f_0+f_1, f_2+f_3)
     return __hadd_rn(__low2half(t), __high2half(t));
 }
 // k=128 only: the left-to-right product chain of a reference lane over its four elements,
@@ -143,10 +144,10 @@ __device__ __forceinline__ __half pair_partial(const V8h& p, const V8h& q) {
 __device__ __forceinline__ float chain_partial_k128(const V8f& a, const V8f& b) {
     float c[2];
 #pragma unroll
-    for (int h = 0; h < 2; h++) {
-        float acc = __fmaf_rn(a.x[4 * h], b.x[4 * h], __fmul_rn(a.x[4 * h + 1], b.x[4 * h + 1]));
-        acc = __fmaf_rn(a.x[4 * h + 2], b.x[4 * h + 2], acc);
-        c[h] = __fmaf_rn(a.x[4 * h + 3], b.x[4 * h + 3], acc);
+    for (int h = 0; h < 2; h++) {          // h = 0: e0..e3 at positions 0 2 4 6;  h = 1: e4..e7 at 1 3 5 7
+        float acc = __fmaf_rn(a.x[h], b.x[h], __fmul_rn(a.x[2 + h], b.x[2 + h]));
+        acc = __fmaf_rn(a.x[4 + h], b.x[4 + h], acc);
+        c[h] = __fmaf_rn(a.x[6 + h], b.x[6 + h], acc);
     }
     return __fadd_rn(c[0], c[1]);
 }
@@ -274,28 +275,77 @@ __device__ __forceinline__ void update_one(const Consts& c, float r, uint32_t uc
     }
 }
 
-// The records of one chunk (TS ratings), one per lane of the worker.
-struct Chunk {
-    float r; uint32_t u, i;
-    int cnt;            // valid ratings in the chunk (0: no chunk)
-    unsigned dup;       // bit j: the user of rating j also occurs among the D ratings before it
-    uint64_t base;      // stream position of its first rating
+// ---- asynchronous row copies (global -> the worker's shared-memory rings) ----------------------
+// Rows are fetched with cp.async, not with loads into registers: a register load ties the wait for
+// an old row to every younger load that shares its scoreboard, which exposes one full memory
+// latency per rating; copy groups complete in order, so waiting for the group of rating j leaves
+// the copies of ratings j+1 .. j+D in flight.
+__device__ __forceinline__ void cp16(void* smem_dst, const void* gsrc) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Slot layout: the first 16 bytes of every lane, then (fp32 rows) the second 16 bytes of every lane,
+// so that 128-bit shared-memory accesses of neighbouring lanes never collide on a bank.
+template <int K, int MODE>
+__device__ __forceinline__ void cp_row(unsigned char* slot, const Arena& A, uint32_t code, int m) {
+    const uint32_t row = code & kIdMask;
+    if (is_f32<MODE>(code)) {
+        const unsigned char* g = reinterpret_cast<const unsigned char*>(A.f32 + (size_t)row * K) + 32 * m;
+        cp16(slot + 16 * m, g);
+        if constexpr (MODE != ROWS_HALF) cp16(slot + 2 * K + 16 * m, g + 16);
+    } else {
+        cp16(slot + 16 * m, reinterpret_cast<const unsigned char*>(A.f16 + (size_t)row * K) + 16 * m);
+    }
+}
+template <int K, int MODE>
+__device__ __forceinline__ Raw<MODE> lds_row(const unsigned char* slot, uint32_t code, int m) {
+    Raw<MODE> r;
+    r.a = *reinterpret_cast<const uint4*>(slot + 16 * m);
+    if constexpr (MODE != ROWS_HALF) {
+        if (is_f32<MODE>(code)) r.b = *reinterpret_cast<const uint4*>(slot + 2 * K + 16 * m);
+    }
+    return r;
+}
+
+// One rating as the worker's lanes read it from shared memory (one 128-bit broadcast load).
+constexpr uint32_t F_VALID = 1u;    // there is a rating at this position
+constexpr uint32_t F_UDUP = 2u;     // its user also occurs among the NS ratings before it: read the row at use
+constexpr uint32_t F_RS = 4u;       // its item differs from the item of the rating before it (a run starts)
+constexpr uint32_t F_IDUP = 8u;     // run start whose item also occurs among the NS ratings before it
+
+constexpr int kSpan = 8;            // consecutive chunks handed out together (one ticket per span)
+
+// Shared memory of one worker: two chunks of records, then the user ring, then the item ring.
+template <int K, int MODE, int NS> struct WorkerSmem {
+    static constexpr int TS = K / 8;
+    static constexpr int kRowBytes = K * (MODE == ROWS_HALF ? 2 : 4);
+    static constexpr int kRecBytes = 2 * TS * 16;
+    static constexpr int kBytes = kRecBytes + 2 * NS * kRowBytes;
 };
 
-// DEEP: user-row prefetch depth 8 (binary16 rows) / 4 (fp32 or mixed rows), for launches with few
-// workers per SM, where each worker must hide memory latency on its own.  Otherwise depth 2, which
-// keeps the register count low enough for many resident workers.
-template <int K, int KIND, int MODE, bool STATS, bool DEEP>
+// NS: slots per ring.  Rows are requested D = NS-1 ratings ahead.
+template <int K, int KIND, int MODE, bool STATS, int NS>
 __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
-    constexpr int TS = K / 8;                      // lanes per worker = ratings per chunk
-    constexpr int D = DEEP ? (MODE == ROWS_HALF ? 8 : 4) : 2;
-    static_assert(TS % D == 0, "the prefetch ring must divide the chunk");
+    using SM = WorkerSmem<K, MODE, NS>;
+    constexpr int TS = SM::TS;                     // lanes per worker = ratings per chunk
+    constexpr int D = NS - 1;
+    static_assert(TS % NS == 0, "the ring must divide the chunk");
+    extern __shared__ __align__(16) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31;
     const int m = lane % TS;
     const unsigned wmask = (TS == 32) ? 0xffffffffu : (((1u << TS) - 1u) << (lane - m));
     const uint64_t worker = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) / TS;
     const uint64_t W = a.workers;
     const uint64_t nchunks = (a.s.n + TS - 1) / TS;
+    const uint64_t nspans = (nchunks + kSpan - 1) / kSpan;
+
+    unsigned char* const mine = smem_raw + (size_t)(threadIdx.x / TS) * SM::kBytes;
+    uint4* const recs = reinterpret_cast<uint4*>(mine);                  // [2][TS]
+    unsigned char* const uring = mine + SM::kRecBytes;                    // [NS][kRowBytes]
+    unsigned char* const iring = uring + NS * SM::kRowBytes;              // [NS][kRowBytes]
 
     Consts c;
     c.lr = a.lr; c.lam = a.lam;
@@ -307,13 +357,32 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
     // only the mixed-precision mode reads the precision bit of an id
     constexpr uint32_t kKeep = (MODE == ROWS_DYN) ? 0xffffffffu : kIdMask;
 
-    // Chunk pipeline, four stages deep so that no stage waits for the one before it:
-    //   ticket (atomic on the work counter) -> record loads -> repeat marking -> use.
-    // fetch_chunk only issues the loads; mark_repeats, run one chunk later when the data has
-    // arrived, flags the ratings whose user also occurs among the D ratings before them (those rows
-    // cannot be prefetched: they must be read after the earlier update has been stored).
+    if (worker >= W) return;
+
+    // ---- which chunks this worker processes ----
+    // Spans of kSpan consecutive chunks: span `worker`, span `worker + W`, then spans 2W + ticket from
+    // the shared counter.  A ticket is requested one span before it is needed and stays in lane 0
+    // until then, so the launch neither waits for the counter nor depends on all blocks being resident.
+    uint64_t span_cur = worker, span_next = worker + W;
+    int kin = 0;
+    unsigned long long ticket = (m == 0) ? atomicAdd(a.next_chunk, 1ull) : 0ull;
+    auto next_chunk_id = [&]() -> uint64_t {
+        if (span_cur >= nspans) return ~0ull;
+        const uint64_t ci = span_cur * kSpan + kin;
+        if (++kin == kSpan) {
+            kin = 0;
+            span_cur = span_next;
+            const unsigned lo = __shfl_sync(wmask, (unsigned)ticket, 0, TS), hi = __shfl_sync(wmask, (unsigned)(ticket >> 32), 0, TS);
+            span_next = 2 * W + (((uint64_t)hi << 32) | lo);
+            ticket = (m == 0) ? atomicAdd(a.next_chunk, 1ull) : 0ull;
+        }
+        return ci < nchunks ? ci : ~0ull;
+    };
+
+    // ---- chunk pipeline: global loads (registers) -> flags -> records in shared memory -> use ----
+    struct Loaded { float r; uint32_t u, i; int cnt; uint64_t base; };
     auto fetch_chunk = [&](uint64_t ci) {
-        Chunk k; k.r = 0.f; k.u = kNoRow; k.i = 0; k.cnt = 0; k.dup = 0; k.base = 0;
+        Loaded k; k.r = 0.f; k.u = kNoRow; k.i = kNoRow; k.cnt = 0; k.base = 0;
         if (ci < nchunks) {
             k.base = ci * TS;
             const uint64_t left = a.s.n - k.base;
@@ -326,164 +395,128 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
         }
         return k;
     };
-    auto mark_repeats = [&](Chunk& k, const Chunk& before) {
-        if (k.cnt > 0) {
-            bool mine = false;
+    uint32_t prev_u = kNoRow, prev_i = kNoRow;        // lane m: rating m of the chunk before `inflight`
+    Loaded inflight = fetch_chunk(next_chunk_id());
+    uint64_t base0 = 0, base1 = 0;              // stream position of the first rating of each buffer
+    // Turns `inflight` into records in buffer `b` and starts loading the chunk after it.
+    auto publish = [&](int b) {
+        bool udup = false, idup = false, rs = false;
 #pragma unroll
-            for (int d = 1; d <= D; d++) {
-                const int src = (m - d) & (TS - 1);
-                const uint32_t here = __shfl_sync(wmask, k.u, src, TS);
-                const uint32_t prev = __shfl_sync(wmask, before.u, src, TS);
-                mine |= ((m >= d) ? here : prev) == k.u;
-            }
-            k.dup = __ballot_sync(wmask, mine && m < k.cnt) >> (lane - m);
+        for (int d = 1; d <= NS; d++) {
+            // the rating d places earlier: lane m-d of this chunk, or lane m-d+TS of the previous one;
+            // the SOURCE lane knows which of its two values a reader d lanes further on wants
+            const bool from_this = m < TS - d;
+            const uint32_t su = __shfl_sync(wmask, from_this ? inflight.u : prev_u, (m - d) & (TS - 1), TS);
+            const uint32_t si = __shfl_sync(wmask, from_this ? inflight.i : prev_i, (m - d) & (TS - 1), TS);
+            udup |= su == inflight.u;
+            if (d == 1) rs = si != inflight.i; else idup |= si == inflight.i;
+        }
+        uint32_t f = 0;
+        if (m < inflight.cnt) f = F_VALID | (udup ? F_UDUP : 0u) | (rs ? F_RS : 0u) | ((rs && idup) ? F_IDUP : 0u);
+        recs[b * TS + m] = make_uint4(inflight.u, inflight.i, f, __float_as_uint(inflight.r));
+        if (b) base1 = inflight.base; else base0 = inflight.base;
+        prev_u = inflight.u; prev_i = inflight.i;
+        inflight = (inflight.cnt > 0) ? fetch_chunk(next_chunk_id()) : inflight;
+        __syncwarp(wmask);
+    };
+    publish(0);
+    publish(1);
+
+    // item row of the current run
+    uint32_t cur_ic = kNoRow;
+    Raw<MODE> q;
+
+    // item-side statistics of the current run of equal item groups
+    V8f gq_acc; float nq_acc = 0.f; uint32_t acc_group = kNoRow;
+#pragma unroll
+    for (int t = 0; t < 8; t++) gq_acc.x[t] = 0.f;
+    // this block's private set of accumulators (fewer workers per address, less serialisation)
+    const size_t my_set = STATS ? (size_t)(blockIdx.x % (unsigned)a.st.copies) * a.st.copy_stride : 0;
+    float* const gsum_p = a.st.gsum_p + my_set; float* const gsum_q = a.st.gsum_q + my_set;
+    float* const nsum_p = a.st.nsum_p + my_set; float* const nsum_q = a.st.nsum_q + my_set;
+    auto flush_item_stats = [&]() {
+        if (acc_group != kNoRow) {
+            red_add8(gsum_q + (size_t)acc_group * K + 8 * m, gq_acc);
+            if (m == 0) atomicAdd(nsum_q + acc_group, nq_acc);
         }
     };
-    // chunk ids: worker, worker + W, then 2W + (ticket from the shared counter); a ticket is
-    // requested one chunk before it is needed and stays in lane 0 until then
-    auto request_ticket = [&]() -> unsigned long long {
-        return (m == 0) ? atomicAdd(a.next_chunk, 1ull) : 0ull;
+    auto record = [&](const Sample& smp, uint32_t uc, uint32_t ic) {
+        if (smp.user) {
+            const uint32_t g = a.st.ugroup[uc & kIdMask];
+            const float n = worker_sum<TS>(pair_partial(smp.gp, smp.gp), wmask);
+            red_add8(gsum_p + (size_t)g * K + 8 * m, smp.gp);
+            if (m == 0) atomicAdd(nsum_p + g, n);
+        }
+        if (smp.item) {
+            const uint32_t g = a.st.igroup[ic & kIdMask];
+            const float n = worker_sum<TS>(pair_partial(smp.gq, smp.gq), wmask);
+            if (g != acc_group) {
+                flush_item_stats();
+                acc_group = g; nq_acc = 0.f;
+#pragma unroll
+                for (int t = 0; t < 8; t++) gq_acc.x[t] = 0.f;
+            }
+#pragma unroll
+            for (int t = 0; t < 8; t++) gq_acc.x[t] = __fadd_rn(gq_acc.x[t], smp.gq.x[t]);
+            nq_acc = __fadd_rn(nq_acc, n);
+        }
     };
-    auto ticket_chunk = [&](unsigned long long t) -> uint64_t {
-        const unsigned lo = __shfl_sync(wmask, (unsigned)t, 0, TS), hi = __shfl_sync(wmask, (unsigned)(t >> 32), 0, TS);
-        return 2 * W + (((uint64_t)hi << 32) | lo);
+    Sample smp;
+
+    // requests the rows of the rating described by record `rx` into ring slot `slot`
+    auto request_rows = [&](const uint4& rx, int slot) {
+        if ((rx.z & (F_VALID | F_UDUP)) == F_VALID) cp_row<K, MODE>(uring + slot * SM::kRowBytes, a.P, rx.x, m);
+        if ((rx.z & (F_VALID | F_RS | F_IDUP)) == (F_VALID | F_RS)) cp_row<K, MODE>(iring + slot * SM::kRowBytes, a.Q, rx.y, m);
+        cp_commit();
     };
-
-    if (worker < W) {
-        Chunk none; none.r = 0.f; none.u = kNoRow; none.i = 0; none.cnt = 0; none.dup = 0; none.base = 0;
-        Chunk cur = fetch_chunk(worker);
-        Chunk nxt = fetch_chunk(worker + W);
-        unsigned long long ticket = request_ticket();
-        Chunk nn = fetch_chunk(ticket_chunk(ticket));        // only this very first ticket is waited for
-        ticket = request_ticket();
-        mark_repeats(cur, none);
-        mark_repeats(nxt, cur);
-
-        Raw<MODE> ring[D];             // slot j % D: prefetched user row of rating j of the current chunk
-        unsigned stale = 0;            // bit t: slot t was not prefetched and is read at use
-        bool primed = false;           // the ring holds the first D rows of `cur`
-
-        // item row of the current run, and the prefetched row of the run after it
-        uint32_t cur_ic = kNoRow, nxt_ic = kNoRow;
-        Raw<MODE> q, qn;
-
-        // item-side statistics of the current run of equal item groups
-        V8f gq_acc; float nq_acc = 0.f; uint32_t acc_group = kNoRow;
+    // prologue: the rows of the first D ratings, one copy group per rating
 #pragma unroll
-        for (int t = 0; t < 8; t++) gq_acc.x[t] = 0.f;
-        // this block's private set of accumulators (fewer workers per address, less serialisation)
-        const size_t my_set = STATS ? (size_t)(blockIdx.x % (unsigned)a.st.copies) * a.st.copy_stride : 0;
-        float* const gsum_p = a.st.gsum_p + my_set; float* const gsum_q = a.st.gsum_q + my_set;
-        float* const nsum_p = a.st.nsum_p + my_set; float* const nsum_q = a.st.nsum_q + my_set;
-        auto flush_item_stats = [&]() {
-            if (acc_group != kNoRow) {
-                red_add8(gsum_q + (size_t)acc_group * K + 8 * m, gq_acc);
-                if (m == 0) atomicAdd(nsum_q + acc_group, nq_acc);
-            }
-        };
-        auto record = [&](const Sample& smp, uint32_t uc, uint32_t ic) {
-            if (smp.user) {
-                const uint32_t g = a.st.ugroup[uc & kIdMask];
-                const float n = worker_sum<TS>(pair_partial(smp.gp, smp.gp), wmask);
-                red_add8(gsum_p + (size_t)g * K + 8 * m, smp.gp);
-                if (m == 0) atomicAdd(nsum_p + g, n);
-            }
-            if (smp.item) {
-                const uint32_t g = a.st.igroup[ic & kIdMask];
-                const float n = worker_sum<TS>(pair_partial(smp.gq, smp.gq), wmask);
-                if (g != acc_group) {
-                    flush_item_stats();
-                    acc_group = g; nq_acc = 0.f;
-#pragma unroll
-                    for (int t = 0; t < 8; t++) gq_acc.x[t] = 0.f;
-                }
-#pragma unroll
-                for (int t = 0; t < 8; t++) gq_acc.x[t] = __fadd_rn(gq_acc.x[t], smp.gq.x[t]);
-                nq_acc = __fadd_rn(nq_acc, n);
-            }
-        };
-        Sample smp;
+    for (int t = 0; t < D; t++) request_rows(recs[t], t);
 
-        // switches the cached item row when the item changes; `j` is the rating's index in `cur`
-        auto item_row = [&](uint32_t ic, int j) {
-            if (ic != cur_ic) {
-                if (cur_ic != kNoRow) st_row<K, MODE>(a.Q, cur_ic, m, q);
-                if (ic == nxt_ic) q = qn; else q = ld_row<K, MODE>(a.Q, ic, m);
-                cur_ic = ic;
-                nxt_ic = kNoRow;               // a prefetched row is used at most once, right after its fetch
-                // prefetch the row of the next run: first different item later in this chunk, else
-                // the first item of the worker's next chunk
-                const unsigned later = __ballot_sync(wmask, cur.i != ic && m > j && m < cur.cnt) >> (lane - m);
-                uint32_t cand = kNoRow;
-                if (later) cand = __shfl_sync(wmask, cur.i, __ffs(later) - 1, TS);
-                else if (nxt.cnt > 0) cand = __shfl_sync(wmask, nxt.i, 0, TS);
-                if (cand != kNoRow && cand != ic) { qn = ld_row<K, MODE>(a.Q, cand, m); nxt_ic = cand; }
-            }
-        };
-
-        while (cur.cnt > 0) {
-            if (cur.cnt == TS) {
-                // ---- full chunk: software-pipelined ----
-                if (!primed) {
-                    stale = 0;
-#pragma unroll
-                    for (int t = 0; t < D; t++) {
-                        const uint32_t ut = __shfl_sync(wmask, cur.u, t, TS);
-                        if ((cur.dup >> t) & 1u) stale |= 1u << t; else ring[t] = ld_row<K, MODE>(a.P, ut, m);
-                    }
-                }
-                const bool next_full = (nxt.cnt == TS);
+    int cb = 0;                                     // buffer of the chunk in use
+    for (;;) {
+        const uint4* const rc = recs + cb * TS;
+        const uint4* const rn = recs + (cb ^ 1) * TS;
+        bool more = true;
 #pragma unroll 1
-                for (int jb = 0; jb < TS; jb += D) {
+        for (int jb = 0; jb < TS && more; jb += NS) {
 #pragma unroll
-                    for (int t = 0; t < D; t++) {
-                        const int j = jb + t;
-                        const float r = __shfl_sync(wmask, cur.r, j, TS);
-                        const uint32_t uc = __shfl_sync(wmask, cur.u, j, TS);
-                        const uint32_t ic = __shfl_sync(wmask, cur.i, j, TS);
-                        const bool sampled = STATS && (cur.base + j >= a.st.first_sample_pos);
-                        item_row(ic, j);
-                        Raw<MODE> p = ring[t];
-                        if (stale & (1u << t)) { p = ld_row<K, MODE>(a.P, uc, m); stale &= ~(1u << t); }
-                        // refill the slot with the row of the rating D ahead
-                        const int x = j + D;
-                        if (x < TS) {
-                            const uint32_t ux = __shfl_sync(wmask, cur.u, x, TS);
-                            if ((cur.dup >> x) & 1u) stale |= 1u << t; else ring[t] = ld_row<K, MODE>(a.P, ux, m);
-                        } else if (next_full) {
-                            const uint32_t ux = __shfl_sync(wmask, nxt.u, x - TS, TS);
-                            if ((nxt.dup >> (x - TS)) & 1u) stale |= 1u << t; else ring[t] = ld_row<K, MODE>(a.P, ux, m);
-                        }
-                        update_one<K, KIND, MODE, STATS>(c, r, uc, ic, p, q, sampled, smp, wmask);
-                        st_row<K, MODE>(a.P, uc, m, p);
-                        if (STATS && sampled) record(smp, uc, ic);
-                    }
+            for (int t = 0; t < NS; t++) {
+                const int j = jb + t;
+                const uint4 rec = rc[j];
+                if (!(rec.z & F_VALID)) { more = false; break; }
+                const uint32_t uc = rec.x, ic = rec.y;
+                const float r = __uint_as_float(rec.w);
+                const bool sampled = STATS && ((cb ? base1 : base0) + j >= a.st.first_sample_pos);
+                cp_wait<(D > 0 ? D - 1 : 0)>();
+                if (rec.z & F_RS) {
+                    if (cur_ic != kNoRow) st_row<K, MODE>(a.Q, cur_ic, m, q);
+                    if (rec.z & F_IDUP) q = ld_row<K, MODE>(a.Q, ic, m);
+                    else q = lds_row<K, MODE>(iring + t * SM::kRowBytes, ic, m);
+                    cur_ic = ic;
                 }
-                primed = next_full;
-            } else {
-                // ---- ragged last chunk: plain sequential ----
-                for (int j = 0; j < cur.cnt; j++) {
-                    const float r = __shfl_sync(wmask, cur.r, j, TS);
-                    const uint32_t uc = __shfl_sync(wmask, cur.u, j, TS);
-                    const uint32_t ic = __shfl_sync(wmask, cur.i, j, TS);
-                    const bool sampled = STATS && (cur.base + j >= a.st.first_sample_pos);
-                    item_row(ic, j);
-                    Raw<MODE> p = ld_row<K, MODE>(a.P, uc, m);
-                    update_one<K, KIND, MODE, STATS>(c, r, uc, ic, p, q, sampled, smp, wmask);
-                    st_row<K, MODE>(a.P, uc, m, p);
-                    if (STATS && sampled) record(smp, uc, ic);
+                Raw<MODE> p;
+                if (rec.z & F_UDUP) p = ld_row<K, MODE>(a.P, uc, m);
+                else p = lds_row<K, MODE>(uring + t * SM::kRowBytes, uc, m);
+                // request the rows of the rating D ahead into the slot that was read one rating ago
+                {
+                    const int x = j + D;
+                    const uint4 rx = (x < TS) ? rc[x] : rn[x - TS];
+                    request_rows(rx, (t + D) & (NS - 1));
                 }
-                primed = false;
+                update_one<K, KIND, MODE, STATS>(c, r, uc, ic, p, q, sampled, smp, wmask);
+                st_row<K, MODE>(a.P, uc, m, p);
+                if (STATS && sampled) record(smp, uc, ic);
             }
-            cur = nxt;
-            nxt = nn;
-            mark_repeats(nxt, cur);
-            nn = (nxt.cnt > 0) ? fetch_chunk(ticket_chunk(ticket)) : none;
-            if (nn.cnt > 0) ticket = request_ticket();
         }
-        if (cur_ic != kNoRow) st_row<K, MODE>(a.Q, cur_ic, m, q);
-        if (STATS) flush_item_stats();
+        if (!more) break;
+        __syncwarp(wmask);           // every lane has read this buffer's records
+        publish(cb);                 // the chunk after next takes the buffer of the finished one
+        cb ^= 1;
     }
+    cp_wait<0>();
+    if (cur_ic != kNoRow) st_row<K, MODE>(a.Q, cur_ic, m, q);
+    if (STATS) flush_item_stats();
 }
 
 __global__ void reduce_stats_kernel(float* sets, int copies, size_t stride, size_t n) {
@@ -504,38 +537,61 @@ int sm_count() {
     return sms;
 }
 
+template <int K, int KIND, int MODE, bool STATS, int NS>
+cudaError_t launch_ns(KernelArgs a, unsigned warps_per_sm, unsigned workers, cudaStream_t st, LaunchShape* shape) {
+    constexpr int TS = K / 8;
+    constexpr int kPerWarp = 32 / TS;
+    using SM = WorkerSmem<K, MODE, NS>;
+    auto kern = train_kernel<K, KIND, MODE, STATS, NS>;
+    int grid, block;
+    const unsigned warps = (workers + kPerWarp - 1) / kPerWarp;
+    if (warps <= 8) {
+        // a single block (deterministic runs, tiny worker counts) uses exactly the requested workers
+        grid = 1; block = (int)(32 * warps);
+        a.workers = workers;
+    } else {
+        // the same number of warps on every SM, in blocks of at most 8 warps, and no more blocks than
+        // the SM can hold at once (registers, shared memory)
+        const unsigned sms = (unsigned)sm_count();
+        unsigned blocks_per_sm = (warps_per_sm + 7) / 8;
+        const unsigned warps_per_block = (warps_per_sm + blocks_per_sm - 1) / blocks_per_sm;
+        block = (int)(32 * warps_per_block);
+        const size_t smem_block = (size_t)warps_per_block * kPerWarp * SM::kBytes;
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_block);
+        if (e != cudaSuccess) return e;
+        int fit = 0;
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&fit, kern, block, smem_block);
+        if (e != cudaSuccess) return e;
+        if (fit < 1) return cudaErrorLaunchOutOfResources;
+        if (blocks_per_sm > (unsigned)fit) blocks_per_sm = (unsigned)fit;
+        grid = (int)(sms * blocks_per_sm);
+        a.workers = (unsigned)grid * warps_per_block * kPerWarp;
+    }
+    const size_t smem = (size_t)(block / 32) * kPerWarp * SM::kBytes;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    kern<<<grid, block, smem, st>>>(a);
+    if (shape) { shape->grid = grid; shape->block = block; shape->smem = smem; shape->workers = a.workers; }
+    return cudaGetLastError();
+}
+
+// Launches with few warps per SM get deep rings (each worker hides the memory latency on its own);
+// launches that fill the SM get shallow ones, which is what the shared memory allows there.
 template <int K, int KIND, int MODE, bool STATS>
 cudaError_t launch_one(const KernelArgs& args, unsigned workers, cudaStream_t st, LaunchShape* shape) {
     constexpr int TS = K / 8;
     constexpr int kPerWarp = 32 / TS;
-    KernelArgs a = args;
-    // Spread the workers evenly: the same number of warps on every SM, in blocks of at most 8 warps.
+    constexpr int kDeep = (MODE == ROWS_HALF) ? 8 : 4;
+    constexpr int kShallow = kDeep / 2;
     if (workers < 1) workers = 1;
-    // more workers than can be resident at once (64 warps per SM) only add launch overhead
+    // more workers than can ever be resident at once (64 warps per SM) only add launch overhead
     const unsigned resident_cap = (unsigned)sm_count() * 64u * kPerWarp;
     if (workers > resident_cap) workers = resident_cap;
     const unsigned warps = (workers + kPerWarp - 1) / kPerWarp;
-    int grid, block;
-    unsigned per_sm = warps;
-    if (warps <= 8) {
-        grid = 1; block = (int)(32 * warps);
-    } else {
-        const unsigned sms = (unsigned)sm_count();
-        per_sm = (warps + sms - 1) / sms;
-        const unsigned blocks_per_sm = (per_sm + 7) / 8;
-        const unsigned warps_per_block = (per_sm + blocks_per_sm - 1) / blocks_per_sm;
-        grid = (int)(sms * blocks_per_sm);
-        block = (int)(32 * warps_per_block);
-    }
-    const bool deep = per_sm <= 12;
-    auto kern = deep ? train_kernel<K, KIND, MODE, STATS, true> : train_kernel<K, KIND, MODE, STATS, false>;
-    const size_t smem = 0;
-    const unsigned capacity = (unsigned)grid * (unsigned)(block / 32) * kPerWarp;
-    // a single block (deterministic runs, tiny worker counts) uses exactly the requested workers
-    a.workers = (grid == 1) ? workers : capacity;
-    kern<<<grid, block, smem, st>>>(a);
-    if (shape) { shape->grid = grid; shape->block = block; shape->smem = smem; shape->workers = a.workers; }
-    return cudaGetLastError();
+    const unsigned sms = (unsigned)sm_count();
+    const unsigned per_sm = warps <= 8 ? warps : (warps + sms - 1) / sms;
+    if (per_sm <= 20) return launch_ns<K, KIND, MODE, STATS, kDeep>(args, per_sm, workers, st, shape);
+    return launch_ns<K, KIND, MODE, STATS, kShallow>(args, per_sm, workers, st, shape);
 }
 
 template <int K>
