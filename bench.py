@@ -222,9 +222,9 @@ def run_sharded(args, S, M, cfg, rank, world, local_rank):
             "metric": "rating updates/sec (k=128)", "value": value, "unit": "updates/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f16+f32", "data": "synthetic",
-            "config": {"workload": args.workload_desc, "parallelism": f"users pinned on {world} GPUs, {world} item blocks rotating by NCCL send/recv",
+            "config": {"workload": args.workload_desc, "parallelism": f"users pinned on {world} GPUs, {world} interleaved item blocks rotating by NCCL send/recv",
                        "l2": "inputs larger than L2", "rmse_before": rmse_before, "rmse_after": rmse_after,
-                       "item_block_rows": plan.block_rows, "max_ratings_on_one_rank": int(mx.item()),
+                       "item_blocks": "row r of the degree-sorted item index belongs to block r mod N", "max_ratings_on_one_rank": int(mx.item()),
                        "nvlink_bytes_sent_per_rank_per_step": sent / max(args.steps, 1), "workers_per_gpu": workers,
                        "timing": "CUDA events on the engine's stream around the K steps, max over ranks", "wall_ms_per_step_rank0": wall_ms / max(args.steps, 1)},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak * world, "unit": "GB/s", "frac": achieved / (peak * world),

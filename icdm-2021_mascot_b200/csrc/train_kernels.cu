@@ -5,12 +5,23 @@
 // model converges per epoch.  This engine keeps that meaning of `-wg` - a worker is a group of
 // K/8 lanes (16 for k=128, 8 for k=64; two or four workers per warp) that applies its ratings
 // strictly one after the other - and gets its speed from making each worker fast instead of adding
-// workers: every lane holds eight consecutive physical elements of a row (one 128-bit access for
-// binary16 storage, two for fp32), the rating records of a chunk are fetched coalesced one chunk
-// ahead, user rows are prefetched up to eight ratings ahead into a register ring, the row of an
-// item that repeats (the stream is item-sorted inside shuffle windows) stays in registers for the
-// whole run, and the next run's item row is prefetched when a run starts.  In the steady state a
-// worker waits for nothing but its own dot-product reduction.
+// workers:
+//   * every lane holds eight consecutive physical elements of a row (one 128-bit access for
+//     binary16 storage, two for fp32);
+//   * the rating records of a chunk (one rating per lane) are loaded one chunk ahead, tagged
+//     (repeated user, start of an item run, repeated item) and put into shared memory, from where
+//     the worker reads one rating with a single 128-bit broadcast load;
+//   * rows travel global -> shared memory by cp.async into small per-worker rings, user rows a few
+//     ratings ahead, item rows one rating ahead; copy groups complete in order, so the wait for the
+//     row of rating j leaves the younger copies in flight (register loads cannot do that: the wait
+//     for an old load also waits for every younger load on the same scoreboard);
+//   * the row of an item that repeats (the stream is item-sorted inside shuffle windows) stays in
+//     registers for the whole run and is written back once;
+//   * chunks are handed out in spans of eight through one atomic ticket per span.
+// The leads are short on purpose.  Between the request of a row and its write-back every update
+// another worker makes to that row is lost, so the loss grows with (workers x lead); measured on
+// the 100M-rating configuration a lead of seven ratings on both sides costs 1.5 % of final RMSE
+// where three (users) and one (items) cost nothing.
 //
 // ELEMENT ORDER.  layout.cuh stores rows permuted so that lane m of a worker holds the elements of
 // reference lanes m and m+16 (k=128) or m, m+16, m+8, m+24 (k=64).  With pair products
@@ -326,13 +337,16 @@ template <int K, int MODE, int NS> struct WorkerSmem {
     static constexpr int kBytes = kRecBytes + 2 * NS * kRowBytes;
 };
 
-// NS: slots per ring.  Rows are requested D = NS-1 ratings ahead.
-template <int K, int KIND, int MODE, bool STATS, int NS>
+// NS: slots per ring.  User rows are requested D ratings ahead, item rows DI ratings ahead
+// (DI <= D <= NS-1).  The lead is kept as short as the memory latency allows: a row that another
+// worker updates between the request and the write-back loses that update, and the chance of that
+// grows with the lead.
+template <int K, int KIND, int MODE, bool STATS, int NS, int D, int DI>
 __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
     using SM = WorkerSmem<K, MODE, NS>;
     constexpr int TS = SM::TS;                     // lanes per worker = ratings per chunk
-    constexpr int D = NS - 1;
     static_assert(TS % NS == 0, "the ring must divide the chunk");
+    static_assert(DI >= 1 && DI <= D && D <= NS - 1, "leads must fit the ring");
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31;
     const int m = lane % TS;
@@ -413,7 +427,7 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
         }
         uint32_t f = 0;
         if (m < inflight.cnt) f = F_VALID | (udup ? F_UDUP : 0u) | (rs ? F_RS : 0u) | ((rs && idup) ? F_IDUP : 0u);
-        recs[b * TS + m] = make_uint4(inflight.u, inflight.i, f, __float_as_uint(inflight.r));
+        recs[b * TS + m] = make_uint4(f, inflight.i, inflight.u, __float_as_uint(inflight.r));
         if (b) base1 = inflight.base; else base0 = inflight.base;
         prev_u = inflight.u; prev_i = inflight.i;
         inflight = (inflight.cnt > 0) ? fetch_chunk(next_chunk_id()) : inflight;
@@ -463,15 +477,28 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
     };
     Sample smp;
 
-    // requests the rows of the rating described by record `rx` into ring slot `slot`
-    auto request_rows = [&](const uint4& rx, int slot) {
-        if ((rx.z & (F_VALID | F_UDUP)) == F_VALID) cp_row<K, MODE>(uring + slot * SM::kRowBytes, a.P, rx.x, m);
-        if ((rx.z & (F_VALID | F_RS | F_IDUP)) == (F_VALID | F_RS)) cp_row<K, MODE>(iring + slot * SM::kRowBytes, a.Q, rx.y, m);
-        cp_commit();
+    // requests the user row of the rating with record `rx` / the item row of the rating whose first
+    // two record words are `ri`, into ring slot `slot`
+    auto request_user = [&](const uint4& rx, int slot) {
+        if ((rx.x & (F_VALID | F_UDUP)) == F_VALID) cp_row<K, MODE>(uring + slot * SM::kRowBytes, a.P, rx.z, m);
     };
-    // prologue: the rows of the first D ratings, one copy group per rating
+    auto request_item = [&](const uint2& ri, int slot) {
+        if ((ri.x & (F_VALID | F_RS | F_IDUP)) == (F_VALID | F_RS)) cp_row<K, MODE>(iring + slot * SM::kRowBytes, a.Q, ri.y, m);
+    };
+    // Copy groups complete in order.  Every iteration commits two: first the item row of the rating
+    // DI ahead, then the user row of the rating D ahead.  When rating j is used, the groups younger
+    // than its item row's are 2*DI-1 and those younger than its user row's are 2*(D-1); waiting for
+    // exactly that many to remain pending leaves every younger copy in flight.
+    constexpr int kPendUser = 2 * (D - 1);
+    constexpr int kPendItem = (2 * DI - 1 < kPendUser) ? 2 * DI - 1 : kPendUser;
+    // prologue: the groups of the iterations -D .. -1
 #pragma unroll
-    for (int t = 0; t < D; t++) request_rows(recs[t], t);
+    for (int t = 0; t < D; t++) {
+        if (t - (D - DI) >= 0) request_item(*reinterpret_cast<const uint2*>(recs + (t - (D - DI))), t - (D - DI));
+        cp_commit();
+        request_user(recs[t], t);
+        cp_commit();
+    }
 
     int cb = 0;                                     // buffer of the chunk in use
     for (;;) {
@@ -484,25 +511,30 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
             for (int t = 0; t < NS; t++) {
                 const int j = jb + t;
                 const uint4 rec = rc[j];
-                if (!(rec.z & F_VALID)) { more = false; break; }
-                const uint32_t uc = rec.x, ic = rec.y;
+                if (!(rec.x & F_VALID)) { more = false; break; }
+                const uint32_t uc = rec.z, ic = rec.y;
                 const float r = __uint_as_float(rec.w);
                 const bool sampled = STATS && ((cb ? base1 : base0) + j >= a.st.first_sample_pos);
-                cp_wait<(D > 0 ? D - 1 : 0)>();
-                if (rec.z & F_RS) {
+                if (rec.x & F_RS) {
+                    cp_wait<kPendItem>();
                     if (cur_ic != kNoRow) st_row<K, MODE>(a.Q, cur_ic, m, q);
-                    if (rec.z & F_IDUP) q = ld_row<K, MODE>(a.Q, ic, m);
+                    if (rec.x & F_IDUP) q = ld_row<K, MODE>(a.Q, ic, m);
                     else q = lds_row<K, MODE>(iring + t * SM::kRowBytes, ic, m);
                     cur_ic = ic;
+                } else {
+                    cp_wait<kPendUser>();
                 }
                 Raw<MODE> p;
-                if (rec.z & F_UDUP) p = ld_row<K, MODE>(a.P, uc, m);
+                if (rec.x & F_UDUP) p = ld_row<K, MODE>(a.P, uc, m);
                 else p = lds_row<K, MODE>(uring + t * SM::kRowBytes, uc, m);
-                // request the rows of the rating D ahead into the slot that was read one rating ago
+                // request the user row of the rating D ahead and the item row of the rating DI ahead,
+                // into slots whose previous contents have been consumed
                 {
-                    const int x = j + D;
-                    const uint4 rx = (x < TS) ? rc[x] : rn[x - TS];
-                    request_rows(rx, (t + D) & (NS - 1));
+                    const int x = j + D, xi = j + DI;
+                    request_item(*reinterpret_cast<const uint2*>((xi < TS) ? rc + xi : rn + (xi - TS)), (t + DI) & (NS - 1));
+                    cp_commit();
+                    request_user((x < TS) ? rc[x] : rn[x - TS], (t + D) & (NS - 1));
+                    cp_commit();
                 }
                 update_one<K, KIND, MODE, STATS>(c, r, uc, ic, p, q, sampled, smp, wmask);
                 st_row<K, MODE>(a.P, uc, m, p);
@@ -537,12 +569,12 @@ int sm_count() {
     return sms;
 }
 
-template <int K, int KIND, int MODE, bool STATS, int NS>
+template <int K, int KIND, int MODE, bool STATS, int NS, int D, int DI>
 cudaError_t launch_ns(KernelArgs a, unsigned warps_per_sm, unsigned workers, cudaStream_t st, LaunchShape* shape) {
     constexpr int TS = K / 8;
     constexpr int kPerWarp = 32 / TS;
     using SM = WorkerSmem<K, MODE, NS>;
-    auto kern = train_kernel<K, KIND, MODE, STATS, NS>;
+    auto kern = train_kernel<K, KIND, MODE, STATS, NS, D, DI>;
     int grid, block;
     const unsigned warps = (workers + kPerWarp - 1) / kPerWarp;
     if (warps <= 8) {
@@ -575,14 +607,10 @@ cudaError_t launch_ns(KernelArgs a, unsigned warps_per_sm, unsigned workers, cud
     return cudaGetLastError();
 }
 
-// Launches with few warps per SM get deep rings (each worker hides the memory latency on its own);
-// launches that fill the SM get shallow ones, which is what the shared memory allows there.
 template <int K, int KIND, int MODE, bool STATS>
 cudaError_t launch_one(const KernelArgs& args, unsigned workers, cudaStream_t st, LaunchShape* shape) {
     constexpr int TS = K / 8;
     constexpr int kPerWarp = 32 / TS;
-    constexpr int kDeep = (MODE == ROWS_HALF) ? 8 : 4;
-    constexpr int kShallow = kDeep / 2;
     if (workers < 1) workers = 1;
     // more workers than can ever be resident at once (64 warps per SM) only add launch overhead
     const unsigned resident_cap = (unsigned)sm_count() * 64u * kPerWarp;
@@ -590,8 +618,14 @@ cudaError_t launch_one(const KernelArgs& args, unsigned workers, cudaStream_t st
     const unsigned warps = (workers + kPerWarp - 1) / kPerWarp;
     const unsigned sms = (unsigned)sm_count();
     const unsigned per_sm = warps <= 8 ? warps : (warps + sms - 1) / sms;
-    if (per_sm <= 20) return launch_ns<K, KIND, MODE, STATS, kDeep>(args, per_sm, workers, st, shape);
-    return launch_ns<K, KIND, MODE, STATS, kShallow>(args, per_sm, workers, st, shape);
+    // Rings of four slots: user rows are requested three ratings ahead, item rows one rating ahead.
+    // Launches that fill the SM with fp32 rows only have the shared memory for two slots.
+    if constexpr (MODE == ROWS_HALF) {
+        return launch_ns<K, KIND, MODE, STATS, 4, 3, 1>(args, per_sm, workers, st, shape);
+    } else {
+        if (per_sm <= 20) return launch_ns<K, KIND, MODE, STATS, 4, 3, 1>(args, per_sm, workers, st, shape);
+        return launch_ns<K, KIND, MODE, STATS, 2, 1, 1>(args, per_sm, workers, st, shape);
+    }
 }
 
 template <int K>

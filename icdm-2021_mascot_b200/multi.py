@@ -2,8 +2,10 @@
 
 Scheme (the reference is single-GPU; this has no counterpart there): the users are dealt to the
 ranks so that every rank gets the same mix of degrees, and with them their ratings and their rows of
-P; the items - in the engine's degree-sorted index space - are cut into `world` contiguous blocks of
-about equal rating count.  Sub-epoch s: rank g trains its ratings that fall into item block
+P; the items - in the engine's degree-sorted index space - are dealt round-robin into `world` blocks
+(row r belongs to block r mod world), so that every block holds the same mix of popular and rare
+items: the ranks then take the same time for a sub-epoch whichever block they hold, and no rank
+ever has all its workers on a handful of very popular rows.  Sub-epoch s: rank g trains its ratings that fall into item block
 (g + s) mod world, then hands that block of Q to rank g-1 and receives block (g + s + 1) mod world
 from rank g+1.  At any time the ranks work on disjoint users AND disjoint items, so there are no
 races between GPUs, and after `world` sub-epochs every block is back home.  The only data-path
@@ -17,13 +19,12 @@ import numpy as np
 
 
 class Plan:
-    """Who owns which user, which item block an item belongs to, and the row range of each block."""
+    """Who owns which user and which item block an item belongs to."""
 
-    def __init__(self, world, user_rank, item_block, block_rows, user_degree, item_degree, item_sorted_index):
+    def __init__(self, world, user_rank, item_block, user_degree, item_degree, item_sorted_index):
         self.world = world
         self.user_rank = user_rank                # [n_users] compact id -> rank
-        self.item_block = item_block              # [n_items] compact id -> block
-        self.block_rows = block_rows              # [(row_begin, row_end)] in item sorted-index space
+        self.item_block = item_block              # [n_items] compact id -> block (= sorted index mod world)
         self.user_degree = user_degree
         self.item_degree = item_degree
         self.item_sorted_index = item_sorted_index
@@ -44,20 +45,8 @@ def make_plan(train_u, train_i, n_users, n_items, world):
     user_rank[user_sorted[::-1]] = np.where(rnd % 2 == 0, idx, world - 1 - idx)
     item_sorted_index = np.empty(n_items, np.uint32)
     item_sorted_index[item_sorted] = np.arange(n_items, dtype=np.uint32)
-    # contiguous blocks of about equal rating count (an item is never split)
-    cum = np.cumsum(item_degree[item_sorted].astype(np.int64))
-    total = int(cum[-1]) if n_items else 0
-    bounds = [0]
-    for b in range(1, world):
-        cut = int(np.searchsorted(cum, total * b / world, side="left")) + 1
-        bounds.append(min(max(cut, bounds[-1]), n_items))
-    bounds.append(n_items)
-    block_rows = [(bounds[b], bounds[b + 1]) for b in range(world)]
-    block_of_row = np.zeros(n_items, np.int32)
-    for b, (lo, hi) in enumerate(block_rows):
-        block_of_row[lo:hi] = b
-    item_block = block_of_row[item_sorted_index]
-    return Plan(world, user_rank, item_block, block_rows, user_degree, item_degree, item_sorted_index)
+    item_block = (item_sorted_index % np.uint32(world)).astype(np.int32)
+    return Plan(world, user_rank, item_block, user_degree, item_degree, item_sorted_index)
 
 
 def shard_ratings(plan, rank, train, test):
@@ -89,19 +78,28 @@ def workers_per_rank(n_train_global, world):
 def exchange_block(dist, shard, send_block, recv_block, dst, src):
     """Hand `send_block` to rank dst and take `recv_block` from rank src (in place, both arenas).
 
-    On GPUs the caller has made the engine's stream the current one (shard.device_order()), so the
-    transfer starts when the kernel queued before it has finished and the next kernel waits for it:
-    the ordering is done by the device, the host never waits."""
+    A block is a strided set of rows, so it is packed into a contiguous buffer for the transfer and
+    unpacked on arrival.  On GPUs the caller has made the engine's stream the current one
+    (shard.device_order()), so packing and transfer start when the kernel queued before them has
+    finished and the next kernel waits for the unpacking: the ordering is done by the device, the
+    host never waits."""
+    import torch
     if send_block == recv_block and dst == src:
         return 0
     ops, nbytes = [], 0
     for t in shard.block_tensors(send_block):
-        ops.append(dist.P2POp(dist.isend, t, dst))
-        nbytes += t.numel() * t.element_size()
+        packed = t.contiguous()
+        ops.append(dist.P2POp(dist.isend, packed, dst))
+        nbytes += packed.numel() * packed.element_size()
+    arriving = []
     for t in shard.block_tensors(recv_block):
-        ops.append(dist.P2POp(dist.irecv, t, src))
+        buf = torch.empty(t.shape, dtype=t.dtype, device=t.device)
+        ops.append(dist.P2POp(dist.irecv, buf, src))
+        arriving.append((t, buf))
     for req in dist.batch_isend_irecv(ops):
         req.wait()
+    for t, buf in arriving:
+        t.copy_(buf)
     return nbytes
 
 
@@ -135,7 +133,9 @@ def gather_item_factors(dist, shard, world):
     with shard.device_order():
         for b in range(world):
             for t in shard.block_tensors(b):
-                dist.broadcast(t, src=b)
+                buf = t.contiguous()
+                dist.broadcast(buf, src=b)
+                t.copy_(buf)
     shard.sync()
 
 
@@ -163,6 +163,7 @@ class EngineShard:
         self.M, self.plan, self.rank = M, plan, rank
         mine, seg, my_test = shard_ratings(plan, rank, train, test)
         self.n_local = int(mine.size)
+        self.n_items = int(n_items)
         self.engine = M.Engine(cfg)
         self.engine.set_ratings_sharded(mine, seg, my_test, n_users, n_items, plan.user_degree, plan.item_degree)
         self.device = torch.device("cuda", int(cfg.device))
@@ -175,13 +176,14 @@ class EngineShard:
         return torch.cuda.stream(self.stream)
 
     def block_tensors(self, b):
+        """Strided byte views [rows of block b, bytes per row] of the item arenas."""
         import torch
         if b not in self._views:
-            lo, hi = self.plan.block_rows[b]
             views = []
-            for ptr, nbytes in self.engine.item_rows(lo, hi):
+            for ptr, nbytes in self.engine.item_rows(0, self.n_items):
                 if ptr and nbytes:
-                    views.append(torch.as_tensor(_DeviceBytes(ptr, nbytes), device=self.device))
+                    whole = torch.as_tensor(_DeviceBytes(ptr, nbytes), device=self.device).view(self.n_items, nbytes // self.n_items)
+                    views.append(whole[b::self.plan.world])
             self._views[b] = views
         return self._views[b]
 

@@ -66,10 +66,10 @@ class OracleShard:
         self.processed = 0
 
     def block_tensors(self, b):
-        lo, hi = self.plan.block_rows[b]
-        # raw bytes, like the device views of the real engine
-        return [torch.from_numpy(self.model.Q16[lo:hi].reshape(-1).view(np.uint8)),
-                torch.from_numpy(self.model.Q32[lo:hi].reshape(-1).view(np.uint8))]
+        # strided views of raw bytes [rows of the block, bytes per row], like the device views of the real engine
+        n, w = self.model.Q16.shape[0], self.plan.world
+        return [torch.from_numpy(self.model.Q16.view(np.uint8).reshape(n, -1))[b::w],
+                torch.from_numpy(self.model.Q32.view(np.uint8).reshape(n, -1))[b::w]]
 
     def is_check_epoch(self, epoch):
         return self.O.is_check_epoch(epoch, HYPER["epochs"], HYPER["interval"])
@@ -189,8 +189,7 @@ def test_plan_is_a_partition_with_balanced_users():
     R, test, P, Q, n_users, n_items = dataset()
     for world in (1, 2, 4, 8):
         plan = multi.make_plan(R["u"], R["i"], n_users, n_items, world)
-        assert plan.block_rows[0][0] == 0 and plan.block_rows[-1][1] == n_items
-        assert all(plan.block_rows[b][1] == plan.block_rows[b + 1][0] for b in range(world - 1))
+        assert plan.item_block.min() == 0 and plan.item_block.max() == world - 1
         total = 0
         for rank in range(world):
             mine, seg, my_test = multi.shard_ratings(plan, rank, R, test)
@@ -198,7 +197,10 @@ def test_plan_is_a_partition_with_balanced_users():
             assert seg[0] == 0 and seg[-1] == mine.size and (np.diff(seg.astype(np.int64)) >= 0).all()
             for b in range(world):
                 rows = plan.item_sorted_index[mine["i"][int(seg[b]):int(seg[b + 1])]]
-                assert ((rows >= plan.block_rows[b][0]) & (rows < plan.block_rows[b][1])).all()
+                assert (rows % world == b).all()
+        # every block gets about the same number of ratings (same mix of popular and rare items)
+        per_block = np.bincount(plan.item_block[R["i"]], minlength=world)
+        assert per_block.max() <= 1.25 * per_block.mean() + plan.item_degree.max()
         assert total == R.size
         per_rank = np.bincount(plan.user_rank[R["u"]], minlength=world)
         assert per_rank.max() <= 1.25 * per_rank.mean() + plan.user_degree.max()
