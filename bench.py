@@ -41,37 +41,68 @@ def _load(name, path):
 
 
 class ClockSampler(threading.Thread):
-    """Samples SM clock and throttle reasons of one GPU while the timed region runs."""
+    """Samples SM clocks and throttle reasons of the given GPUs while the timed region runs.
+
+    Reads through NVML inside this process (a query takes microseconds); falls back to polling
+    `nvidia-smi` when the NVML binding is missing.  Read-only: no setting of any GPU is touched."""
 
     FIELDS = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+    # bits of nvmlDeviceGetCurrentClocksEventReasons
+    BITS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
 
-    def __init__(self, index):
+    def __init__(self, indices):
         super().__init__(daemon=True)
-        self.index = index
-        self.samples = []
+        self.indices = [indices] if isinstance(indices, int) else list(indices)
+        self.mhz, self.max_mhz, self.reasons = [], None, set()
+        self.count = 0
         self.stop_flag = threading.Event()
 
-    def run(self):
+    def _run_nvml(self):
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            hs = [pynvml.nvmlDeviceGetHandleByIndex(i) for i in self.indices]
+            self.max_mhz = float(max(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM) for h in hs))
+            reasons_of = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+            while not self.stop_flag.is_set():
+                for h in hs:
+                    self.mhz.append(float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)))
+                    mask = int(reasons_of(h))
+                    self.reasons.update(n for n, bit in self.BITS.items() if mask & bit)
+                self.count += 1
+                self.stop_flag.wait(0.05)
+        finally:
+            pynvml.nvmlShutdown()
+
+    def _run_smi(self):
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         while not self.stop_flag.is_set():
             try:
-                out = subprocess.run(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                out = subprocess.run(["nvidia-smi", "-i", ",".join(str(i) for i in self.indices), f"--query-gpu={self.FIELDS}",
                                       "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
-                parts = [p.strip() for p in out.strip().split(",")]
-                if len(parts) >= 6:
-                    self.samples.append(parts)
+                for row in out.strip().splitlines():
+                    parts = [p.strip() for p in row.split(",")]
+                    if len(parts) >= 6 and parts[0].replace(".", "").isdigit():
+                        self.mhz.append(float(parts[0])); self.max_mhz = float(parts[1])
+                        self.reasons.update(n for j, n in enumerate(names) if parts[2 + j].lower().startswith("active"))
+                self.count += 1
             except Exception:
                 pass
-            self.stop_flag.wait(0.1)
+            self.stop_flag.wait(0.5)
+
+    def run(self):
+        try:
+            self._run_nvml()
+        except Exception:
+            self._run_smi()
 
     def summary(self):
-        if not self.samples:
+        if not self.mhz:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        mhz = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for j, n in enumerate(names) if any(s[2 + j].lower().startswith("active") for s in self.samples)]
-        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": float(self.samples[0][1]),
-                "reasons": reasons, "samples": len(self.samples)}
+        order = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        return {"sm_mhz": statistics.median(self.mhz), "sm_max_mhz": self.max_mhz,
+                "reasons": [n for n in order if n in self.reasons], "samples": self.count, "gpus": self.indices}
 
 
 def measured_peak():
@@ -190,21 +221,29 @@ def run_sharded(args, S, M, cfg, rank, world, local_rank):
         MU.train_epoch(dist, shard, rank, world, epoch, comm_device=dev); epoch += 1
     MU.gather_item_factors(dist, shard, world)
     rmse_before = MU.global_rmse(dist, shard, world, comm_device=dev)
-    sampler = ClockSampler(local_rank)
-    sampler.start()
+    sampler = ClockSampler(list(range(world)))      # rank 0 watches every GPU of the job
+    if rank == 0:
+        sampler.start()
     # device time: CUDA events on the engine's stream, which also orders the block transfers
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     dist.barrier(); shard.sync(); torch.cuda.synchronize()
     t0 = time.perf_counter()
     ev0.record(shard.stream)
     sent = 0
+    marks = []
     for _ in range(args.steps):
+        chk = 1 if shard.is_check_epoch(epoch) else 0
         b, _pr = MU.train_epoch(dist, shard, rank, world, epoch, comm_device=dev); epoch += 1
         sent += b
+        ev = torch.cuda.Event(enable_timing=True); ev.record(shard.stream)
+        marks.append((ev, chk, int(_pr[0]) + int(_pr[1])))
     ev1.record(shard.stream)
     shard.sync(); torch.cuda.synchronize()
     wall_ms = (time.perf_counter() - t0) * 1e3
     mine_ms = ev0.elapsed_time(ev1)
+    per_step, prev = [], ev0
+    for ev, chk, promoted in marks:
+        per_step.append([round(prev.elapsed_time(ev), 3), chk, promoted]); prev = ev
     dist.barrier()
     t = torch.tensor([mine_ms], dtype=torch.float64, device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -213,7 +252,9 @@ def run_sharded(args, S, M, cfg, rank, world, local_rank):
     mx = loc.clone(); dist.all_reduce(mx, op=dist.ReduceOp.MAX)
     MU.gather_item_factors(dist, shard, world)
     rmse_after = MU.global_rmse(dist, shard, world, comm_device=dev)
-    sampler.stop_flag.set(); sampler.join(timeout=3)
+    sampler.stop_flag.set()
+    if rank == 0:
+        sampler.join(timeout=3)
     if rank == 0:
         peak, peak_kind = measured_peak()
         value = n_train * args.steps / (total_ms * 1e-3)
@@ -225,7 +266,7 @@ def run_sharded(args, S, M, cfg, rank, world, local_rank):
             "config": {"workload": args.workload_desc, "parallelism": f"users pinned on {world} GPUs, {world} interleaved item blocks rotating by NCCL send/recv",
                        "l2": "inputs larger than L2", "rmse_before": rmse_before, "rmse_after": rmse_after,
                        "item_blocks": "row r of the degree-sorted item index belongs to block r mod N", "max_ratings_on_one_rank": int(mx.item()),
-                       "nvlink_bytes_sent_per_rank_per_step": sent / max(args.steps, 1), "workers_per_gpu": workers,
+                       "nvlink_bytes_sent_per_rank_per_step": sent / max(args.steps, 1), "workers_per_gpu": workers, "rank0_ms_check_flag_promoted_groups_per_step": per_step,
                        "timing": "CUDA events on the engine's stream around the K steps, max over ranks", "wall_ms_per_step_rank0": wall_ms / max(args.steps, 1)},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak * world, "unit": "GB/s", "frac": achieved / (peak * world),
                          "traffic": None, "peak_kind": f"of {peak_kind} (x{world} GPUs)"},

@@ -118,11 +118,15 @@ def train_epoch(dist, shard, rank, world, epoch, comm_device="cpu"):
                 sent += exchange_block(dist, shard, b, (rank + s + 1) % world, (rank - 1) % world, (rank + 1) % world)
         promoted = (0, 0)
         if check:
-            sums = [torch.from_numpy(a).to(comm_device) for a in shard.stats_fetch()]
+            parts = shard.stats_fetch()
             if world > 1:
-                for t in sums:
-                    dist.all_reduce(t)
-            promoted = shard.stats_apply(epoch, *[t.cpu().numpy() for t in sums])
+                # one message for the four arrays
+                flat = torch.from_numpy(np.concatenate([np.asarray(a, np.float32).reshape(-1) for a in parts])).to(comm_device)
+                dist.all_reduce(flat)
+                flat = flat.cpu().numpy()
+                cuts = np.cumsum([0] + [a.size for a in parts])
+                parts = [flat[cuts[j]:cuts[j + 1]] for j in range(len(parts))]
+            promoted = shard.stats_apply(epoch, *parts)
     return sent, promoted
 
 
