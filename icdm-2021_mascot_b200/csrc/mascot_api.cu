@@ -25,6 +25,10 @@ struct mascot_handle {
     int K = 0;
     TrainKind kind = KIND_MIXED;
     bool grouped = false;          // m-quantization / g-switching active (MASCOT variant)
+    // MuPPET precision policy (mf_methods.cu:586-601): index into {8, 12, 14, 16, 32} and its history
+    int mup_idx = 0, mup_switched_epoch = -1, mup_violations = 0;
+    float mup_max_diversity = -1.f;
+    std::vector<float> mup_norms_epoch, mup_sums_epoch;
     cudaStream_t stream = nullptr;
     cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
 
@@ -175,6 +179,12 @@ uint64_t algorithmic_bytes(const mascot_handle* h) {
     return (uint64_t)total;
 }
 
+// MuPPET's ladder of pass widths (mf_methods.cu:597).
+int muppet_width_at(int idx) {
+    static const int widths[5] = {8, 12, 14, 16, 32};
+    return widths[idx < 0 ? 0 : (idx < 4 ? idx : 4)];
+}
+
 size_t stats_floats(const mascot_handle* h) {
     return (size_t)(h->uend.size() + h->iend.size()) * (h->K + 1);
 }
@@ -301,8 +311,9 @@ int mascot_create(const mascot_config* cfg, mascot_handle** out) {
         case MASCOT_V_SGD: kind = KIND_FP32; break;
         case MASCOT_V_MPT: kind = KIND_MPT; break;
         case MASCOT_V_MEMQUANT: kind = KIND_MEMQUANT; break;
-        case MASCOT_V_AFP: case MASCOT_V_MUPPET:
-            return fail(nullptr, MASCOT_ERR_UNSUPPORTED, "AFP / MuPPET trainers are not implemented by this engine yet");
+        case MASCOT_V_MUPPET: kind = KIND_MUPPET; break;
+        case MASCOT_V_AFP:
+            return fail(nullptr, MASCOT_ERR_UNSUPPORTED, "the AFP trainer is not implemented by this engine yet");
         default: return fail(nullptr, MASCOT_ERR_BAD_ARG, "unknown training variant");
     }
     int ndev = 0;
@@ -314,6 +325,8 @@ int mascot_create(const mascot_config* cfg, mascot_handle** out) {
     mascot_handle* h = new (std::nothrow) mascot_handle();
     if (!h) return fail(nullptr, MASCOT_ERR_OOM, "host allocation failed");
     h->cfg = *cfg; h->K = (int)cfg->k; h->kind = kind; h->grouped = (cfg->version == MASCOT_V_MASCOT);
+    h->mup_idx = cfg->is_yahoo ? 1 : 0;            // mf_methods.cu:600-601
+    for (int j = 0; j < 5; j++) if (cfg->muppet_width == (uint32_t)muppet_width_at(j)) h->mup_idx = j;
     h->lr.resize(cfg->epoch);
     for (uint32_t e = 0; e < cfg->epoch; e++) h->lr[e] = lr_at(*cfg, e);
     cudaError_t e = cudaSetDevice(cfg->device);
@@ -519,6 +532,39 @@ unsigned worker_count(const mascot_handle* h, uint64_t n) {
     return (unsigned)std::min<uint64_t>(std::max<uint64_t>(n / 8192, 512), 1u << 20);
 }
 
+// Width of MuPPET's forward and backward pass this epoch (mf_methods.cu:597, 623-624).
+int muppet_bits(const mascot_handle* h) { return muppet_width_at(h->mup_idx); }
+
+// MuPPET's switching rule after epoch e (mf_methods.cu:586-595, 660-695): over the last three epochs,
+// gradient diversity = sum of the sampled squared gradient norms / squared norm of the summed sampled
+// updates; when the largest diversity seen since the last switch exceeds the current one by more than a
+// decaying threshold, the next wider format is used from the next epoch on.
+void muppet_policy(mascot_handle* h, uint32_t epoch) {
+    const int K = h->K, e = (int)epoch, resolution = 3;
+    const float alpha = 1.0f, beta = 1.5f, lambda_thr = 0.3f;
+    const float threshold = alpha + (beta * std::exp(-1 * lambda_thr * (e)));
+    if ((int)h->mup_norms_epoch.size() <= e) { h->mup_norms_epoch.resize(e + 1, 0.f); h->mup_sums_epoch.resize((size_t)(e + 1) * K, 0.f); }
+    h->mup_norms_epoch[e] = h->h_stats[(size_t)2 * K];                       // nsum_p[0]
+    std::copy(h->h_stats.begin(), h->h_stats.begin() + K, h->mup_sums_epoch.begin() + (size_t)e * K);
+    if (e - h->mup_switched_epoch < resolution) return;
+    float norms = 0.f, sq = 0.f;
+    std::vector<float> acc(K, 0.f);
+    for (int w = e - resolution + 1; w <= e; w++) {
+        norms += h->mup_norms_epoch[w];
+        for (int d = 0; d < K; d++) acc[d] += h->mup_sums_epoch[(size_t)w * K + d];
+    }
+    for (int d = 0; d < K; d++) sq += powf(acc[d], 2);
+    const float diversity = norms / sq;
+    h->mup_max_diversity = h->mup_max_diversity < diversity ? diversity : h->mup_max_diversity;
+    const float ratio = h->mup_max_diversity / diversity;
+    if (ratio > threshold && ++h->mup_violations == 1) {
+        if (h->mup_idx < 4) h->mup_idx++;
+        h->mup_switched_epoch = e;
+        h->mup_max_diversity = -1.f;
+        h->mup_violations = 0;
+    }
+}
+
 SampleStats stats_view(mascot_handle* h) {
     const int ug = (int)h->uend.size(), ig = (int)h->iend.size(), K = h->K;
     SampleStats st;
@@ -549,14 +595,14 @@ int train_range(mascot_handle* h, float lr, uint64_t begin, uint64_t end, bool c
     if (head > 0) {
         Stream sa = s; sa.n = head;
         CU(h, launch_train(h->K, h->kind, sa, h->P, h->Q, lr, h->cfg.lambda, nullptr, any_f32, workers,
-                           h->d_work_counter, h->stream, shape));
+                           h->d_work_counter, muppet_bits(h), h->stream, shape));
         (*launches)++;
     }
     if (head < n) {
         Stream sb; sb.r = s.r + head; sb.u = s.u + head; sb.i = s.i + head; sb.n = n - head;
         const SampleStats st = stats_view(h);
         CU(h, launch_train(h->K, h->kind, sb, h->P, h->Q, lr, h->cfg.lambda, &st, any_f32, workers,
-                           h->d_work_counter, h->stream, shape));
+                           h->d_work_counter, muppet_bits(h), h->stream, shape));
         (*launches)++;
     }
     return MASCOT_OK;
@@ -690,7 +736,10 @@ int mascot_train_epoch(mascot_handle* h, uint32_t epoch, mascot_epoch_stats* out
     if (!h->have_ratings || !h->have_factors) return fail(h, MASCOT_ERR_STATE, "ratings and factors must be set before training");
     CU(h, cudaSetDevice(h->cfg.device));
     const float lr = epoch < h->lr.size() ? h->lr[epoch] : lr_at(h->cfg, epoch);
-    const bool check = h->grouped && is_check_epoch(h->cfg, epoch);
+    const bool muppet = h->kind == KIND_MUPPET;
+    const int bits_this_epoch = muppet ? muppet_bits(h) : 0;
+    // MuPPET samples every epoch (its statistics feed the width policy), MASCOT on its check epochs
+    const bool check = muppet || (h->grouped && is_check_epoch(h->cfg, epoch));
     uint32_t launches = 0, promoted_u = 0, promoted_i = 0;
     const uint64_t bytes_this_epoch = algorithmic_bytes(h);    // with the precisions the kernel is about to see
     CU(h, cudaEventRecord(h->ev[0], h->stream));
@@ -711,13 +760,14 @@ int mascot_train_epoch(mascot_handle* h, uint32_t epoch, mascot_epoch_stats* out
         rc = fetch_stats(h, nullptr);
         h->stats_copies = saved;
         if (rc != MASCOT_OK) return rc;
-        if ((rc = apply_stats(h, epoch, &promoted_u, &promoted_i, &launches)) != MASCOT_OK) return rc;
+        if (muppet) muppet_policy(h, epoch);
+        else if ((rc = apply_stats(h, epoch, &promoted_u, &promoted_i, &launches)) != MASCOT_OK) return rc;
     }
     CU(h, cudaEventRecord(h->ev[3], h->stream));
     CU(h, cudaEventSynchronize(h->ev[3]));
     if (out) {
         std::memset(out, 0, sizeof(*out));
-        out->updates = h->n_train; out->lr = lr; out->error_check = check ? 1 : 0;
+        out->updates = h->n_train; out->lr = lr; out->error_check = check ? 1 : 0; out->pass_bits = (uint32_t)bits_this_epoch;
         out->promoted_user_groups = promoted_u; out->promoted_item_groups = promoted_i; out->kernel_launches = launches;
         out->algorithmic_bytes = bytes_this_epoch;
         out->workers = shape.workers;

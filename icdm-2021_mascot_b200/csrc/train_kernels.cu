@@ -208,6 +208,7 @@ struct Consts {
     __half mpt_scale;             // mpt_sgd_kernel.h:15-16
     __half2 mpt_lam;              // mf_methods.cu:764-765
     float mpt_rev;
+    int bits;                     // MuPPET: width of the forward and the backward pass
 };
 
 // Sampled statistics (mascot_sgd_kernel.h:240-277): per group the element-wise sum of the gradients
@@ -231,11 +232,140 @@ struct KernelArgs {
     Arena P, Q;
     float lr, lam;
     SampleStats st;
+    int bits;                     // MuPPET pass width
     unsigned workers;             // concurrent sequential workers actually launched
     unsigned long long* next_chunk;   // work counter, zero at launch: chunks beyond the first two per
                                       // worker are handed out dynamically, so the launch never depends on
                                       // every block being resident at the same time
 };
+
+// ---- MuPPET (muppet/muppet_sgd_kernel.h:7-48, 121-264; _k64.h) -------------------------------
+// Power-of-two scale for a `bits`-wide fixed-point grid that covers [lo, hi]: the reference takes
+// floor(log2(min(|qmax/hi|, |qmin/lo|))) with qmax = 2^(bits-1)-0.5, qmin = -2^(bits-1)-0.5, stores
+// it in an unsigned index (negative -> 0) and scales by 2^index.
+__device__ __forceinline__ float muppet_scale(int bits, float hi, float lo) {
+    if (hi == 0.f && lo == 0.f) return 1.f;
+    const float val = (float)(1 << (bits - 1));
+    const float top = __fadd_rn(__fsub_rn(val, 1.f), 0.5f), bottom = __fsub_rn(-val, 0.5f);
+    const float best = fminf(fabsf(__fdiv_rn(top, hi)), fabsf(__fdiv_rn(bottom, lo)));
+    const float idx = floorf(log2f(best));
+    if (!(idx > 0.f)) return 1.f;
+    const int e = idx > 127.f ? 128 : (int)idx;
+    return e >= 128 ? __int_as_float(0x7f800000) : __int_as_float((e + 127) << 23);
+}
+__device__ __forceinline__ float fix_round(float v, float s, float s_rev) { return __fmul_rn(roundf(__fmul_rn(v, s)), s_rev); }
+__device__ __forceinline__ int sat8(float v) { return v > 127.f ? 127 : (v < -128.f ? -128 : (int)v); }
+__device__ __forceinline__ V8h fix_round_half(const V8f& x, float s, float s_rev) {
+    V8h h;
+#pragma unroll
+    for (int t = 0; t < 4; t++)
+        h.v[t] = __halves2half2(__float2half_rn(fix_round(x.x[2 * t], s, s_rev)), __float2half_rn(fix_round(x.x[2 * t + 1], s, s_rev)));
+    return h;
+}
+template <int TS> __device__ __forceinline__ float worker_min(float x, unsigned wmask) {
+#pragma unroll
+    for (int d = TS / 2; d >= 1; d >>= 1) x = fminf(x, __shfl_xor_sync(wmask, x, d));
+    return x;
+}
+template <int TS> __device__ __forceinline__ float worker_max(float x, unsigned wmask) {
+#pragma unroll
+    for (int d = TS / 2; d >= 1; d >>= 1) x = fmaxf(x, __shfl_xor_sync(wmask, x, d));
+    return x;
+}
+// Squared norm of both gradients the way the reference groups it: per reference lane
+// (norm_p + norm_q), then the lane tree.  A lane here holds two (k=128) or four (k=64) reference lanes.
+template <int K>
+__device__ __forceinline__ float muppet_norm_partial(const V8f& gp, const V8f& gq) {
+    auto sq = [](const V8f& g, int a, int b) { return __fmaf_rn(g.x[a], g.x[a], __fmul_rn(g.x[b], g.x[b])); };
+    if (K == 128) {
+        const float la = __fadd_rn(__fadd_rn(sq(gp, 0, 2), sq(gp, 4, 6)), __fadd_rn(sq(gq, 0, 2), sq(gq, 4, 6)));
+        const float lb = __fadd_rn(__fadd_rn(sq(gp, 1, 3), sq(gp, 5, 7)), __fadd_rn(sq(gq, 1, 3), sq(gq, 5, 7)));
+        return __fadd_rn(la, lb);
+    }
+    const float l0 = __fadd_rn(sq(gp, 0, 2), sq(gq, 0, 2)), l1 = __fadd_rn(sq(gp, 4, 6), sq(gq, 4, 6));
+    const float l2 = __fadd_rn(sq(gp, 1, 3), sq(gq, 1, 3)), l3 = __fadd_rn(sq(gp, 5, 7), sq(gq, 5, 7));
+    return __fadd_rn(__fadd_rn(l0, l1), __fadd_rn(l2, l3));
+}
+
+template <int K>
+__device__ __forceinline__ void muppet_update(const Consts& c, float r, V8f& p, V8f& q, V8f& gp, V8f& gq, unsigned wmask) {
+    constexpr int TS = K / 8;
+    const int bits = c.bits;
+    float pmin = 0.f, pmax = 0.f, qmin = 0.f, qmax = 0.f, sp = 1.f, sq = 1.f, pred;
+    if (bits != 32) {
+        pmin = pmax = p.x[0]; qmin = qmax = q.x[0];
+#pragma unroll
+        for (int t = 1; t < 8; t++) {
+            pmin = fminf(pmin, p.x[t]); pmax = fmaxf(pmax, p.x[t]);
+            qmin = fminf(qmin, q.x[t]); qmax = fmaxf(qmax, q.x[t]);
+        }
+        pmin = worker_min<TS>(pmin, wmask); pmax = worker_max<TS>(pmax, wmask);
+        qmin = worker_min<TS>(qmin, wmask); qmax = worker_max<TS>(qmax, wmask);
+        sp = muppet_scale(bits, pmax, pmin); sq = muppet_scale(bits, qmax, qmin);
+    }
+    if (bits == 8) {
+        int acc = 0;
+#pragma unroll
+        for (int t = 0; t < 8; t++) acc += sat8(roundf(__fmul_rn(p.x[t], sp))) * sat8(roundf(__fmul_rn(q.x[t], sq)));
+#pragma unroll
+        for (int d = TS / 2; d >= 1; d >>= 1) acc += __shfl_xor_sync(wmask, acc, d);
+        pred = __fdiv_rn((float)acc, __fmul_rn(sp, sq));
+    } else if (bits == 32) {
+        pred = worker_sum<TS>(pair_partial(p, q), wmask);
+    } else {
+        // binary16 on the fixed-point grid; the two halves of the reference's half2 accumulator go
+        // through the lane tree separately and meet at the end
+        const V8h ph = fix_round_half(p, sp, __fdiv_rn(1.f, sp)), qh = fix_round_half(q, sq, __fdiv_rn(1.f, sq));
+        __half2 xy;
+        if (K == 128) {
+            const __half2 xab = __hfma2(ph.v[0], qh.v[0], __hmul2_rn(ph.v[2], qh.v[2]));   // (x of lane m, x of lane m+16)
+            const __half2 yab = __hfma2(ph.v[1], qh.v[1], __hmul2_rn(ph.v[3], qh.v[3]));
+            xy = __hadd2_rn(__lows2half2(xab, yab), __highs2half2(xab, yab));              // tree step 16
+        } else {
+            const __half2 x = __hadd2_rn(__hmul2_rn(ph.v[0], qh.v[0]), __hmul2_rn(ph.v[2], qh.v[2]));   // step 16: (m)+(m+16), (m+8)+(m+24)
+            const __half2 y = __hadd2_rn(__hmul2_rn(ph.v[1], qh.v[1]), __hmul2_rn(ph.v[3], qh.v[3]));
+            xy = __hadd2_rn(__lows2half2(x, y), __highs2half2(x, y));                                   // step 8
+        }
+#pragma unroll
+        for (int d = TS / 2; d >= 1; d >>= 1) {
+            const unsigned o = __shfl_xor_sync(wmask, *reinterpret_cast<unsigned*>(&xy), d);
+            xy = __hadd2_rn(xy, *reinterpret_cast<const __half2*>(&o));
+        }
+        pred = __half2float(__hadd_rn(__low2half(xy), __high2half(xy)));
+    }
+    const float ruv = __fsub_rn(r, pred);
+    const float nlam = -c.lam;
+    float sb = 1.f;
+    if (bits != 32) {
+        const float bmin = fminf(fminf(pmin, qmin), fminf(nlam, ruv)), bmax = fmaxf(fmaxf(pmax, qmax), fmaxf(nlam, ruv));
+        sb = muppet_scale(bits, bmax, bmin);
+    }
+    if (bits == 8) {
+        const float rev2 = __fdiv_rn(1.f, __fmul_rn(sb, sb));
+        const int ei = sat8(roundf(__fmul_rn(ruv, sb))), li = sat8(roundf(__fmul_rn(nlam, sb)));
+#pragma unroll
+        for (int t = 0; t < 8; t++) {
+            const int pi = sat8(roundf(__fmul_rn(p.x[t], sb))), qi = sat8(roundf(__fmul_rn(q.x[t], sb)));
+            gp.x[t] = __fmul_rn((float)(qi * ei + pi * li), rev2);
+            gq.x[t] = __fmul_rn((float)(pi * ei + qi * li), rev2);
+        }
+    } else if (bits == 32) {
+        gp = grad(ruv, q, c.lam, p); gq = grad(ruv, p, c.lam, q);
+    } else {
+        const float sb_rev = __fdiv_rn(1.f, sb);
+        const __half2 e2 = __half2half2(__float2half_rn(fix_round(ruv, sb, sb_rev)));
+        const __half2 l2 = __half2half2(__float2half_rn(fix_round(nlam, sb, sb_rev)));
+        const V8h ph = fix_round_half(p, sb, sb_rev), qh = fix_round_half(q, sb, sb_rev);
+        V8h gph, gqh;
+#pragma unroll
+        for (int t = 0; t < 4; t++) {
+            gph.v[t] = __hadd2_rn(__hmul2_rn(qh.v[t], e2), __hmul2_rn(ph.v[t], l2));
+            gqh.v[t] = __hadd2_rn(__hmul2_rn(ph.v[t], e2), __hmul2_rn(qh.v[t], l2));
+        }
+        gp = widen(gph); gq = widen(gqh);
+    }
+    p = step(c.lr, gp, p); q = step(c.lr, gq, q);
+}
 
 // One update.  p_raw / q_raw are the row slices in their storage precision; both are replaced by the
 // updated values.  Statistics go to `acc` when the rating is sampled.
@@ -257,6 +387,11 @@ __device__ __forceinline__ void update_one(const Consts& c, float r, uint32_t uc
             qo.x[s] = __fmaf_rn(c.lr, __fmul_rn(c.mpt_rev, gq.x[s]), q.x[s]);
         }
         put(p_raw, po); put(q_raw, qo);
+    } else if constexpr (KIND == KIND_MUPPET) {
+        V8f p = as_v8f(p_raw), q = as_v8f(q_raw);
+        muppet_update<K>(c, r, p, q, smp.gp, smp.gq, wmask);
+        put(p_raw, p); put(q_raw, q);
+        if (STATS && sampled && c.bits != 32) smp.user = true;
     } else if constexpr (KIND == KIND_MEMQUANT) {
         const V8f p = widen(as_v8h(p_raw)), q = widen(as_v8h(q_raw));
         const float part = (K == 128) ? chain_partial_k128(p, q) : pair_partial(p, q);
@@ -368,6 +503,7 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
     c.mpt_scale = __float2half_rn(1000.0f);
     c.mpt_lam = __half2half2(__float2half_rn(__fmul_rn(a.lam, 1000.0f)));
     c.mpt_rev = __fdiv_rn(1.0f, 1000.0f);
+    c.bits = a.bits;
     // only the mixed-precision mode reads the precision bit of an id
     constexpr uint32_t kKeep = (MODE == ROWS_DYN) ? 0xffffffffu : kIdMask;
 
@@ -455,6 +591,19 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
         }
     };
     auto record = [&](const Sample& smp, uint32_t uc, uint32_t ic) {
+        if constexpr (KIND == KIND_MUPPET) {
+            // muppet_sgd_kernel.h:266-285: the squared norm of both gradients goes to the worker's
+            // running sum, the element-wise sum of both gradients to k shared accumulators
+            if (smp.user) {
+                const float n = worker_sum<TS>(muppet_norm_partial<K>(smp.gp, smp.gq), wmask);
+                V8f both;
+#pragma unroll
+                for (int t = 0; t < 8; t++) both.x[t] = __fadd_rn(smp.gp.x[t], smp.gq.x[t]);
+                red_add8(gsum_p + 8 * m, both);
+                nq_acc = __fadd_rn(nq_acc, n);
+            }
+            return;
+        }
         if (smp.user) {
             const uint32_t g = a.st.ugroup[uc & kIdMask];
             const float n = worker_sum<TS>(pair_partial(smp.gp, smp.gp), wmask);
@@ -548,7 +697,10 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
     }
     cp_wait<0>();
     if (cur_ic != kNoRow) st_row<K, MODE>(a.Q, cur_ic, m, q);
-    if (STATS) flush_item_stats();
+    if (STATS) {
+        if constexpr (KIND == KIND_MUPPET) { if (m == 0) atomicAdd(nsum_p, nq_acc); }
+        else flush_item_stats();
+    }
 }
 
 __global__ void reduce_stats_kernel(float* sets, int copies, size_t stride, size_t n) {
@@ -640,6 +792,9 @@ cudaError_t launch_k(TrainKind kind, const KernelArgs& a, bool stats, bool any_f
         case KIND_FP32: return launch_one<K, KIND_FP32, ROWS_F32, false>(a, workers, st, sh);
         case KIND_MPT: return launch_one<K, KIND_MPT, ROWS_F32, false>(a, workers, st, sh);
         case KIND_MEMQUANT: return launch_one<K, KIND_MEMQUANT, ROWS_HALF, false>(a, workers, st, sh);
+        case KIND_MUPPET:
+            return stats ? launch_one<K, KIND_MUPPET, ROWS_F32, true>(a, workers, st, sh)
+                         : launch_one<K, KIND_MUPPET, ROWS_F32, false>(a, workers, st, sh);
     }
     return cudaErrorInvalidValue;
 }
@@ -655,9 +810,9 @@ cudaError_t launch_reduce_stats(float* sets, int copies, size_t copy_stride, siz
 
 cudaError_t launch_train(int K, TrainKind kind, const Stream& s, Arena P, Arena Q, float lr, float lam,
                          const SampleStats* stats, bool any_f32_rows, unsigned workers, unsigned long long* work_counter,
-                         cudaStream_t st, LaunchShape* shape) {
+                         int bits, cudaStream_t st, LaunchShape* shape) {
     KernelArgs a;
-    a.s = s; a.P = P; a.Q = Q; a.lr = lr; a.lam = lam; a.workers = workers; a.next_chunk = work_counter;
+    a.s = s; a.P = P; a.Q = Q; a.lr = lr; a.lam = lam; a.workers = workers; a.next_chunk = work_counter; a.bits = bits;
     if (stats) a.st = *stats;
     if (s.n == 0) { if (shape) *shape = LaunchShape(); return cudaSuccess; }
     cudaError_t e0 = cudaMemsetAsync(work_counter, 0, sizeof(unsigned long long), st);

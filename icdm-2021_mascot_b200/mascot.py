@@ -36,7 +36,7 @@ class Config(C.Structure):
         ("item_group_num", C.c_uint32), ("k", C.c_uint32), ("num_workers", C.c_uint32), ("epoch", C.c_uint32),
         ("thread_block_size", C.c_uint32), ("version", C.c_uint32), ("is_yahoo", C.c_uint32),
         ("deterministic", C.c_uint32), ("shuffle", C.c_uint32), ("seed", C.c_uint64), ("device", C.c_int32),
-        ("reserved", C.c_uint32 * 7),
+        ("muppet_width", C.c_uint32), ("reserved", C.c_uint32 * 6),
     ]
 
 
@@ -44,7 +44,7 @@ class EpochStats(C.Structure):
     _fields_ = [
         ("updates", C.c_uint64), ("lr", C.c_float), ("kernel_ms", C.c_float), ("total_ms", C.c_float),
         ("error_check", C.c_uint32), ("promoted_user_groups", C.c_uint32), ("promoted_item_groups", C.c_uint32),
-        ("kernel_launches", C.c_uint32), ("workers", C.c_uint32), ("reserved0", C.c_uint32),
+        ("kernel_launches", C.c_uint32), ("workers", C.c_uint32), ("pass_bits", C.c_uint32),
         ("algorithmic_bytes", C.c_uint64),
     ]
 

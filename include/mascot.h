@@ -90,7 +90,9 @@ typedef struct mascot_config {
                                        4096 ratings; 0: the caller's order, untouched                  */
     uint64_t seed;               /* seeds the stream permutation and mascot_init_factors()      */
     int32_t device;              /* CUDA device ordinal                                         */
-    uint32_t reserved[7];
+    uint32_t muppet_width;       /* extension: first pass width of MuPPET, 8/12/14/16/32; 0 = the reference's start
+                                    (8, or 12 for Yahoo input; mf_methods.cu:597-601) */
+    uint32_t reserved[6];
 } mascot_config;
 
 typedef struct mascot_epoch_stats {
@@ -103,7 +105,7 @@ typedef struct mascot_epoch_stats {
     uint32_t promoted_item_groups;
     uint32_t kernel_launches;    /* kernels launched by this call                               */
     uint32_t workers;            /* concurrent sequential workers the update kernel ran with    */
-    uint32_t reserved0;
+    uint32_t pass_bits;          /* MuPPET: width of this epoch's forward/backward pass (8, 12, 14, 16, 32); else 0 */
     uint64_t algorithmic_bytes;  /* factor bytes the update rule reads + writes this epoch:
                                     sum over ratings of 2*k*(bytes per user element + bytes per
                                     item element), 2 for fp16 storage and 4 for fp32            */

@@ -28,6 +28,10 @@
 #define MO_REF_DOT_F16 1
 #define MO_REF_INNER_F16 1
 #define MO_REF_MPT_OUTER 1
+/* MuPPET binary16 passes: hmul2(a,b) + hmul2(c,d) -> hfma2(a, b, hmul2(c, d)); the sum of the two
+ * halves of ONE hmul2 result stays an unfused add. */
+#define MO_REF_MUP_FWD_F16 1
+#define MO_REF_MUP_BWD_F16 0
 
 /* ------------------------------------------------------------------------------------------ */
 /* contraction rule sets                                                                       */
@@ -44,6 +48,8 @@ void mo_rules_reference_build(mo_rules* r) {
     r->chain_f32 = MO_REF_CHAIN_F32;
     r->norm_f32 = MO_REF_NORM_F32;
     r->dot_f16 = MO_REF_DOT_F16;
+    r->mup_fwd_f16 = MO_REF_MUP_FWD_F16;
+    r->mup_bwd_f16 = MO_REF_MUP_BWD_F16;
     r->inner_f16 = MO_REF_INNER_F16;
     r->mpt_outer = MO_REF_MPT_OUTER;
 }
@@ -436,6 +442,119 @@ void mo_mpt_run(int k, const mo_node* R, const uint32_t* seq, uint64_t nseq, flo
             else { p[d] = p[d] + (lr * (rev * gp)); q[d] = q[d] + (lr * (rev * gq)); }
         }
     }
+}
+
+/* ------------------------------------------------------------------------------------------ */
+/* MuPPET (-v 3): muppet/muppet_sgd_kernel.h:7-48 (helpers), 50-292 (k=128), _k64.h:1-212     */
+/* ------------------------------------------------------------------------------------------ */
+/* get_only_scaling_factor (muppet_sgd_kernel.h:7-19) followed by the assignment to an unsigned
+ * index (a negative float becomes 0 on the device) and exp2f of that index. */
+static float muppet_scale(int bits, float max_v, float min_v) {
+    if (max_v == 0 && min_v == 0) return 1.0f;                 /* index 0 */
+    float val = (float)(1 << (bits - 1));
+    float top = (val - 1) + 0.5f, bottom = (-val) - 0.5f;
+    float range_best = fminf(fabsf(top / max_v), fabsf(bottom / min_v));
+    float idx = floorf((float)log2((double)range_best));
+    if (!(idx > 0)) return 1.0f;
+    if (idx > 4294967295.0f) idx = 4294967295.0f;
+    return exp2f(idx);
+}
+static inline int sat8(float v) { return v > 127.f ? 127 : (v < -128.f ? -128 : (int)v); }
+static inline float fix_round(float v, float s, float s_rev) { return roundf(v * s) * s_rev; }
+
+void mo_muppet_run(int k, const mo_node* R, const uint32_t* seq, uint64_t nseq, float* P, float* Q,
+                   float lr, float lam, int bits_fwd, int bits_bwd, uint64_t first_sample_pos,
+                   float* sum_updated_val, float* sum_norms, const mo_rules* ru) {
+    const int slots = k / 32;
+    float gp[128], gq[128], x[32];
+    float norm_total = 0.f;
+    for (uint64_t t = 0; t < nseq; t++) {
+        const mo_node* n = &R[seq ? seq[t] : t];
+        float* p = P + (size_t)n->u * k; float* q = Q + (size_t)n->i * k;
+        float pmin = p[0], pmax = p[0], qmin = q[0], qmax = q[0];
+        float sp = 1.f, sq = 1.f, pred;
+        if (bits_fwd != 32) {
+            for (int d = 1; d < k; d++) { pmin = fminf(pmin, p[d]); pmax = fmaxf(pmax, p[d]); qmin = fminf(qmin, q[d]); qmax = fmaxf(qmax, q[d]); }
+            sp = muppet_scale(bits_fwd, pmax, pmin); sq = muppet_scale(bits_fwd, qmax, qmin);
+        }
+        if (bits_fwd == 8) {
+            int acc = 0;
+            for (int d = 0; d < k; d++) acc += sat8(roundf(p[d] * sp)) * sat8(roundf(q[d] * sq));
+            pred = (float)acc / (sp * sq);
+        } else if (bits_fwd == 32) {
+            pred = dot_f32(k, p, q, ru->dot_f32);
+        } else {
+            /* binary16 pairs (slot 0, slot 1) and (slot 2, slot 3) of every lane; both halves go
+             * through the lane tree separately and are added at the end (muppet_sgd_kernel.h:170-194) */
+            const float sp_rev = 1 / sp, sq_rev = 1 / sq;
+            uint16_t xs[32], ys[32];
+            for (int l = 0; l < 32; l++) {
+                uint16_t ph[4], qh[4];
+                for (int s = 0; s < slots; s++) {
+                    ph[s] = mo_f2h(fix_round(p[l + 32 * s], sp, sp_rev));
+                    qh[s] = mo_f2h(fix_round(q[l + 32 * s], sq, sq_rev));
+                }
+                if (slots == 4) {
+                    xs[l] = pair_f16(ph[0], qh[0], ph[2], qh[2], ru->mup_fwd_f16);
+                    ys[l] = pair_f16(ph[1], qh[1], ph[3], qh[3], ru->mup_fwd_f16);
+                } else {
+                    xs[l] = mo_hmul(ph[0], qh[0]); ys[l] = mo_hmul(ph[1], qh[1]);
+                }
+            }
+            pred = mo_h2f(mo_hadd(tree32_f16(xs), tree32_f16(ys)));
+        }
+        const float ruv = n->r - pred;
+        float sb = 1.f;
+        if (bits_bwd != 32) {
+            /* with a 32-bit forward pass the extrema were never computed on the device; the host
+             * policy always runs both passes at the same width, so that case does not occur */
+            float bmin = fminf(fminf(pmin, qmin), fminf(-1 * lam, ruv));
+            float bmax = fmaxf(fmaxf(pmax, qmax), fmaxf(-1 * lam, ruv));
+            sb = muppet_scale(bits_bwd, bmax, bmin);
+        }
+        if (bits_bwd == 8) {
+            const float rev2 = 1 / (sb * sb);
+            const int e_i = sat8(roundf(ruv * sb)), l_i = sat8(roundf(-1.0f * lam * sb));
+            for (int d = 0; d < k; d++) {
+                const int pi = sat8(roundf(p[d] * sb)), qi = sat8(roundf(q[d] * sb));
+                gp[d] = (float)(qi * e_i + pi * l_i) * rev2;
+                gq[d] = (float)(pi * e_i + qi * l_i) * rev2;
+            }
+        } else if (bits_bwd == 32) {
+            for (int d = 0; d < k; d++) {
+                gp[d] = inner_f32(ruv, q[d], lam, p[d], ru->inner_f32);
+                gq[d] = inner_f32(ruv, p[d], lam, q[d], ru->inner_f32);
+            }
+        } else {
+            const float sb_rev = 1 / sb;
+            const uint16_t e_h = mo_f2h(fix_round(ruv, sb, sb_rev)), l_h = mo_f2h(fix_round(-1 * lam, sb, sb_rev));
+            for (int d = 0; d < k; d++) {
+                const uint16_t ph = mo_f2h(fix_round(p[d], sb, sb_rev)), qh = mo_f2h(fix_round(q[d], sb, sb_rev));
+                gp[d] = mo_h2f(pair_f16(qh, e_h, ph, l_h, ru->mup_bwd_f16));
+                gq[d] = mo_h2f(pair_f16(ph, e_h, qh, l_h, ru->mup_bwd_f16));
+            }
+        }
+        for (int d = 0; d < k; d++) {
+            p[d] = outer_f32(p[d], lr, gp[d], ru->outer_f32);
+            q[d] = outer_f32(q[d], lr, gq[d], ru->outer_f32);
+        }
+        if (bits_fwd != 32 && bits_bwd != 32 && t >= first_sample_pos && sum_updated_val) {
+            for (int l = 0; l < 32; l++) {
+                float np_, nq_;
+                if (slots == 4) {
+                    np_ = pair_f32(gp[l], gp[l], gp[l + 32], gp[l + 32], ru->norm_f32) + pair_f32(gp[l + 64], gp[l + 64], gp[l + 96], gp[l + 96], ru->norm_f32);
+                    nq_ = pair_f32(gq[l], gq[l], gq[l + 32], gq[l + 32], ru->norm_f32) + pair_f32(gq[l + 64], gq[l + 64], gq[l + 96], gq[l + 96], ru->norm_f32);
+                } else {
+                    np_ = pair_f32(gp[l], gp[l], gp[l + 32], gp[l + 32], ru->norm_f32);
+                    nq_ = pair_f32(gq[l], gq[l], gq[l + 32], gq[l + 32], ru->norm_f32);
+                }
+                x[l] = np_ + nq_;
+            }
+            norm_total += tree32_f32(x);
+            for (int d = 0; d < k; d++) sum_updated_val[d] += gp[d] + gq[d];
+        }
+    }
+    if (sum_norms) *sum_norms = norm_total;
 }
 
 /* ------------------------------------------------------------------------------------------ */

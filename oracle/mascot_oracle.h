@@ -38,6 +38,8 @@ typedef struct {
     int inner_f16;
     int mpt_outer;  /* p + lr*(rev*g):   0 literal | 1 fma(lr, rev*g, p)                                */
     int stats_sum;  /* (gp + gq) in MuPPET statistics etc.: reserved                                    */
+    int mup_fwd_f16; /* MuPPET/AFP binary16 forward pass, hmul2(a,b) + hmul2(c,d): coding as dot_f32    */
+    int mup_bwd_f16; /* MuPPET/AFP binary16 backward pass, result.x + result.y of one hmul2: as dot_f32 */
 } mo_rules;
 
 void mo_rules_literal(mo_rules* r);
@@ -81,6 +83,13 @@ void mo_mascot_run(int k, const mo_node* R, const uint32_t* seq, uint64_t nseq,
                    const mo_rules* rules);
 void mo_mpt_run(int k, const mo_node* R, const uint32_t* seq, uint64_t nseq, float* P, float* Q,
                 float lr, float lam, const mo_rules* rules);
+/* MuPPET (-v 3): muppet/muppet_sgd_kernel.h:50-292, muppet_sgd_kernel_k64.h:1-212.  fp32 factors,
+ * forward and backward pass in `bits_fwd` / `bits_bwd` (8: int8 dot products, 32: fp32, else
+ * fixed-point-rounded binary16).  Ratings at sequence positions >= first_sample_pos add to
+ * sum_updated_val[k] and *sum_norms when neither pass is 32-bit. */
+void mo_muppet_run(int k, const mo_node* R, const uint32_t* seq, uint64_t nseq, float* P, float* Q,
+                   float lr, float lam, int bits_fwd, int bits_bwd, uint64_t first_sample_pos,
+                   float* sum_updated_val, float* sum_norms, const mo_rules* rules);
 void mo_memquant_run(int k, const mo_node* R, const uint32_t* seq, uint64_t nseq, uint16_t* P, uint16_t* Q,
                      float lr, float lam, const mo_rules* rules);
 

@@ -364,3 +364,89 @@ def test_lr_zero_keeps_fp32_factors_and_init_is_seeded(mascot):
     P2, _ = eng.get_factors(0)
     assert_bit_equal(P0, P2, "same seed, same factors")
     eng.close()
+
+
+# --------------------------------------------------------------------------------------------
+# MuPPET (-v 3)
+# --------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", [f"muppet_k{k}_b{b}" for k in KS for b in (8, 12, 14, 16, 32)])
+def test_golden_muppet(mascot, oracle, golden, name):
+    """The reference kernel's factors and both sampled statistics, at every pass width."""
+    I, G = golden
+    c = golden_case(I, G, name, oracle)
+    seq = c["seq"]
+    n = len(seq)
+    train = mascot.as_ratings(np.ascontiguousarray(c["R"][seq]))
+    ratio = (n - c["fs"] + 0.01) / n                       # the engine samples the last int(n * ratio) ratings
+    assert int(np.float32(n) * np.float32(ratio)) == n - c["fs"]
+    eng = make_engine(mascot, mascot.V_MUPPET, c["k"], learning_rate=c["lr"], lam=c["lam"], sample_ratio=ratio,
+                      muppet_width=c["extra0"])
+    eng.set_ratings(train, train[:1], c["nu"], c["ni"])
+    eng.set_factors(c["P"], c["Q"])
+    st = eng.train_epoch(0)
+    assert st.pass_bits == c["extra0"]
+    P, Q = eng.get_factors(0)
+    gp, _gq, np_, _nq = eng.sample_stats()
+    eng.close()
+    assert_bit_equal(P, G[name + ".P_out"], "P")
+    assert_bit_equal(Q, G[name + ".Q_out"], "Q")
+    assert_bit_equal(gp[:c["k"]], G[name + ".sum_updated_val"], "sum_updated_val")
+    assert_bit_equal(np_[:1], G[name + ".sum_norms"], "sum_norms")
+
+
+def muppet_policy_step(state, e, k, sums, norm):
+    """mf_methods.cu:602, 660-695 restated: returns the index into (8, 12, 14, 16, 32) for the next epoch."""
+    state["norms"].append(np.float32(norm)); state["sums"].append(np.asarray(sums, np.float32).copy())
+    thr = np.float32(1.0) + np.float32(1.5) * np.exp(np.float32(-1 * np.float32(0.3) * e), dtype=np.float32)
+    if e - state["switched"] < 3:
+        return
+    norms = np.float32(0)
+    acc = np.zeros(k, np.float32)
+    for w in range(e - 2, e + 1):
+        norms = np.float32(norms + state["norms"][w]); acc = (acc + state["sums"][w]).astype(np.float32)
+    sq = np.float32(0)
+    for d in range(k):
+        sq = np.float32(sq + np.float32(acc[d]) * np.float32(acc[d]))
+    with np.errstate(all="ignore"):
+        div = np.float32(norms) / np.float32(sq)
+        state["max"] = div if state["max"] < div else state["max"]
+        ratio = np.float32(state["max"]) / div
+    if ratio > thr:
+        state["idx"] = min(state["idx"] + 1, 4); state["switched"] = e; state["max"] = np.float32(-1)
+
+
+@pytest.mark.parametrize("k,start_width,scale,switch_expected", [(64, 0, 0.1, True), (128, 14, 0.2, False)])
+def test_muppet_epochs_with_width_policy_bit_exact(mascot, oracle, k, start_width, scale, switch_expected):
+    """Twelve deterministic epochs of -v 3: every epoch's factors and statistics come from the oracle's
+    restatement at the width the host policy chose, and the engine must choose the same widths.  The
+    k=64 problem crosses the 8 -> 12 bit switch at epoch 7; the k=128 run starts at 14 bits."""
+    rng = np.random.default_rng(300 + k)
+    n_users, n_items, n = 97, 83, 3001
+    R, P, Q = random_problem(rng, n_users, n_items, n, k, scale=scale)
+    eng = make_engine(mascot, mascot.V_MUPPET, k, sample_ratio=0.25, learning_rate=0.03, muppet_width=start_width)
+    eng.set_ratings(R, R[:300], n_users, n_items)
+    eng.set_factors(P, Q)
+    lrs = oracle.lr_schedule(0.03, 0.1, 50)
+    rules = oracle.rules_reference()
+    Po, Qo = P.copy(), Q.copy()
+    widths = (8, 12, 14, 16, 32)
+    state = dict(idx=widths.index(start_width) if start_width else 0, switched=-1, max=np.float32(-1), norms=[], sums=[])
+    fsp = n - int(np.float32(n) * np.float32(0.25))
+    seen = []
+    for e in range(12):
+        bits = widths[state["idx"]]
+        st = eng.train_epoch(e)
+        assert st.pass_bits == bits, f"epoch {e}: engine ran {st.pass_bits} bits, policy says {bits}"
+        seen.append(bits)
+        suv, sn = oracle.muppet_run(k, R, None, Po, Qo, float(lrs[e]), 0.05, bits, bits, rules, first_sample_pos=fsp)
+        assert np.isfinite(Po).all() and np.isfinite(Qo).all()
+        gp, _gq, np_, _nq = eng.sample_stats()
+        assert_bit_equal(gp[:k], suv, f"sum_updated_val epoch {e}")
+        assert_bit_equal(np_[:1], np.float32(sn), f"sum_norms epoch {e}")
+        muppet_policy_step(state, e, k, suv, sn)
+    Pg, Qg = eng.get_factors(0)
+    eng.close()
+    assert_bit_equal(Pg, Po, "P")
+    assert_bit_equal(Qg, Qo, "Q")
+    if switch_expected:
+        assert len(set(seen)) > 1, "the run should cross at least one width switch"

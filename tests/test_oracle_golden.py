@@ -52,6 +52,23 @@ def test_mpt_matches_reference_kernel(oracle, golden, k):
     assert_bit_equal(Q, G[name + ".Q_out"], "Q")
 
 
+@pytest.mark.parametrize("name", [f"muppet_k{k}_b{b}" for k in KS for b in (8, 12, 14, 16, 32)])
+def test_muppet_matches_reference_kernel(oracle, golden, name):
+    """Factors and both sampled statistics of muppet_sgd_k128/k64_hogwild_kernel at every pass width."""
+    I, G = golden
+    c = golden_case(I, G, name, oracle)
+    P, Q = c["P"].copy(), c["Q"].copy()
+    bits = c["extra0"]
+    suv, sn = oracle.muppet_run(c["k"], c["R"], c["seq"], P, Q, c["lr"], c["lam"], bits, bits, oracle.rules_reference(),
+                                first_sample_pos=c["fs"])
+    assert_bit_equal(P, G[name + ".P_out"], "P")
+    assert_bit_equal(Q, G[name + ".Q_out"], "Q")
+    assert_bit_equal(suv, G[name + ".sum_updated_val"], "sum_updated_val")
+    assert_bit_equal(np.float32(sn), G[name + ".sum_norms"], "sum_norms")
+    if bits == 32:
+        assert sn == 0 and not suv.any(), "no statistics at full width (muppet_sgd_kernel.h:266)"
+
+
 @pytest.mark.parametrize("name", [f"memquant_k{k}{s}" for k in KS for s in ("", "_tight")])
 def test_fp16_storage_trainer_matches_reference_kernel(oracle, golden, name):
     I, G = golden
