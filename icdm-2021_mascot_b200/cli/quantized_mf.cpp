@@ -4,8 +4,7 @@
 //   -i train  -y test  -o out  -l epochs(50)  -k 64|128(128)  -b lambda(0.015)  -a lr(0.01)  -d decay(0.1)
 //   -wg workers  -bl block(128)  -v variant(7)  -s|-r sample ratio(0.01)  -ug / -ig groups(10)
 //   -e error threshold(0.001)  -it interval(1)  -rc save reconst test set(0)
-// Variants: 1 MASCOT, 4 MPT, 5 FP32 SGD, 7 fp16 storage (2 AFP and 3 MuPPET are reported as not
-// implemented).  Additive flags: -seed N, -det 1 (sequential verification mode), -dev N.
+// Variants: 1 MASCOT, 2 AFP, 3 MuPPET, 4 MPT, 5 FP32 SGD, 7 fp16 storage.  Additive flags: -seed N, -det 1 (sequential verification mode), -dev N.
 // Difference: when -wg is absent the engine picks the worker count itself (the reference defaults to
 // 2048 warps, a setting tuned for a 36-SM GPU).
 #include <chrono>

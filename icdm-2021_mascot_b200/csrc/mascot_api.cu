@@ -312,8 +312,7 @@ int mascot_create(const mascot_config* cfg, mascot_handle** out) {
         case MASCOT_V_MPT: kind = KIND_MPT; break;
         case MASCOT_V_MEMQUANT: kind = KIND_MEMQUANT; break;
         case MASCOT_V_MUPPET: kind = KIND_MUPPET; break;
-        case MASCOT_V_AFP:
-            return fail(nullptr, MASCOT_ERR_UNSUPPORTED, "the AFP trainer is not implemented by this engine yet");
+        case MASCOT_V_AFP: kind = KIND_AFP; break;
         default: return fail(nullptr, MASCOT_ERR_BAD_ARG, "unknown training variant");
     }
     int ndev = 0;
@@ -579,7 +578,7 @@ SampleStats stats_view(mascot_handle* h) {
 // Runs the update kernel over stream positions [begin, end).  With `collect`, the last
 // sample_ratio of the range (mf_methods.cu:102-103, 173-174) goes through the statistics kernel -
 // a second launch, so that only the sampled fraction pays for the statistics.
-int train_range(mascot_handle* h, float lr, uint64_t begin, uint64_t end, bool collect, LaunchShape* shape, uint32_t* launches) {
+int train_range(mascot_handle* h, float lr, uint32_t epoch, uint64_t begin, uint64_t end, bool collect, LaunchShape* shape, uint32_t* launches) {
     if (end <= begin) return MASCOT_OK;
     const uint64_t n = end - begin;
     bool any_f32 = false;
@@ -595,14 +594,14 @@ int train_range(mascot_handle* h, float lr, uint64_t begin, uint64_t end, bool c
     if (head > 0) {
         Stream sa = s; sa.n = head;
         CU(h, launch_train(h->K, h->kind, sa, h->P, h->Q, lr, h->cfg.lambda, nullptr, any_f32, workers,
-                           h->d_work_counter, muppet_bits(h), h->stream, shape));
+                           h->d_work_counter, muppet_bits(h), (int)epoch, h->stream, shape));
         (*launches)++;
     }
     if (head < n) {
         Stream sb; sb.r = s.r + head; sb.u = s.u + head; sb.i = s.i + head; sb.n = n - head;
         const SampleStats st = stats_view(h);
         CU(h, launch_train(h->K, h->kind, sb, h->P, h->Q, lr, h->cfg.lambda, &st, any_f32, workers,
-                           h->d_work_counter, muppet_bits(h), h->stream, shape));
+                           h->d_work_counter, muppet_bits(h), (int)epoch, h->stream, shape));
         (*launches)++;
     }
     return MASCOT_OK;
@@ -688,7 +687,7 @@ int mascot_train_segment(mascot_handle* h, uint32_t epoch, uint32_t segment, uin
     const float lr = epoch < h->lr.size() ? h->lr[epoch] : lr_at(h->cfg, epoch);
     LaunchShape shape; uint32_t launches = 0;
     CU(h, cudaEventRecord(h->ev[0], h->stream));
-    const int rc = train_range(h, lr, h->seg_off[segment], h->seg_off[segment + 1], collect_stats && h->grouped, &shape, &launches);
+    const int rc = train_range(h, lr, epoch, h->seg_off[segment], h->seg_off[segment + 1], collect_stats && h->grouped, &shape, &launches);
     if (rc != MASCOT_OK) return rc;
     CU(h, cudaEventRecord(h->ev[3], h->stream));
     if (out) {
@@ -748,7 +747,7 @@ int mascot_train_epoch(mascot_handle* h, uint32_t epoch, mascot_epoch_stats* out
     LaunchShape shape;
     int rc;
     for (size_t sgm = 0; sgm + 1 < h->seg_off.size(); sgm++)
-        if ((rc = train_range(h, lr, h->seg_off[sgm], h->seg_off[sgm + 1], check, &shape, &launches)) != MASCOT_OK) return rc;
+        if ((rc = train_range(h, lr, epoch, h->seg_off[sgm], h->seg_off[sgm + 1], check, &shape, &launches)) != MASCOT_OK) return rc;
     if (check && h->stats_copies > 1) {
         CU(h, launch_reduce_stats(h->d_stats, h->stats_copies, h->stats_stride, stats_floats(h), h->stream));
         launches++;

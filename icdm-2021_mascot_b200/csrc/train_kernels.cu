@@ -209,6 +209,7 @@ struct Consts {
     __half2 mpt_lam;              // mf_methods.cu:764-765
     float mpt_rev;
     int bits;                     // MuPPET: width of the forward and the backward pass
+    int afp_epoch, afp_init_threshold;   // AFP: epoch index; ratings per worker / 10 (afp_sgd_kernel.h:143)
 };
 
 // Sampled statistics (mascot_sgd_kernel.h:240-277): per group the element-wise sum of the gradients
@@ -233,6 +234,7 @@ struct KernelArgs {
     float lr, lam;
     SampleStats st;
     int bits;                     // MuPPET pass width
+    int epoch;                    // AFP: epoch index
     unsigned workers;             // concurrent sequential workers actually launched
     unsigned long long* next_chunk;   // work counter, zero at launch: chunks beyond the first two per
                                       // worker are handed out dynamically, so the launch never depends on
@@ -287,6 +289,66 @@ __device__ __forceinline__ float muppet_norm_partial(const V8f& gp, const V8f& g
     return __fadd_rn(__fadd_rn(l0, l1), __fadd_rn(l2, l3));
 }
 
+// ---- passes shared by MuPPET and AFP ------------------------------------------------------------
+// int8 forward pass: saturated fixed-point values, exact integer dot product, one division
+template <int TS>
+__device__ __forceinline__ float forward_int8(const V8f& p, const V8f& q, float sp, float sq, unsigned wmask) {
+    int acc = 0;
+#pragma unroll
+    for (int t = 0; t < 8; t++) acc += sat8(roundf(__fmul_rn(p.x[t], sp))) * sat8(roundf(__fmul_rn(q.x[t], sq)));
+#pragma unroll
+    for (int d = TS / 2; d >= 1; d >>= 1) acc += __shfl_xor_sync(wmask, acc, d);
+    return __fdiv_rn((float)acc, __fmul_rn(sp, sq));
+}
+// binary16 forward pass on the fixed-point grid; the two halves of the reference's half2 accumulator
+// go through the lane tree separately and meet at the end (muppet_sgd_kernel.h:170-194,
+// afp_sgd_kernel.h:252-273)
+template <int K>
+__device__ __forceinline__ float forward_half(const V8f& p, const V8f& q, float sp, float sq, unsigned wmask) {
+    constexpr int TS = K / 8;
+    const V8h ph = fix_round_half(p, sp, __fdiv_rn(1.f, sp)), qh = fix_round_half(q, sq, __fdiv_rn(1.f, sq));
+    __half2 xy;
+    if (K == 128) {
+        const __half2 xab = __hfma2(ph.v[0], qh.v[0], __hmul2_rn(ph.v[2], qh.v[2]));   // (x of lane m, x of lane m+16)
+        const __half2 yab = __hfma2(ph.v[1], qh.v[1], __hmul2_rn(ph.v[3], qh.v[3]));
+        xy = __hadd2_rn(__lows2half2(xab, yab), __highs2half2(xab, yab));              // tree step 16
+    } else {
+        const __half2 x = __hadd2_rn(__hmul2_rn(ph.v[0], qh.v[0]), __hmul2_rn(ph.v[2], qh.v[2]));   // step 16: (m)+(m+16), (m+8)+(m+24)
+        const __half2 y = __hadd2_rn(__hmul2_rn(ph.v[1], qh.v[1]), __hmul2_rn(ph.v[3], qh.v[3]));
+        xy = __hadd2_rn(__lows2half2(x, y), __highs2half2(x, y));                                   // step 8
+    }
+#pragma unroll
+    for (int d = TS / 2; d >= 1; d >>= 1) {
+        const unsigned o = __shfl_xor_sync(wmask, *reinterpret_cast<unsigned*>(&xy), d);
+        xy = __hadd2_rn(xy, *reinterpret_cast<const __half2*>(&o));
+    }
+    return __half2float(__hadd_rn(__low2half(xy), __high2half(xy)));
+}
+// backward passes: g_p = q*e + p*(-lam), g_q = p*e + q*(-lam) in int8 or binary16 fixed point
+__device__ __forceinline__ void backward_int8(const V8f& p, const V8f& q, float ruv, float nlam, float sb, V8f& gp, V8f& gq) {
+    const float rev2 = __fdiv_rn(1.f, __fmul_rn(sb, sb));
+    const int ei = sat8(roundf(__fmul_rn(ruv, sb))), li = sat8(roundf(__fmul_rn(nlam, sb)));
+#pragma unroll
+    for (int t = 0; t < 8; t++) {
+        const int pi = sat8(roundf(__fmul_rn(p.x[t], sb))), qi = sat8(roundf(__fmul_rn(q.x[t], sb)));
+        gp.x[t] = __fmul_rn((float)(qi * ei + pi * li), rev2);
+        gq.x[t] = __fmul_rn((float)(pi * ei + qi * li), rev2);
+    }
+}
+__device__ __forceinline__ void backward_half(const V8f& p, const V8f& q, float ruv, float nlam, float sb, V8f& gp, V8f& gq) {
+    const float sb_rev = __fdiv_rn(1.f, sb);
+    const __half2 e2 = __half2half2(__float2half_rn(fix_round(ruv, sb, sb_rev)));
+    const __half2 l2 = __half2half2(__float2half_rn(fix_round(nlam, sb, sb_rev)));
+    const V8h ph = fix_round_half(p, sb, sb_rev), qh = fix_round_half(q, sb, sb_rev);
+    V8h gph, gqh;
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+        gph.v[t] = __hadd2_rn(__hmul2_rn(qh.v[t], e2), __hmul2_rn(ph.v[t], l2));
+        gqh.v[t] = __hadd2_rn(__hmul2_rn(ph.v[t], e2), __hmul2_rn(qh.v[t], l2));
+    }
+    gp = widen(gph); gq = widen(gqh);
+}
+
 template <int K>
 __device__ __forceinline__ void muppet_update(const Consts& c, float r, V8f& p, V8f& q, V8f& gp, V8f& gq, unsigned wmask) {
     constexpr int TS = K / 8;
@@ -303,36 +365,9 @@ __device__ __forceinline__ void muppet_update(const Consts& c, float r, V8f& p, 
         qmin = worker_min<TS>(qmin, wmask); qmax = worker_max<TS>(qmax, wmask);
         sp = muppet_scale(bits, pmax, pmin); sq = muppet_scale(bits, qmax, qmin);
     }
-    if (bits == 8) {
-        int acc = 0;
-#pragma unroll
-        for (int t = 0; t < 8; t++) acc += sat8(roundf(__fmul_rn(p.x[t], sp))) * sat8(roundf(__fmul_rn(q.x[t], sq)));
-#pragma unroll
-        for (int d = TS / 2; d >= 1; d >>= 1) acc += __shfl_xor_sync(wmask, acc, d);
-        pred = __fdiv_rn((float)acc, __fmul_rn(sp, sq));
-    } else if (bits == 32) {
-        pred = worker_sum<TS>(pair_partial(p, q), wmask);
-    } else {
-        // binary16 on the fixed-point grid; the two halves of the reference's half2 accumulator go
-        // through the lane tree separately and meet at the end
-        const V8h ph = fix_round_half(p, sp, __fdiv_rn(1.f, sp)), qh = fix_round_half(q, sq, __fdiv_rn(1.f, sq));
-        __half2 xy;
-        if (K == 128) {
-            const __half2 xab = __hfma2(ph.v[0], qh.v[0], __hmul2_rn(ph.v[2], qh.v[2]));   // (x of lane m, x of lane m+16)
-            const __half2 yab = __hfma2(ph.v[1], qh.v[1], __hmul2_rn(ph.v[3], qh.v[3]));
-            xy = __hadd2_rn(__lows2half2(xab, yab), __highs2half2(xab, yab));              // tree step 16
-        } else {
-            const __half2 x = __hadd2_rn(__hmul2_rn(ph.v[0], qh.v[0]), __hmul2_rn(ph.v[2], qh.v[2]));   // step 16: (m)+(m+16), (m+8)+(m+24)
-            const __half2 y = __hadd2_rn(__hmul2_rn(ph.v[1], qh.v[1]), __hmul2_rn(ph.v[3], qh.v[3]));
-            xy = __hadd2_rn(__lows2half2(x, y), __highs2half2(x, y));                                   // step 8
-        }
-#pragma unroll
-        for (int d = TS / 2; d >= 1; d >>= 1) {
-            const unsigned o = __shfl_xor_sync(wmask, *reinterpret_cast<unsigned*>(&xy), d);
-            xy = __hadd2_rn(xy, *reinterpret_cast<const __half2*>(&o));
-        }
-        pred = __half2float(__hadd_rn(__low2half(xy), __high2half(xy)));
-    }
+    if (bits == 8) pred = forward_int8<TS>(p, q, sp, sq, wmask);
+    else if (bits == 32) pred = worker_sum<TS>(pair_partial(p, q), wmask);
+    else pred = forward_half<K>(p, q, sp, sq, wmask);
     const float ruv = __fsub_rn(r, pred);
     const float nlam = -c.lam;
     float sb = 1.f;
@@ -340,38 +375,129 @@ __device__ __forceinline__ void muppet_update(const Consts& c, float r, V8f& p, 
         const float bmin = fminf(fminf(pmin, qmin), fminf(nlam, ruv)), bmax = fmaxf(fmaxf(pmax, qmax), fmaxf(nlam, ruv));
         sb = muppet_scale(bits, bmax, bmin);
     }
-    if (bits == 8) {
-        const float rev2 = __fdiv_rn(1.f, __fmul_rn(sb, sb));
-        const int ei = sat8(roundf(__fmul_rn(ruv, sb))), li = sat8(roundf(__fmul_rn(nlam, sb)));
-#pragma unroll
-        for (int t = 0; t < 8; t++) {
-            const int pi = sat8(roundf(__fmul_rn(p.x[t], sb))), qi = sat8(roundf(__fmul_rn(q.x[t], sb)));
-            gp.x[t] = __fmul_rn((float)(qi * ei + pi * li), rev2);
-            gq.x[t] = __fmul_rn((float)(pi * ei + qi * li), rev2);
-        }
-    } else if (bits == 32) {
-        gp = grad(ruv, q, c.lam, p); gq = grad(ruv, p, c.lam, q);
-    } else {
-        const float sb_rev = __fdiv_rn(1.f, sb);
-        const __half2 e2 = __half2half2(__float2half_rn(fix_round(ruv, sb, sb_rev)));
-        const __half2 l2 = __half2half2(__float2half_rn(fix_round(nlam, sb, sb_rev)));
-        const V8h ph = fix_round_half(p, sb, sb_rev), qh = fix_round_half(q, sb, sb_rev);
-        V8h gph, gqh;
-#pragma unroll
-        for (int t = 0; t < 4; t++) {
-            gph.v[t] = __hadd2_rn(__hmul2_rn(qh.v[t], e2), __hmul2_rn(ph.v[t], l2));
-            gqh.v[t] = __hadd2_rn(__hmul2_rn(ph.v[t], e2), __hmul2_rn(qh.v[t], l2));
-        }
-        gp = widen(gph); gq = widen(gqh);
-    }
+    if (bits == 8) backward_int8(p, q, ruv, nlam, sb, gp, gq);
+    else if (bits == 32) { gp = grad(ruv, q, c.lam, p); gq = grad(ruv, p, c.lam, q); }
+    else backward_half(p, q, ruv, nlam, sb, gp, gq);
     p = step(c.lr, gp, p); q = step(c.lr, gq, q);
+}
+
+// ---- AFP (afp/afp_sgd_kernel.h:1-125 helpers, 127-376 k=128; afp_sgd_kernel_k64.h) ----------------
+// One side's quantization parameters and the rating count at which they are estimated next.  The
+// reference keeps three of these per warp for a whole kernel launch; here per worker.
+struct AfpSide { int n; float scale; float mov_avg; long long next; };
+struct AfpState { AfpSide user, item, back; long long cur; };
+
+// log2 in double precision, rounded once to float: the CPU restatement computes it the same way, so
+// both take identical re-estimation decisions (it runs only when parameters are re-estimated).
+__device__ __forceinline__ float log2_rounded(float x) { return (float)log2((double)x); }
+
+// 2^|ceil(log2(range / (2^(bits-1) - 1)))| (afp_sgd_kernel.h:8-16, 112-118); exponent capped at 126
+__device__ __forceinline__ float afp_scale(int bits, float range) {
+    if (range == 0.f) return 1.f;
+    const float top = bits == 8 ? 127.f : 32767.f;
+    const float e = fabsf(ceilf(log2_rounded(__fdiv_rn(range, top))));
+    const int ei = e > 126.f ? 126 : (int)e;
+    return __int_as_float((ei + 127) << 23);
+}
+// Sum of magnitudes of the values a reference lane adds, left to right, before and after 8-bit
+// rounding; `G` reference lanes live in this lane, `N` values each, v[g][j].
+template <int G, int N>
+__device__ __forceinline__ void afp_lane_sums(const float (&v)[G][N], float scale, float rev, float& sum, float& sum_q) {
+    float s[G], sq[G];
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        s[g] = fabsf(v[g][0]); sq[g] = fabsf(__fmul_rn(roundf(__fmul_rn(v[g][0], scale)), rev));
+#pragma unroll
+        for (int j = 1; j < N; j++) {
+            s[g] = __fadd_rn(s[g], fabsf(v[g][j]));
+            sq[g] = __fadd_rn(sq[g], fabsf(__fmul_rn(roundf(__fmul_rn(v[g][j], scale)), rev)));
+        }
+    }
+    if (G == 2) { sum = __fadd_rn(s[0], s[1]); sum_q = __fadd_rn(sq[0], sq[1]); }
+    else { sum = __fadd_rn(__fadd_rn(s[0], s[1]), __fadd_rn(s[2], s[3])); sum_q = __fadd_rn(__fadd_rn(sq[0], sq[1]), __fadd_rn(sq[2], sq[3])); }
+}
+// QEM / QEM_BP (afp_sgd_kernel.h:31-104): log2(1 + relative loss of the magnitude sum under 8 bits)
+template <int K>
+__device__ __forceinline__ float afp_qem(const V8f& x, float max_val, unsigned wmask) {
+    constexpr int TS = K / 8;
+    const float scale = afp_scale(8, max_val), rev = __fdiv_rn(1.f, scale);
+    float sum, sum_q;
+    if (K == 128) {
+        const float v[2][4] = {{x.x[0], x.x[2], x.x[4], x.x[6]}, {x.x[1], x.x[3], x.x[5], x.x[7]}};
+        afp_lane_sums<2, 4>(v, scale, rev, sum, sum_q);
+    } else {
+        const float v[4][2] = {{x.x[0], x.x[2]}, {x.x[4], x.x[6]}, {x.x[1], x.x[3]}, {x.x[5], x.x[7]}};
+        afp_lane_sums<4, 2>(v, scale, rev, sum, sum_q);
+    }
+    sum = worker_sum<TS>(sum, wmask); sum_q = worker_sum<TS>(sum_q, wmask);
+    return log2_rounded(__fadd_rn(fabsf(__fdiv_rn(__fsub_rn(sum, sum_q), sum)), 1.f));
+}
+template <int K>
+__device__ __forceinline__ float afp_qem_back(const V8f& p, const V8f& q, float lam, float ruv, float max_val, unsigned wmask) {
+    constexpr int TS = K / 8;
+    const float scale = afp_scale(8, max_val), rev = __fdiv_rn(1.f, scale);
+    float sum, sum_q;
+    if (K == 128) {
+        const float v[2][10] = {{p.x[0], p.x[2], p.x[4], p.x[6], q.x[0], q.x[2], q.x[4], q.x[6], lam, ruv},
+                                {p.x[1], p.x[3], p.x[5], p.x[7], q.x[1], q.x[3], q.x[5], q.x[7], lam, ruv}};
+        afp_lane_sums<2, 10>(v, scale, rev, sum, sum_q);
+    } else {
+        const float v[4][6] = {{p.x[0], p.x[2], q.x[0], q.x[2], lam, ruv}, {p.x[4], p.x[6], q.x[4], q.x[6], lam, ruv},
+                               {p.x[1], p.x[3], q.x[1], q.x[3], lam, ruv}, {p.x[5], p.x[7], q.x[5], q.x[7], lam, ruv}};
+        afp_lane_sums<4, 6>(v, scale, rev, sum, sum_q);
+    }
+    sum = worker_sum<TS>(sum, wmask); sum_q = worker_sum<TS>(sum_q, wmask);
+    return log2_rounded(__fadd_rn(fabsf(__fdiv_rn(__fsub_rn(sum, sum_q), sum)), 1.f));
+}
+// QPA (afp_sgd_kernel.h:106-125) and the bookkeeping around each call (196-206)
+__device__ __forceinline__ void afp_requantize(AfpSide& s, float diff, float range, long long cur, int epoch, int init_threshold) {
+    const float threshold = 0.0005, alpha = 0.04, beta = 0.1, delta = 100, gamma = 2;
+    if (cur == 0) s.mov_avg = range;
+    const float prev = s.mov_avg;
+    s.n = diff <= threshold ? 8 : 16;
+    s.scale = afp_scale(s.n, range);
+    s.mov_avg = __fmaf_rn(alpha, range, __fmul_rn(__fsub_rn(1.0f, alpha), prev));
+    const float i1 = __fmul_rn(__fmul_rn(delta, diff), diff), i2 = fabsf(__fsub_rn(s.mov_avg, prev));
+    int itv = __float2int_rz(__fsub_rn(__fdiv_rn(beta, fmaxf(i1, i2)), gamma));     // saturates; NaN -> 0
+    if (epoch == 0 && cur < init_threshold) itv = 1;
+    s.next += itv;
+}
+__device__ __forceinline__ float abs_max8(const V8f& x) {
+    float m = fabsf(x.x[0]);
+#pragma unroll
+    for (int t = 1; t < 8; t++) m = fmaxf(m, fabsf(x.x[t]));
+    return m;
+}
+
+template <int K>
+__device__ __forceinline__ void afp_update(const Consts& c, AfpState& st, float r, V8f& p, V8f& q, unsigned wmask) {
+    constexpr int TS = K / 8;
+    const long long cur = st.cur;
+    float pmax = 0.f, qmax = 0.f;
+    const bool need_back = cur == st.back.next;
+    if (cur == st.user.next || need_back) pmax = worker_max<TS>(abs_max8(p), wmask);
+    if (cur == st.item.next || need_back) qmax = worker_max<TS>(abs_max8(q), wmask);
+    if (cur == st.user.next) afp_requantize(st.user, afp_qem<K>(p, pmax, wmask), pmax, cur, c.afp_epoch, c.afp_init_threshold);
+    if (cur == st.item.next) afp_requantize(st.item, afp_qem<K>(q, qmax, wmask), qmax, cur, c.afp_epoch, c.afp_init_threshold);
+    const float pred = (st.user.n == 8 && st.item.n == 8) ? forward_int8<TS>(p, q, st.user.scale, st.item.scale, wmask)
+                                                          : forward_half<K>(p, q, st.user.scale, st.item.scale, wmask);
+    const float ruv = __fsub_rn(r, pred);
+    if (need_back) {
+        const float range = fmaxf(fmaxf(fmaxf(pmax, qmax), fabsf(c.lam)), fabsf(ruv));
+        afp_requantize(st.back, afp_qem_back<K>(p, q, c.lam, ruv, range, wmask), range, cur, c.afp_epoch, c.afp_init_threshold);
+    }
+    V8f gp, gq;
+    if (st.back.n == 8) backward_int8(p, q, ruv, -c.lam, st.back.scale, gp, gq);
+    else backward_half(p, q, ruv, -c.lam, st.back.scale, gp, gq);
+    p = step(c.lr, gp, p); q = step(c.lr, gq, q);
+    st.cur = cur + 1;
 }
 
 // One update.  p_raw / q_raw are the row slices in their storage precision; both are replaced by the
 // updated values.  Statistics go to `acc` when the rating is sampled.
 template <int K, int KIND, int MODE, bool STATS>
 __device__ __forceinline__ void update_one(const Consts& c, float r, uint32_t uc, uint32_t ic, Raw<MODE>& p_raw, Raw<MODE>& q_raw,
-                                           bool sampled, Sample& smp, unsigned wmask) {
+                                           bool sampled, Sample& smp, AfpState& afp, unsigned wmask) {
     constexpr int TS = K / 8;
     if (STATS) { smp.user = false; smp.item = false; }
     if constexpr (KIND == KIND_MPT) {
@@ -392,6 +518,10 @@ __device__ __forceinline__ void update_one(const Consts& c, float r, uint32_t uc
         muppet_update<K>(c, r, p, q, smp.gp, smp.gq, wmask);
         put(p_raw, p); put(q_raw, q);
         if (STATS && sampled && c.bits != 32) smp.user = true;
+    } else if constexpr (KIND == KIND_AFP) {
+        V8f p = as_v8f(p_raw), q = as_v8f(q_raw);
+        afp_update<K>(c, afp, r, p, q, wmask);
+        put(p_raw, p); put(q_raw, q);
     } else if constexpr (KIND == KIND_MEMQUANT) {
         const V8f p = widen(as_v8h(p_raw)), q = widen(as_v8h(q_raw));
         const float part = (K == 128) ? chain_partial_k128(p, q) : pair_partial(p, q);
@@ -504,6 +634,8 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
     c.mpt_lam = __half2half2(__float2half_rn(__fmul_rn(a.lam, 1000.0f)));
     c.mpt_rev = __fdiv_rn(1.0f, 1000.0f);
     c.bits = a.bits;
+    c.afp_epoch = a.epoch;
+    c.afp_init_threshold = (int)((float)((a.s.n + W - 1) / W) / 10.0f);
     // only the mixed-precision mode reads the precision bit of an id
     constexpr uint32_t kKeep = (MODE == ROWS_DYN) ? 0xffffffffu : kIdMask;
 
@@ -625,6 +757,8 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
         }
     };
     Sample smp;
+    AfpState afp;
+    afp.user = AfpSide{8, 1.f, 0.f, 0}; afp.item = afp.user; afp.back = afp.user; afp.cur = 0;
 
     // requests the user row of the rating with record `rx` / the item row of the rating whose first
     // two record words are `ri`, into ring slot `slot`
@@ -685,7 +819,7 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
                     request_user((x < TS) ? rc[x] : rn[x - TS], (t + D) & (NS - 1));
                     cp_commit();
                 }
-                update_one<K, KIND, MODE, STATS>(c, r, uc, ic, p, q, sampled, smp, wmask);
+                update_one<K, KIND, MODE, STATS>(c, r, uc, ic, p, q, sampled, smp, afp, wmask);
                 st_row<K, MODE>(a.P, uc, m, p);
                 if (STATS && sampled) record(smp, uc, ic);
             }
@@ -792,6 +926,7 @@ cudaError_t launch_k(TrainKind kind, const KernelArgs& a, bool stats, bool any_f
         case KIND_FP32: return launch_one<K, KIND_FP32, ROWS_F32, false>(a, workers, st, sh);
         case KIND_MPT: return launch_one<K, KIND_MPT, ROWS_F32, false>(a, workers, st, sh);
         case KIND_MEMQUANT: return launch_one<K, KIND_MEMQUANT, ROWS_HALF, false>(a, workers, st, sh);
+        case KIND_AFP: return launch_one<K, KIND_AFP, ROWS_F32, false>(a, workers, st, sh);
         case KIND_MUPPET:
             return stats ? launch_one<K, KIND_MUPPET, ROWS_F32, true>(a, workers, st, sh)
                          : launch_one<K, KIND_MUPPET, ROWS_F32, false>(a, workers, st, sh);
@@ -810,9 +945,9 @@ cudaError_t launch_reduce_stats(float* sets, int copies, size_t copy_stride, siz
 
 cudaError_t launch_train(int K, TrainKind kind, const Stream& s, Arena P, Arena Q, float lr, float lam,
                          const SampleStats* stats, bool any_f32_rows, unsigned workers, unsigned long long* work_counter,
-                         int bits, cudaStream_t st, LaunchShape* shape) {
+                         int bits, int epoch, cudaStream_t st, LaunchShape* shape) {
     KernelArgs a;
-    a.s = s; a.P = P; a.Q = Q; a.lr = lr; a.lam = lam; a.workers = workers; a.next_chunk = work_counter; a.bits = bits;
+    a.s = s; a.P = P; a.Q = Q; a.lr = lr; a.lam = lam; a.workers = workers; a.next_chunk = work_counter; a.bits = bits; a.epoch = epoch;
     if (stats) a.st = *stats;
     if (s.n == 0) { if (shape) *shape = LaunchShape(); return cudaSuccess; }
     cudaError_t e0 = cudaMemsetAsync(work_counter, 0, sizeof(unsigned long long), st);

@@ -32,6 +32,8 @@
  * halves of ONE hmul2 result stays an unfused add. */
 #define MO_REF_MUP_FWD_F16 1
 #define MO_REF_MUP_BWD_F16 0
+/* AFP moving average: follows the general pattern; the golden vectors cannot tell the variants apart. */
+#define MO_REF_AFP_AVG 1
 
 /* ------------------------------------------------------------------------------------------ */
 /* contraction rule sets                                                                       */
@@ -50,6 +52,7 @@ void mo_rules_reference_build(mo_rules* r) {
     r->dot_f16 = MO_REF_DOT_F16;
     r->mup_fwd_f16 = MO_REF_MUP_FWD_F16;
     r->mup_bwd_f16 = MO_REF_MUP_BWD_F16;
+    r->afp_avg = MO_REF_AFP_AVG;
     r->inner_f16 = MO_REF_INNER_F16;
     r->mpt_outer = MO_REF_MPT_OUTER;
 }
@@ -555,6 +558,132 @@ void mo_muppet_run(int k, const mo_node* R, const uint32_t* seq, uint64_t nseq, 
         }
     }
     if (sum_norms) *sum_norms = norm_total;
+}
+
+/* ------------------------------------------------------------------------------------------ */
+/* AFP (-v 2): afp/afp_sgd_kernel.h:1-125 (helpers), 127-376 (k=128), _k64.h:1-277             */
+/* ------------------------------------------------------------------------------------------ */
+/* log2 as the restatement computes it: in double precision, rounded once to float (the device code
+ * of this repository does the same, so that both sides take identical decisions). */
+static inline float log2_rounded(float x) { return (float)log2((double)x); }
+
+/* |ceil(log2(range / (2^(bits-1) - 1)))| (afp_sgd_kernel.h:8-16, 112-118), kept inside the range of
+ * float exponents (an all-zero row would give infinity). */
+static int afp_exponent(int bits, float range) {
+    if (range == 0) return 0;
+    float e = fabsf(ceilf(log2_rounded(range / (exp2f((float)(bits - 1)) - 1))));
+    return e > 126.f ? 126 : (int)e;
+}
+
+typedef struct { int n; float scale; float mov_avg; int64_t next; } afp_side;
+
+/* QEM / QEM_BP (afp_sgd_kernel.h:31-104): relative loss of the sum of magnitudes under 8-bit
+ * fixed point; `vals` holds, per lane, the lane's values in the order the reference adds them. */
+static float afp_qem(float vals[32][10], int per_lane, float max_val) {
+    const float scale = exp2f((float)afp_exponent(8, max_val)), rev = 1 / scale;
+    float xq[32], x[32];
+    for (int l = 0; l < 32; l++) {
+        float sq = fabsf(roundf(vals[l][0] * scale) * rev), sv = fabsf(vals[l][0]);
+        for (int j = 1; j < per_lane; j++) { sq = sq + fabsf(roundf(vals[l][j] * scale) * rev); sv = sv + fabsf(vals[l][j]); }
+        xq[l] = sq; x[l] = sv;
+    }
+    const float sum_q = tree32_f32(xq), sum = tree32_f32(x);
+    return log2_rounded(fabsf((sum - sum_q) / sum) + 1);
+}
+
+/* QPA (afp_sgd_kernel.h:106-125) plus the bookkeeping around it (196-206). */
+static void afp_requantize(afp_side* s, float diff, float range, int64_t cur_iter, int epoch, int init_threshold, int avg_mode) {
+    const float threshold = 0.0005, alpha = 0.04, beta = 0.1, delta = 100, gamma = 2;
+    if (cur_iter == 0) s->mov_avg = range;
+    const float prev = s->mov_avg;
+    if (diff <= threshold) { s->n = 8; s->scale = exp2f((float)afp_exponent(8, range)); }
+    else { s->n = 16; s->scale = exp2f((float)afp_exponent(16, range)); }
+    const float keep = 1.0f - alpha;
+    if (avg_mode == 1) s->mov_avg = fmaf(alpha, range, keep * prev);
+    else if (avg_mode == 2) s->mov_avg = fmaf(keep, prev, alpha * range);
+    else s->mov_avg = alpha * range + keep * prev;
+    const float i1 = delta * diff * diff, i2 = fabsf(s->mov_avg - prev);
+    const float f = (beta / fmaxf(i1, i2)) - gamma;
+    int64_t itv = (f != f) ? 0 : (f >= 2147483648.0f ? 2147483647 : (f <= -2147483648.0f ? -2147483647 - 1 : (int64_t)f));
+    if (epoch == 0 && cur_iter < init_threshold) itv = 1;
+    s->next += itv;
+}
+
+void mo_afp_run(int k, const mo_node* R, const uint32_t* seq, uint64_t nseq, float* P, float* Q,
+                float lr, float lam, int epoch, int init_threshold, const mo_rules* ru) {
+    const int slots = k / 32;
+    afp_side us = {8, 1.f, 0.f, 0}, is = {8, 1.f, 0.f, 0}, bs = {8, 1.f, 0.f, 0};
+    float vals[32][10], gp[128], gq[128];
+    for (uint64_t t = 0; t < nseq; t++) {
+        const int64_t cur = (int64_t)t;
+        const mo_node* n = &R[seq ? seq[t] : t];
+        float* p = P + (size_t)n->u * k; float* q = Q + (size_t)n->i * k;
+        float pmax = 0.f, qmax = 0.f;
+        for (int d = 0; d < k; d++) { pmax = fmaxf(pmax, fabsf(p[d])); qmax = fmaxf(qmax, fabsf(q[d])); }
+        if (cur == us.next) {
+            for (int l = 0; l < 32; l++) for (int s = 0; s < slots; s++) vals[l][s] = p[l + 32 * s];
+            afp_requantize(&us, afp_qem(vals, slots, pmax), pmax, cur, epoch, init_threshold, ru->afp_avg);
+        }
+        if (cur == is.next) {
+            for (int l = 0; l < 32; l++) for (int s = 0; s < slots; s++) vals[l][s] = q[l + 32 * s];
+            afp_requantize(&is, afp_qem(vals, slots, qmax), qmax, cur, epoch, init_threshold, ru->afp_avg);
+        }
+        float pred;
+        if (us.n == 8 && is.n == 8) {
+            int acc = 0;
+            for (int d = 0; d < k; d++) acc += sat8(roundf(p[d] * us.scale)) * sat8(roundf(q[d] * is.scale));
+            pred = (float)acc / (us.scale * is.scale);
+        } else {
+            const float sp_rev = 1 / us.scale, sq_rev = 1 / is.scale;
+            uint16_t xs[32], ys[32];
+            for (int l = 0; l < 32; l++) {
+                uint16_t ph[4], qh[4];
+                for (int s = 0; s < slots; s++) {
+                    ph[s] = mo_f2h(fix_round(p[l + 32 * s], us.scale, sp_rev));
+                    qh[s] = mo_f2h(fix_round(q[l + 32 * s], is.scale, sq_rev));
+                }
+                if (slots == 4) {
+                    xs[l] = pair_f16(ph[0], qh[0], ph[2], qh[2], ru->mup_fwd_f16);
+                    ys[l] = pair_f16(ph[1], qh[1], ph[3], qh[3], ru->mup_fwd_f16);
+                } else {
+                    xs[l] = mo_hmul(ph[0], qh[0]); ys[l] = mo_hmul(ph[1], qh[1]);
+                }
+            }
+            pred = mo_h2f(mo_hadd(tree32_f16(xs), tree32_f16(ys)));
+        }
+        const float ruv = n->r - pred;
+        if (cur == bs.next) {
+            const float range = fmaxf(fmaxf(fmaxf(pmax, qmax), fabsf(lam)), fabsf(ruv));
+            for (int l = 0; l < 32; l++) {
+                int j = 0;
+                for (int s = 0; s < slots; s++) vals[l][j++] = p[l + 32 * s];
+                for (int s = 0; s < slots; s++) vals[l][j++] = q[l + 32 * s];
+                vals[l][j++] = lam; vals[l][j++] = ruv;       /* every lane adds them (afp_sgd_kernel.h:84-86) */
+            }
+            afp_requantize(&bs, afp_qem(vals, 2 * slots + 2, range), range, cur, epoch, init_threshold, ru->afp_avg);
+        }
+        if (bs.n == 8) {
+            const float rev2 = 1 / (bs.scale * bs.scale);
+            const int e_i = sat8(roundf(ruv * bs.scale)), l_i = sat8(roundf(-1.0f * lam * bs.scale));
+            for (int d = 0; d < k; d++) {
+                const int pi = sat8(roundf(p[d] * bs.scale)), qi = sat8(roundf(q[d] * bs.scale));
+                gp[d] = (float)(qi * e_i + pi * l_i) * rev2;
+                gq[d] = (float)(pi * e_i + qi * l_i) * rev2;
+            }
+        } else {
+            const float sb_rev = 1 / bs.scale;
+            const uint16_t e_h = mo_f2h(fix_round(ruv, bs.scale, sb_rev)), l_h = mo_f2h(fix_round(-1.0f * lam, bs.scale, sb_rev));
+            for (int d = 0; d < k; d++) {
+                const uint16_t ph = mo_f2h(fix_round(p[d], bs.scale, sb_rev)), qh = mo_f2h(fix_round(q[d], bs.scale, sb_rev));
+                gp[d] = mo_h2f(pair_f16(qh, e_h, ph, l_h, ru->mup_bwd_f16));
+                gq[d] = mo_h2f(pair_f16(ph, e_h, qh, l_h, ru->mup_bwd_f16));
+            }
+        }
+        for (int d = 0; d < k; d++) {
+            p[d] = outer_f32(p[d], lr, gp[d], ru->outer_f32);
+            q[d] = outer_f32(q[d], lr, gq[d], ru->outer_f32);
+        }
+    }
 }
 
 /* ------------------------------------------------------------------------------------------ */

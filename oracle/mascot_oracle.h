@@ -40,6 +40,7 @@ typedef struct {
     int stats_sum;  /* (gp + gq) in MuPPET statistics etc.: reserved                                    */
     int mup_fwd_f16; /* MuPPET/AFP binary16 forward pass, hmul2(a,b) + hmul2(c,d): coding as dot_f32    */
     int mup_bwd_f16; /* MuPPET/AFP binary16 backward pass, result.x + result.y of one hmul2: as dot_f32 */
+    int afp_avg;     /* AFP moving average alpha*range + (1-alpha)*prev: coding as dot_f32                */
 } mo_rules;
 
 void mo_rules_literal(mo_rules* r);
@@ -90,6 +91,12 @@ void mo_mpt_run(int k, const mo_node* R, const uint32_t* seq, uint64_t nseq, flo
 void mo_muppet_run(int k, const mo_node* R, const uint32_t* seq, uint64_t nseq, float* P, float* Q,
                    float lr, float lam, int bits_fwd, int bits_bwd, uint64_t first_sample_pos,
                    float* sum_updated_val, float* sum_norms, const mo_rules* rules);
+/* AFP (-v 2): afp/afp_sgd_kernel.h:1-376, afp_sgd_kernel_k64.h:1-277.  One sequential worker: the
+ * per-warp state of the reference (three sets of quantization parameters and their re-estimation
+ * counters) lives for the whole sequence.  `epoch` and `init_threshold` are the kernel arguments
+ * that force re-estimation at every rating early in the first epoch. */
+void mo_afp_run(int k, const mo_node* R, const uint32_t* seq, uint64_t nseq, float* P, float* Q,
+                float lr, float lam, int epoch, int init_threshold, const mo_rules* rules);
 void mo_memquant_run(int k, const mo_node* R, const uint32_t* seq, uint64_t nseq, uint16_t* P, uint16_t* Q,
                      float lr, float lam, const mo_rules* rules);
 

@@ -16,7 +16,7 @@ NODE = np.dtype([("r", np.float32), ("u", np.uint32), ("i", np.uint32)])
 
 class Rules(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("dot_f32", "inner_f32", "outer_f32", "chain_f32", "norm_f32",
-                                       "dot_f16", "inner_f16", "mpt_outer", "stats_sum", "mup_fwd_f16", "mup_bwd_f16")]
+                                       "dot_f16", "inner_f16", "mpt_outer", "stats_sum", "mup_fwd_f16", "mup_bwd_f16", "afp_avg")]
 
     def __repr__(self):
         return "Rules(" + ", ".join(f"{n}={getattr(self, n)}" for n, _ in self._fields_) + ")"
@@ -155,6 +155,14 @@ def muppet_run(k, R, seq, P, Q, lr, lam, bits_fwd, bits_bwd, rules, first_sample
     lib().mo_muppet_run(C.c_int(k), _p(R), _p(seq), C.c_uint64(nseq), _p(P), _p(Q), C.c_float(lr), C.c_float(lam),
                         C.c_int(bits_fwd), C.c_int(bits_bwd), C.c_uint64(fsp), _p(suv), _p(sn), C.byref(rules))
     return suv, float(sn[0])
+
+
+def afp_run(k, R, seq, P, Q, lr, lam, epoch, init_threshold, rules):
+    R = as_nodes(R)
+    seq = _seq(seq)
+    nseq = seq.size if seq is not None else R.size
+    lib().mo_afp_run(C.c_int(k), _p(R), _p(seq), C.c_uint64(nseq), _p(P), _p(Q), C.c_float(lr), C.c_float(lam),
+                     C.c_int(epoch), C.c_int(init_threshold), C.byref(rules))
 
 
 def memquant_run(k, R, seq, P16, Q16, lr, lam, rules):

@@ -450,3 +450,49 @@ def test_muppet_epochs_with_width_policy_bit_exact(mascot, oracle, k, start_widt
     assert_bit_equal(Qg, Qo, "Q")
     if switch_expected:
         assert len(set(seen)) > 1, "the run should cross at least one width switch"
+
+
+# --------------------------------------------------------------------------------------------
+# AFP (-v 2)
+# --------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", [f"afp_k{k}_e{e}" for k in KS for e in (0, 1)])
+def test_golden_afp(mascot, oracle, golden, name):
+    """The reference kernel's factors; the golden case's epoch index is reproduced by a schedule
+    without decay, so that epoch 1 runs at the case's learning rate as well."""
+    I, G = golden
+    c = golden_case(I, G, name, oracle)
+    seq = c["seq"]
+    train = mascot.as_ratings(np.ascontiguousarray(c["R"][seq]))
+    eng = make_engine(mascot, mascot.V_AFP, c["k"], learning_rate=c["lr"], lam=c["lam"], decay=0.0)
+    eng.set_ratings(train, train[:1], c["nu"], c["ni"])
+    eng.set_factors(c["P"], c["Q"])
+    st = eng.train_epoch(c["extra0"])
+    assert st.updates == len(seq) and np.float32(st.lr) == np.float32(c["lr"])
+    P, Q = eng.get_factors(0)
+    eng.close()
+    assert_bit_equal(P, G[name + ".P_out"], "P")
+    assert_bit_equal(Q, G[name + ".Q_out"], "Q")
+
+
+@pytest.mark.parametrize("k", KS)
+def test_afp_epochs_bit_exact(mascot, oracle, k):
+    """Four deterministic epochs of -v 2 on a ragged problem: the worker's format state (8/16 bits per
+    side, re-estimation intervals) must follow the oracle's restatement rating by rating."""
+    rng = np.random.default_rng(400 + k)
+    n_users, n_items, n = 131, 89, 4003
+    R, P, Q = random_problem(rng, n_users, n_items, n, k, scale=0.2)
+    eng = make_engine(mascot, mascot.V_AFP, k)
+    eng.set_ratings(R, R[:300], n_users, n_items)
+    eng.set_factors(P, Q)
+    lrs = oracle.lr_schedule(0.01, 0.1, 50)
+    rules = oracle.rules_reference()
+    Po, Qo = P.copy(), Q.copy()
+    threshold = int(np.float32(n) / np.float32(10.0))
+    for e in range(4):
+        eng.train_epoch(e)
+        oracle.afp_run(k, R, None, Po, Qo, float(lrs[e]), 0.05, e, threshold, rules)
+    Pg, Qg = eng.get_factors(0)
+    eng.close()
+    assert np.isfinite(Po).all()
+    assert_bit_equal(Pg, Po, "P")
+    assert_bit_equal(Qg, Qo, "Q")

@@ -69,6 +69,19 @@ def test_muppet_matches_reference_kernel(oracle, golden, name):
         assert sn == 0 and not suv.any(), "no statistics at full width (muppet_sgd_kernel.h:266)"
 
 
+@pytest.mark.parametrize("name", [f"afp_k{k}_e{e}" for k in KS for e in (0, 1)])
+def test_afp_matches_reference_kernel(oracle, golden, name):
+    """afp_sgd_k128/k64_hogwild_kernel in its first epoch (formats re-estimated at every rating for the
+    first tenth) and in a later one (re-estimation intervals from QPA)."""
+    I, G = golden
+    c = golden_case(I, G, name, oracle)
+    P, Q = c["P"].copy(), c["Q"].copy()
+    threshold = int(np.float32(c["uc"] * c["vec"]) / np.float32(10.0))          # afp_sgd_kernel.h:143
+    oracle.afp_run(c["k"], c["R"], c["seq"], P, Q, c["lr"], c["lam"], c["extra0"], threshold, oracle.rules_reference())
+    assert_bit_equal(P, G[name + ".P_out"], "P")
+    assert_bit_equal(Q, G[name + ".Q_out"], "Q")
+
+
 @pytest.mark.parametrize("name", [f"memquant_k{k}{s}" for k in KS for s in ("", "_tight")])
 def test_fp16_storage_trainer_matches_reference_kernel(oracle, golden, name):
     I, G = golden
