@@ -51,11 +51,14 @@ struct LaunchShape {
 // any group has been promoted (otherwise every row is binary16); `work_counter` is 8 bytes of device
 // scratch the launch resets and uses to hand out chunks; `bits` is the width of MuPPET's forward and
 // backward pass (8, 12, 14, 16 or 32; ignored by the other kinds), `epoch` the epoch index (AFP
-// re-estimates its formats at every rating early in epoch 0).  Returns the launch shape used.
+// re-estimates its formats at every rating early in epoch 0).  With `add_user_delta` (ignored for a
+// single worker) user rows are written back as reductions of their change, so that concurrent
+// updates of one user by several workers are not lost.  Returns the launch shape used.
 // MuPPET statistics use gsum_p[0..K) (sum of the sampled updates, physical order) and nsum_p[0].
 cudaError_t launch_train(int K, TrainKind kind, const Stream& s, Arena P, Arena Q, float lr, float lam,
                          const SampleStats* stats, bool any_f32_rows, unsigned workers,
-                         unsigned long long* work_counter, int bits, int epoch, cudaStream_t st, LaunchShape* shape);
+                         unsigned long long* work_counter, int bits, int epoch, bool add_user_delta,
+                         cudaStream_t st, LaunchShape* shape);
 
 // Folds the private statistic sets of a launch into set 0 (sets are added in index order).
 cudaError_t launch_reduce_stats(float* sets, int copies, size_t copy_stride, size_t floats_per_set, cudaStream_t st);

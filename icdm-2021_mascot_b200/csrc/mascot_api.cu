@@ -594,14 +594,14 @@ int train_range(mascot_handle* h, float lr, uint32_t epoch, uint64_t begin, uint
     if (head > 0) {
         Stream sa = s; sa.n = head;
         CU(h, launch_train(h->K, h->kind, sa, h->P, h->Q, lr, h->cfg.lambda, nullptr, any_f32, workers,
-                           h->d_work_counter, muppet_bits(h), (int)epoch, h->stream, shape));
+                           h->d_work_counter, muppet_bits(h), (int)epoch, h->cfg.plain_user_stores == 0, h->stream, shape));
         (*launches)++;
     }
     if (head < n) {
         Stream sb; sb.r = s.r + head; sb.u = s.u + head; sb.i = s.i + head; sb.n = n - head;
         const SampleStats st = stats_view(h);
         CU(h, launch_train(h->K, h->kind, sb, h->P, h->Q, lr, h->cfg.lambda, &st, any_f32, workers,
-                           h->d_work_counter, muppet_bits(h), (int)epoch, h->stream, shape));
+                           h->d_work_counter, muppet_bits(h), (int)epoch, h->cfg.plain_user_stores == 0, h->stream, shape));
         (*launches)++;
     }
     return MASCOT_OK;

@@ -132,6 +132,30 @@ __device__ __forceinline__ void st_row(const Arena& A, uint32_t code, int m, con
     }
 }
 
+// Adds (now - before) to a row instead of storing `now`: with several workers on the same row at the
+// same time a plain store erases what the others wrote since this worker read the row, a reduction
+// keeps it.  When nobody else touched the row the result equals `now` (the difference of two nearby
+// values is exact).  128-bit vector reductions, fire and forget.
+template <int K, int MODE>
+__device__ __forceinline__ void add_row_delta(const Arena& A, uint32_t code, int m, const Raw<MODE>& now, const Raw<MODE>& before) {
+    const uint32_t row = code & kIdMask;
+    if (is_f32<MODE>(code)) {
+        if constexpr (MODE != ROWS_HALF) {
+            float4* p = reinterpret_cast<float4*>(A.f32 + (size_t)row * K) + 2 * m;
+            const V8f n = v8f_of(now.a, now.b), o = v8f_of(before.a, before.b);
+            atomicAdd(p, make_float4(__fsub_rn(n.x[0], o.x[0]), __fsub_rn(n.x[1], o.x[1]), __fsub_rn(n.x[2], o.x[2]), __fsub_rn(n.x[3], o.x[3])));
+            atomicAdd(p + 1, make_float4(__fsub_rn(n.x[4], o.x[4]), __fsub_rn(n.x[5], o.x[5]), __fsub_rn(n.x[6], o.x[6]), __fsub_rn(n.x[7], o.x[7])));
+        }
+    } else {
+        const V8h n = v8h_of(now.a), o = v8h_of(before.a);
+        unsigned d[4];
+#pragma unroll
+        for (int t = 0; t < 4; t++) { const __half2 x = __hsub2(n.v[t], o.v[t]); d[t] = *reinterpret_cast<const unsigned*>(&x); }
+        uint4* p = reinterpret_cast<uint4*>(A.f16 + (size_t)row * K) + m;
+        asm volatile("red.global.add.noftz.v4.f16x2 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(d[0]), "r"(d[1]), "r"(d[2]), "r"(d[3]) : "memory");
+    }
+}
+
 // ---- lane partials -------------------------------------------------------------------------
 // A lane's elements e0..e7 sit at positions 0 2 4 6 1 3 5 7 (layout.cuh), i.e. as the binary16 pairs
 // (e0,e4) (e1,e5) (e2,e6) (e3,e7).  Lane partial: (f_0 + f_1) + (f_2 + f_3) with
@@ -235,6 +259,7 @@ struct KernelArgs {
     SampleStats st;
     int bits;                     // MuPPET pass width
     int epoch;                    // AFP: epoch index
+    int add_user_delta;           // user rows are written back as reductions of the change (concurrent launches)
     unsigned workers;             // concurrent sequential workers actually launched
     unsigned long long* next_chunk;   // work counter, zero at launch: chunks beyond the first two per
                                       // worker are handed out dynamically, so the launch never depends on
@@ -819,8 +844,10 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
                     request_user((x < TS) ? rc[x] : rn[x - TS], (t + D) & (NS - 1));
                     cp_commit();
                 }
+                const Raw<MODE> p_before = p;
                 update_one<K, KIND, MODE, STATS>(c, r, uc, ic, p, q, sampled, smp, afp, wmask);
-                st_row<K, MODE>(a.P, uc, m, p);
+                if (a.add_user_delta) add_row_delta<K, MODE>(a.P, uc, m, p, p_before);
+                else st_row<K, MODE>(a.P, uc, m, p);
                 if (STATS && sampled) record(smp, uc, ic);
             }
         }
@@ -863,6 +890,7 @@ cudaError_t launch_ns(KernelArgs a, unsigned warps_per_sm, unsigned workers, cud
     auto kern = train_kernel<K, KIND, MODE, STATS, NS, D, DI>;
     int grid, block;
     const unsigned warps = (workers + kPerWarp - 1) / kPerWarp;
+    if (workers <= 1) a.add_user_delta = 0;      // a single worker has nobody to race with: plain stores
     if (warps <= 8) {
         // a single block (deterministic runs, tiny worker counts) uses exactly the requested workers
         grid = 1; block = (int)(32 * warps);
@@ -945,8 +973,9 @@ cudaError_t launch_reduce_stats(float* sets, int copies, size_t copy_stride, siz
 
 cudaError_t launch_train(int K, TrainKind kind, const Stream& s, Arena P, Arena Q, float lr, float lam,
                          const SampleStats* stats, bool any_f32_rows, unsigned workers, unsigned long long* work_counter,
-                         int bits, int epoch, cudaStream_t st, LaunchShape* shape) {
+                         int bits, int epoch, bool add_user_delta, cudaStream_t st, LaunchShape* shape) {
     KernelArgs a;
+    a.add_user_delta = add_user_delta ? 1 : 0;
     a.s = s; a.P = P; a.Q = Q; a.lr = lr; a.lam = lam; a.workers = workers; a.next_chunk = work_counter; a.bits = bits; a.epoch = epoch;
     if (stats) a.st = *stats;
     if (s.n == 0) { if (shape) *shape = LaunchShape(); return cudaSuccess; }

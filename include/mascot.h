@@ -92,7 +92,10 @@ typedef struct mascot_config {
     int32_t device;              /* CUDA device ordinal                                         */
     uint32_t muppet_width;       /* extension: first pass width of MuPPET, 8/12/14/16/32; 0 = the reference's start
                                     (8, or 12 for Yahoo input; mf_methods.cu:597-601) */
-    uint32_t reserved[6];
+    uint32_t plain_user_stores;  /* extension: 0 (default) = with more than one worker, user rows are written back as
+                                    reductions of their change, so racing updates of one user are not lost;
+                                    1 = plain stores like the reference (racing updates overwrite each other) */
+    uint32_t reserved[5];
 } mascot_config;
 
 typedef struct mascot_epoch_stats {

@@ -243,11 +243,25 @@ def test_mascot_training_with_switching_bit_exact(mascot, oracle, k):
     eng.close()
 
 
+def assert_within_one_ulp(got, want, half_storage, what):
+    """old + (new - old) against new: exact unless new - old is not representable, and then off by at
+    most half an ulp of the LARGER of old and new.  Bound used: one ulp (of the storage format) of the
+    largest magnitude in the matrix; and all but 3 % of the values must be exactly equal."""
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    eps = 2.0 ** -10 if half_storage else 2.0 ** -23
+    d = np.abs(got - want)
+    assert d.max() <= eps * np.abs(want).max(), f"{what}: largest difference {d.max():.3e}"
+    assert (d != 0).mean() <= 0.03, f"{what}: {(d != 0).mean():.4f} of the values differ"
+
+
 @pytest.mark.parametrize("k", KS)
+@pytest.mark.parametrize("plain_stores", [1, 0])
 @pytest.mark.parametrize("version", ["sgd", "mascot_hh", "mascot_fh", "mascot_hf", "mascot_ff"])
-def test_full_grid_on_conflict_free_ratings_bit_exact(mascot, oracle, k, version):
+def test_full_grid_on_conflict_free_ratings_bit_exact(mascot, oracle, k, version, plain_stores):
     """Throughput mode (persistent grid, shuffled stream): when no two ratings share a user or an
-    item the result does not depend on the schedule, so the Hogwild kernel must equal the oracle."""
+    item the result does not depend on the schedule, so the Hogwild kernel must equal the oracle -
+    bit for bit with plain stores; with the default write-back of user rows (a reduction of the
+    change) a user value may differ by one ulp where new - old is not exactly representable."""
     rng = np.random.default_rng(11 + k)
     n = 20011
     R = np.empty(n, mascot.RATING)
@@ -256,7 +270,8 @@ def test_full_grid_on_conflict_free_ratings_bit_exact(mascot, oracle, k, version
     P = (rng.standard_normal((n, k)) * 0.2).astype(np.float32)
     Q = (rng.standard_normal((n, k)) * 0.2).astype(np.float32)
     vid = mascot.V_SGD if version == "sgd" else mascot.V_MASCOT
-    eng = make_engine(mascot, vid, k, deterministic=0, shuffle=1, seed=99, user_group_num=10, item_group_num=10)
+    eng = make_engine(mascot, vid, k, deterministic=0, shuffle=1, seed=99, user_group_num=10, item_group_num=10,
+                      plain_user_stores=plain_stores)
     eng.set_ratings(R, R[:100], n, n)
     eng.set_factors(P, Q)
     # every entity has degree 1, so each side is a single group: promoting it switches the whole side
@@ -279,7 +294,10 @@ def test_full_grid_on_conflict_free_ratings_bit_exact(mascot, oracle, k, version
         model.run(Rs, None, 0.01, 0.05, rules)
         Po, Qo = model.factors()
         Pg, Qg = eng.get_factors(1)
-    assert_bit_equal(Pg, Po, "P")
+    if plain_stores:
+        assert_bit_equal(Pg, Po, "P")
+    else:
+        assert_within_one_ulp(Pg, Po, version in ("mascot_hh", "mascot_hf"), "P")
     assert_bit_equal(Qg, Qo, "Q")
     eng.close()
 
