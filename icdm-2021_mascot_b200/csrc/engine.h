@@ -76,6 +76,8 @@ cudaError_t launch_encode_stream(const void* d_src_aos, uint64_t n, bool shuffle
                                  float* r, uint32_t* u, uint32_t* i, uint32_t* src_out, uint32_t src_base,
                                  cudaStream_t st);
 cudaError_t launch_recode(uint32_t* ids, uint64_t n, const uint8_t* prec_row, cudaStream_t st);
+// Sets the "stored in fp32" flag of n per-row bytes (the other flags stay).
+cudaError_t launch_mark_fp32(uint8_t* row_flags, uint32_t n, cudaStream_t st);
 cudaError_t launch_scatter_factors(int K, const float* src, uint32_t rows, const uint32_t* row_map,
                                    bool round_through_half, __half* dst16, float* dst32, cudaStream_t st);
 cudaError_t launch_gather_factors(int K, Arena a, const uint8_t* prec_row, uint32_t rows,

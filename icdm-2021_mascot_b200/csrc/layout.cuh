@@ -78,8 +78,13 @@ MASCOT_HD inline uint64_t permute_index(uint64_t j, uint64_t n, uint64_t seed) {
     return x;
 }
 
-// Bit 31 of a stream id selects the arena a row lives in: 0 binary16, 1 fp32.
+// Bit 31 of a stream id selects the arena a row lives in: 0 binary16, 1 fp32.  Bit 30 marks a user
+// row that so many workers update at the same time that its write-back stays a plain store (see
+// the update kernel).  The per-row byte tables carry the same two flags in bits 0 and 1.
 constexpr uint32_t kPrecBit = 0x80000000u;
-constexpr uint32_t kIdMask = 0x7fffffffu;
+constexpr uint32_t kHotBit = 0x40000000u;
+constexpr uint32_t kIdMask = 0x3fffffffu;
+constexpr uint8_t kRowPrec = 1, kRowHot = 2;
+MASCOT_HD inline uint32_t row_flags_to_code(uint8_t b) { return ((b & kRowPrec) ? kPrecBit : 0u) | ((b & kRowHot) ? kHotBit : 0u); }
 
 }  // namespace mascot

@@ -29,6 +29,7 @@ struct mascot_handle {
     int mup_idx = 0, mup_switched_epoch = -1, mup_violations = 0;
     float mup_max_diversity = -1.f;
     std::vector<float> mup_norms_epoch, mup_sums_epoch;
+    std::vector<uint32_t> urow_degree;           // training degree of every user row (row space of the arenas)
     cudaStream_t stream = nullptr;
     cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
 
@@ -189,6 +190,8 @@ size_t stats_floats(const mascot_handle* h) {
     return (size_t)(h->uend.size() + h->iend.size()) * (h->K + 1);
 }
 
+unsigned worker_count(const mascot_handle* h, uint64_t n);
+
 int upload_side_tables(mascot_handle* h, bool users) {
     const uint32_t n = users ? h->n_users : h->n_items;
     const std::vector<uint32_t>& end = users ? h->uend : h->iend;
@@ -197,7 +200,17 @@ int upload_side_tables(mascot_handle* h, bool users) {
     std::vector<uint8_t> prow(n);
     uint32_t s = 0;
     for (size_t g = 0; g < end.size(); g++)
-        for (; s <= end[g] && s < n; s++) { group[s] = (uint16_t)g; prow[s] = prec[g]; }
+        for (; s <= end[g] && s < n; s++) { group[s] = (uint16_t)g; prow[s] = prec[g] ? kRowPrec : 0; }
+    if (users) {
+        // A user whose ratings are so many that several workers hold its row at any time keeps the plain
+        // store: adding up the changes of many concurrent, equally stale updates multiplies the step and
+        // can diverge, while a plain store lets one of them win.  Expected number of workers inside their
+        // read-to-write span of a row: workers x 4 ratings x degree / n.  Measured: 23 still converges
+        // as well as the reference (20M-rating configuration), 82 diverges (252M-rating one); marked above 32.
+        const uint64_t w_est = std::min<uint64_t>(worker_count(h, h->n_train), 16384);
+        for (uint32_t r = 0; r < n && r < h->urow_degree.size(); r++)
+            if ((uint64_t)h->urow_degree[r] * w_est > 8 * h->n_train) prow[r] |= kRowHot;
+    }
     uint16_t** dg = users ? &h->d_ugroup : &h->d_igroup;
     uint8_t** dp = users ? &h->d_uprec_row : &h->d_iprec_row;
     CU(h, dev_alloc(dg, n)); CU(h, dev_alloc(dp, n));
@@ -244,7 +257,7 @@ int promote_group(mascot_handle* h, bool users, size_t g) {
     uint8_t* prow = users ? h->d_uprec_row : h->d_iprec_row;
     const uint32_t b = g ? end[g - 1] + 1 : 0, e = end[g] + 1;
     CU(h, launch_promote_rows(h->K, users ? h->P : h->Q, b, e, h->stream));
-    CU(h, cudaMemsetAsync(prow + b, 1, e - b, h->stream));
+    CU(h, launch_mark_fp32(prow + b, e - b, h->stream));
     prec[g] = 1;
     return MASCOT_OK;
 }
@@ -386,6 +399,7 @@ int mascot_set_ratings_sharded(mascot_handle* h, const mascot_rating* train, uin
     if (h->grouped) {
         std::vector<uint32_t> s2o, cnt;
         degree_sort(train, n_train, true, n_users, user_degree, s2o, h->user2sorted, cnt);
+        h->urow_degree = cnt;                      // sorted position -> degree
         make_groups(cnt, h->cfg.user_group_num, h->uend);
         degree_sort(train, n_train, false, n_items, item_degree, s2o, h->item2sorted, cnt);
         make_groups(cnt, h->cfg.item_group_num, h->iend);
@@ -402,6 +416,8 @@ int mascot_set_ratings_sharded(mascot_handle* h, const mascot_rating* train, uin
         }
     } else {
         h->user2sorted.clear(); h->item2sorted.clear();
+        h->urow_degree.assign(n_users, 0);
+        for (uint64_t j = 0; j < n_train; j++) h->urow_degree[train[j].u]++;
         h->uend.assign(1, n_users - 1); h->iend.assign(1, n_items - 1);
         const uint8_t p = (h->kind == KIND_MEMQUANT) ? 0 : 1;
         h->uprec.assign(1, p); h->iprec.assign(1, p);

@@ -33,8 +33,8 @@ __global__ void encode_kernel(const NodeAos* src, uint64_t n, int shuffle, uint6
         const NodeAos nd = src[s];
         uint32_t uu = umap ? umap[nd.u] : nd.u;
         uint32_t ii = imap ? imap[nd.i] : nd.i;
-        if (uprec[uu]) uu |= kPrecBit;
-        if (iprec[ii]) ii |= kPrecBit;
+        uu |= row_flags_to_code(uprec[uu]);
+        ii |= row_flags_to_code(iprec[ii]);
         r[j] = nd.r; u[j] = uu; i[j] = ii;
         if (src_out) src_out[j] = src_base + (uint32_t)s;
     }
@@ -83,8 +83,8 @@ __global__ void __launch_bounds__(kSortThreads) encode_sorted_kernel(
                 const NodeAos nd = src[s];
                 uint32_t uu = umap ? umap[nd.u] : nd.u;
                 uint32_t ii = keys[t];
-                if (uprec[uu]) uu |= kPrecBit;
-                if (iprec[ii]) ii |= kPrecBit;
+                uu |= row_flags_to_code(uprec[uu]);
+                ii |= row_flags_to_code(iprec[ii]);
                 r[out] = nd.r; u[out] = uu; i[out] = ii;
                 if (src_out) src_out[out] = src_base + (uint32_t)s;
             }
@@ -95,7 +95,7 @@ __global__ void __launch_bounds__(kSortThreads) encode_sorted_kernel(
 __global__ void recode_kernel(uint32_t* ids, uint64_t n, const uint8_t* prec_row) {
     for (uint64_t j = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; j < n; j += (uint64_t)gridDim.x * blockDim.x) {
         const uint32_t id = ids[j] & kIdMask;
-        ids[j] = prec_row[id] ? (id | kPrecBit) : id;
+        ids[j] = id | row_flags_to_code(prec_row[id]);
     }
 }
 
@@ -126,7 +126,7 @@ __global__ void gather_kernel(const __half* a16, const float* a32, const uint8_t
         const int d = (int)(t % K);
         const uint32_t row = row_map ? row_map[e] : e;
         const size_t o = (size_t)row * K + phys_of_logical(K, d);
-        dst[t] = prec_row[row] ? a32[o] : __half2float(a16[o]);
+        dst[t] = (prec_row[row] & kRowPrec) ? a32[o] : __half2float(a16[o]);
     }
 }
 
@@ -176,6 +176,15 @@ cudaError_t launch_encode_stream(const void* d_src_aos, uint64_t n, bool shuffle
         encode_kernel<<<grid_for(n, 256), 256, 0, st>>>(src, n, 0, seed, user_map, item_map, uprec_row, iprec_row,
                                                          r, u, i, src_out, src_base);
     }
+    return cudaGetLastError();
+}
+
+__global__ void mark_fp32_kernel(uint8_t* flags, uint32_t n) {
+    for (uint32_t j = blockIdx.x * blockDim.x + threadIdx.x; j < n; j += gridDim.x * blockDim.x) flags[j] |= kRowPrec;
+}
+cudaError_t launch_mark_fp32(uint8_t* row_flags, uint32_t n, cudaStream_t st) {
+    if (n == 0) return cudaSuccess;
+    mark_fp32_kernel<<<grid_for(n, 256), 256, 0, st>>>(row_flags, n);
     return cudaGetLastError();
 }
 

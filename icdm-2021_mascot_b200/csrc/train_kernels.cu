@@ -134,7 +134,8 @@ __device__ __forceinline__ void st_row(const Arena& A, uint32_t code, int m, con
 
 // Adds (now - before) to a row instead of storing `now`: with several workers on the same row at the
 // same time a plain store erases what the others wrote since this worker read the row, a reduction
-// keeps it.  When nobody else touched the row the result equals `now` (the difference of two nearby
+// keeps it.  (Not used for rows flagged kHotBit: summing the changes of very many concurrent updates
+// that all started from the same stale value multiplies the step; there the plain store stays.)  When nobody else touched the row the result equals `now` (the difference of two nearby
 // values is exact).  128-bit vector reductions, fire and forget.
 template <int K, int MODE>
 __device__ __forceinline__ void add_row_delta(const Arena& A, uint32_t code, int m, const Raw<MODE>& now, const Raw<MODE>& before) {
@@ -620,23 +621,23 @@ constexpr uint32_t F_IDUP = 8u;     // run start whose item also occurs among th
 constexpr int kSpan = 8;            // consecutive chunks handed out together (one ticket per span)
 
 // Shared memory of one worker: two chunks of records, then the user ring, then the item ring.
-template <int K, int MODE, int NS> struct WorkerSmem {
+template <int K, int MODE, int NS, int NSI> struct WorkerSmem {
     static constexpr int TS = K / 8;
     static constexpr int kRowBytes = K * (MODE == ROWS_HALF ? 2 : 4);
     static constexpr int kRecBytes = 2 * TS * 16;
-    static constexpr int kBytes = kRecBytes + 2 * NS * kRowBytes;
+    static constexpr int kBytes = kRecBytes + (NS + NSI) * kRowBytes;
 };
 
-// NS: slots per ring.  User rows are requested D ratings ahead, item rows DI ratings ahead
-// (DI <= D <= NS-1).  The lead is kept as short as the memory latency allows: a row that another
+// NS / NSI: slots of the user / item ring.  User rows are requested D ratings ahead, item rows DI
+// ratings ahead (DI <= D <= NS-1, DI <= NSI-1).  The lead is kept as short as the memory latency allows: a row that another
 // worker updates between the request and the write-back loses that update, and the chance of that
 // grows with the lead.
-template <int K, int KIND, int MODE, bool STATS, int NS, int D, int DI>
+template <int K, int KIND, int MODE, bool STATS, int NS, int NSI, int D, int DI>
 __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
-    using SM = WorkerSmem<K, MODE, NS>;
+    using SM = WorkerSmem<K, MODE, NS, NSI>;
     constexpr int TS = SM::TS;                     // lanes per worker = ratings per chunk
     static_assert(TS % NS == 0, "the ring must divide the chunk");
-    static_assert(DI >= 1 && DI <= D && D <= NS - 1, "leads must fit the ring");
+    static_assert(DI >= 1 && DI <= D && D <= NS - 1 && DI <= NSI - 1 && NS % NSI == 0, "leads must fit the rings");
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31;
     const int m = lane % TS;
@@ -649,7 +650,7 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
     unsigned char* const mine = smem_raw + (size_t)(threadIdx.x / TS) * SM::kBytes;
     uint4* const recs = reinterpret_cast<uint4*>(mine);                  // [2][TS]
     unsigned char* const uring = mine + SM::kRecBytes;                    // [NS][kRowBytes]
-    unsigned char* const iring = uring + NS * SM::kRowBytes;              // [NS][kRowBytes]
+    unsigned char* const iring = uring + NS * SM::kRowBytes;              // [NSI][kRowBytes]
 
     Consts c;
     c.lr = a.lr; c.lam = a.lam;
@@ -662,7 +663,7 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
     c.afp_epoch = a.epoch;
     c.afp_init_threshold = (int)((float)((a.s.n + W - 1) / W) / 10.0f);
     // only the mixed-precision mode reads the precision bit of an id
-    constexpr uint32_t kKeep = (MODE == ROWS_DYN) ? 0xffffffffu : kIdMask;
+    constexpr uint32_t kKeep = (MODE == ROWS_DYN) ? 0xffffffffu : (kIdMask | kHotBit);
 
     if (worker >= W) return;
 
@@ -802,7 +803,7 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
     // prologue: the groups of the iterations -D .. -1
 #pragma unroll
     for (int t = 0; t < D; t++) {
-        if (t - (D - DI) >= 0) request_item(*reinterpret_cast<const uint2*>(recs + (t - (D - DI))), t - (D - DI));
+        if (t - (D - DI) >= 0) request_item(*reinterpret_cast<const uint2*>(recs + (t - (D - DI))), (t - (D - DI)) & (NSI - 1));
         cp_commit();
         request_user(recs[t], t);
         cp_commit();
@@ -827,7 +828,7 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
                     cp_wait<kPendItem>();
                     if (cur_ic != kNoRow) st_row<K, MODE>(a.Q, cur_ic, m, q);
                     if (rec.x & F_IDUP) q = ld_row<K, MODE>(a.Q, ic, m);
-                    else q = lds_row<K, MODE>(iring + t * SM::kRowBytes, ic, m);
+                    else q = lds_row<K, MODE>(iring + (t & (NSI - 1)) * SM::kRowBytes, ic, m);
                     cur_ic = ic;
                 } else {
                     cp_wait<kPendUser>();
@@ -839,14 +840,14 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
                 // into slots whose previous contents have been consumed
                 {
                     const int x = j + D, xi = j + DI;
-                    request_item(*reinterpret_cast<const uint2*>((xi < TS) ? rc + xi : rn + (xi - TS)), (t + DI) & (NS - 1));
+                    request_item(*reinterpret_cast<const uint2*>((xi < TS) ? rc + xi : rn + (xi - TS)), (t + DI) & (NSI - 1));
                     cp_commit();
                     request_user((x < TS) ? rc[x] : rn[x - TS], (t + D) & (NS - 1));
                     cp_commit();
                 }
                 const Raw<MODE> p_before = p;
                 update_one<K, KIND, MODE, STATS>(c, r, uc, ic, p, q, sampled, smp, afp, wmask);
-                if (a.add_user_delta) add_row_delta<K, MODE>(a.P, uc, m, p, p_before);
+                if (a.add_user_delta && !(uc & kHotBit)) add_row_delta<K, MODE>(a.P, uc, m, p, p_before);
                 else st_row<K, MODE>(a.P, uc, m, p);
                 if (STATS && sampled) record(smp, uc, ic);
             }
@@ -882,12 +883,12 @@ int sm_count() {
     return sms;
 }
 
-template <int K, int KIND, int MODE, bool STATS, int NS, int D, int DI>
+template <int K, int KIND, int MODE, bool STATS, int NS, int NSI, int D, int DI>
 cudaError_t launch_ns(KernelArgs a, unsigned warps_per_sm, unsigned workers, cudaStream_t st, LaunchShape* shape) {
     constexpr int TS = K / 8;
     constexpr int kPerWarp = 32 / TS;
-    using SM = WorkerSmem<K, MODE, NS>;
-    auto kern = train_kernel<K, KIND, MODE, STATS, NS, D, DI>;
+    using SM = WorkerSmem<K, MODE, NS, NSI>;
+    auto kern = train_kernel<K, KIND, MODE, STATS, NS, NSI, D, DI>;
     int grid, block;
     const unsigned warps = (workers + kPerWarp - 1) / kPerWarp;
     if (workers <= 1) a.add_user_delta = 0;      // a single worker has nobody to race with: plain stores
@@ -932,13 +933,15 @@ cudaError_t launch_one(const KernelArgs& args, unsigned workers, cudaStream_t st
     const unsigned warps = (workers + kPerWarp - 1) / kPerWarp;
     const unsigned sms = (unsigned)sm_count();
     const unsigned per_sm = warps <= 8 ? warps : (warps + sms - 1) / sms;
-    // Rings of four slots: user rows are requested three ratings ahead, item rows one rating ahead.
-    // Launches that fill the SM with fp32 rows only have the shared memory for two slots.
+    // User ring of four slots (rows requested three ratings ahead), item ring of two (one rating ahead).
+    // Requesting user rows seven ahead was measured on the 100M- and the 252M-rating configuration and
+    // changed nothing: the kernel is not waiting for memory.  Launches that fill the SM with fp32 rows
+    // only have the shared memory for a user ring of two.
     if constexpr (MODE == ROWS_HALF) {
-        return launch_ns<K, KIND, MODE, STATS, 4, 3, 1>(args, per_sm, workers, st, shape);
+        return launch_ns<K, KIND, MODE, STATS, 4, 2, 3, 1>(args, per_sm, workers, st, shape);
     } else {
-        if (per_sm <= 20) return launch_ns<K, KIND, MODE, STATS, 4, 3, 1>(args, per_sm, workers, st, shape);
-        return launch_ns<K, KIND, MODE, STATS, 2, 1, 1>(args, per_sm, workers, st, shape);
+        if (per_sm <= 20) return launch_ns<K, KIND, MODE, STATS, 4, 2, 3, 1>(args, per_sm, workers, st, shape);
+        return launch_ns<K, KIND, MODE, STATS, 2, 2, 1, 1>(args, per_sm, workers, st, shape);
     }
 }
 
