@@ -514,3 +514,59 @@ def test_afp_epochs_bit_exact(mascot, oracle, k):
     assert np.isfinite(Po).all()
     assert_bit_equal(Pg, Po, "P")
     assert_bit_equal(Qg, Qo, "Q")
+
+
+# --------------------------------------------------------------------------------------------
+# replacing the training stream, stream handle
+# --------------------------------------------------------------------------------------------
+def test_reload_train_replaces_the_stream(mascot, oracle):
+    """mascot_reload_train: the next epoch runs over the new ratings (same and different length), with
+    the factors it already has."""
+    rng = np.random.default_rng(77)
+    k, n_users, n_items = 64, 60, 50
+    R1, P, Q = random_problem(rng, n_users, n_items, 1500, k)
+    R2, _, _ = random_problem(rng, n_users, n_items, 1500, k)
+    R3, _, _ = random_problem(rng, n_users, n_items, 777, k)
+    eng = make_engine(mascot, mascot.V_SGD, k)
+    eng.set_ratings(R1, R1[:100], n_users, n_items)
+    eng.set_factors(P, Q)
+    lrs = oracle.lr_schedule(0.01, 0.1, 50)
+    rules = oracle.rules_reference()
+    Po, Qo = P.copy(), Q.copy()
+    for e, R in enumerate((R1, R2, R3)):
+        if e:
+            eng.reload_train(R)
+        st = eng.train_epoch(e)
+        assert st.updates == R.size
+        oracle.sgd_run(k, R, None, Po, Qo, float(lrs[e]), 0.05, rules)
+    Pg, Qg = eng.get_factors(0)
+    eng.close()
+    assert_bit_equal(Pg, Po, "P")
+    assert_bit_equal(Qg, Qo, "Q")
+
+
+def test_stream_handle_orders_caller_work(mascot):
+    """mascot_get_stream: a torch copy queued on the engine's stream sees the factors of the epoch
+    queued before it without any host-side wait in between."""
+    import torch
+    rng = np.random.default_rng(5)
+    k, n_users, n_items = 64, 40, 30
+    R, P, Q = random_problem(rng, n_users, n_items, 900, k)
+    eng = make_engine(mascot, mascot.V_SGD, k)
+    eng.set_ratings(R, R[:50], n_users, n_items)
+    eng.set_factors(P, Q)
+    ext = torch.cuda.ExternalStream(eng.stream_handle(), device=torch.device("cuda", 0))
+    (p16, b16), (p32, b32) = eng.item_rows(0, n_items)
+    assert p16 == 0 and b32 == n_items * k * 4, "the fp32 trainer keeps only the fp32 arena"
+
+    class Raw:
+        __cuda_array_interface__ = {"shape": (b32,), "typestr": "|u1", "data": (p32, False), "version": 2}
+    view = torch.as_tensor(Raw(), device="cuda:0")
+    eng.train_segment(0, 0, wait=False)
+    with torch.cuda.stream(ext):
+        snap = view.clone()
+    ext.synchronize()
+    _, Qg = eng.get_factors(0)
+    eng.close()
+    got = np.sort(snap.cpu().numpy().view(np.float32))
+    assert (got == np.sort(Qg.reshape(-1))).all(), "the copy ran after the kernel (same values, row-internal order is the library's)"
