@@ -32,6 +32,12 @@ struct mascot_handle {
     std::vector<uint32_t> urow_degree;           // training degree of every user row (row space of the arenas)
     cudaStream_t stream = nullptr;
     cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
+    // streamed epochs: a copy stream and two staging buffers, so that the upload of one piece of the
+    // rating array overlaps the encoding and the updates of the piece before it
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t ev_copied[2] = {nullptr, nullptr}, ev_free[2] = {nullptr, nullptr};
+    mascot_rating* d_stage[2] = {nullptr, nullptr};
+    uint64_t stage_ratings = 0;
 
     uint32_t n_users = 0, n_items = 0;
     uint64_t n_train = 0, n_test = 0;
@@ -360,6 +366,12 @@ int mascot_destroy(mascot_handle* h) {
     free_ratings(h);
     dev_free(h->d_scratch); dev_free(h->d_work_counter);
     for (auto& ev : h->ev) if (ev) cudaEventDestroy(ev);
+    for (int b = 0; b < 2; b++) {
+        if (h->ev_copied[b]) cudaEventDestroy(h->ev_copied[b]);
+        if (h->ev_free[b]) cudaEventDestroy(h->ev_free[b]);
+        if (h->d_stage[b]) cudaFree(h->d_stage[b]);
+    }
+    if (h->copy_stream) cudaStreamDestroy(h->copy_stream);
     if (h->stream) cudaStreamDestroy(h->stream);
     delete h;
     return MASCOT_OK;
@@ -594,16 +606,21 @@ SampleStats stats_view(mascot_handle* h) {
 // Runs the update kernel over stream positions [begin, end).  With `collect`, the last
 // sample_ratio of the range (mf_methods.cu:102-103, 173-174) goes through the statistics kernel -
 // a second launch, so that only the sampled fraction pays for the statistics.
-int train_range(mascot_handle* h, float lr, uint32_t epoch, uint64_t begin, uint64_t end, bool collect, LaunchShape* shape, uint32_t* launches) {
+// `policy_n` (0 = the range's own length) is the stream length the automatic worker count is taken
+// from; `head_override` (when not ~0) is the number of leading ratings of the range that are NOT sampled.
+int train_range(mascot_handle* h, float lr, uint32_t epoch, uint64_t begin, uint64_t end, bool collect, LaunchShape* shape, uint32_t* launches,
+                uint64_t policy_n = 0, uint64_t head_override = ~0ull) {
     if (end <= begin) return MASCOT_OK;
     const uint64_t n = end - begin;
     bool any_f32 = false;
     for (uint8_t p : h->uprec) any_f32 |= p != 0;
     for (uint8_t p : h->iprec) any_f32 |= p != 0;
-    const unsigned workers = worker_count(h, n);
+    const unsigned workers = worker_count(h, policy_n ? policy_n : n);
     Stream s; s.r = h->tr_r + begin; s.u = h->tr_u + begin; s.i = h->tr_i + begin; s.n = n;
     uint64_t head = n;
-    if (collect) {
+    if (head_override != ~0ull) {
+        head = std::min<uint64_t>(head_override, n);
+    } else if (collect) {
         const uint64_t sample_num = (uint64_t)((float)n * h->cfg.sample_ratio);
         head = n - std::min<uint64_t>(sample_num, n);
     }
@@ -783,6 +800,93 @@ int mascot_train_epoch(mascot_handle* h, uint32_t epoch, mascot_epoch_stats* out
     if (out) {
         std::memset(out, 0, sizeof(*out));
         out->updates = h->n_train; out->lr = lr; out->error_check = check ? 1 : 0; out->pass_bits = (uint32_t)bits_this_epoch;
+        out->promoted_user_groups = promoted_u; out->promoted_item_groups = promoted_i; out->kernel_launches = launches;
+        out->algorithmic_bytes = bytes_this_epoch;
+        out->workers = shape.workers;
+        cudaEventElapsedTime(&out->kernel_ms, h->ev[1], h->ev[2]);
+        cudaEventElapsedTime(&out->total_ms, h->ev[0], h->ev[3]);
+    }
+    return MASCOT_OK;
+}
+
+int mascot_train_epoch_streamed(mascot_handle* h, uint32_t epoch, const mascot_rating* train, uint64_t n_train, mascot_epoch_stats* out) {
+    if (!h || (!train && n_train)) return MASCOT_ERR_BAD_ARG;
+    if (!h->have_ratings || !h->have_factors) return fail(h, MASCOT_ERR_STATE, "ratings and factors must be set before training");
+    if (h->kind == KIND_AFP) return fail(h, MASCOT_ERR_UNSUPPORTED, "the AFP trainer keeps its per-worker state for a whole epoch: use mascot_train_epoch");
+    CU(h, cudaSetDevice(h->cfg.device));
+    constexpr uint64_t kPiece = 8ull << 20;           // ratings per piece (96 MiB of input)
+    if (!h->copy_stream) {
+        CU(h, cudaStreamCreateWithFlags(&h->copy_stream, cudaStreamNonBlocking));
+        for (int b = 0; b < 2; b++) {
+            CU(h, cudaEventCreateWithFlags(&h->ev_copied[b], cudaEventDisableTiming));
+            CU(h, cudaEventCreateWithFlags(&h->ev_free[b], cudaEventDisableTiming));
+        }
+    }
+    const uint64_t piece = std::min<uint64_t>(kPiece, std::max<uint64_t>(n_train, 1));
+    if (h->stage_ratings < piece) {
+        for (int b = 0; b < 2; b++) { if (h->d_stage[b]) cudaFree(h->d_stage[b]); h->d_stage[b] = nullptr; }
+        h->stage_ratings = 0;
+        for (int b = 0; b < 2; b++) CU(h, cudaMalloc(&h->d_stage[b], sizeof(mascot_rating) * piece));
+        h->stage_ratings = piece;
+    }
+    if (n_train != h->n_train) {
+        dev_free(h->tr_r); dev_free(h->tr_u); dev_free(h->tr_i); dev_free(h->tr_src);
+        CU(h, dev_alloc(&h->tr_r, n_train)); CU(h, dev_alloc(&h->tr_u, n_train)); CU(h, dev_alloc(&h->tr_i, n_train));
+        if (n_train < (1ull << 32)) CU(h, dev_alloc(&h->tr_src, n_train));
+        h->n_train = n_train;
+    }
+    // the pieces become the segments of the resident stream (seeded permutation inside each piece)
+    h->seg_off.clear();
+    for (uint64_t off = 0; off < n_train; off += piece) h->seg_off.push_back(off);
+    h->seg_off.push_back(n_train);
+
+    const float lr = epoch < h->lr.size() ? h->lr[epoch] : lr_at(h->cfg, epoch);
+    const bool muppet = h->kind == KIND_MUPPET;
+    const int bits_this_epoch = muppet ? muppet_bits(h) : 0;
+    const bool check = muppet || (h->grouped && is_check_epoch(h->cfg, epoch));
+    uint32_t launches = 0, promoted_u = 0, promoted_i = 0;
+    const uint64_t bytes_this_epoch = algorithmic_bytes(h);
+    uint64_t first_sample = n_train;
+    if (check) first_sample = n_train - std::min<uint64_t>((uint64_t)((float)n_train * h->cfg.sample_ratio), n_train);
+    CU(h, cudaEventRecord(h->ev[0], h->stream));
+    if (check) CU(h, cudaMemsetAsync(h->d_stats, 0, sizeof(float) * h->stats_stride * h->stats_copies, h->stream));
+    CU(h, cudaEventRecord(h->ev[1], h->stream));
+    LaunchShape shape;
+    int rc;
+    for (size_t c = 0; c + 1 < h->seg_off.size(); c++) {
+        const int b = (int)(c & 1);
+        const uint64_t off = h->seg_off[c], len = h->seg_off[c + 1] - off;
+        if (c >= 2) CU(h, cudaStreamWaitEvent(h->copy_stream, h->ev_free[b], 0));
+        CU(h, cudaMemcpyAsync(h->d_stage[b], train + off, sizeof(mascot_rating) * len, cudaMemcpyHostToDevice, h->copy_stream));
+        CU(h, cudaEventRecord(h->ev_copied[b], h->copy_stream));
+        CU(h, cudaStreamWaitEvent(h->stream, h->ev_copied[b], 0));
+        CU(h, launch_encode_stream(h->d_stage[b], len, h->cfg.shuffle != 0, h->cfg.seed + 0x9e3779b97f4a7c15ull * c, h->d_umap, h->d_imap,
+                                   h->d_uprec_row, h->d_iprec_row, h->n_items, h->tr_r + off, h->tr_u + off, h->tr_i + off,
+                                   h->tr_src ? h->tr_src + off : nullptr, (uint32_t)off, h->stream));
+        launches++;
+        CU(h, cudaEventRecord(h->ev_free[b], h->stream));
+        const uint64_t head = first_sample <= off ? 0 : std::min<uint64_t>(first_sample - off, len);
+        if ((rc = train_range(h, lr, epoch, off, off + len, check, &shape, &launches, n_train, head)) != MASCOT_OK) return rc;
+    }
+    if (check && h->stats_copies > 1) {
+        CU(h, launch_reduce_stats(h->d_stats, h->stats_copies, h->stats_stride, stats_floats(h), h->stream));
+        launches++;
+    }
+    CU(h, cudaEventRecord(h->ev[2], h->stream));
+    if (check) {
+        const int saved = h->stats_copies;
+        h->stats_copies = 1;
+        rc = fetch_stats(h, nullptr);
+        h->stats_copies = saved;
+        if (rc != MASCOT_OK) return rc;
+        if (muppet) muppet_policy(h, epoch);
+        else if ((rc = apply_stats(h, epoch, &promoted_u, &promoted_i, &launches)) != MASCOT_OK) return rc;
+    }
+    CU(h, cudaEventRecord(h->ev[3], h->stream));
+    CU(h, cudaEventSynchronize(h->ev[3]));
+    if (out) {
+        std::memset(out, 0, sizeof(*out));
+        out->updates = n_train; out->lr = lr; out->error_check = check ? 1 : 0; out->pass_bits = (uint32_t)bits_this_epoch;
         out->promoted_user_groups = promoted_u; out->promoted_item_groups = promoted_i; out->kernel_launches = launches;
         out->algorithmic_bytes = bytes_this_epoch;
         out->workers = shape.workers;

@@ -25,7 +25,7 @@ EXPORTS = [
     "mascot_get_factors", "mascot_get_group_info", "mascot_get_index_maps", "mascot_get_sample_stats",
     "mascot_get_test_ratings", "mascot_promote_group", "mascot_reload_train", "mascot_stream_source_index", "mascot_get_stream_order", "mascot_rmse_host", "mascot_rmse_device", "mascot_rmse_device_noalloc",
     "mascot_set_ratings_sharded", "mascot_is_check_epoch", "mascot_stats_begin", "mascot_train_segment", "mascot_stats_fetch",
-    "mascot_stats_apply", "mascot_item_rows", "mascot_sync", "mascot_get_stream", "mascot_eval_sq_error",
+    "mascot_stats_apply", "mascot_item_rows", "mascot_sync", "mascot_get_stream", "mascot_eval_sq_error", "mascot_train_epoch_streamed",
 ]
 
 
@@ -209,6 +209,17 @@ class Engine:
         """Replace the training stream from a raw host address (the per-step input path)."""
         self._check(self._lib.mascot_reload_train(self._h, C.c_void_p(train_ptr), C.c_uint64(n_train)))
         self.n_train = n_train
+
+    def train_epoch_streamed_raw(self, epoch, train_ptr, n_train):
+        """One epoch over a rating array in host memory (upload overlapped with the updates)."""
+        st = EpochStats()
+        self._check(self._lib.mascot_train_epoch_streamed(self._h, C.c_uint32(epoch), C.c_void_p(train_ptr), C.c_uint64(n_train), C.byref(st)))
+        self.n_train = n_train
+        return st
+
+    def train_epoch_streamed(self, epoch, train):
+        train = as_ratings(train)
+        return self.train_epoch_streamed_raw(epoch, train.ctypes.data, train.size)
 
     def reload_train(self, train):
         train = as_ratings(train)

@@ -215,6 +215,16 @@ MASCOT_API int mascot_set_ratings_sharded(mascot_handle* h, const mascot_rating*
                                const uint64_t* segment_offsets, uint32_t n_segments,
                                const mascot_rating* test, uint64_t n_test, uint32_t n_users, uint32_t n_items,
                                const uint32_t* user_degree, const uint32_t* item_degree);
+/* One epoch over a rating array that is still in HOST memory (pinned memory for a real overlap):
+ * the array is uploaded in pieces of 8Mi ratings on a copy stream while the piece before it is
+ * encoded and trained, so the epoch costs max(upload, updates) instead of their sum.  The seeded
+ * permutation and the item-sorted windows stay inside a piece; afterwards the pieces are the
+ * segments of the resident stream, as after mascot_reload_train.  Ids must be those given to
+ * mascot_set_ratings (same users/items); the statistics of a check epoch come from the last
+ * sample_ratio of the whole array.  No reference counterpart (the reference uploads once,
+ * mf_methods.cu:41-42).  AFP is not supported here (its per-worker state spans a whole epoch). */
+MASCOT_API int mascot_train_epoch_streamed(mascot_handle* h, uint32_t epoch, const mascot_rating* train, uint64_t n_train,
+                                mascot_epoch_stats* stats);
 /* 1 when `epoch` computes group errors (mf_methods.cu:168-175), else 0. */
 MASCOT_API int mascot_is_check_epoch(const mascot_handle* h, uint32_t epoch);
 /* Zero the statistic accumulators (start of a check epoch). */

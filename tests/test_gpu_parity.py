@@ -570,3 +570,49 @@ def test_stream_handle_orders_caller_work(mascot):
     eng.close()
     got = np.sort(snap.cpu().numpy().view(np.float32))
     assert (got == np.sort(Qg.reshape(-1))).all(), "the copy ran after the kernel (same values, row-internal order is the library's)"
+
+
+def test_streamed_epoch_equals_resident_epoch(mascot, oracle):
+    """mascot_train_epoch_streamed on host ratings == mascot_train_epoch on the resident stream, for a
+    MASCOT run through its first check epochs (factors, statistics and precisions bit for bit)."""
+    rng = np.random.default_rng(91)
+    k, n_users, n_items, n = 128, 150, 120, 6001
+    R, P, Q = random_problem(rng, n_users, n_items, n, k, scale=0.2)
+    engines = []
+    for _ in range(2):
+        eng = make_engine(mascot, mascot.V_MASCOT, k, user_group_num=5, item_group_num=4, sample_ratio=0.3, interval=1,
+                          error_threshold=0.5)
+        eng.set_ratings(R, R[:200], n_users, n_items)
+        eng.set_factors(P, Q)
+        engines.append(eng)
+    a, b = engines
+    for e in range(8):
+        sa = a.train_epoch(e)
+        sb = b.train_epoch_streamed(e, R)
+        assert (sa.error_check, sa.promoted_user_groups, sa.promoted_item_groups) == (sb.error_check, sb.promoted_user_groups, sb.promoted_item_groups)
+        for x, y in zip(a.sample_stats(), b.sample_stats()):
+            assert_bit_equal(x, y, f"statistics epoch {e}")
+    for x, y in zip(a.get_factors(1), b.get_factors(1)):
+        assert_bit_equal(x, y, "factors")
+    assert a.group_info(0)[1].tolist() == b.group_info(0)[1].tolist()
+    a.close(); b.close()
+
+
+def test_streamed_epoch_over_two_pieces_bit_exact(mascot, oracle):
+    """A rating array longer than one upload piece (8Mi ratings): the pieces are trained in order, each
+    exactly once, and the deterministic result equals the sequential oracle."""
+    rng = np.random.default_rng(92)
+    k, n_users, n_items = 64, 3000, 2000
+    n = (8 << 20) + 1234
+    R, P, Q = random_problem(rng, n_users, n_items, n, k, scale=0.1)
+    eng = make_engine(mascot, mascot.V_SGD, k)
+    eng.set_ratings(R[:1000], R[:100], n_users, n_items)
+    eng.set_factors(P, Q)
+    st = eng.train_epoch_streamed(0, R)
+    assert st.updates == n
+    Pg, Qg = eng.get_factors(0)
+    eng.close()
+    Po, Qo = P.copy(), Q.copy()
+    oracle.sgd_run(k, R, None, Po, Qo, 0.01, 0.05, oracle.rules_reference())
+    assert_bit_equal(Pg, Po, "P")
+    assert_bit_equal(Qg, Qo, "Q")
