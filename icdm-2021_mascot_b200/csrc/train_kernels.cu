@@ -935,14 +935,9 @@ cudaError_t launch_one(const KernelArgs& args, unsigned workers, cudaStream_t st
     const unsigned per_sm = warps <= 8 ? warps : (warps + sms - 1) / sms;
     // User ring of four slots (rows requested three ratings ahead), item ring of two (one rating ahead).
     // Requesting user rows seven ahead was measured on the 100M- and the 252M-rating configuration and
-    // changed nothing: the kernel is not waiting for memory.  Launches that fill the SM with fp32 rows
-    // only have the shared memory for a user ring of two.
-    if constexpr (MODE == ROWS_HALF) {
-        return launch_ns<K, KIND, MODE, STATS, 4, 2, 3, 1>(args, per_sm, workers, st, shape);
-    } else {
-        if (per_sm <= 20) return launch_ns<K, KIND, MODE, STATS, 4, 2, 3, 1>(args, per_sm, workers, st, shape);
-        return launch_ns<K, KIND, MODE, STATS, 2, 2, 1, 1>(args, per_sm, workers, st, shape);
-    }
+    // changed nothing: the kernel is not waiting for memory.  With fp32 rows the slots are twice as large
+    // and the occupancy query below trims the number of blocks per SM accordingly.
+    return launch_ns<K, KIND, MODE, STATS, 4, 2, 3, 1>(args, per_sm, workers, st, shape);
 }
 
 template <int K>
