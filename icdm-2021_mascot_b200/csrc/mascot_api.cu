@@ -553,9 +553,12 @@ namespace {
 unsigned worker_count(const mascot_handle* h, uint64_t n) {
     // -wg 0 = automatic: one worker per 8192 ratings keeps the sequential depth per worker - and with
     // it the convergence per epoch - at the level of the reference's tuned runs; the launch caps the
-    // count at what the GPU can keep resident.
+    // count at what the GPU can keep resident.  Small sets (under 1.5M ratings) would leave most SMs
+    // idle at that rate: they get one worker per 512 ratings, at most 1536 (measured on the 0.8M-rating
+    // configuration: final RMSE still below the reference's, three times the throughput of 512 workers).
     if (h->cfg.deterministic) return 1u;
     if (h->cfg.num_workers) return h->cfg.num_workers;
+    if (n < 1500000) return (unsigned)std::min<uint64_t>(std::max<uint64_t>(n / 512, 512), 1536);
     return (unsigned)std::min<uint64_t>(std::max<uint64_t>(n / 8192, 512), 1u << 20);
 }
 

@@ -76,7 +76,8 @@ typedef struct mascot_config {
                                        fewer workers lose fewer updates of popular rows to races and
                                        converge faster per epoch, more workers run faster; rounded up
                                        to fill every SM evenly; 0 = automatic (one per 8192 training
-                                       ratings, at least 512, at most what the GPU keeps resident)
+                                       ratings, at least 512, at most what the GPU keeps resident;
+                                       sets under 1.5M ratings: one per 512 ratings, at most 1536)
                                                                                    default 2048        */
     uint32_t epoch;              /* -l   number of epochs          default 50                  */
     uint32_t thread_block_size;  /* -bl  accepted for CLI parity, not used (blocks are sized per SM) */
