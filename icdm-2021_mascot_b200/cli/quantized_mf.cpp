@@ -4,7 +4,8 @@
 //   -i train  -y test  -o out  -l epochs(50)  -k 64|128(128)  -b lambda(0.015)  -a lr(0.01)  -d decay(0.1)
 //   -wg workers  -bl block(128)  -v variant(7)  -s|-r sample ratio(0.01)  -ug / -ig groups(10)
 //   -e error threshold(0.001)  -it interval(1)  -rc save reconst test set(0)
-// Variants: 1 MASCOT, 2 AFP, 3 MuPPET, 4 MPT, 5 FP32 SGD, 7 fp16 storage.  Additive flags: -seed N, -det 1 (sequential verification mode), -dev N.
+// Variants: 1 MASCOT, 2 AFP, 3 MuPPET, 4 MPT, 5 FP32 SGD, 6 MASCOT "naive" (same engine path as 1),
+// 7 fp16 storage, 8 whole-model switching.  Additive flags: -seed N, -det 1 (sequential verification mode), -dev N.
 // Difference: when -wg is absent the engine picks the worker count itself (the reference defaults to
 // 2048 warps, a setting tuned for a 36-SM GPU).
 #include <chrono>
@@ -104,7 +105,7 @@ int main(int argc, const char* argv[]) {
     if (mascot_set_ratings(h, data.train.data(), data.train.size(), data.test.data(), data.test.size(), n_users, n_items) != MASCOT_OK)
         return die("set_ratings");
     const double preprocess_us = now_us() - t_pre;
-    if (cfg.version == MASCOT_V_MASCOT) {
+    if (cfg.version == MASCOT_V_MASCOT || cfg.version == MASCOT_V_NAIVE) {
         for (int side = 0; side < 2; side++) {
             uint32_t ng = 0;
             mascot_get_group_info(h, side, &ng, nullptr, nullptr, nullptr);

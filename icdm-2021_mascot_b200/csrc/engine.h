@@ -37,7 +37,8 @@ struct SampleStats {
     size_t copy_stride = 0;
 };
 
-enum TrainKind { KIND_MIXED = 0, KIND_FP32 = 1, KIND_MPT = 2, KIND_MEMQUANT = 3, KIND_MUPPET = 4, KIND_AFP = 5 };
+enum TrainKind { KIND_MIXED = 0, KIND_FP32 = 1, KIND_MPT = 2, KIND_MEMQUANT = 3, KIND_MUPPET = 4, KIND_AFP = 5,
+                 KIND_SWITCH = 6 /* all rows binary16, MASCOT arithmetic, statistics in MuPPET's form */ };
 
 struct LaunchShape {
     int grid = 0;

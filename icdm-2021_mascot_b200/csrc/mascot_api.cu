@@ -30,6 +30,8 @@ struct mascot_handle {
     float mup_max_diversity = -1.f;
     std::vector<float> mup_norms_epoch, mup_sums_epoch;
     std::vector<uint32_t> urow_degree;           // training degree of every user row (row space of the arenas)
+    bool switched_to_fp32 = false;               // whole-model switching trainer: the switch has happened
+    float switch_initial_error = 1.f;            // its error at epoch index 5 (mf_methods.cu:1444, 1530)
     cudaStream_t stream = nullptr;
     cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
     // streamed epochs: a copy stream and two staging buffers, so that the upload of one piece of the
@@ -330,6 +332,8 @@ int mascot_create(const mascot_config* cfg, mascot_handle** out) {
         case MASCOT_V_SGD: kind = KIND_FP32; break;
         case MASCOT_V_MPT: kind = KIND_MPT; break;
         case MASCOT_V_MEMQUANT: kind = KIND_MEMQUANT; break;
+        case MASCOT_V_NAIVE: kind = KIND_MIXED; break;
+        case MASCOT_V_SWITCH_ONLY: kind = KIND_SWITCH; break;
         case MASCOT_V_MUPPET: kind = KIND_MUPPET; break;
         case MASCOT_V_AFP: kind = KIND_AFP; break;
         default: return fail(nullptr, MASCOT_ERR_BAD_ARG, "unknown training variant");
@@ -342,7 +346,7 @@ int mascot_create(const mascot_config* cfg, mascot_handle** out) {
     if (cfg->device < 0 || cfg->device >= ndev) return fail(nullptr, MASCOT_ERR_NO_DEVICE, "requested CUDA device does not exist");
     mascot_handle* h = new (std::nothrow) mascot_handle();
     if (!h) return fail(nullptr, MASCOT_ERR_OOM, "host allocation failed");
-    h->cfg = *cfg; h->K = (int)cfg->k; h->kind = kind; h->grouped = (cfg->version == MASCOT_V_MASCOT);
+    h->cfg = *cfg; h->K = (int)cfg->k; h->kind = kind; h->grouped = (cfg->version == MASCOT_V_MASCOT || cfg->version == MASCOT_V_NAIVE);
     h->mup_idx = cfg->is_yahoo ? 1 : 0;            // mf_methods.cu:600-601
     for (int j = 0; j < 5; j++) if (cfg->muppet_width == (uint32_t)muppet_width_at(j)) h->mup_idx = j;
     h->lr.resize(cfg->epoch);
@@ -431,7 +435,7 @@ int mascot_set_ratings_sharded(mascot_handle* h, const mascot_rating* train, uin
         h->urow_degree.assign(n_users, 0);
         for (uint64_t j = 0; j < n_train; j++) h->urow_degree[train[j].u]++;
         h->uend.assign(1, n_users - 1); h->iend.assign(1, n_items - 1);
-        const uint8_t p = (h->kind == KIND_MEMQUANT) ? 0 : 1;
+        const uint8_t p = (h->kind == KIND_MEMQUANT || h->kind == KIND_SWITCH) ? 0 : 1;
         h->uprec.assign(1, p); h->iprec.assign(1, p);
         h->udeg_sum.assign(1, n_train); h->ideg_sum.assign(1, n_train);
     }
@@ -462,7 +466,7 @@ int mascot_set_ratings_sharded(mascot_handle* h, const mascot_rating* train, uin
 
     // --- factor arenas and statistics ---
     const size_t pu = (size_t)n_users * h->K, qi = (size_t)n_items * h->K;
-    if (h->kind == KIND_MIXED || h->kind == KIND_MEMQUANT) { CU(h, dev_alloc(&h->P.f16, pu)); CU(h, dev_alloc(&h->Q.f16, qi)); }
+    if (h->kind == KIND_MIXED || h->kind == KIND_MEMQUANT || h->kind == KIND_SWITCH) { CU(h, dev_alloc(&h->P.f16, pu)); CU(h, dev_alloc(&h->Q.f16, qi)); }
     if (h->kind != KIND_MEMQUANT) { CU(h, dev_alloc(&h->P.f32, pu)); CU(h, dev_alloc(&h->Q.f32, qi)); }
     h->stats_copies = h->cfg.deterministic ? 1 : kStatCopies;
     h->stats_stride = (stats_floats(h) + 63) / 64 * 64;
@@ -595,6 +599,32 @@ void muppet_policy(mascot_handle* h, uint32_t epoch) {
     }
 }
 
+int promote_group(mascot_handle* h, bool users, size_t g);
+int recode_side(mascot_handle* h, bool users);
+
+// Whole-model switching trainer after a check epoch (mf_methods.cu:1515-1545): error = squared norm of
+// the summed sampled updates / sum of their squared norms, relative to its value at epoch index 5;
+// above the threshold every row is widened to fp32 and the fp32 trainer takes over.
+int switch_only_policy(mascot_handle* h, uint32_t epoch, uint32_t* promoted_u, uint32_t* promoted_i) {
+    const int K = h->K;
+    float sq = 0.f;
+    for (int d = 0; d < K; d++) sq += powf(h->h_stats[d], 2);
+    float error = sq / h->h_stats[(size_t)2 * K];
+    error = error / h->switch_initial_error;
+    h->uerr[0] = error; h->ierr[0] = error;
+    if (epoch == 5) h->switch_initial_error = error;
+    if (epoch > 5 && error > h->cfg.error_threshold) {
+        int rc;
+        if ((rc = promote_group(h, true, 0)) != MASCOT_OK) return rc;
+        if ((rc = promote_group(h, false, 0)) != MASCOT_OK) return rc;
+        if ((rc = recode_side(h, true)) != MASCOT_OK) return rc;
+        if ((rc = recode_side(h, false)) != MASCOT_OK) return rc;
+        h->switched_to_fp32 = true;
+        *promoted_u = 1; *promoted_i = 1;
+    }
+    return MASCOT_OK;
+}
+
 SampleStats stats_view(mascot_handle* h) {
     const int ug = (int)h->uend.size(), ig = (int)h->iend.size(), K = h->K;
     SampleStats st;
@@ -619,6 +649,8 @@ int train_range(mascot_handle* h, float lr, uint32_t epoch, uint64_t begin, uint
     for (uint8_t p : h->uprec) any_f32 |= p != 0;
     for (uint8_t p : h->iprec) any_f32 |= p != 0;
     const unsigned workers = worker_count(h, policy_n ? policy_n : n);
+    // after its switch the whole-model switching trainer is the plain fp32 trainer (sgd_kernel.h:296-326)
+    const TrainKind kind = (h->kind == KIND_SWITCH && h->switched_to_fp32) ? KIND_FP32 : h->kind;
     Stream s; s.r = h->tr_r + begin; s.u = h->tr_u + begin; s.i = h->tr_i + begin; s.n = n;
     uint64_t head = n;
     if (head_override != ~0ull) {
@@ -629,14 +661,14 @@ int train_range(mascot_handle* h, float lr, uint32_t epoch, uint64_t begin, uint
     }
     if (head > 0) {
         Stream sa = s; sa.n = head;
-        CU(h, launch_train(h->K, h->kind, sa, h->P, h->Q, lr, h->cfg.lambda, nullptr, any_f32, workers,
+        CU(h, launch_train(h->K, kind, sa, h->P, h->Q, lr, h->cfg.lambda, nullptr, any_f32, workers,
                            h->d_work_counter, muppet_bits(h), (int)epoch, h->cfg.plain_user_stores == 0, h->stream, shape));
         (*launches)++;
     }
     if (head < n) {
         Stream sb; sb.r = s.r + head; sb.u = s.u + head; sb.i = s.i + head; sb.n = n - head;
         const SampleStats st = stats_view(h);
-        CU(h, launch_train(h->K, h->kind, sb, h->P, h->Q, lr, h->cfg.lambda, &st, any_f32, workers,
+        CU(h, launch_train(h->K, kind, sb, h->P, h->Q, lr, h->cfg.lambda, &st, any_f32, workers,
                            h->d_work_counter, muppet_bits(h), (int)epoch, h->cfg.plain_user_stores == 0, h->stream, shape));
         (*launches)++;
     }
@@ -774,7 +806,8 @@ int mascot_train_epoch(mascot_handle* h, uint32_t epoch, mascot_epoch_stats* out
     const bool muppet = h->kind == KIND_MUPPET;
     const int bits_this_epoch = muppet ? muppet_bits(h) : 0;
     // MuPPET samples every epoch (its statistics feed the width policy), MASCOT on its check epochs
-    const bool check = muppet || (h->grouped && is_check_epoch(h->cfg, epoch));
+    const bool switch_only = h->kind == KIND_SWITCH;
+    const bool check = muppet || ((h->grouped || (switch_only && !h->switched_to_fp32)) && is_check_epoch(h->cfg, epoch));
     uint32_t launches = 0, promoted_u = 0, promoted_i = 0;
     const uint64_t bytes_this_epoch = algorithmic_bytes(h);    // with the precisions the kernel is about to see
     CU(h, cudaEventRecord(h->ev[0], h->stream));
@@ -796,6 +829,7 @@ int mascot_train_epoch(mascot_handle* h, uint32_t epoch, mascot_epoch_stats* out
         h->stats_copies = saved;
         if (rc != MASCOT_OK) return rc;
         if (muppet) muppet_policy(h, epoch);
+        else if (switch_only) { if ((rc = switch_only_policy(h, epoch, &promoted_u, &promoted_i)) != MASCOT_OK) return rc; }
         else if ((rc = apply_stats(h, epoch, &promoted_u, &promoted_i, &launches)) != MASCOT_OK) return rc;
     }
     CU(h, cudaEventRecord(h->ev[3], h->stream));
@@ -846,7 +880,8 @@ int mascot_train_epoch_streamed(mascot_handle* h, uint32_t epoch, const mascot_r
     const float lr = epoch < h->lr.size() ? h->lr[epoch] : lr_at(h->cfg, epoch);
     const bool muppet = h->kind == KIND_MUPPET;
     const int bits_this_epoch = muppet ? muppet_bits(h) : 0;
-    const bool check = muppet || (h->grouped && is_check_epoch(h->cfg, epoch));
+    const bool switch_only = h->kind == KIND_SWITCH;
+    const bool check = muppet || ((h->grouped || (switch_only && !h->switched_to_fp32)) && is_check_epoch(h->cfg, epoch));
     uint32_t launches = 0, promoted_u = 0, promoted_i = 0;
     const uint64_t bytes_this_epoch = algorithmic_bytes(h);
     uint64_t first_sample = n_train;
@@ -883,6 +918,7 @@ int mascot_train_epoch_streamed(mascot_handle* h, uint32_t epoch, const mascot_r
         h->stats_copies = saved;
         if (rc != MASCOT_OK) return rc;
         if (muppet) muppet_policy(h, epoch);
+        else if (switch_only) { if ((rc = switch_only_policy(h, epoch, &promoted_u, &promoted_i)) != MASCOT_OK) return rc; }
         else if ((rc = apply_stats(h, epoch, &promoted_u, &promoted_i, &launches)) != MASCOT_OK) return rc;
     }
     CU(h, cudaEventRecord(h->ev[3], h->stream));

@@ -749,9 +749,9 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
         }
     };
     auto record = [&](const Sample& smp, uint32_t uc, uint32_t ic) {
-        if constexpr (KIND == KIND_MUPPET) {
-            // muppet_sgd_kernel.h:266-285: the squared norm of both gradients goes to the worker's
-            // running sum, the element-wise sum of both gradients to k shared accumulators
+        if constexpr (KIND == KIND_MUPPET || KIND == KIND_SWITCH) {
+            // muppet_sgd_kernel.h:266-285, sgd_kernel.h:266-285: the squared norm of both gradients goes to the
+            // worker's running sum, the element-wise sum of both gradients to k shared accumulators
             if (smp.user) {
                 const float n = worker_sum<TS>(muppet_norm_partial<K>(smp.gp, smp.gq), wmask);
                 V8f both;
@@ -860,7 +860,7 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
     cp_wait<0>();
     if (cur_ic != kNoRow) st_row<K, MODE>(a.Q, cur_ic, m, q);
     if (STATS) {
-        if constexpr (KIND == KIND_MUPPET) { if (m == 0) atomicAdd(nsum_p, nq_acc); }
+        if constexpr (KIND == KIND_MUPPET || KIND == KIND_SWITCH) { if (m == 0) atomicAdd(nsum_p, nq_acc); }
         else flush_item_stats();
     }
 }
@@ -953,6 +953,9 @@ cudaError_t launch_k(TrainKind kind, const KernelArgs& a, bool stats, bool any_f
         case KIND_MPT: return launch_one<K, KIND_MPT, ROWS_F32, false>(a, workers, st, sh);
         case KIND_MEMQUANT: return launch_one<K, KIND_MEMQUANT, ROWS_HALF, false>(a, workers, st, sh);
         case KIND_AFP: return launch_one<K, KIND_AFP, ROWS_F32, false>(a, workers, st, sh);
+        case KIND_SWITCH:
+            return stats ? launch_one<K, KIND_SWITCH, ROWS_HALF, true>(a, workers, st, sh)
+                         : launch_one<K, KIND_SWITCH, ROWS_HALF, false>(a, workers, st, sh);
         case KIND_MUPPET:
             return stats ? launch_one<K, KIND_MUPPET, ROWS_F32, true>(a, workers, st, sh)
                          : launch_one<K, KIND_MUPPET, ROWS_F32, false>(a, workers, st, sh);

@@ -14,7 +14,7 @@ LIB_PATH = os.environ.get("MASCOT_LIB_PATH", os.path.join(HERE, "libmascot.so"))
 
 RATING = np.dtype([("r", np.float32), ("u", np.uint32), ("i", np.uint32)])
 
-V_MASCOT, V_AFP, V_MUPPET, V_MPT, V_SGD, V_MEMQUANT = 1, 2, 3, 4, 5, 7
+V_MASCOT, V_AFP, V_MUPPET, V_MPT, V_SGD, V_NAIVE, V_MEMQUANT, V_SWITCH_ONLY = 1, 2, 3, 4, 5, 6, 7, 8
 
 OK, ERR_BAD_ARG, ERR_CUDA, ERR_OOM, ERR_STATE, ERR_NO_DEVICE, ERR_TIMEOUT, ERR_UNSUPPORTED, ERR_COMM = \
     0, -1, -2, -3, -4, -5, -6, -7, -8

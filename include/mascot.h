@@ -50,7 +50,11 @@ enum {
     MASCOT_V_MUPPET = 3,    /* muppet_training_mf            mf_methods.cu:529-711  */
     MASCOT_V_MPT = 4,       /* mixed_precision_training_mf   mf_methods.cu:713-818  */
     MASCOT_V_SGD = 5,       /* training_single_mf            mf_methods.cu:820-924  */
-    MASCOT_V_MEMQUANT = 7   /* training_mem_quant_mf         mf_methods.cu:1303-1394 */
+    MASCOT_V_NAIVE = 6,     /* mascot_training_mf_naive      mf_methods.cu:926-1301: the same arithmetic as
+                               variant 1 with a slower group lookup in the reference; runs as variant 1 here */
+    MASCOT_V_MEMQUANT = 7,  /* training_mem_quant_mf         mf_methods.cu:1303-1394 */
+    MASCOT_V_SWITCH_ONLY = 8 /* training_switching_only      mf_methods.cu:1396-1562: the whole model in
+                               binary16 until one sampled error test switches all of it to fp32 */
 };
 
 /* One rating; same 12-byte record as the reference's `Node` (common_struct.h:8-12). */

@@ -17,7 +17,7 @@ import numpy as np
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 from bundle import write_bundle  # noqa: E402
 
-KIND = dict(sgd=0, mascot=1, mpt=2, memquant=3, muppet=4, afp=5, rmse=6)
+KIND = dict(sgd=0, mascot=1, mpt=2, memquant=3, muppet=4, afp=5, rmse=6, switching=7)
 
 
 def half_round(a):
@@ -135,6 +135,14 @@ def main():
         c = rmse_case(rng, k, 64, 48, 1300)
         tight_ratings(rng, c, matching=False)
         cases[f"rmse_{t}_tight"] = c
+
+    # Third batch (appended, so that the random stream of the cases above stays what it was): the
+    # whole-model switching trainer (-v 8, k=128 only in the reference), before and after its switch.
+    cases["switching_k128_half"] = training_case(rng, "switching", 128, 15, 13, 36, 2, 24, 10, 81, 0.01, 0.05,
+                                                 extra0=0, half_rows=True)
+    cases["switching_k128_half_big"] = training_case(rng, "switching", 128, 40, 30, 300, 3, 100, 120, 82, 0.02, 0.015,
+                                                     scale=0.3, extra0=0, half_rows=True)
+    cases["switching_k128_float"] = training_case(rng, "switching", 128, 15, 13, 36, 2, 24, 10, 83, 0.01, 0.05, extra0=1)
 
     arrays = {"cases": np.frombuffer("\n".join(cases).encode(), np.uint8)}
     for name, c in cases.items():

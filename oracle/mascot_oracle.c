@@ -462,6 +462,23 @@ static float muppet_scale(int bits, float max_v, float min_v) {
     if (idx > 4294967295.0f) idx = 4294967295.0f;
     return exp2f(idx);
 }
+/* Squared norm of both gradients in the grouping of muppet_sgd_kernel.h:267-277 and
+ * sgd_kernel.h:266-276: per lane (norm_p + norm_q), then the lane tree. */
+static float norm_pq_tree(int k, const float* gp, const float* gq, int mode) {
+    float x[32];
+    for (int l = 0; l < 32; l++) {
+        float np_, nq_;
+        if (k == 128) {
+            np_ = pair_f32(gp[l], gp[l], gp[l + 32], gp[l + 32], mode) + pair_f32(gp[l + 64], gp[l + 64], gp[l + 96], gp[l + 96], mode);
+            nq_ = pair_f32(gq[l], gq[l], gq[l + 32], gq[l + 32], mode) + pair_f32(gq[l + 64], gq[l + 64], gq[l + 96], gq[l + 96], mode);
+        } else {
+            np_ = pair_f32(gp[l], gp[l], gp[l + 32], gp[l + 32], mode);
+            nq_ = pair_f32(gq[l], gq[l], gq[l + 32], gq[l + 32], mode);
+        }
+        x[l] = np_ + nq_;
+    }
+    return tree32_f32(x);
+}
 static inline int sat8(float v) { return v > 127.f ? 127 : (v < -128.f ? -128 : (int)v); }
 static inline float fix_round(float v, float s, float s_rev) { return roundf(v * s) * s_rev; }
 
@@ -542,18 +559,40 @@ void mo_muppet_run(int k, const mo_node* R, const uint32_t* seq, uint64_t nseq, 
             q[d] = outer_f32(q[d], lr, gq[d], ru->outer_f32);
         }
         if (bits_fwd != 32 && bits_bwd != 32 && t >= first_sample_pos && sum_updated_val) {
-            for (int l = 0; l < 32; l++) {
-                float np_, nq_;
-                if (slots == 4) {
-                    np_ = pair_f32(gp[l], gp[l], gp[l + 32], gp[l + 32], ru->norm_f32) + pair_f32(gp[l + 64], gp[l + 64], gp[l + 96], gp[l + 96], ru->norm_f32);
-                    nq_ = pair_f32(gq[l], gq[l], gq[l + 32], gq[l + 32], ru->norm_f32) + pair_f32(gq[l + 64], gq[l + 64], gq[l + 96], gq[l + 96], ru->norm_f32);
-                } else {
-                    np_ = pair_f32(gp[l], gp[l], gp[l + 32], gp[l + 32], ru->norm_f32);
-                    nq_ = pair_f32(gq[l], gq[l], gq[l + 32], gq[l + 32], ru->norm_f32);
-                }
-                x[l] = np_ + nq_;
-            }
-            norm_total += tree32_f32(x);
+            norm_total += norm_pq_tree(k, gp, gq, ru->norm_f32);
+            for (int d = 0; d < k; d++) sum_updated_val[d] += gp[d] + gq[d];
+        }
+    }
+    if (sum_norms) *sum_norms = norm_total;
+}
+
+/* ------------------------------------------------------------------------------------------ */
+/* whole-model switching trainer (-v 8): sgd/sgd_kernel.h:166-330                               */
+/* ------------------------------------------------------------------------------------------ */
+void mo_switching_run(int k, const mo_node* R, const uint32_t* seq, uint64_t nseq, void* Pv, void* Qv, int precision,
+                      float lr, float lam, uint64_t first_sample_pos, float* sum_updated_val, float* sum_norms,
+                      const mo_rules* ru) {
+    if (precision) {
+        /* fmaf(lr, e*q - lam*p, p): the compiled form of the plain fp32 trainer */
+        mo_sgd_run(k, R, seq, nseq, (float*)Pv, (float*)Qv, lr, lam, ru);
+        if (sum_norms) *sum_norms = 0.f;
+        return;
+    }
+    uint16_t* P = (uint16_t*)Pv; uint16_t* Q = (uint16_t*)Qv;
+    const uint16_t lr_h = mo_f2h(lr), lam_h = mo_f2h(lam);
+    float gp[128], gq[128], norm_total = 0.f;
+    for (uint64_t t = 0; t < nseq; t++) {
+        const mo_node* n = &R[seq ? seq[t] : t];
+        uint16_t* p = P + (size_t)n->u * k; uint16_t* q = Q + (size_t)n->i * k;
+        const uint16_t e = mo_hsub(mo_f2h(n->r), dot_f16(k, p, q, ru->dot_f16));
+        for (int d = 0; d < k; d++) {
+            const uint16_t pv = p[d], qv = q[d];
+            const uint16_t tp = inner_f16(e, qv, lam_h, pv, ru->inner_f16), tq = inner_f16(e, pv, lam_h, qv, ru->inner_f16);
+            p[d] = mo_hfma(lr_h, tp, pv); q[d] = mo_hfma(lr_h, tq, qv);
+            gp[d] = mo_h2f(tp); gq[d] = mo_h2f(tq);
+        }
+        if (t >= first_sample_pos && sum_updated_val) {
+            norm_total += norm_pq_tree(k, gp, gq, ru->norm_f32);
             for (int d = 0; d < k; d++) sum_updated_val[d] += gp[d] + gq[d];
         }
     }

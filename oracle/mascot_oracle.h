@@ -91,6 +91,13 @@ void mo_mpt_run(int k, const mo_node* R, const uint32_t* seq, uint64_t nseq, flo
 void mo_muppet_run(int k, const mo_node* R, const uint32_t* seq, uint64_t nseq, float* P, float* Q,
                    float lr, float lam, int bits_fwd, int bits_bwd, uint64_t first_sample_pos,
                    float* sum_updated_val, float* sum_norms, const mo_rules* rules);
+/* Whole-model switching trainer (-v 8, k=128 in the reference): sgd/sgd_kernel.h:166-330.
+ * precision 0: every row binary16, arithmetic of MASCOT's all-binary16 case, sampled statistics in
+ * MuPPET's form (one norm sum, one k-vector of summed updates); precision 1: fp32 with explicit fmaf,
+ * no statistics.  P/Q point to uint16_t (precision 0) or float (precision 1) rows. */
+void mo_switching_run(int k, const mo_node* R, const uint32_t* seq, uint64_t nseq, void* P, void* Q, int precision,
+                      float lr, float lam, uint64_t first_sample_pos, float* sum_updated_val, float* sum_norms,
+                      const mo_rules* rules);
 /* AFP (-v 2): afp/afp_sgd_kernel.h:1-376, afp_sgd_kernel_k64.h:1-277.  One sequential worker: the
  * per-warp state of the reference (three sets of quantization parameters and their re-estimation
  * counters) lives for the whole sequence.  `epoch` and `init_threshold` are the kernel arguments

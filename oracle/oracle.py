@@ -157,6 +157,20 @@ def muppet_run(k, R, seq, P, Q, lr, lam, bits_fwd, bits_bwd, rules, first_sample
     return suv, float(sn[0])
 
 
+def switching_run(k, R, seq, P, Q, precision, lr, lam, rules, first_sample_pos=None):
+    """-v 8 trainer: P, Q are uint16 arrays (binary16 bit patterns) for precision 0, float32 for 1.
+    Returns (sum_updated_val[k], sum_norms); P, Q are updated in place."""
+    R = as_nodes(R)
+    seq = _seq(seq)
+    nseq = seq.size if seq is not None else R.size
+    fsp = nseq if first_sample_pos is None else first_sample_pos
+    suv = np.zeros(k, np.float32)
+    sn = np.zeros(1, np.float32)
+    lib().mo_switching_run(C.c_int(k), _p(R), _p(seq), C.c_uint64(nseq), _p(P), _p(Q), C.c_int(precision), C.c_float(lr),
+                           C.c_float(lam), C.c_uint64(fsp), _p(suv), _p(sn), C.byref(rules))
+    return suv, float(sn[0])
+
+
 def afp_run(k, R, seq, P, Q, lr, lam, epoch, init_threshold, rules):
     R = as_nodes(R)
     seq = _seq(seq)

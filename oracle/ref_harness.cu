@@ -228,6 +228,61 @@ int main(int argc, char** argv) {
             put(out, name + ".nsum_p", 0, nsp.data(), ug); put(out, name + ".nsum_q", 0, nsq.data(), ig);
             for (void* d : up) cudaFree(d);
             for (void* d : ip) cudaFree(d);
+            if (k == 128) {
+                // the "naive" variant (-v 6) on the same inputs and the same random sequence: it differs
+                // from the kernel above only in how it looks a row's group up
+                std::vector<void*> up2, ip2;
+                build(P, uend, uprec, (int)ug, up2); build(Q, iend, iprec, (int)ig, ip2);
+                void** dUp2 = to_dev(up2.data(), ug); void** dIp2 = to_dev(ip2.data(), ig);
+                CK(cudaMemset(dGp, 0, sizeof(float) * ug * k)); CK(cudaMemset(dGq, 0, sizeof(float) * ig * k));
+                seed_state<<<1, 1>>>(dState, seed);
+                naive_mascot_sgd_k128_hogwild_kernel<<<1, 32>>>(dR, nnz, dUp2, dIp2, dState, lr, k, update_count, vec, lam,
+                    dUend, dIend, dUprec, dIprec, dGp, dGq, dNp, dNq, first_sample, (int)ug, (int)ig);
+                CK(cudaDeviceSynchronize());
+                std::vector<float> P2(np), Q2(nq);
+                fetch(P2.data(), uend, uprec, (int)ug, up2); fetch(Q2.data(), iend, iprec, (int)ig, ip2);
+                CK(cudaMemcpy(gp.data(), dGp, sizeof(float) * ug * k, cudaMemcpyDeviceToHost));
+                CK(cudaMemcpy(gq.data(), dGq, sizeof(float) * ig * k, cudaMemcpyDeviceToHost));
+                CK(cudaMemcpy(nsp.data(), dNp, sizeof(float) * ug, cudaMemcpyDeviceToHost));
+                CK(cudaMemcpy(nsq.data(), dNq, sizeof(float) * ig, cudaMemcpyDeviceToHost));
+                put(out, name + ".naive_P_out", 0, P2.data(), np); put(out, name + ".naive_Q_out", 0, Q2.data(), nq);
+                put(out, name + ".naive_gsum_p", 0, gp.data(), ug * k); put(out, name + ".naive_gsum_q", 0, gq.data(), ig * k);
+                put(out, name + ".naive_nsum_p", 0, nsp.data(), ug); put(out, name + ".naive_nsum_q", 0, nsq.data(), ig);
+                for (void* d : up2) cudaFree(d);
+                for (void* d : ip2) cudaFree(d);
+            }
+        } else if (kind == 7) {  // whole-model switching trainer (-v 8): binary16 (extra0 = 0) or fp32 (1)
+            float *dSum, *dNorms;
+            CK(cudaMalloc(&dSum, sizeof(float) * k)); CK(cudaMemset(dSum, 0, sizeof(float) * k));
+            CK(cudaMalloc(&dNorms, sizeof(float))); CK(cudaMemset(dNorms, 0, sizeof(float)));
+            const unsigned char cur_precision = (unsigned char)extra0;
+            std::vector<__half> hp(np), hq(nq);
+            void *dP, *dQ;
+            if (!cur_precision) {
+                for (size_t j = 0; j < np; j++) hp[j] = __float2half_rn(P[j]);
+                for (size_t j = 0; j < nq; j++) hq[j] = __float2half_rn(Q[j]);
+                dP = to_dev(hp.data(), np); dQ = to_dev(hq.data(), nq);
+            } else {
+                dP = to_dev(P, np); dQ = to_dev(Q, nq);
+            }
+            switching_only_sgd_k128_hogwild_kernel<<<1, 32>>>(dR, nnz, dP, dQ, dState, lr, k, update_count, vec, lam,
+                                                               cur_precision, first_sample, dSum, dNorms);
+            CK(cudaDeviceSynchronize());
+            if (!cur_precision) {
+                CK(cudaMemcpy(hp.data(), dP, sizeof(__half) * np, cudaMemcpyDeviceToHost));
+                CK(cudaMemcpy(hq.data(), dQ, sizeof(__half) * nq, cudaMemcpyDeviceToHost));
+                for (size_t j = 0; j < np; j++) Pout[j] = __half2float(hp[j]);
+                for (size_t j = 0; j < nq; j++) Qout[j] = __half2float(hq[j]);
+            } else {
+                CK(cudaMemcpy(Pout.data(), dP, sizeof(float) * np, cudaMemcpyDeviceToHost));
+                CK(cudaMemcpy(Qout.data(), dQ, sizeof(float) * nq, cudaMemcpyDeviceToHost));
+            }
+            std::vector<float> sv(k); float nrm;
+            CK(cudaMemcpy(sv.data(), dSum, sizeof(float) * k, cudaMemcpyDeviceToHost));
+            CK(cudaMemcpy(&nrm, dNorms, sizeof(float), cudaMemcpyDeviceToHost));
+            put(out, name + ".sum_updated_val", 0, sv.data(), k);
+            put(out, name + ".sum_norms", 0, &nrm, 1);
+            cudaFree(dP); cudaFree(dQ); cudaFree(dSum); cudaFree(dNorms);
         } else if (kind == 3) {  // fp16 storage, fp32 arithmetic
             std::vector<__half> hp(np), hq(nq);
             for (size_t j = 0; j < np; j++) hp[j] = __float2half_rn(P[j]);

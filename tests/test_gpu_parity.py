@@ -616,3 +616,109 @@ def test_streamed_epoch_over_two_pieces_bit_exact(mascot, oracle):
     oracle.sgd_run(k, R, None, Po, Qo, 0.01, 0.05, oracle.rules_reference())
     assert_bit_equal(Pg, Po, "P")
     assert_bit_equal(Qg, Qo, "Q")
+
+
+# --------------------------------------------------------------------------------------------
+# whole-model switching trainer (-v 8) and the naive variant (-v 6)
+# --------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", ["switching_k128_half", "switching_k128_half_big"])
+def test_golden_switching_only_half(mascot, oracle, golden, name):
+    """The reference kernel's binary16 phase: factors and both sampled statistics.  Epoch index 5 is the
+    first check epoch; without decay it runs at the case's learning rate."""
+    I, G = golden
+    if name + ".P_out" not in G:
+        pytest.skip("tests/golden/harness_out.bin predates this case")
+    c = golden_case(I, G, name, oracle)
+    seq = c["seq"]
+    n = len(seq)
+    train = mascot.as_ratings(np.ascontiguousarray(c["R"][seq]))
+    ratio = (n - c["fs"] + 0.01) / n
+    assert int(np.float32(n) * np.float32(ratio)) == n - c["fs"]
+    eng = make_engine(mascot, mascot.V_SWITCH_ONLY, c["k"], learning_rate=c["lr"], lam=c["lam"], decay=0.0, sample_ratio=ratio,
+                      interval=1, error_threshold=1e30)
+    eng.set_ratings(train, train[:1], c["nu"], c["ni"])
+    eng.set_factors(c["P"], c["Q"])
+    st = eng.train_epoch(5)
+    assert st.error_check == 1 and np.float32(st.lr) == np.float32(c["lr"])
+    P, Q = eng.get_factors(0)
+    gp, _gq, np_, _nq = eng.sample_stats()
+    eng.close()
+    assert_bit_equal(P, G[name + ".P_out"], "P")
+    assert_bit_equal(Q, G[name + ".Q_out"], "Q")
+    assert_bit_equal(gp[:c["k"]], G[name + ".sum_updated_val"], "sum_updated_val")
+    assert_bit_equal(np_[:1], G[name + ".sum_norms"], "sum_norms")
+
+
+def test_golden_switching_only_float_phase_is_the_fp32_trainer(mascot, oracle, golden):
+    I, G = golden
+    name = "switching_k128_float"
+    if name + ".P_out" not in G:
+        pytest.skip("tests/golden/harness_out.bin predates this case")
+    c = golden_case(I, G, name, oracle)
+    P, Q = replay_through_engine(mascot, mascot.V_SGD, c)
+    assert_bit_equal(P, G[name + ".P_out"], "P")
+    assert_bit_equal(Q, G[name + ".Q_out"], "Q")
+
+
+def test_switching_only_run_with_its_switch_bit_exact(mascot, oracle):
+    """Ten deterministic epochs of -v 8 with a threshold that forces the switch: binary16 epochs, the
+    error test of mf_methods.cu:1515-1545 on the check epochs, then fp32 epochs - all against the oracle."""
+    rng = np.random.default_rng(500)
+    k, n_users, n_items, n = 128, 90, 70, 2501
+    R, P, Q = random_problem(rng, n_users, n_items, n, k, scale=0.2)
+    threshold = 1.0001
+    eng = make_engine(mascot, mascot.V_SWITCH_ONLY, k, sample_ratio=0.2, interval=1, error_threshold=threshold, epoch=10)
+    eng.set_ratings(R, R[:200], n_users, n_items)
+    eng.set_factors(P, Q)
+    lrs = oracle.lr_schedule(0.01, 0.1, 10)
+    rules = oracle.rules_reference()
+    P16, Q16 = oracle.f2h(P), oracle.f2h(Q)
+    P32 = Q32 = None
+    fsp = n - int(np.float32(n) * np.float32(0.2))
+    initial, switched_at = np.float32(1), None
+    for e in range(10):
+        st = eng.train_epoch(e)
+        if P32 is None:
+            check = oracle.is_check_epoch(e, 10, 1)
+            assert st.error_check == int(check)
+            suv, sn = oracle.switching_run(k, R, None, P16, Q16, 0, float(lrs[e]), 0.05, rules, first_sample_pos=fsp if check else None)
+            if check:
+                sq = np.float32(0)
+                for d in range(k):
+                    sq = np.float32(sq + np.float32(suv[d]) * np.float32(suv[d]))
+                err = np.float32(np.float32(sq / np.float32(sn)) / initial)
+                if e == 5:
+                    initial = err
+                if e > 5 and err > np.float32(threshold):
+                    P32, Q32 = oracle.h2f(P16), oracle.h2f(Q16)
+                    switched_at = e
+                    assert st.promoted_user_groups == 1 and st.promoted_item_groups == 1
+                else:
+                    assert st.promoted_user_groups == 0
+        else:
+            assert st.error_check == 0
+            oracle.switching_run(k, R, None, P32, Q32, 1, float(lrs[e]), 0.05, rules)
+    assert switched_at is not None and switched_at < 9, "the run should cross the switch"
+    Pg, Qg = eng.get_factors(0)
+    eng.close()
+    assert_bit_equal(Pg, P32, "P")
+    assert_bit_equal(Qg, Q32, "Q")
+
+
+@pytest.mark.parametrize("k", KS)
+def test_naive_variant_runs_as_mascot(mascot, k):
+    """-v 6 is -v 1 with another group lookup in the reference: same engine path, same result."""
+    rng = np.random.default_rng(600 + k)
+    n_users, n_items, n = 80, 60, 2000
+    R, P, Q = random_problem(rng, n_users, n_items, n, k, scale=0.2)
+    out = []
+    for v in (mascot.V_MASCOT, mascot.V_NAIVE):
+        eng = make_engine(mascot, v, k, user_group_num=4, item_group_num=3, sample_ratio=0.3, interval=1, error_threshold=0.5)
+        eng.set_ratings(R, R[:100], n_users, n_items)
+        eng.set_factors(P, Q)
+        for e in range(7):
+            eng.train_epoch(e)
+        out.append(eng.get_factors(0))
+        eng.close()
+    assert_bit_equal(out[0][0], out[1][0], "P")
+    assert_bit_equal(out[0][1], out[1][1], "Q")

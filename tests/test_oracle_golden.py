@@ -69,6 +69,39 @@ def test_muppet_matches_reference_kernel(oracle, golden, name):
         assert sn == 0 and not suv.any(), "no statistics at full width (muppet_sgd_kernel.h:266)"
 
 
+@pytest.mark.parametrize("name", ["switching_k128_half", "switching_k128_half_big", "switching_k128_float"])
+def test_switching_only_trainer_matches_reference_kernel(oracle, golden, name):
+    """switching_only_sgd_k128_hogwild_kernel (-v 8) before (binary16 rows, statistics) and after its switch."""
+    I, G = golden
+    if name + ".P_out" not in G:
+        pytest.skip("tests/golden/harness_out.bin predates this case: regenerate it with oracle/_ref/ref_harness on a GPU")
+    c = golden_case(I, G, name, oracle)
+    precision = c["extra0"]
+    if precision:
+        P, Q = c["P"].copy(), c["Q"].copy()
+    else:
+        P, Q = oracle.f2h(c["P"]), oracle.f2h(c["Q"])
+    suv, sn = oracle.switching_run(c["k"], c["R"], c["seq"], P, Q, precision, c["lr"], c["lam"], oracle.rules_reference(),
+                                   first_sample_pos=c["fs"])
+    if not precision:
+        P, Q = oracle.h2f(P), oracle.h2f(Q)
+    assert_bit_equal(P, G[name + ".P_out"], "P")
+    assert_bit_equal(Q, G[name + ".Q_out"], "Q")
+    assert_bit_equal(suv, G[name + ".sum_updated_val"], "sum_updated_val")
+    assert_bit_equal(np.float32(sn), G[name + ".sum_norms"], "sum_norms")
+
+
+@pytest.mark.parametrize("name", [f"mascot_k128_{t}" for t in ("mixed", "half", "float", "mixed_big")])
+def test_naive_variant_equals_the_mascot_kernel(golden, name):
+    """naive_mascot_sgd_k128_hogwild_kernel (-v 6) on the same inputs and random sequence as the MASCOT
+    kernel: identical factors and statistics, i.e. it differs only in its group lookup."""
+    _I, G = golden
+    if name + ".naive_P_out" not in G:
+        pytest.skip("tests/golden/harness_out.bin predates this case: regenerate it with oracle/_ref/ref_harness on a GPU")
+    for key in ("P_out", "Q_out", "gsum_p", "gsum_q", "nsum_p", "nsum_q"):
+        assert_bit_equal(G[f"{name}.naive_{key}"], G[f"{name}.{key}"], key)
+
+
 @pytest.mark.parametrize("name", [f"afp_k{k}_e{e}" for k in KS for e in (0, 1)])
 def test_afp_matches_reference_kernel(oracle, golden, name):
     """afp_sgd_k128/k64_hogwild_kernel in its first epoch (formats re-estimated at every rating for the
