@@ -236,8 +236,15 @@ int main(int argc, char** argv) {
                 void** dUp2 = to_dev(up2.data(), ug); void** dIp2 = to_dev(ip2.data(), ig);
                 CK(cudaMemset(dGp, 0, sizeof(float) * ug * k)); CK(cudaMemset(dGq, 0, sizeof(float) * ig * k));
                 seed_state<<<1, 1>>>(dState, seed);
+                // this kernel reads its group ends from tables shifted by one entry, with -1 in front
+                // (mf_methods.cu:1027-1046): entry g is the end of group g-1
+                std::vector<unsigned int> ushift(ug + 1), ishift(ig + 1);
+                ushift[0] = (unsigned int)-1; ishift[0] = (unsigned int)-1;
+                for (uint64_t g = 0; g < ug; g++) ushift[g + 1] = uend[g];
+                for (uint64_t g = 0; g < ig; g++) ishift[g + 1] = iend[g];
+                unsigned int* dUshift = to_dev(ushift.data(), ug + 1); unsigned int* dIshift = to_dev(ishift.data(), ig + 1);
                 naive_mascot_sgd_k128_hogwild_kernel<<<1, 32>>>(dR, nnz, dUp2, dIp2, dState, lr, k, update_count, vec, lam,
-                    dUend, dIend, dUprec, dIprec, dGp, dGq, dNp, dNq, first_sample, (int)ug, (int)ig);
+                    dUshift, dIshift, dUprec, dIprec, dGp, dGq, dNp, dNq, first_sample, (int)ug, (int)ig);
                 CK(cudaDeviceSynchronize());
                 std::vector<float> P2(np), Q2(nq);
                 fetch(P2.data(), uend, uprec, (int)ug, up2); fetch(Q2.data(), iend, iprec, (int)ig, ip2);

@@ -666,7 +666,7 @@ def test_switching_only_run_with_its_switch_bit_exact(mascot, oracle):
     rng = np.random.default_rng(500)
     k, n_users, n_items, n = 128, 90, 70, 2501
     R, P, Q = random_problem(rng, n_users, n_items, n, k, scale=0.2)
-    threshold = 1.0001
+    threshold = 0.4          # the relative error is 0.51 at epoch 6 on this problem: the switch happens there
     eng = make_engine(mascot, mascot.V_SWITCH_ONLY, k, sample_ratio=0.2, interval=1, error_threshold=threshold, epoch=10)
     eng.set_ratings(R, R[:200], n_users, n_items)
     eng.set_factors(P, Q)
