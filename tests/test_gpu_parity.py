@@ -626,8 +626,6 @@ def test_golden_switching_only_half(mascot, oracle, golden, name):
     """The reference kernel's binary16 phase: factors and both sampled statistics.  Epoch index 5 is the
     first check epoch; without decay it runs at the case's learning rate."""
     I, G = golden
-    if name + ".P_out" not in G:
-        pytest.skip("tests/golden/harness_out.bin predates this case")
     c = golden_case(I, G, name, oracle)
     seq = c["seq"]
     n = len(seq)
@@ -652,8 +650,6 @@ def test_golden_switching_only_half(mascot, oracle, golden, name):
 def test_golden_switching_only_float_phase_is_the_fp32_trainer(mascot, oracle, golden):
     I, G = golden
     name = "switching_k128_float"
-    if name + ".P_out" not in G:
-        pytest.skip("tests/golden/harness_out.bin predates this case")
     c = golden_case(I, G, name, oracle)
     P, Q = replay_through_engine(mascot, mascot.V_SGD, c)
     assert_bit_equal(P, G[name + ".P_out"], "P")
