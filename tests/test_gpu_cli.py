@@ -39,7 +39,7 @@ def run(cmd):
     return out.stdout
 
 
-@pytest.mark.parametrize("version,k", [(5, 64), (4, 128), (7, 64)])
+@pytest.mark.parametrize("version,k", [(5, 64), (4, 128), (7, 64), (2, 128), (3, 64), (6, 128), (8, 128)])
 def test_train_save_and_reevaluate_original_id_models(synth, tmp_path, version, k):
     d = str(tmp_path)
     write_dataset(synth, d, "train.tsv", "test.tsv")
