@@ -167,6 +167,7 @@ class EngineShard:
         self.M, self.plan, self.rank = M, plan, rank
         mine, seg, my_test = shard_ratings(plan, rank, train, test)
         self.n_local = int(mine.size)
+        self.local_ratings = mine                   # host copy of this rank's ratings, in segment order
         self.n_items = int(n_items)
         self.engine = M.Engine(cfg)
         self.engine.set_ratings_sharded(mine, seg, my_test, n_users, n_items, plan.user_degree, plan.item_degree)

@@ -60,7 +60,7 @@ def main():
     ap.add_argument("--wg", default="2048")
     ap.add_argument("--seed", type=int, default=4)
     ap.add_argument("--out", default="gpurun_out/reference_gpu.json")
-    ap.add_argument("--dir", default="/tmp/mascot_ref_data")
+    ap.add_argument("--dir", default=os.path.join(HERE, "_ref", "data"), help="where the rating files are written (git-ignored)")
     ap.add_argument("--skip-reference", action="store_true")
     ap.add_argument("--workers", default="0", help="comma list: worker counts (-wg) of this engine to try (0 = the configuration's)")
     args = ap.parse_args()
