@@ -198,6 +198,28 @@ def cpu_baseline_sample(S, cfg, seed, budget_s=15.0):
             "sample": f"{reps} passes over the first {n} ratings of the workload, {threads} host threads, Hogwild"}
 
 
+def sharded_e2e(args, MU, dist, shard, rank, world, dev, epoch, n_train):
+    """End to end at N GPUs: every step uploads each rank's ratings from pinned host memory again,
+    trains the epoch (all sub-epochs and hand-overs) and reads the global test RMSE back."""
+    import torch
+    host = torch.from_numpy(np.ascontiguousarray(shard.local_ratings).view(np.int32).reshape(-1, 3)).pin_memory()
+    e2e_steps = max(2, min(args.steps, 5))
+    dist.barrier(); shard.sync(); torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    for _ in range(e2e_steps):
+        shard.engine.reload_train_raw(host.data_ptr(), shard.n_local)          # H2D of this step's inputs
+        MU.train_epoch(dist, shard, rank, world, epoch, comm_device=dev); epoch += 1
+        MU.gather_item_factors(dist, shard, world)
+        MU.global_rmse(dist, shard, world, comm_device=dev)                     # D2H of the step's result
+    shard.sync(); torch.cuda.synchronize()
+    te = torch.tensor([time.perf_counter() - t1], dtype=torch.float64, device=dev)
+    dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_s = float(te.item())
+    return {"value": n_train * e2e_steps / e2e_s, "unit": "updates/s", "h2d_bytes_per_step": int(12 * n_train),
+            "d2h_bytes_per_step": int(16 * world), "steps": e2e_steps, "ms_per_step": 1e3 * e2e_s / e2e_steps,
+            "timing": "wall clock between barriers, max over ranks (the upload is a host call)"}
+
+
 def run_sharded(args, S, M, cfg, rank, world, local_rank):
     """N > 1: one process per GPU, users pinned per rank, item blocks rotating (multi.py)."""
     import torch
@@ -256,22 +278,7 @@ def run_sharded(args, S, M, cfg, rank, world, local_rank):
     # epoch (all sub-epochs and hand-overs) and reads the global test RMSE back ----
     e2e = None
     if not args.no_e2e:
-        host = torch.from_numpy(shard.local_ratings.view(np.uint32).reshape(-1, 3)).pin_memory()
-        e2e_steps = max(2, min(args.steps, 5))
-        dist.barrier(); shard.sync(); torch.cuda.synchronize()
-        t1 = time.perf_counter()
-        for _ in range(e2e_steps):
-            shard.engine.reload_train_raw(host.data_ptr(), shard.n_local)          # H2D of this step's inputs
-            MU.train_epoch(dist, shard, rank, world, epoch, comm_device=dev); epoch += 1
-            MU.gather_item_factors(dist, shard, world)
-            MU.global_rmse(dist, shard, world, comm_device=dev)                     # D2H of the step's result
-        shard.sync(); torch.cuda.synchronize()
-        te = torch.tensor([time.perf_counter() - t1], dtype=torch.float64, device=dev)
-        dist.all_reduce(te, op=dist.ReduceOp.MAX)
-        e2e_s = float(te.item())
-        e2e = {"value": n_train * e2e_steps / e2e_s, "unit": "updates/s", "h2d_bytes_per_step": int(12 * n_train),
-               "d2h_bytes_per_step": int(16 * world), "steps": e2e_steps, "ms_per_step": 1e3 * e2e_s / e2e_steps,
-               "timing": "wall clock between barriers, max over ranks (the upload is a host call)"}
+        e2e = sharded_e2e(args, MU, dist, shard, rank, world, dev, epoch, n_train)
     sampler.stop_flag.set()
     if rank == 0:
         sampler.join(timeout=3)
