@@ -105,6 +105,16 @@ class ClockSampler(threading.Thread):
                 "reasons": [n for n in order if n in self.reasons], "samples": self.count, "gpus": self.indices}
 
 
+# The reference's own CUDA build (oracle/_ref/quantized_mf, sm_100) on the same synthetic data and one
+# B200, measured with oracle/run_reference_gpu.py; quoted beside the engine's numbers, not re-run here.
+REFERENCE_CUDA_BUILD = {
+    "c1": {"updates_per_s": 2.90e9, "wg": 2048, "final_rmse": 1.03972, "epochs": 20},
+    "c2": {"updates_per_s": 1.53e9, "wg": 2048, "final_rmse": 0.618434, "epochs": 50},
+    "c3": {"updates_per_s": 2.55e9, "wg": 2304, "final_rmse": 0.638323, "epochs": 50},
+    "c4": {"updates_per_s": 1.559e9, "wg": 2048, "final_rmse": 0.601266, "epochs": 50},
+}
+
+
 def measured_peak():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -433,7 +443,8 @@ def main():
         "config": {"workload": args.workload_desc, "l2": "inputs larger than L2 (1.2 GB rating stream + 123 MB user factors per epoch)",
                    "check_epochs_in_timed_region": checks, "kernel_ms_per_step": kern_ms / args.steps,
                    "wall_ms_per_step": wall_ms / args.steps, "rmse_before": rmse_before, "rmse_after": rmse_after,
-                   "kernel_ms_and_check_flag_per_step": per_epoch, "workers": int(st.workers)},
+                   "kernel_ms_and_check_flag_per_step": per_epoch, "workers": int(st.workers),
+                   "reference_cuda_build": REFERENCE_CUDA_BUILD.get(args.workload) if args.scale == 1.0 else None},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": traffic, "peak_kind": f"of {peak_kind}",
                      "algorithmic_bytes_per_launch": alg_bytes / args.steps,
