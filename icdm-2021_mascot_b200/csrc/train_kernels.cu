@@ -18,10 +18,12 @@
 //   * the row of an item that repeats (the stream is item-sorted inside shuffle windows) stays in
 //     registers for the whole run and is written back once;
 //   * chunks are handed out in spans of eight through one atomic ticket per span.
-// The leads are short on purpose.  Between the request of a row and its write-back every update
-// another worker makes to that row is lost, so the loss grows with (workers x lead); measured on
-// the 100M-rating configuration a lead of seven ratings on both sides costs 1.5 % of final RMSE
-// where three (users) and one (items) cost nothing.
+//   * user rows are written back as vector reductions of their change whenever several workers run,
+//     so racing updates of one user add up instead of overwriting each other (add_row_delta).
+// The item lead is short on purpose.  Between the request of an item row and its write-back (a plain
+// store, once per run) every update another worker makes to that row is lost, so the loss grows with
+// (workers x lead); measured on the 100M-rating configuration with plain stores on both sides, a lead
+// of seven ratings costs 1.5 % of final RMSE where three (users) and one (items) cost nothing.
 //
 // ELEMENT ORDER.  layout.cuh stores rows permuted so that lane m of a worker holds the elements of
 // reference lanes m and m+16 (k=128) or m, m+16, m+8, m+24 (k=64).  With pair products
@@ -32,6 +34,9 @@
 //   fp32 / binary16   mascot/mascot_sgd_kernel.h:343-407     all fp32                   :408-443
 //   (sgd/sgd_kernel.h:35-76 compiles to the same operations as the all-fp32 case)
 //   MPT               mpt/mpt_sgd_kernel.h:38-91              fp16 storage (-v 7)  sgd/sgd_kernel.h:110-161
+//   MuPPET            muppet/muppet_sgd_kernel.h:121-285      AFP                  afp/afp_sgd_kernel.h:194-371
+//   whole-model switching (-v 8)  sgd/sgd_kernel.h:205-326 (binary16 phase = the all-binary16 case above
+//   with MuPPET's form of the statistics; fp32 phase = the fp32 trainer)
 // including the fused multiply-adds the compiled reference executes.  Every operation is written
 // with a rounding-mode intrinsic so that ptxas cannot contract or re-associate anything further.
 //
