@@ -909,19 +909,30 @@ cudaError_t launch_ns(KernelArgs a, unsigned warps_per_sm, unsigned workers, cud
         const unsigned warps_per_block = (warps_per_sm + blocks_per_sm - 1) / blocks_per_sm;
         block = (int)(32 * warps_per_block);
         const size_t smem_block = (size_t)warps_per_block * kPerWarp * SM::kBytes;
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_block);
-        if (e != cudaSuccess) return e;
-        int fit = 0;
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&fit, kern, block, smem_block);
-        if (e != cudaSuccess) return e;
+        // the answer for a block shape does not change: asked once per shape and device (a sharded
+        // epoch launches this kernel once per sub-epoch)
+        static int known_block = 0, known_fit = 0, known_dev = -1;
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (known_block != block || known_dev != dev) {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_block);
+            if (e != cudaSuccess) return e;
+            int f = 0;
+            e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&f, kern, block, smem_block);
+            if (e != cudaSuccess) return e;
+            known_block = block; known_fit = f; known_dev = dev;
+        }
+        const int fit = known_fit;
         if (fit < 1) return cudaErrorLaunchOutOfResources;
         if (blocks_per_sm > (unsigned)fit) blocks_per_sm = (unsigned)fit;
         grid = (int)(sms * blocks_per_sm);
         a.workers = (unsigned)grid * warps_per_block * kPerWarp;
     }
     const size_t smem = (size_t)(block / 32) * kPerWarp * SM::kBytes;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
+    if (grid == 1) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
     kern<<<grid, block, smem, st>>>(a);
     if (shape) { shape->grid = grid; shape->block = block; shape->smem = smem; shape->workers = a.workers; }
     return cudaGetLastError();

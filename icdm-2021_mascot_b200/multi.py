@@ -174,19 +174,29 @@ class EngineShard:
         self.device = torch.device("cuda", int(cfg.device))
         self.stream = torch.cuda.ExternalStream(self.engine.stream_handle(), device=self.device)
         self._views = {}
+        self._live = None
 
     def device_order(self):
         """Context in which torch's current stream is the engine's stream."""
         import torch
         return torch.cuda.stream(self.stream)
 
+    def _live_arenas(self):
+        """(binary16 arena holds live item rows, fp32 arena holds live item rows): an item row lives in
+        exactly one of them, by its group's precision, so an arena without live rows need not travel.
+        Every rank reaches the same answer, because all take the same switching decisions."""
+        if self._live is None:
+            prec = self.engine.group_info(1)[1]
+            self._live = (bool((prec == 0).any()), bool((prec != 0).any()))
+        return self._live
+
     def block_tensors(self, b):
-        """Strided byte views [rows of block b, bytes per row] of the item arenas."""
+        """Strided byte views [rows of block b, bytes per row] of the item arenas that hold live rows."""
         import torch
         if b not in self._views:
             views = []
-            for ptr, nbytes in self.engine.item_rows(0, self.n_items):
-                if ptr and nbytes:
+            for live, (ptr, nbytes) in zip(self._live_arenas(), self.engine.item_rows(0, self.n_items)):
+                if live and ptr and nbytes:
                     whole = torch.as_tensor(_DeviceBytes(ptr, nbytes), device=self.device).view(self.n_items, nbytes // self.n_items)
                     views.append(whole[b::self.plan.world])
             self._views[b] = views
@@ -208,7 +218,11 @@ class EngineShard:
         return self.engine.stats_fetch()
 
     def stats_apply(self, epoch, *sums):
-        return self.engine.stats_apply(epoch, *sums)
+        promoted = self.engine.stats_apply(epoch, *sums)
+        if promoted[1]:
+            self._live = None                     # item groups changed precision: re-derive which arenas travel
+            self._views.clear()
+        return promoted
 
     def eval_sq_error(self):
         return self.engine.eval_sq_error()

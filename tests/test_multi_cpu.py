@@ -66,10 +66,15 @@ class OracleShard:
         self.processed = 0
 
     def block_tensors(self, b):
-        # strided views of raw bytes [rows of the block, bytes per row], like the device views of the real engine
+        # strided views of raw bytes [rows of the block, bytes per row], like the device views of the real
+        # engine; as there, an arena travels only while it holds live rows (a row lives in exactly one)
         n, w = self.model.Q16.shape[0], self.plan.world
-        return [torch.from_numpy(self.model.Q16.view(np.uint8).reshape(n, -1))[b::w],
-                torch.from_numpy(self.model.Q32.view(np.uint8).reshape(n, -1))[b::w]]
+        views = []
+        if (self.model.iprec == 0).any():
+            views.append(torch.from_numpy(self.model.Q16.view(np.uint8).reshape(n, -1))[b::w])
+        if (self.model.iprec != 0).any():
+            views.append(torch.from_numpy(self.model.Q32.view(np.uint8).reshape(n, -1))[b::w])
+        return views
 
     def is_check_epoch(self, epoch):
         return self.O.is_check_epoch(epoch, HYPER["epochs"], HYPER["interval"])
