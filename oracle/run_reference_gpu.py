@@ -4,7 +4,7 @@ box, and report both: update-kernel time per epoch, updates/s and the test-RMSE 
 TEST / MEASUREMENT INFRASTRUCTURE.  Needs oracle/_ref/quantized_mf (built from the reference tree by
 `make -C oracle ref`; the binary travels, the reference sources do not) and a GPU.
 
-    python oracle/run_reference_gpu.py --workload c2 --epochs 20 --wg 2048,9472 --out gpurun_out/ref_c2.json
+    python oracle/run_reference_gpu.py --workload c2 --epochs 20 --wg 2048,9472 --out ref_c2.json
 
 The reference sizes the dynamic shared memory of its MASCOT kernel 8 bytes short when a side has
 more than 62 groups; that stays inside the allocation unless the requested size is within 8 bytes of
@@ -59,7 +59,7 @@ def main():
     ap.add_argument("--epochs", type=int, default=20)
     ap.add_argument("--wg", default="2048")
     ap.add_argument("--seed", type=int, default=4)
-    ap.add_argument("--out", default="gpurun_out/reference_gpu.json")
+    ap.add_argument("--out", default="reference_gpu.json")
     ap.add_argument("--dir", default=os.path.join(HERE, "_ref", "data"), help="where the rating files are written (git-ignored)")
     ap.add_argument("--skip-reference", action="store_true")
     ap.add_argument("--workers", default="0", help="comma list: worker counts (-wg) of this engine to try (0 = the configuration's)")
