@@ -638,11 +638,11 @@ template <int K, int MODE, int NS, int NSI> struct WorkerSmem {
 // worker updates between the request and the write-back loses that update, and the chance of that
 // grows with the lead.
 template <int K, int KIND, int MODE, bool STATS, int NS, int NSI, int D, int DI>
-__global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
+__global__ void __launch_bounds__(256, (MODE == ROWS_HALF && !STATS) ? 4 : 3) train_kernel(const KernelArgs a) {
     using SM = WorkerSmem<K, MODE, NS, NSI>;
     constexpr int TS = SM::TS;                     // lanes per worker = ratings per chunk
     static_assert(TS % NS == 0, "the ring must divide the chunk");
-    static_assert(DI >= 1 && DI <= D && D <= NS - 1 && DI <= NSI - 1 && NS % NSI == 0, "leads must fit the rings");
+    static_assert(DI >= 1 && DI <= D && D == NS - 1 && DI <= NSI - 1 && NS % NSI == 0, "leads must fit the rings");
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31;
     const int m = lane % TS;
@@ -805,12 +805,17 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
     // exactly that many to remain pending leaves every younger copy in flight.
     constexpr int kPendUser = 2 * (D - 1);
     constexpr int kPendItem = (2 * DI - 1 < kPendUser) ? 2 * DI - 1 : kPendUser;
+    // The records of the ratings j .. j+D live in a register queue indexed like the user ring (the
+    // record of rating x in slot x mod NS): each record is read from shared memory once, D ratings
+    // before its rating is processed, and serves the user request, the item request and the update.
+    uint4 rq[NS];
     // prologue: the groups of the iterations -D .. -1
 #pragma unroll
     for (int t = 0; t < D; t++) {
-        if (t - (D - DI) >= 0) request_item(*reinterpret_cast<const uint2*>(recs + (t - (D - DI))), (t - (D - DI)) & (NSI - 1));
+        rq[t] = recs[t];
+        if (t - (D - DI) >= 0) request_item(make_uint2(rq[t - (D - DI)].x, rq[t - (D - DI)].y), (t - (D - DI)) & (NSI - 1));
         cp_commit();
-        request_user(recs[t], t);
+        request_user(rq[t], t);
         cp_commit();
     }
 
@@ -824,7 +829,11 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
 #pragma unroll
             for (int t = 0; t < NS; t++) {
                 const int j = jb + t;
-                const uint4 rec = rc[j];
+                {   // the record of the rating D ahead takes the slot of the rating processed last
+                    const int x = j + D;
+                    rq[(t + D) & (NS - 1)] = (x < TS) ? rc[x] : rn[x - TS];
+                }
+                const uint4 rec = rq[t];
                 if (!(rec.x & F_VALID)) { more = false; break; }
                 const uint32_t uc = rec.z, ic = rec.y;
                 const float r = __uint_as_float(rec.w);
@@ -844,10 +853,10 @@ __global__ void __launch_bounds__(256) train_kernel(const KernelArgs a) {
                 // request the user row of the rating D ahead and the item row of the rating DI ahead,
                 // into slots whose previous contents have been consumed
                 {
-                    const int x = j + D, xi = j + DI;
-                    request_item(*reinterpret_cast<const uint2*>((xi < TS) ? rc + xi : rn + (xi - TS)), (t + DI) & (NSI - 1));
+                    const uint4& ri = rq[(t + DI) & (NS - 1)];
+                    request_item(make_uint2(ri.x, ri.y), (t + DI) & (NSI - 1));
                     cp_commit();
-                    request_user((x < TS) ? rc[x] : rn[x - TS], (t + D) & (NS - 1));
+                    request_user(rq[(t + D) & (NS - 1)], (t + D) & (NS - 1));
                     cp_commit();
                 }
                 const Raw<MODE> p_before = p;
