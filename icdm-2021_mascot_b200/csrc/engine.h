@@ -40,6 +40,15 @@ struct SampleStats {
 enum TrainKind { KIND_MIXED = 0, KIND_FP32 = 1, KIND_MPT = 2, KIND_MEMQUANT = 3, KIND_MUPPET = 4, KIND_AFP = 5,
                  KIND_SWITCH = 6 /* all rows binary16, MASCOT arithmetic, statistics in MuPPET's form */ };
 
+// Which storage precisions the ratings of a launch combine (mixed-precision trainer only).  The
+// stream is kept partitioned by this class, so that each part runs an instantiation without
+// per-rating precision tests; ROWCLASS_ANY reads the precision bit of every id instead.
+enum RowClass { ROWCLASS_HH = 0,   // binary16 user row, binary16 item row
+                ROWCLASS_HF = 1,   // binary16 user row, fp32 item row
+                ROWCLASS_FH = 2,   // fp32 user row, binary16 item row
+                ROWCLASS_FF = 3,   // both fp32
+                ROWCLASS_ANY = 4 };
+
 struct LaunchShape {
     int grid = 0;
     int block = 0;
@@ -48,8 +57,8 @@ struct LaunchShape {
 };
 
 // Update kernels.  `stats` == nullptr -> plain epoch.  `workers` = requested number of concurrent
-// sequential workers (1 = fully sequential); `any_f32_rows` tells the mixed-precision trainer whether
-// any group has been promoted (otherwise every row is binary16); `work_counter` is 8 bytes of device
+// sequential workers (1 = fully sequential); `row_class` tells the mixed-precision trainer which
+// precisions the ratings of this range combine (ignored by the other kinds); `work_counter` is 8 bytes of device
 // scratch the launch resets and uses to hand out chunks; `bits` is the width of MuPPET's forward and
 // backward pass (8, 12, 14, 16 or 32; ignored by the other kinds), `epoch` the epoch index (AFP
 // re-estimates its formats at every rating early in epoch 0).  With `add_user_delta` (ignored for a
@@ -57,7 +66,7 @@ struct LaunchShape {
 // updates of one user by several workers are not lost.  Returns the launch shape used.
 // MuPPET statistics use gsum_p[0..K) (sum of the sampled updates, physical order) and nsum_p[0].
 cudaError_t launch_train(int K, TrainKind kind, const Stream& s, Arena P, Arena Q, float lr, float lam,
-                         const SampleStats* stats, bool any_f32_rows, unsigned workers,
+                         const SampleStats* stats, RowClass row_class, unsigned workers,
                          unsigned long long* work_counter, int bits, int epoch, bool add_user_delta,
                          cudaStream_t st, LaunchShape* shape);
 
@@ -77,6 +86,17 @@ cudaError_t launch_encode_stream(const void* d_src_aos, uint64_t n, bool shuffle
                                  float* r, uint32_t* u, uint32_t* i, uint32_t* src_out, uint32_t src_base,
                                  cudaStream_t st);
 cudaError_t launch_recode(uint32_t* ids, uint64_t n, const uint8_t* prec_row, cudaStream_t st);
+// Stable partition of a coded stream by precision class inside every segment: rating j goes to the
+// position given by the stable order of (segment, class), class = 2 * (user row fp32) + (item row fp32).
+// Inputs r/u/i/src (src may be null) stay untouched; the result goes to r2/u2/i2/src2.  key_* (n u16),
+// idx_* (n u32) and temp (partition_temp_bytes) are scratch; d_first receives, for every key
+// segment * 4 + class, the first position holding it (all ones when the key does not occur).
+size_t partition_temp_bytes(uint64_t n, int key_bits);
+cudaError_t launch_partition_by_class(const float* r, const uint32_t* u, const uint32_t* i, const uint32_t* src, uint64_t n,
+                                      const uint64_t* d_seg_off, int nseg, int key_bits,
+                                      uint16_t* key_a, uint16_t* key_b, uint32_t* idx_a, uint32_t* idx_b,
+                                      void* temp, size_t temp_bytes, unsigned long long* d_first,
+                                      float* r2, uint32_t* u2, uint32_t* i2, uint32_t* src2, cudaStream_t st);
 // Sets the "stored in fp32" flag of n per-row bytes (the other flags stay).
 cudaError_t launch_mark_fp32(uint8_t* row_flags, uint32_t n, cudaStream_t st);
 cudaError_t launch_scatter_factors(int K, const float* src, uint32_t rows, const uint32_t* row_map,
@@ -85,6 +105,9 @@ cudaError_t launch_gather_factors(int K, Arena a, const uint8_t* prec_row, uint3
                                   const uint32_t* row_map, float* dst, cudaStream_t st);
 cudaError_t launch_promote_rows(int K, Arena a, uint32_t row_begin, uint32_t row_end, cudaStream_t st);
 cudaError_t launch_init_normal(float* dst, uint64_t count, uint64_t seed, uint64_t stream_id, cudaStream_t st);
+
+// Number of SMs of the current device (cached per device).
+int sm_count();
 
 // Records the message returned by mascot_last_error(NULL) for handle-free entry points.
 void set_global_error(const char* msg);

@@ -57,7 +57,14 @@ struct mascot_handle {
     int stats_copies = 1; size_t stats_stride = 0;
     float* d_block_err = nullptr;
     unsigned long long* d_work_counter = nullptr;
-    void* d_scratch = nullptr; size_t scratch_bytes = 0;   // staging for mascot_reload_train
+    // grow-only device scratch shared by mascot_reload_train (staging of the uploaded array) and by the
+    // partition of the stream by precision class; released by mascot_release_scratch / mascot_destroy
+    void* d_scratch = nullptr; size_t scratch_bytes = 0;
+    // Mixed-precision trainer, several workers: once a group has been promoted the stream is kept
+    // partitioned, inside every segment, into the four precision classes (see RowClass); cls_off holds
+    // five stream positions per segment: the starts of the classes and the end of the segment.
+    bool partitioned = false;
+    std::vector<uint64_t> cls_off;
 
     // host
     std::vector<uint32_t> user2sorted, item2sorted, uend, iend;
@@ -277,6 +284,93 @@ int recode_side(mascot_handle* h, bool users) {
     return MASCOT_OK;
 }
 
+int need_scratch(mascot_handle* h, size_t bytes) {
+    if (h->scratch_bytes >= bytes) return MASCOT_OK;
+    dev_free(h->d_scratch); h->scratch_bytes = 0;
+    CU(h, cudaMalloc(&h->d_scratch, bytes));
+    h->scratch_bytes = bytes;
+    return MASCOT_OK;
+}
+
+bool any_fp32_group(const mascot_handle* h) {
+    for (uint8_t p : h->uprec) if (p) return true;
+    for (uint8_t p : h->iprec) if (p) return true;
+    return false;
+}
+
+// Re-orders the segments [seg_first, seg_first + seg_count) of the coded stream so that, inside each
+// segment, the ratings of one precision class are contiguous (stable: the order inside a class is the
+// order before), and records the class boundaries.  Called after the precision bits of the ids changed
+// (promotion + recode) or after a stream was encoded while promoted groups exist.  The single-worker
+// deterministic mode keeps the caller's order and never partitions.
+int partition_segments(mascot_handle* h, size_t seg_first, size_t seg_count) {
+    const size_t nseg_all = h->seg_off.size() - 1;
+    if (h->cls_off.size() != nseg_all * 5) {
+        h->cls_off.assign(nseg_all * 5, 0);
+        for (size_t sg = 0; sg < nseg_all; sg++) {          // everything in the first class
+            h->cls_off[sg * 5] = h->seg_off[sg];
+            for (int c = 1; c <= 4; c++) h->cls_off[sg * 5 + c] = h->seg_off[sg + 1];
+        }
+    }
+    const uint64_t begin = h->seg_off[seg_first], end = h->seg_off[seg_first + seg_count], n = end - begin;
+    if (n == 0) return MASCOT_OK;
+    int key_bits = 2;
+    while ((1ull << key_bits) < seg_count * 4) key_bits++;
+    auto up = [](size_t b) { return (b + 255) / 256 * 256; };
+    const size_t temp_bytes = partition_temp_bytes(n, key_bits);
+    const size_t b_key = up(sizeof(uint16_t) * n), b_idx = up(sizeof(uint32_t) * n), b_seg = up(sizeof(uint64_t) * (seg_count + 1));
+    const size_t b_first = up(sizeof(unsigned long long) * seg_count * 4);
+    const size_t total = 2 * b_key + 2 * b_idx + 4 * b_idx + b_seg + b_first + up(temp_bytes);
+    int rc = need_scratch(h, total);
+    if (rc != MASCOT_OK) return rc;
+    unsigned char* base = static_cast<unsigned char*>(h->d_scratch);
+    uint16_t* key_a = reinterpret_cast<uint16_t*>(base); base += b_key;
+    uint16_t* key_b = reinterpret_cast<uint16_t*>(base); base += b_key;
+    uint32_t* idx_a = reinterpret_cast<uint32_t*>(base); base += b_idx;
+    uint32_t* idx_b = reinterpret_cast<uint32_t*>(base); base += b_idx;
+    float* r2 = reinterpret_cast<float*>(base); base += b_idx;
+    uint32_t* u2 = reinterpret_cast<uint32_t*>(base); base += b_idx;
+    uint32_t* i2 = reinterpret_cast<uint32_t*>(base); base += b_idx;
+    uint32_t* s2 = reinterpret_cast<uint32_t*>(base); base += b_idx;
+    uint64_t* d_seg = reinterpret_cast<uint64_t*>(base); base += b_seg;
+    unsigned long long* d_first = reinterpret_cast<unsigned long long*>(base); base += b_first;
+    void* temp = base;
+    std::vector<uint64_t> rel(seg_count + 1);
+    for (size_t j = 0; j <= seg_count; j++) rel[j] = h->seg_off[seg_first + j] - begin;
+    CU(h, cudaMemcpyAsync(d_seg, rel.data(), sizeof(uint64_t) * rel.size(), cudaMemcpyHostToDevice, h->stream));
+    uint32_t* src = h->tr_src ? h->tr_src + begin : nullptr;
+    CU(h, launch_partition_by_class(h->tr_r + begin, h->tr_u + begin, h->tr_i + begin, src, n, d_seg, (int)seg_count, key_bits,
+                                    key_a, key_b, idx_a, idx_b, temp, temp_bytes, d_first, r2, u2, i2, s2, h->stream));
+    CU(h, cudaMemcpyAsync(h->tr_r + begin, r2, sizeof(float) * n, cudaMemcpyDeviceToDevice, h->stream));
+    CU(h, cudaMemcpyAsync(h->tr_u + begin, u2, sizeof(uint32_t) * n, cudaMemcpyDeviceToDevice, h->stream));
+    CU(h, cudaMemcpyAsync(h->tr_i + begin, i2, sizeof(uint32_t) * n, cudaMemcpyDeviceToDevice, h->stream));
+    if (src) CU(h, cudaMemcpyAsync(src, s2, sizeof(uint32_t) * n, cudaMemcpyDeviceToDevice, h->stream));
+    std::vector<unsigned long long> first(seg_count * 4);
+    CU(h, cudaMemcpyAsync(first.data(), d_first, sizeof(unsigned long long) * first.size(), cudaMemcpyDeviceToHost, h->stream));
+    CU(h, cudaStreamSynchronize(h->stream));          // `rel` and `first` are host buffers of this call
+    for (size_t j = 0; j < seg_count; j++) {
+        uint64_t* off = &h->cls_off[(seg_first + j) * 5];
+        off[4] = h->seg_off[seg_first + j + 1];
+        for (int c = 3; c >= 0; c--) off[c] = first[j * 4 + c] == ~0ull ? off[c + 1] : begin + first[j * 4 + c];
+    }
+    return MASCOT_OK;
+}
+
+// The stream is partitioned when that pays: mixed-precision trainer, more than one worker, at least
+// one promoted group, and sizes the 16-bit sort key and the 32-bit permutation can express.
+bool wants_partition(const mascot_handle* h) {
+    return h->grouped && !h->cfg.deterministic && any_fp32_group(h) && h->n_train < (1ull << 32) &&
+           (h->seg_off.size() - 1) * 4 <= 65536;
+}
+
+int partition_all(mascot_handle* h) {
+    h->partitioned = false;
+    if (!wants_partition(h)) return MASCOT_OK;
+    const int rc = partition_segments(h, 0, h->seg_off.size() - 1);
+    if (rc == MASCOT_OK) h->partitioned = true;
+    return rc;
+}
+
 float reference_rmse_from_partials(const std::vector<float>& part, uint64_t n) {
     float sum = 0;                                  // rmse.h:183-186: float accumulation in block order
     for (float v : part) sum += v;
@@ -410,6 +504,7 @@ int mascot_set_ratings_sharded(mascot_handle* h, const mascot_rating* train, uin
     free_ratings(h);
     h->n_users = n_users; h->n_items = n_items; h->n_train = n_train; h->n_test = n_test;
     h->seg_off = seg;
+    h->cls_off.clear(); h->partitioned = false;
 
     // --- m-quantization set-up on the host (one-off) ---
     if (h->grouped) {
@@ -491,17 +586,17 @@ int mascot_reload_train(mascot_handle* h, const mascot_rating* train, uint64_t n
         if (n_train < (1ull << 32)) CU(h, dev_alloc(&h->tr_src, n_train));
         h->n_train = n_train;
         h->seg_off.assign({0, n_train});           // a stream of another length is one segment
+        h->cls_off.clear(); h->partitioned = false;
     }
     if (!n_train) return MASCOT_OK;
     const size_t bytes = sizeof(mascot_rating) * n_train;
-    if (h->scratch_bytes < bytes) {
-        dev_free(h->d_scratch); h->scratch_bytes = 0;
-        CU(h, cudaMalloc(&h->d_scratch, bytes));
-        h->scratch_bytes = bytes;
-    }
+    int rc = need_scratch(h, bytes);
+    if (rc != MASCOT_OK) return rc;
     CU(h, cudaMemcpyAsync(h->d_scratch, train, bytes, cudaMemcpyHostToDevice, h->stream));
     CU(h, encode_segments(h, static_cast<const mascot_rating*>(h->d_scratch), h->seg_off, h->cfg.shuffle != 0,
                           h->tr_r, h->tr_u, h->tr_i, h->tr_src));
+    h->cls_off.clear();
+    if ((rc = partition_all(h)) != MASCOT_OK) return rc;      // the new stream carries the current precisions
     CU(h, cudaStreamSynchronize(h->stream));
     return MASCOT_OK;
 }
@@ -636,41 +731,53 @@ SampleStats stats_view(mascot_handle* h) {
     return st;
 }
 
-// Runs the update kernel over stream positions [begin, end).  With `collect`, the last
-// sample_ratio of the range (mf_methods.cu:102-103, 173-174) goes through the statistics kernel -
-// a second launch, so that only the sampled fraction pays for the statistics.
-// `policy_n` (0 = the range's own length) is the stream length the automatic worker count is taken
-// from; `head_override` (when not ~0) is the number of leading ratings of the range that are NOT sampled.
-int train_range(mascot_handle* h, float lr, uint32_t epoch, uint64_t begin, uint64_t end, bool collect, LaunchShape* shape, uint32_t* launches,
-                uint64_t policy_n = 0, uint64_t head_override = ~0ull) {
+// Runs the update kernel over stream positions [begin, end), all of whose ratings are of row class
+// `cls`.  With `collect`, the last sample_ratio of the range (mf_methods.cu:102-103, 173-174) goes
+// through the statistics kernel - a second launch, so that only the sampled fraction pays for the
+// statistics.  `policy_n` (0 = the range's own length) is the stream length the automatic worker
+// count is taken from.
+int train_span(mascot_handle* h, float lr, uint32_t epoch, uint64_t begin, uint64_t end, RowClass cls, bool collect,
+               LaunchShape* shape, uint32_t* launches, uint64_t policy_n) {
     if (end <= begin) return MASCOT_OK;
     const uint64_t n = end - begin;
-    bool any_f32 = false;
-    for (uint8_t p : h->uprec) any_f32 |= p != 0;
-    for (uint8_t p : h->iprec) any_f32 |= p != 0;
     const unsigned workers = worker_count(h, policy_n ? policy_n : n);
     // after its switch the whole-model switching trainer is the plain fp32 trainer (sgd_kernel.h:296-326)
     const TrainKind kind = (h->kind == KIND_SWITCH && h->switched_to_fp32) ? KIND_FP32 : h->kind;
     Stream s; s.r = h->tr_r + begin; s.u = h->tr_u + begin; s.i = h->tr_i + begin; s.n = n;
     uint64_t head = n;
-    if (head_override != ~0ull) {
-        head = std::min<uint64_t>(head_override, n);
-    } else if (collect) {
+    if (collect) {
         const uint64_t sample_num = (uint64_t)((float)n * h->cfg.sample_ratio);
         head = n - std::min<uint64_t>(sample_num, n);
     }
     if (head > 0) {
         Stream sa = s; sa.n = head;
-        CU(h, launch_train(h->K, kind, sa, h->P, h->Q, lr, h->cfg.lambda, nullptr, any_f32, workers,
+        CU(h, launch_train(h->K, kind, sa, h->P, h->Q, lr, h->cfg.lambda, nullptr, cls, workers,
                            h->d_work_counter, muppet_bits(h), (int)epoch, h->cfg.plain_user_stores == 0, h->stream, shape));
         (*launches)++;
     }
     if (head < n) {
         Stream sb; sb.r = s.r + head; sb.u = s.u + head; sb.i = s.i + head; sb.n = n - head;
         const SampleStats st = stats_view(h);
-        CU(h, launch_train(h->K, kind, sb, h->P, h->Q, lr, h->cfg.lambda, &st, any_f32, workers,
+        CU(h, launch_train(h->K, kind, sb, h->P, h->Q, lr, h->cfg.lambda, &st, cls, workers,
                            h->d_work_counter, muppet_bits(h), (int)epoch, h->cfg.plain_user_stores == 0, h->stream, shape));
         (*launches)++;
+    }
+    return MASCOT_OK;
+}
+
+// One segment of the stream: a single launch while every row is binary16 (or in the single-worker
+// mode, which reads each id's precision bit), else one launch per non-empty precision class.  On a
+// check epoch every launched range contributes its own sampled tail.
+int train_range(mascot_handle* h, float lr, uint32_t epoch, size_t segment, bool collect, LaunchShape* shape, uint32_t* launches,
+                uint64_t policy_n = 0) {
+    const uint64_t begin = h->seg_off[segment], end = h->seg_off[segment + 1];
+    if (!policy_n) policy_n = end - begin;
+    if (!h->partitioned)
+        return train_span(h, lr, epoch, begin, end, any_fp32_group(h) ? ROWCLASS_ANY : ROWCLASS_HH, collect, shape, launches, policy_n);
+    const uint64_t* off = &h->cls_off[segment * 5];
+    for (int c = 0; c < 4; c++) {
+        const int rc = train_span(h, lr, epoch, off[c], off[c + 1], (RowClass)c, collect, shape, launches, policy_n);
+        if (rc != MASCOT_OK) return rc;
     }
     return MASCOT_OK;
 }
@@ -727,6 +834,10 @@ int apply_stats(mascot_handle* h, uint32_t epoch, uint32_t* promoted_u, uint32_t
                 if (launches) (*launches) += 2;
             }
         }
+        if (*promoted_u + *promoted_i) {
+            if ((rc = partition_all(h)) != MASCOT_OK) return rc;
+            if (launches && h->partitioned) (*launches) += 4;
+        }
     }
     return MASCOT_OK;
 }
@@ -755,7 +866,7 @@ int mascot_train_segment(mascot_handle* h, uint32_t epoch, uint32_t segment, uin
     const float lr = epoch < h->lr.size() ? h->lr[epoch] : lr_at(h->cfg, epoch);
     LaunchShape shape; uint32_t launches = 0;
     CU(h, cudaEventRecord(h->ev[0], h->stream));
-    const int rc = train_range(h, lr, epoch, h->seg_off[segment], h->seg_off[segment + 1], collect_stats && h->grouped, &shape, &launches);
+    const int rc = train_range(h, lr, epoch, segment, collect_stats && h->grouped, &shape, &launches);
     if (rc != MASCOT_OK) return rc;
     CU(h, cudaEventRecord(h->ev[3], h->stream));
     if (out) {
@@ -816,7 +927,7 @@ int mascot_train_epoch(mascot_handle* h, uint32_t epoch, mascot_epoch_stats* out
     LaunchShape shape;
     int rc;
     for (size_t sgm = 0; sgm + 1 < h->seg_off.size(); sgm++)
-        if ((rc = train_range(h, lr, epoch, h->seg_off[sgm], h->seg_off[sgm + 1], check, &shape, &launches)) != MASCOT_OK) return rc;
+        if ((rc = train_range(h, lr, epoch, sgm, check, &shape, &launches)) != MASCOT_OK) return rc;
     if (check && h->stats_copies > 1) {
         CU(h, launch_reduce_stats(h->d_stats, h->stats_copies, h->stats_stride, stats_floats(h), h->stream));
         launches++;
@@ -876,6 +987,9 @@ int mascot_train_epoch_streamed(mascot_handle* h, uint32_t epoch, const mascot_r
     h->seg_off.clear();
     for (uint64_t off = 0; off < n_train; off += piece) h->seg_off.push_back(off);
     h->seg_off.push_back(n_train);
+    h->cls_off.clear();
+    h->partitioned = false;
+    const bool partition_pieces = wants_partition(h);
 
     const float lr = epoch < h->lr.size() ? h->lr[epoch] : lr_at(h->cfg, epoch);
     const bool muppet = h->kind == KIND_MUPPET;
@@ -884,8 +998,6 @@ int mascot_train_epoch_streamed(mascot_handle* h, uint32_t epoch, const mascot_r
     const bool check = muppet || ((h->grouped || (switch_only && !h->switched_to_fp32)) && is_check_epoch(h->cfg, epoch));
     uint32_t launches = 0, promoted_u = 0, promoted_i = 0;
     const uint64_t bytes_this_epoch = algorithmic_bytes(h);
-    uint64_t first_sample = n_train;
-    if (check) first_sample = n_train - std::min<uint64_t>((uint64_t)((float)n_train * h->cfg.sample_ratio), n_train);
     CU(h, cudaEventRecord(h->ev[0], h->stream));
     if (check) CU(h, cudaMemsetAsync(h->d_stats, 0, sizeof(float) * h->stats_stride * h->stats_copies, h->stream));
     CU(h, cudaEventRecord(h->ev[1], h->stream));
@@ -903,8 +1015,13 @@ int mascot_train_epoch_streamed(mascot_handle* h, uint32_t epoch, const mascot_r
                                    h->tr_src ? h->tr_src + off : nullptr, (uint32_t)off, h->stream));
         launches++;
         CU(h, cudaEventRecord(h->ev_free[b], h->stream));
-        const uint64_t head = first_sample <= off ? 0 : std::min<uint64_t>(first_sample - off, len);
-        if ((rc = train_range(h, lr, epoch, off, off + len, check, &shape, &launches, n_train, head)) != MASCOT_OK) return rc;
+        if (partition_pieces) {
+            // the piece was encoded with the current precisions: bring its classes together before training it
+            if ((rc = partition_segments(h, c, 1)) != MASCOT_OK) return rc;
+            h->partitioned = true;
+            launches += 4;
+        }
+        if ((rc = train_range(h, lr, epoch, c, check, &shape, &launches, n_train)) != MASCOT_OK) return rc;
     }
     if (check && h->stats_copies > 1) {
         CU(h, launch_reduce_stats(h->d_stats, h->stats_copies, h->stats_stride, stats_floats(h), h->stream));
@@ -1049,6 +1166,7 @@ int mascot_promote_group(mascot_handle* h, int side, uint32_t group) {
     CU(h, cudaSetDevice(h->cfg.device));
     int rc = promote_group(h, users, group);
     if (rc == MASCOT_OK) rc = recode_side(h, users);
+    if (rc == MASCOT_OK) rc = partition_all(h);
     if (rc != MASCOT_OK) return rc;
     CU(h, cudaStreamSynchronize(h->stream));
     return MASCOT_OK;

@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 
 #include <cub/block/block_radix_sort.cuh>
+#include <cub/device/device_radix_sort.cuh>
 
 #include "engine.h"
 #include "layout.cuh"
@@ -17,7 +18,7 @@ struct NodeAos { float r; uint32_t u; uint32_t i; };
 
 inline int grid_for(uint64_t n, int block) {
     uint64_t g = (n + block - 1) / block;
-    const uint64_t cap = 148ull * 16;
+    const uint64_t cap = (uint64_t)sm_count() * 16;
     return (int)(g < 1 ? 1 : (g > cap ? cap : g));
 }
 
@@ -143,16 +144,64 @@ __device__ __forceinline__ uint64_t splitmix64(uint64_t x) {
     return x ^ (x >> 31);
 }
 
-// N(0, 0.01^2) like init_rand_feature_single (model_init.cu:19-28), from a counter-based
-// generator: element t of stream `sid` depends only on (seed, sid, t).
+// ---- reproducible double arithmetic for the factor initialisation -------------------------------
+// The library logarithm and cosine are accurate to a unit in the last place but not correctly rounded,
+// so a host program cannot reproduce their results bit for bit.  The two functions below use only
+// single IEEE-754 operations (add, multiply, divide - written as intrinsics so that nothing is fused)
+// in a fixed order; the same sequence on a host gives the same bits.
+__device__ __forceinline__ double rmul(double a, double b) { return __dmul_rn(a, b); }
+__device__ __forceinline__ double radd(double a, double b) { return __dadd_rn(a, b); }
+
+// ln(x) for a normal x in (0, 1]: x = m * 2^e with m in (sqrt(1/2), sqrt(2)], s = (m-1)/(m+1),
+// ln(m) = 2s * (1 + z/3 + z^2/5 + ... + z^10/21), z = s^2 <= 0.0295 (truncation below 1e-17).
+__device__ double exact_log(double x) {
+    const long long bits = __double_as_longlong(x);
+    int e = (int)((bits >> 52) & 0x7ff) - 1023;
+    double m = __longlong_as_double((bits & 0xfffffffffffffLL) | 0x3ff0000000000000LL);
+    if (m > 1.4142135623730951) { m = rmul(m, 0.5); e += 1; }
+    const double f = radd(m, -1.0);
+    const double s = __ddiv_rn(f, radd(2.0, f));
+    const double z = rmul(s, s);
+    double p = 1.0 / 21.0;
+    p = radd(rmul(p, z), 1.0 / 19.0); p = radd(rmul(p, z), 1.0 / 17.0); p = radd(rmul(p, z), 1.0 / 15.0);
+    p = radd(rmul(p, z), 1.0 / 13.0); p = radd(rmul(p, z), 1.0 / 11.0); p = radd(rmul(p, z), 1.0 / 9.0);
+    p = radd(rmul(p, z), 1.0 / 7.0); p = radd(rmul(p, z), 1.0 / 5.0); p = radd(rmul(p, z), 1.0 / 3.0);
+    p = radd(rmul(p, z), 1.0);
+    return radd(rmul((double)e, 0.6931471805599453), rmul(rmul(2.0, s), p));
+}
+
+// cos(pi * y) for y in [0, 2], y a multiple of 2^-52: y = q/2 + r with |r| <= 1/4 (exact), then the
+// Taylor series of cos or sin of t = pi*r (|t| <= 0.786, truncation below 1e-17).
+__device__ double exact_cospi(double y) {
+    const int q = (int)floor(radd(rmul(y, 2.0), 0.5));
+    const double r = radd(y, -rmul((double)q, 0.5));
+    const double t = rmul(r, 3.141592653589793), t2 = rmul(t, t);
+    double c = 1.0 / 20922789888000.0;                       // 1/16!
+    c = radd(rmul(c, t2), -1.0 / 87178291200.0); c = radd(rmul(c, t2), 1.0 / 479001600.0);
+    c = radd(rmul(c, t2), -1.0 / 3628800.0); c = radd(rmul(c, t2), 1.0 / 40320.0);
+    c = radd(rmul(c, t2), -1.0 / 720.0); c = radd(rmul(c, t2), 1.0 / 24.0);
+    c = radd(rmul(c, t2), -0.5); c = radd(rmul(c, t2), 1.0);
+    double sn = 1.0 / 355687428096000.0;                     // 1/17!
+    sn = radd(rmul(sn, t2), -1.0 / 1307674368000.0); sn = radd(rmul(sn, t2), 1.0 / 6227020800.0);
+    sn = radd(rmul(sn, t2), -1.0 / 39916800.0); sn = radd(rmul(sn, t2), 1.0 / 362880.0);
+    sn = radd(rmul(sn, t2), -1.0 / 5040.0); sn = radd(rmul(sn, t2), 1.0 / 120.0);
+    sn = radd(rmul(sn, t2), -1.0 / 6.0); sn = radd(rmul(sn, t2), 1.0);
+    sn = rmul(sn, t);
+    switch (q & 3) { case 0: return c; case 1: return -sn; case 2: return -c; default: return sn; }
+}
+
+// N(0, 0.01^2) like init_rand_feature_single (model_init.cu:19-28), from a counter-based generator:
+// element t of stream `sid` depends only on (seed, sid, t) - two splitmix64 draws, Box-Muller with the
+// reproducible logarithm and cosine above, one rounding to float.  A host program that follows the
+// same steps gets the same factors bit for bit.
 __global__ void init_normal_kernel(float* dst, uint64_t count, uint64_t seed, uint64_t sid) {
     for (uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; t < count; t += (uint64_t)gridDim.x * blockDim.x) {
         const uint64_t z = splitmix64(splitmix64(seed ^ (sid * 0xd1342543de82ef95ull)) + t);
-        const double u1 = ((double)(z >> 11) + 1.0) * (1.0 / 9007199254740993.0);   // (0,1)
+        const double u1 = rmul((double)((z >> 11) + 1), 1.0 / 9007199254740992.0);    // (0, 1]
         const uint64_t z2 = splitmix64(z);
-        const double u2 = (double)(z2 >> 11) * (1.0 / 9007199254740992.0);
-        const double nrm = sqrt(-2.0 * log(u1)) * cospi(2.0 * u2);
-        dst[t] = (float)(nrm * 0.01);
+        const double u2 = rmul((double)(z2 >> 11), 1.0 / 9007199254740992.0);         // [0, 1)
+        const double radius = __dsqrt_rn(rmul(-2.0, exact_log(u1)));
+        dst[t] = (float)rmul(rmul(radius, exact_cospi(rmul(2.0, u2))), 0.01);
     }
 }
 
@@ -169,7 +218,8 @@ cudaError_t launch_encode_stream(const void* d_src_aos, uint64_t n, bool shuffle
         int key_bits = 1;
         while (key_bits < 31 && (1ull << key_bits) < (uint64_t)n_items + 1) key_bits++;
         const uint64_t windows = (n + kWindow - 1) / kWindow;
-        const int grid = (int)(windows < 148 * 8 ? windows : 148 * 8);
+        const uint64_t cap = (uint64_t)sm_count() * 8;
+        const int grid = (int)(windows < cap ? windows : cap);
         encode_sorted_kernel<<<grid, kSortThreads, 0, st>>>(src, n, seed, user_map, item_map, uprec_row, iprec_row,
                                                              key_bits, r, u, i, src_out, src_base);
     } else {
@@ -191,6 +241,58 @@ cudaError_t launch_mark_fp32(uint8_t* row_flags, uint32_t n, cudaStream_t st) {
 cudaError_t launch_recode(uint32_t* ids, uint64_t n, const uint8_t* prec_row, cudaStream_t st) {
     if (n == 0) return cudaSuccess;
     recode_kernel<<<grid_for(n, 256), 256, 0, st>>>(ids, n, prec_row);
+    return cudaGetLastError();
+}
+
+// ---- partition of the stream by precision class ---------------------------------------------
+// key = segment * 4 + class, class = 2 * (user row is fp32) + (item row is fp32).  A stable sort by
+// that key keeps the segments where they are and, inside each, puts the ratings of one class next to
+// each other in their previous order (so runs of equal items stay runs).
+__global__ void class_key_kernel(const uint32_t* u, const uint32_t* i, uint64_t n, const uint64_t* seg_off, int nseg,
+                                 uint16_t* key, uint32_t* idx) {
+    for (uint64_t j = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; j < n; j += (uint64_t)gridDim.x * blockDim.x) {
+        int lo = 0, hi = nseg - 1;                    // last segment whose offset is <= j
+        while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (seg_off[mid] <= j) lo = mid; else hi = mid - 1; }
+        const uint32_t cls = ((u[j] & kPrecBit) ? 2u : 0u) | ((i[j] & kPrecBit) ? 1u : 0u);
+        key[j] = (uint16_t)(lo * 4 + cls);
+        idx[j] = (uint32_t)j;
+    }
+}
+__global__ void class_gather_kernel(const uint32_t* perm, uint64_t n, const float* r, const uint32_t* u, const uint32_t* i,
+                                    const uint32_t* src, float* r2, uint32_t* u2, uint32_t* i2, uint32_t* src2) {
+    for (uint64_t j = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; j < n; j += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t s = perm[j];
+        r2[j] = r[s]; u2[j] = u[s]; i2[j] = i[s];
+        if (src) src2[j] = src[s];
+    }
+}
+// first[k] = smallest position whose key is k (entries of absent keys keep their preset value)
+__global__ void class_first_kernel(const uint16_t* key_sorted, uint64_t n, unsigned long long* first) {
+    for (uint64_t j = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; j < n; j += (uint64_t)gridDim.x * blockDim.x)
+        if (j == 0 || key_sorted[j] != key_sorted[j - 1]) first[key_sorted[j]] = j;
+}
+
+size_t partition_temp_bytes(uint64_t n, int key_bits) {
+    size_t bytes = 0;
+    cub::DeviceRadixSort::SortPairs(nullptr, bytes, (const uint16_t*)nullptr, (uint16_t*)nullptr, (const uint32_t*)nullptr,
+                                    (uint32_t*)nullptr, n, 0, key_bits);
+    return bytes;
+}
+
+cudaError_t launch_partition_by_class(const float* r, const uint32_t* u, const uint32_t* i, const uint32_t* src, uint64_t n,
+                                      const uint64_t* d_seg_off, int nseg, int key_bits,
+                                      uint16_t* key_a, uint16_t* key_b, uint32_t* idx_a, uint32_t* idx_b,
+                                      void* temp, size_t temp_bytes, unsigned long long* d_first,
+                                      float* r2, uint32_t* u2, uint32_t* i2, uint32_t* src2, cudaStream_t st) {
+    if (n == 0) return cudaSuccess;
+    const int g = grid_for(n, 256);
+    class_key_kernel<<<g, 256, 0, st>>>(u, i, n, d_seg_off, nseg, key_a, idx_a);
+    cudaError_t e = cub::DeviceRadixSort::SortPairs(temp, temp_bytes, key_a, key_b, idx_a, idx_b, n, 0, key_bits, st);
+    if (e != cudaSuccess) return e;
+    class_gather_kernel<<<g, 256, 0, st>>>(idx_b, n, r, u, i, src, r2, u2, i2, src2);
+    e = cudaMemsetAsync(d_first, 0xff, sizeof(unsigned long long) * (size_t)nseg * 4, st);
+    if (e != cudaSuccess) return e;
+    class_first_kernel<<<g, 256, 0, st>>>(key_b, n, d_first);
     return cudaGetLastError();
 }
 

@@ -46,6 +46,7 @@
 #include <cuda_runtime.h>
 
 #include "engine.h"
+#include "launch_cache.h"
 #include "layout.cuh"
 
 namespace mascot {
@@ -57,8 +58,11 @@ constexpr uint32_t kNoRow = 0xffffffffu;     // never a valid stream id
 struct V8h { __half2 v[4]; };                // eight binary16 values, physical order
 struct V8f { float x[8]; };
 
-// How the rows of a launch are stored.  Known on the host, so the common cases carry no
-// per-rating precision test and no unused registers.
+// How the rows of one side are stored in a launch.  Known on the host, so the common cases carry no
+// per-rating precision test, no unused registers and no oversized ring slots.  The mixed-precision
+// trainer keeps its stream partitioned by (user precision, item precision), and every part runs the
+// instantiation made for it; ROWS_DYN (precision read from bit 31 of the id, per rating) remains for
+// the deterministic single-worker mode, which must follow the stream in its original order.
 enum RowMode { ROWS_HALF = 0, ROWS_F32 = 1, ROWS_DYN = 2 };
 
 // A lane's slice of a row as fetched: 16 bytes for binary16 storage, 32 bytes for fp32 storage.
@@ -526,8 +530,8 @@ __device__ __forceinline__ void afp_update(const Consts& c, AfpState& st, float 
 
 // One update.  p_raw / q_raw are the row slices in their storage precision; both are replaced by the
 // updated values.  Statistics go to `acc` when the rating is sampled.
-template <int K, int KIND, int MODE, bool STATS>
-__device__ __forceinline__ void update_one(const Consts& c, float r, uint32_t uc, uint32_t ic, Raw<MODE>& p_raw, Raw<MODE>& q_raw,
+template <int K, int KIND, int UM, int IM, bool STATS>
+__device__ __forceinline__ void update_one(const Consts& c, float r, uint32_t uc, uint32_t ic, Raw<UM>& p_raw, Raw<IM>& q_raw,
                                            bool sampled, Sample& smp, AfpState& afp, unsigned wmask) {
     constexpr int TS = K / 8;
     if (STATS) { smp.user = false; smp.item = false; }
@@ -560,8 +564,8 @@ __device__ __forceinline__ void update_one(const Consts& c, float r, uint32_t uc
         put(p_raw, narrow(step(c.lr, grad(e, q, c.lam, p), p)));
         put(q_raw, narrow(step(c.lr, grad(e, p, c.lam, q), q)));
     } else {
-        const bool uf = is_f32<MODE>(uc), itf = is_f32<MODE>(ic);
-        if (!uf && !itf) {
+        const bool uf = is_f32<UM>(uc), itf = is_f32<IM>(ic);
+        auto both_half = [&]() {
             const V8h p = as_v8h(p_raw), q = as_v8h(q_raw);
             const __half dot = worker_sum<TS>(pair_partial(p, q), wmask);
             const __half2 e = __half2half2(__hsub_rn(__float2half_rn(r), dot));
@@ -569,7 +573,8 @@ __device__ __forceinline__ void update_one(const Consts& c, float r, uint32_t uc
             put(p_raw, step(c.lr_h, gp, p));
             put(q_raw, step(c.lr_h, gq, q));
             if (STATS && sampled) { smp.gp = widen(gp); smp.gq = widen(gq); smp.user = true; smp.item = true; }
-        } else if constexpr (MODE != ROWS_HALF) {
+        };
+        auto some_f32 = [&]() {
             const V8f p = uf ? as_v8f(p_raw) : widen(as_v8h(p_raw));
             const V8f q = itf ? as_v8f(q_raw) : widen(as_v8h(q_raw));
             const float e = __fsub_rn(r, worker_sum<TS>(pair_partial(p, q), wmask));
@@ -578,7 +583,10 @@ __device__ __forceinline__ void update_one(const Consts& c, float r, uint32_t uc
             if (uf) put(p_raw, po); else put(p_raw, narrow(po));
             if (itf) put(q_raw, qo); else put(q_raw, narrow(qo));
             if (STATS && sampled) { smp.gp = gp; smp.gq = gq; smp.user = !uf; smp.item = !itf; }
-        }
+        };
+        if constexpr (UM == ROWS_HALF && IM == ROWS_HALF) both_half();
+        else if constexpr (UM != ROWS_DYN && IM != ROWS_DYN) some_f32();
+        else { if (!uf && !itf) both_half(); else some_f32(); }
     }
 }
 
@@ -625,21 +633,23 @@ constexpr uint32_t F_IDUP = 8u;     // run start whose item also occurs among th
 
 constexpr int kSpan = 8;            // consecutive chunks handed out together (one ticket per span)
 
-// Shared memory of one worker: two chunks of records, then the user ring, then the item ring.
-template <int K, int MODE, int NS, int NSI> struct WorkerSmem {
+// Shared memory of one worker: two chunks of records, then the user ring, then the item ring.  A ring
+// slot is as large as the widest row its side can hold in this launch.
+template <int K, int UM, int IM, int NS, int NSI> struct WorkerSmem {
     static constexpr int TS = K / 8;
-    static constexpr int kRowBytes = K * (MODE == ROWS_HALF ? 2 : 4);
+    static constexpr int kURowBytes = K * (UM == ROWS_HALF ? 2 : 4);
+    static constexpr int kIRowBytes = K * (IM == ROWS_HALF ? 2 : 4);
     static constexpr int kRecBytes = 2 * TS * 16;
-    static constexpr int kBytes = kRecBytes + (NS + NSI) * kRowBytes;
+    static constexpr int kBytes = kRecBytes + NS * kURowBytes + NSI * kIRowBytes;
 };
 
 // NS / NSI: slots of the user / item ring.  User rows are requested D ratings ahead, item rows DI
 // ratings ahead (DI <= D <= NS-1, DI <= NSI-1).  The lead is kept as short as the memory latency allows: a row that another
 // worker updates between the request and the write-back loses that update, and the chance of that
 // grows with the lead.
-template <int K, int KIND, int MODE, bool STATS, int NS, int NSI, int D, int DI>
-__global__ void __launch_bounds__(256, (MODE == ROWS_HALF && !STATS) ? 4 : 3) train_kernel(const KernelArgs a) {
-    using SM = WorkerSmem<K, MODE, NS, NSI>;
+template <int K, int KIND, int UM, int IM, bool STATS, int NS, int NSI, int D, int DI>
+__global__ void __launch_bounds__(256, (UM == ROWS_HALF && IM == ROWS_HALF && !STATS) ? 4 : 3) train_kernel(const KernelArgs a) {
+    using SM = WorkerSmem<K, UM, IM, NS, NSI>;
     constexpr int TS = SM::TS;                     // lanes per worker = ratings per chunk
     static_assert(TS % NS == 0, "the ring must divide the chunk");
     static_assert(DI >= 1 && DI <= D && D == NS - 1 && DI <= NSI - 1 && NS % NSI == 0, "leads must fit the rings");
@@ -654,8 +664,8 @@ __global__ void __launch_bounds__(256, (MODE == ROWS_HALF && !STATS) ? 4 : 3) tr
 
     unsigned char* const mine = smem_raw + (size_t)(threadIdx.x / TS) * SM::kBytes;
     uint4* const recs = reinterpret_cast<uint4*>(mine);                  // [2][TS]
-    unsigned char* const uring = mine + SM::kRecBytes;                    // [NS][kRowBytes]
-    unsigned char* const iring = uring + NS * SM::kRowBytes;              // [NSI][kRowBytes]
+    unsigned char* const uring = mine + SM::kRecBytes;                    // [NS][kURowBytes]
+    unsigned char* const iring = uring + NS * SM::kURowBytes;             // [NSI][kIRowBytes]
 
     Consts c;
     c.lr = a.lr; c.lam = a.lam;
@@ -668,7 +678,7 @@ __global__ void __launch_bounds__(256, (MODE == ROWS_HALF && !STATS) ? 4 : 3) tr
     c.afp_epoch = a.epoch;
     c.afp_init_threshold = (int)((float)((a.s.n + W - 1) / W) / 10.0f);
     // only the mixed-precision mode reads the precision bit of an id
-    constexpr uint32_t kKeep = (MODE == ROWS_DYN) ? 0xffffffffu : (kIdMask | kHotBit);
+    constexpr uint32_t kKeep = (UM == ROWS_DYN || IM == ROWS_DYN) ? 0xffffffffu : (kIdMask | kHotBit);
 
     if (worker >= W) return;
 
@@ -737,7 +747,7 @@ __global__ void __launch_bounds__(256, (MODE == ROWS_HALF && !STATS) ? 4 : 3) tr
 
     // item row of the current run
     uint32_t cur_ic = kNoRow;
-    Raw<MODE> q;
+    Raw<IM> q;
 
     // item-side statistics of the current run of equal item groups
     V8f gq_acc; float nq_acc = 0.f; uint32_t acc_group = kNoRow;
@@ -794,10 +804,10 @@ __global__ void __launch_bounds__(256, (MODE == ROWS_HALF && !STATS) ? 4 : 3) tr
     // requests the user row of the rating with record `rx` / the item row of the rating whose first
     // two record words are `ri`, into ring slot `slot`
     auto request_user = [&](const uint4& rx, int slot) {
-        if ((rx.x & (F_VALID | F_UDUP)) == F_VALID) cp_row<K, MODE>(uring + slot * SM::kRowBytes, a.P, rx.z, m);
+        if ((rx.x & (F_VALID | F_UDUP)) == F_VALID) cp_row<K, UM>(uring + slot * SM::kURowBytes, a.P, rx.z, m);
     };
     auto request_item = [&](const uint2& ri, int slot) {
-        if ((ri.x & (F_VALID | F_RS | F_IDUP)) == (F_VALID | F_RS)) cp_row<K, MODE>(iring + slot * SM::kRowBytes, a.Q, ri.y, m);
+        if ((ri.x & (F_VALID | F_RS | F_IDUP)) == (F_VALID | F_RS)) cp_row<K, IM>(iring + slot * SM::kIRowBytes, a.Q, ri.y, m);
     };
     // Copy groups complete in order.  Every iteration commits two: first the item row of the rating
     // DI ahead, then the user row of the rating D ahead.  When rating j is used, the groups younger
@@ -840,16 +850,16 @@ __global__ void __launch_bounds__(256, (MODE == ROWS_HALF && !STATS) ? 4 : 3) tr
                 const bool sampled = STATS && ((cb ? base1 : base0) + j >= a.st.first_sample_pos);
                 if (rec.x & F_RS) {
                     cp_wait<kPendItem>();
-                    if (cur_ic != kNoRow) st_row<K, MODE>(a.Q, cur_ic, m, q);
-                    if (rec.x & F_IDUP) q = ld_row<K, MODE>(a.Q, ic, m);
-                    else q = lds_row<K, MODE>(iring + (t & (NSI - 1)) * SM::kRowBytes, ic, m);
+                    if (cur_ic != kNoRow) st_row<K, IM>(a.Q, cur_ic, m, q);
+                    if (rec.x & F_IDUP) q = ld_row<K, IM>(a.Q, ic, m);
+                    else q = lds_row<K, IM>(iring + (t & (NSI - 1)) * SM::kIRowBytes, ic, m);
                     cur_ic = ic;
                 } else {
                     cp_wait<kPendUser>();
                 }
-                Raw<MODE> p;
-                if (rec.x & F_UDUP) p = ld_row<K, MODE>(a.P, uc, m);
-                else p = lds_row<K, MODE>(uring + t * SM::kRowBytes, uc, m);
+                Raw<UM> p;
+                if (rec.x & F_UDUP) p = ld_row<K, UM>(a.P, uc, m);
+                else p = lds_row<K, UM>(uring + t * SM::kURowBytes, uc, m);
                 // request the user row of the rating D ahead and the item row of the rating DI ahead,
                 // into slots whose previous contents have been consumed
                 {
@@ -859,10 +869,10 @@ __global__ void __launch_bounds__(256, (MODE == ROWS_HALF && !STATS) ? 4 : 3) tr
                     request_user(rq[(t + D) & (NS - 1)], (t + D) & (NS - 1));
                     cp_commit();
                 }
-                const Raw<MODE> p_before = p;
-                update_one<K, KIND, MODE, STATS>(c, r, uc, ic, p, q, sampled, smp, afp, wmask);
-                if (a.add_user_delta && !(uc & kHotBit)) add_row_delta<K, MODE>(a.P, uc, m, p, p_before);
-                else st_row<K, MODE>(a.P, uc, m, p);
+                const Raw<UM> p_before = p;
+                update_one<K, KIND, UM, IM, STATS>(c, r, uc, ic, p, q, sampled, smp, afp, wmask);
+                if (a.add_user_delta && !(uc & kHotBit)) add_row_delta<K, UM>(a.P, uc, m, p, p_before);
+                else st_row<K, UM>(a.P, uc, m, p);
                 if (STATS && sampled) record(smp, uc, ic);
             }
         }
@@ -872,7 +882,7 @@ __global__ void __launch_bounds__(256, (MODE == ROWS_HALF && !STATS) ? 4 : 3) tr
         cb ^= 1;
     }
     cp_wait<0>();
-    if (cur_ic != kNoRow) st_row<K, MODE>(a.Q, cur_ic, m, q);
+    if (cur_ic != kNoRow) st_row<K, IM>(a.Q, cur_ic, m, q);
     if (STATS) {
         if constexpr (KIND == KIND_MUPPET || KIND == KIND_SWITCH) { if (m == 0) atomicAdd(nsum_p, nq_acc); }
         else flush_item_stats();
@@ -887,67 +897,52 @@ __global__ void reduce_stats_kernel(float* sets, int copies, size_t stride, size
     }
 }
 
-int sm_count() {
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    }
-    return sms;
-}
-
-template <int K, int KIND, int MODE, bool STATS, int NS, int NSI, int D, int DI>
+template <int K, int KIND, int UM, int IM, bool STATS, int NS, int NSI, int D, int DI>
 cudaError_t launch_ns(KernelArgs a, unsigned warps_per_sm, unsigned workers, cudaStream_t st, LaunchShape* shape) {
     constexpr int TS = K / 8;
     constexpr int kPerWarp = 32 / TS;
-    using SM = WorkerSmem<K, MODE, NS, NSI>;
-    auto kern = train_kernel<K, KIND, MODE, STATS, NS, NSI, D, DI>;
+    using SM = WorkerSmem<K, UM, IM, NS, NSI>;
+    auto kern = train_kernel<K, KIND, UM, IM, STATS, NS, NSI, D, DI>;
+    // the most dynamic shared memory a launch of this instantiation can ask for: a block of 8 warps
+    constexpr size_t kSmemMax = (size_t)8 * kPerWarp * SM::kBytes;
+    static LaunchCache cache;                    // one per instantiation; see launch_cache.h
     int grid, block;
     const unsigned warps = (workers + kPerWarp - 1) / kPerWarp;
     if (workers <= 1) a.add_user_delta = 0;      // a single worker has nobody to race with: plain stores
+    unsigned blocks_per_sm = 1, warps_per_block = warps;
+    if (warps > 8) {
+        // the same number of warps on every SM, in blocks of at most 8 warps
+        blocks_per_sm = (warps_per_sm + 7) / 8;
+        warps_per_block = (warps_per_sm + blocks_per_sm - 1) / blocks_per_sm;
+    }
+    block = (int)(32 * warps_per_block);
+    const size_t smem = (size_t)warps_per_block * kPerWarp * SM::kBytes;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    int fit = 0;
+    const int rc = cache.lookup(
+        dev, block, smem, kSmemMax,
+        [&](size_t bytes) { return (int)cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes); },
+        [&](int blk, size_t sm, int* f) { return (int)cudaOccupancyMaxActiveBlocksPerMultiprocessor(f, kern, blk, sm); }, &fit);
+    if (rc != 0) return (cudaError_t)rc;
+    if (fit < 1) return cudaErrorLaunchOutOfResources;
     if (warps <= 8) {
         // a single block (deterministic runs, tiny worker counts) uses exactly the requested workers
-        grid = 1; block = (int)(32 * warps);
+        grid = 1;
         a.workers = workers;
     } else {
-        // the same number of warps on every SM, in blocks of at most 8 warps, and no more blocks than
-        // the SM can hold at once (registers, shared memory)
-        const unsigned sms = (unsigned)sm_count();
-        unsigned blocks_per_sm = (warps_per_sm + 7) / 8;
-        const unsigned warps_per_block = (warps_per_sm + blocks_per_sm - 1) / blocks_per_sm;
-        block = (int)(32 * warps_per_block);
-        const size_t smem_block = (size_t)warps_per_block * kPerWarp * SM::kBytes;
-        // the answer for a block shape does not change: asked once per shape and device (a sharded
-        // epoch launches this kernel once per sub-epoch)
-        static int known_block = 0, known_fit = 0, known_dev = -1;
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (known_block != block || known_dev != dev) {
-            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_block);
-            if (e != cudaSuccess) return e;
-            int f = 0;
-            e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&f, kern, block, smem_block);
-            if (e != cudaSuccess) return e;
-            known_block = block; known_fit = f; known_dev = dev;
-        }
-        const int fit = known_fit;
-        if (fit < 1) return cudaErrorLaunchOutOfResources;
+        // no more blocks than the SM can hold at once (registers, shared memory)
         if (blocks_per_sm > (unsigned)fit) blocks_per_sm = (unsigned)fit;
-        grid = (int)(sms * blocks_per_sm);
+        grid = (int)((unsigned)sm_count() * blocks_per_sm);
         a.workers = (unsigned)grid * warps_per_block * kPerWarp;
-    }
-    const size_t smem = (size_t)(block / 32) * kPerWarp * SM::kBytes;
-    if (grid == 1) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
     }
     kern<<<grid, block, smem, st>>>(a);
     if (shape) { shape->grid = grid; shape->block = block; shape->smem = smem; shape->workers = a.workers; }
     return cudaGetLastError();
 }
 
-template <int K, int KIND, int MODE, bool STATS>
+template <int K, int KIND, int UM, int IM, bool STATS>
 cudaError_t launch_one(const KernelArgs& args, unsigned workers, cudaStream_t st, LaunchShape* shape) {
     constexpr int TS = K / 8;
     constexpr int kPerWarp = 32 / TS;
@@ -961,29 +956,33 @@ cudaError_t launch_one(const KernelArgs& args, unsigned workers, cudaStream_t st
     // User ring of four slots (rows requested three ratings ahead), item ring of two (one rating ahead).
     // Requesting user rows seven ahead was measured on the 100M- and the 252M-rating configuration and
     // changed nothing: the kernel is not waiting for memory.  With fp32 rows the slots are twice as large
-    // and the occupancy query below trims the number of blocks per SM accordingly.
-    return launch_ns<K, KIND, MODE, STATS, 4, 2, 3, 1>(args, per_sm, workers, st, shape);
+    // and the occupancy query trims the number of blocks per SM accordingly.
+    return launch_ns<K, KIND, UM, IM, STATS, 4, 2, 3, 1>(args, per_sm, workers, st, shape);
+}
+
+template <int K, int KIND, int UM, int IM>
+cudaError_t launch_st(const KernelArgs& a, bool stats, unsigned workers, cudaStream_t st, LaunchShape* sh) {
+    return stats ? launch_one<K, KIND, UM, IM, true>(a, workers, st, sh) : launch_one<K, KIND, UM, IM, false>(a, workers, st, sh);
 }
 
 template <int K>
-cudaError_t launch_k(TrainKind kind, const KernelArgs& a, bool stats, bool any_f32, unsigned workers, cudaStream_t st, LaunchShape* sh) {
+cudaError_t launch_k(TrainKind kind, const KernelArgs& a, bool stats, RowClass cls, unsigned workers, cudaStream_t st, LaunchShape* sh) {
     switch (kind) {
         case KIND_MIXED:
-            if (any_f32)
-                return stats ? launch_one<K, KIND_MIXED, ROWS_DYN, true>(a, workers, st, sh)
-                             : launch_one<K, KIND_MIXED, ROWS_DYN, false>(a, workers, st, sh);
-            return stats ? launch_one<K, KIND_MIXED, ROWS_HALF, true>(a, workers, st, sh)
-                         : launch_one<K, KIND_MIXED, ROWS_HALF, false>(a, workers, st, sh);
-        case KIND_FP32: return launch_one<K, KIND_FP32, ROWS_F32, false>(a, workers, st, sh);
-        case KIND_MPT: return launch_one<K, KIND_MPT, ROWS_F32, false>(a, workers, st, sh);
-        case KIND_MEMQUANT: return launch_one<K, KIND_MEMQUANT, ROWS_HALF, false>(a, workers, st, sh);
-        case KIND_AFP: return launch_one<K, KIND_AFP, ROWS_F32, false>(a, workers, st, sh);
-        case KIND_SWITCH:
-            return stats ? launch_one<K, KIND_SWITCH, ROWS_HALF, true>(a, workers, st, sh)
-                         : launch_one<K, KIND_SWITCH, ROWS_HALF, false>(a, workers, st, sh);
-        case KIND_MUPPET:
-            return stats ? launch_one<K, KIND_MUPPET, ROWS_F32, true>(a, workers, st, sh)
-                         : launch_one<K, KIND_MUPPET, ROWS_F32, false>(a, workers, st, sh);
+            switch (cls) {
+                case ROWCLASS_HH: return launch_st<K, KIND_MIXED, ROWS_HALF, ROWS_HALF>(a, stats, workers, st, sh);
+                case ROWCLASS_HF: return launch_st<K, KIND_MIXED, ROWS_HALF, ROWS_F32>(a, stats, workers, st, sh);
+                case ROWCLASS_FH: return launch_st<K, KIND_MIXED, ROWS_F32, ROWS_HALF>(a, stats, workers, st, sh);
+                case ROWCLASS_FF: return launch_st<K, KIND_MIXED, ROWS_F32, ROWS_F32>(a, stats, workers, st, sh);
+                case ROWCLASS_ANY: return launch_st<K, KIND_MIXED, ROWS_DYN, ROWS_DYN>(a, stats, workers, st, sh);
+            }
+            return cudaErrorInvalidValue;
+        case KIND_FP32: return launch_one<K, KIND_FP32, ROWS_F32, ROWS_F32, false>(a, workers, st, sh);
+        case KIND_MPT: return launch_one<K, KIND_MPT, ROWS_F32, ROWS_F32, false>(a, workers, st, sh);
+        case KIND_MEMQUANT: return launch_one<K, KIND_MEMQUANT, ROWS_HALF, ROWS_HALF, false>(a, workers, st, sh);
+        case KIND_AFP: return launch_one<K, KIND_AFP, ROWS_F32, ROWS_F32, false>(a, workers, st, sh);
+        case KIND_SWITCH: return launch_st<K, KIND_SWITCH, ROWS_HALF, ROWS_HALF>(a, stats, workers, st, sh);
+        case KIND_MUPPET: return launch_st<K, KIND_MUPPET, ROWS_F32, ROWS_F32>(a, stats, workers, st, sh);
     }
     return cudaErrorInvalidValue;
 }
@@ -997,8 +996,17 @@ cudaError_t launch_reduce_stats(float* sets, int copies, size_t copy_stride, siz
     return cudaGetLastError();
 }
 
+int sm_count() {
+    static int sms[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    int& v = sms[dev & 63];
+    if (!v) cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    return v > 0 ? v : 1;
+}
+
 cudaError_t launch_train(int K, TrainKind kind, const Stream& s, Arena P, Arena Q, float lr, float lam,
-                         const SampleStats* stats, bool any_f32_rows, unsigned workers, unsigned long long* work_counter,
+                         const SampleStats* stats, RowClass row_class, unsigned workers, unsigned long long* work_counter,
                          int bits, int epoch, bool add_user_delta, cudaStream_t st, LaunchShape* shape) {
     KernelArgs a;
     a.add_user_delta = add_user_delta ? 1 : 0;
@@ -1007,8 +1015,8 @@ cudaError_t launch_train(int K, TrainKind kind, const Stream& s, Arena P, Arena 
     if (s.n == 0) { if (shape) *shape = LaunchShape(); return cudaSuccess; }
     cudaError_t e0 = cudaMemsetAsync(work_counter, 0, sizeof(unsigned long long), st);
     if (e0 != cudaSuccess) return e0;
-    if (K == 128) return launch_k<128>(kind, a, stats != nullptr, any_f32_rows, workers, st, shape);
-    if (K == 64) return launch_k<64>(kind, a, stats != nullptr, any_f32_rows, workers, st, shape);
+    if (K == 128) return launch_k<128>(kind, a, stats != nullptr, row_class, workers, st, shape);
+    if (K == 64) return launch_k<64>(kind, a, stats != nullptr, row_class, workers, st, shape);
     return cudaErrorInvalidValue;
 }
 

@@ -7,7 +7,11 @@ sequentially; the harness also records the chunk start positions the kernel drew
 oracle can replay exactly the same update sequence and be compared bit for bit.
 
 Case kinds: 0 fp32 SGD, 1 MASCOT (mixed fp16/fp32 groups + sampled statistics), 2 MPT,
-3 fp16-storage SGD, 4 MuPPET, 5 AFP, 6 test-RMSE.
+3 fp16-storage SGD, 4 MuPPET, 5 AFP, 6 test-RMSE, 7 whole-model switching.
+
+A second bundle, tests/golden/setup_in.bin, holds the cases of kind 8: small rating sets (many tied
+degrees, unrated entities, a single degree class) on which the harness runs the reference's
+m-quantization set-up functions.
 """
 import os
 import sys
@@ -93,6 +97,58 @@ def tight_ratings(rng, c, matching):
     c["R"][:, 2] = i
 
 
+def setup_case(rng, k, n_users, n_items, nnz, n_test, ug, ig, zipf=None, unrated=(0, 0), flat=False):
+    """Ratings for the set-up pipeline: users/items drawn uniformly or by a power law; the last
+    `unrated` users/items never occur; `flat` gives every user the same degree."""
+    ru, ri = n_users - unrated[0], n_items - unrated[1]
+    if flat:
+        u = np.repeat(np.arange(ru, dtype=np.uint32), nnz // ru)
+        nnz = u.size
+        i = rng.integers(0, ri, nnz).astype(np.uint32)
+    else:
+        def draw(n, count):
+            if zipf is None:
+                return rng.integers(0, n, count)
+            w = np.arange(1, n + 1, dtype=np.float64) ** -zipf
+            return rng.permutation(n)[rng.choice(n, size=count, p=w / w.sum())]
+        u = np.concatenate([np.arange(ru), draw(ru, nnz - ru)]).astype(np.uint32)
+        i = np.concatenate([np.arange(ri), draw(ri, nnz - ri)])[rng.permutation(nnz)].astype(np.uint32)
+    R = np.empty((nnz, 3), np.uint32)
+    R[:, 0] = rng.choice(np.arange(0.5, 5.01, 0.5), nnz).astype(np.float32).view(np.uint32)
+    R[:, 1], R[:, 2] = u, i
+    T = np.empty((n_test, 3), np.uint32)
+    T[:, 0] = rng.choice(np.arange(0.5, 5.01, 0.5), n_test).astype(np.float32).view(np.uint32)
+    T[:, 1], T[:, 2] = rng.integers(0, ru, n_test), rng.integers(0, ri, n_test)
+    return {
+        "meta": np.array([8, k, n_users, n_items, nnz, n_test, ug, ig], np.int32),
+        "R": R, "T": T,
+        "P": (rng.standard_normal((n_users, k)) * 0.1).astype(np.float32),
+        "Q": (rng.standard_normal((n_items, k)) * 0.1).astype(np.float32),
+    }
+
+
+def write_cases(cases, filename):
+    arrays = {"cases": np.frombuffer("\n".join(cases).encode(), np.uint8)}
+    for name, c in cases.items():
+        for key, arr in c.items():
+            arrays[f"{name}.{key}"] = arr
+    out = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "tests", "golden", filename)
+    write_bundle(out, arrays)
+    print("wrote", os.path.normpath(out), len(cases), "cases")
+
+
+def setup_main():
+    rng = np.random.default_rng(20211208)
+    cases = {
+        "setup_tiny_k128": setup_case(rng, 128, 37, 23, 150, 40, 5, 4),
+        "setup_zipf_k64": setup_case(rng, 64, 2000, 500, 30000, 300, 100, 100, zipf=1.0),
+        "setup_unrated_k128": setup_case(rng, 128, 60, 40, 300, 50, 6, 6, unrated=(10, 5)),
+        "setup_flat_k64": setup_case(rng, 64, 16, 8, 64, 20, 4, 3, flat=True),
+        "setup_manygroups_k128": setup_case(rng, 128, 300, 200, 4000, 100, 300, 150, zipf=0.8),
+    }
+    write_cases(cases, "setup_in.bin")
+
+
 def main():
     rng = np.random.default_rng(20211207)
     cases = {}
@@ -144,14 +200,9 @@ def main():
                                                      scale=0.3, extra0=0, half_rows=True)
     cases["switching_k128_float"] = training_case(rng, "switching", 128, 15, 13, 36, 2, 24, 10, 83, 0.01, 0.05, extra0=1)
 
-    arrays = {"cases": np.frombuffer("\n".join(cases).encode(), np.uint8)}
-    for name, c in cases.items():
-        for key, arr in c.items():
-            arrays[f"{name}.{key}"] = arr
-    out = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "tests", "golden", "harness_in.bin")
-    write_bundle(out, arrays)
-    print("wrote", os.path.normpath(out), len(cases), "cases")
+    write_cases(cases, "harness_in.bin")
 
 
 if __name__ == "__main__":
     main()
+    setup_main()

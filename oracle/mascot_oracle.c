@@ -149,6 +149,59 @@ void mo_lr_schedule(float alpha, float decay, int epochs, float* out) {
     for (int i = 0; i < epochs; i++) out[i] = (float)((double)alpha / (1.0 + ((double)decay * pow((double)i, 1.5))));
 }
 
+/* Host twin of the engine's seeded factor initialisation (it replaces init_rand_feature_single,
+ * model_init.cu:19-28, whose cuRAND states are seeded with clock()).  Element t of stream `sid`:
+ * two splitmix64 draws -> u1 in (0,1], u2 in [0,1) -> Box-Muller, with a logarithm and a cosine
+ * built from single IEEE-754 operations in a fixed order (this file is compiled with
+ * -ffp-contract=off), so that the device reaches the same bits. */
+static uint64_t mo_splitmix64(uint64_t x) {
+    x += 0x9e3779b97f4a7c15ull;
+    x = (x ^ (x >> 30)) * 0xbf58476d1ce4e5b9ull;
+    x = (x ^ (x >> 27)) * 0x94d049bb133111ebull;
+    return x ^ (x >> 31);
+}
+static double mo_exact_log(double x) {
+    uint64_t bits; memcpy(&bits, &x, 8);
+    int e = (int)((bits >> 52) & 0x7ff) - 1023;
+    uint64_t mb = (bits & 0xfffffffffffffull) | 0x3ff0000000000000ull;
+    double m; memcpy(&m, &mb, 8);
+    if (m > 1.4142135623730951) { m = m * 0.5; e += 1; }
+    const double f = m + -1.0;
+    const double s = f / (2.0 + f);
+    const double z = s * s;
+    static const double c[10] = {1.0 / 19.0, 1.0 / 17.0, 1.0 / 15.0, 1.0 / 13.0, 1.0 / 11.0, 1.0 / 9.0, 1.0 / 7.0, 1.0 / 5.0, 1.0 / 3.0, 1.0};
+    double p = 1.0 / 21.0;
+    for (int j = 0; j < 10; j++) { const double t = p * z; p = t + c[j]; }
+    const double a = (double)e * 0.6931471805599453, b = 2.0 * s;
+    return a + b * p;
+}
+static double mo_exact_cospi(double y) {
+    const int q = (int)floor(y * 2.0 + 0.5);
+    const double r = y + -((double)q * 0.5);
+    const double t = r * 3.141592653589793, t2 = t * t;
+    static const double cc[8] = {-1.0 / 87178291200.0, 1.0 / 479001600.0, -1.0 / 3628800.0, 1.0 / 40320.0, -1.0 / 720.0, 1.0 / 24.0, -0.5, 1.0};
+    static const double sc[8] = {-1.0 / 1307674368000.0, 1.0 / 6227020800.0, -1.0 / 39916800.0, 1.0 / 362880.0, -1.0 / 5040.0, 1.0 / 120.0, -1.0 / 6.0, 1.0};
+    double c = 1.0 / 20922789888000.0, sn = 1.0 / 355687428096000.0;
+    for (int j = 0; j < 8; j++) { const double u = c * t2; c = u + cc[j]; }
+    for (int j = 0; j < 8; j++) { const double u = sn * t2; sn = u + sc[j]; }
+    sn = sn * t;
+    switch (q & 3) { case 0: return c; case 1: return -sn; case 2: return -c; default: return sn; }
+}
+void mo_init_normal(float* dst, uint64_t count, uint64_t seed, uint64_t sid) {
+    const uint64_t base = mo_splitmix64(seed ^ (sid * 0xd1342543de82ef95ull));
+    for (uint64_t t = 0; t < count; t++) {
+        const uint64_t z = mo_splitmix64(base + t);
+        const double u1 = (double)((z >> 11) + 1) * (1.0 / 9007199254740992.0);
+        const uint64_t z2 = mo_splitmix64(z);
+        const double u2 = (double)(z2 >> 11) * (1.0 / 9007199254740992.0);
+        const double l = mo_exact_log(u1);
+        const double radius = sqrt(-2.0 * l);
+        const double cv = mo_exact_cospi(2.0 * u2);
+        const double v = radius * cv;
+        dst[t] = (float)(v * 0.01);
+    }
+}
+
 /* mf_methods.cu:168-175: first check at epoch index 5, then every `interval`, never the last. */
 int mo_is_check_epoch(int e, int epochs, int interval) {
     const int start_idx = 5;

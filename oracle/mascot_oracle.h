@@ -107,6 +107,11 @@ void mo_afp_run(int k, const mo_node* R, const uint32_t* seq, uint64_t nseq, flo
 void mo_memquant_run(int k, const mo_node* R, const uint32_t* seq, uint64_t nseq, uint16_t* P, uint16_t* Q,
                      float lr, float lam, const mo_rules* rules);
 
+/* ---- initialisation ---- */
+/* The engine's seeded N(0, 0.01^2) factor generator, restated for the host: element t of stream
+ * `sid` (1 = user factors, 2 = item factors, both in the caller's row order). */
+void mo_init_normal(float* dst, uint64_t count, uint64_t seed, uint64_t sid);
+
 /* ---- evaluation ---- */
 /* Reference-literal test RMSE: fp32 dot, 512-rating block trees, float sum of block partials. */
 float mo_rmse_literal(int k, const mo_node* T, uint32_t n, const float* P, const float* Q,

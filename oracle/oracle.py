@@ -91,6 +91,13 @@ def lr_schedule(alpha, decay, epochs):
     return out
 
 
+def init_normal(count, seed, sid):
+    """Host twin of the engine's seeded factor initialisation (stream 1: users, 2: items)."""
+    out = np.empty(int(count), np.float32)
+    lib().mo_init_normal(_p(out), C.c_uint64(int(count)), C.c_uint64(int(seed)), C.c_uint64(int(sid)))
+    return out
+
+
 def is_check_epoch(e, epochs, interval):
     return bool(lib().mo_is_check_epoch(C.c_int(e), C.c_int(epochs), C.c_int(interval)))
 

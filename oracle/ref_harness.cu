@@ -6,6 +6,9 @@
 // statistics.  The cuRAND state is seeded with a fixed value and a probe kernel records the
 // chunk start positions the training kernel will draw, so a CPU replay can follow exactly the
 // same sequence of updates.  The outputs become golden vectors for the CPU oracle.
+// Cases of kind 8 run the reference's m-quantization set-up instead (degree histogram and sort,
+// grouping, index maps, remapped ratings, scatter of the factors into the per-group binary16
+// arenas) through the reference's own host functions and dump every table they produce.
 //
 // usage: ref_harness <harness_in.bin> <harness_out.bin>
 #include <cstdio>
@@ -21,8 +24,13 @@
 #include <cuda_fp16.h>
 #include <curand_kernel.h>
 
+#include <thrust/device_ptr.h>
+#include <thrust/sort.h>
+
 #include "common.h"
 #include "common_struct.h"
+#include "preprocess_utils.h"
+#include "model_init.h"
 #include "reduce_kernel.h"
 #include "sgd_kernel.h"
 #include "sgd_kernel_k64.h"
@@ -109,6 +117,63 @@ template <typename T> static T* to_dev(const T* h, size_t n) {
     return d;
 }
 
+
+// kind 8: the reference's set-up pipeline of mascot_training_mf (mf_methods.cu:41-90) on a small
+// seeded rating set: user_item_rating_histogram, split_group_based_equal_size_not_strict_ret_end_idx,
+// matrix_reconstruction (preprocess_utils.h:54-255) and cpy2grouped_parameters_gpu_for_comparison_indexing
+// (model_init.cu:175-222), called as they are.
+static void run_setup_case(const Bundle& in, Bundle& out, const std::string& name) {
+    const int* meta = get<int>(in, name + ".meta");
+    const int k = meta[1], n_users = meta[2], n_items = meta[3], nnz = meta[4], n_test = meta[5];
+    const int ug_req = meta[6], ig_req = meta[7];
+    const Node* R = (const Node*)get<uint32_t>(in, name + ".R");
+    const Node* T = (const Node*)get<uint32_t>(in, name + ".T");
+    const float* P = get<float>(in, name + ".P");
+    const float* Q = get<float>(in, name + ".Q");
+    Mf_info mf;
+    SGD sgd;
+    mf.max_user = n_users; mf.max_item = n_items; mf.n = nnz; mf.test_n = n_test;
+    mf.params.k = k; mf.params.user_group_num = ug_req; mf.params.item_group_num = ig_req;
+    mf.d_R = to_dev(R, nnz);
+    mf.d_test_COO = to_dev(T, n_test);
+    user_item_rating_histogram(&mf);
+    put(out, name + ".user2cnt", 1, mf.user2cnt, n_users); put(out, name + ".item2cnt", 1, mf.item2cnt, n_items);
+    put(out, name + ".user2idx", 1, mf.user2idx, n_users); put(out, name + ".item2idx", 1, mf.item2idx, n_items);
+    split_group_based_equal_size_not_strict_ret_end_idx(&mf);
+    std::cout << std::endl;
+    const unsigned ug = mf.params.user_group_num, ig = mf.params.item_group_num;
+    put(out, name + ".uend", 1, mf.user_group_end_idx, ug); put(out, name + ".iend", 1, mf.item_group_end_idx, ig);
+    put(out, name + ".user_group_idx", 1, mf.user_group_idx, n_users); put(out, name + ".item_group_idx", 1, mf.item_group_idx, n_items);
+    matrix_reconstruction(&mf);
+    put(out, name + ".user2sorted", 1, mf.user2sorted_idx, n_users); put(out, name + ".item2sorted", 1, mf.item2sorted_idx, n_items);
+    put(out, name + ".user_group_size", 1, mf.user_group_size, ug); put(out, name + ".item_group_size", 1, mf.item_group_size, ig);
+    std::vector<Node> Rm(nnz), Tm(n_test);
+    CK(cudaMemcpy(Rm.data(), mf.d_R, sizeof(Node) * nnz, cudaMemcpyDeviceToHost));
+    if (n_test) CK(cudaMemcpy(Tm.data(), mf.d_test_COO, sizeof(Node) * n_test, cudaMemcpyDeviceToHost));
+    put(out, name + ".R_sorted_ids", 1, Rm.data(), (uint64_t)nnz * 3); put(out, name + ".T_sorted_ids", 1, Tm.data(), (uint64_t)n_test * 3);
+    // scatter into the per-group binary16 arenas (mf_methods.cu:80-90 allocates the pointer tables)
+    sgd.d_p = to_dev(P, (size_t)n_users * k); sgd.d_q = to_dev(Q, (size_t)n_items * k);
+    CK(cudaMallocHost(&sgd.user_group_d_ptr, sizeof(void*) * ug)); CK(cudaMallocHost(&sgd.item_group_d_ptr, sizeof(void*) * ig));
+    CK(cudaMallocHost(&sgd.user_group_ptr, sizeof(void*) * ug)); CK(cudaMallocHost(&sgd.item_group_ptr, sizeof(void*) * ig));
+    CK(cudaMalloc(&sgd.d_user_group_ptr, sizeof(void*) * ug)); CK(cudaMalloc(&sgd.d_item_group_ptr, sizeof(void*) * ig));
+    cpy2grouped_parameters_gpu_for_comparison_indexing(&mf, &sgd);
+    auto fetch = [&](void** dptr, const unsigned int* size, unsigned groups, size_t rows, const std::string& key) {
+        std::vector<float> all(rows * k);
+        size_t row0 = 0;
+        for (unsigned g = 0; g < groups; g++) {
+            const size_t cnt = (size_t)size[g] * k;
+            std::vector<__half> h(cnt);
+            if (cnt) CK(cudaMemcpy(h.data(), dptr[g], sizeof(__half) * cnt, cudaMemcpyDeviceToHost));
+            for (size_t j = 0; j < cnt; j++) all[row0 * k + j] = __half2float(h[j]);
+            row0 += size[g];
+        }
+        put(out, name + key, 0, all.data(), rows * k);
+    };
+    fetch(sgd.user_group_d_ptr, mf.user_group_size, ug, n_users, ".P_arena");
+    fetch(sgd.item_group_d_ptr, mf.item_group_size, ig, n_items, ".Q_arena");
+    printf("case %-22s set-up: users %d items %d nnz %d groups %u/%u\n", name.c_str(), n_users, n_items, nnz, ug, ig);
+}
+
 int main(int argc, char** argv) {
     if (argc < 3) { fprintf(stderr, "usage: %s in.bin out.bin\n", argv[0]); return 2; }
     Bundle in = read_bundle(argv[1]);
@@ -126,6 +191,7 @@ int main(int argc, char** argv) {
 
     for (auto& name : cases) {
         const int* meta = get<int>(in, name + ".meta");
+        if (meta[0] == 8) { run_setup_case(in, out, name); continue; }
         const float* hyper = get<float>(in, name + ".hyper");
         int kind = meta[0], k = meta[1], n_users = meta[2], n_items = meta[3], nnz = meta[4];
         int update_count = meta[5], vec = meta[6], first_sample = meta[7], seed = meta[8], extra0 = meta[9];

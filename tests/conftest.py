@@ -47,3 +47,11 @@ def golden():
     from bundle import read_bundle
     gdir = os.path.join(ROOT, "tests", "golden")
     return read_bundle(os.path.join(gdir, "harness_in.bin")), read_bundle(os.path.join(gdir, "harness_out.bin"))
+
+
+@pytest.fixture(scope="session")
+def setup_golden():
+    """Inputs and outputs of the reference's m-quantization set-up functions (oracle/ref_harness.cu, kind 8)."""
+    from bundle import read_bundle
+    gdir = os.path.join(ROOT, "tests", "golden")
+    return read_bundle(os.path.join(gdir, "setup_in.bin")), read_bundle(os.path.join(gdir, "setup_out.bin"))

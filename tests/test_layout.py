@@ -63,3 +63,23 @@ def test_seeded_permutation_is_a_bijection(layout_check, n, seed):
         assert (v != np.arange(n)).mean() > 0.9, "not the identity"
         other = subprocess.run([layout_check, "p", str(n), str(seed + 1)], capture_output=True, text=True, check=True).stdout.split()
         assert (v != np.array([int(x) for x in other])).mean() > 0.9, "depends on the seed"
+
+
+def test_launch_cache_raises_the_shared_memory_limit_once_and_never_lowers_it(tmp_path):
+    """csrc/launch_cache.h: a full-grid launch, then a single-block launch that needs little shared
+    memory, then the full-grid shape again (the order that used to lose the opt-in): the limit is set
+    once per device, to the kernel's largest request, and the occupancy answer is asked once per shape."""
+    exe = str(tmp_path / "launch_cache_check")
+    subprocess.check_call(["g++", "-O1", "-std=c++17", "-I", CSRC, os.path.join(ROOT, "tests", "launch_cache_check.cpp"), "-o", exe])
+    seq = ["0:224:50176", "0:32:7168", "0:224:50176", "1:224:50176", "0:32:7168"]
+    out = subprocess.run([exe, "57344", "0"] + seq, capture_output=True, text=True, check=True).stdout.strip().split("\n")
+    raises = [l for l in out if l.startswith("raise")]
+    assert raises == ["raise dev=0 bytes=57344", "raise dev=1 bytes=57344"]
+    queries = [l for l in out if l.startswith("query")]
+    assert queries == ["query dev=0 block=224 smem=50176", "query dev=0 block=32 smem=7168", "query dev=1 block=224 smem=50176"]
+    launches = [l for l in out if l.startswith("launch")]
+    assert len(launches) == 5 and all(" rc=0 " in l for l in launches)
+    assert launches[0].split("fit=")[1] == launches[2].split("fit=")[1]
+    # a failing raise is reported, and tried again by the next launch
+    out = subprocess.run([exe, "57344", "7", "0:224:50176", "0:224:50176"], capture_output=True, text=True, check=True).stdout
+    assert out.count("raise dev=0") == 2 and out.count("rc=7") == 2

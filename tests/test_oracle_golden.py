@@ -250,6 +250,45 @@ def test_degree_sort_and_grouping(oracle, seed, n, req):
     assert (gof == np.searchsorted(end, np.arange(n), side="left")).all()
 
 
+SETUP_CASES = ["setup_tiny_k128", "setup_zipf_k64", "setup_unrated_k128", "setup_flat_k64", "setup_manygroups_k128"]
+
+
+@pytest.mark.parametrize("name", SETUP_CASES)
+def test_setup_matches_reference_setup_functions(oracle, setup_golden, name):
+    """Degree sort, grouping and index maps of the oracle against the tables the reference's own
+    user_item_rating_histogram / split_group_based_equal_size_not_strict_ret_end_idx /
+    matrix_reconstruction produced for the same ratings (tests/golden/setup_out.bin), including the
+    order of entities with equal degree, unrated entities and a single degree class."""
+    I, G = setup_golden
+    meta = I[name + ".meta"]
+    nu, ni, ug_req, ig_req = int(meta[2]), int(meta[3]), int(meta[6]), int(meta[7])
+    R = I[name + ".R"].reshape(-1, 3)
+    for side, col, n, req in (("user", 1, nu, ug_req), ("item", 2, ni, ig_req)):
+        s2o, o2s, cnt = oracle.degree_sort(R[:, col], n)
+        assert np.array_equal(cnt, G[f"{name}.{side}2cnt"]), "sorted degrees"
+        assert np.array_equal(s2o, G[f"{name}.{side}2idx"]), "sorted position -> id (ties in ascending id order)"
+        assert np.array_equal(o2s, G[f"{name}.{side}2sorted"]), "id -> sorted position"
+        end, gof = oracle.grouping(cnt, req)
+        assert np.array_equal(end, G[f"{name}.{'u' if side == 'user' else 'i'}end"]), "group end indices"
+        assert np.array_equal(gof[o2s], G[f"{name}.{side}_group_idx"]), "group of every id"
+        sizes = np.diff(np.concatenate([[-1], end.astype(np.int64)]))
+        assert np.array_equal(sizes, G[f"{name}.{side}_group_size"])
+    # the remapped rating arrays of matrix_reconst_gpu_triplet
+    _, u2s, _ = oracle.degree_sort(R[:, 1], nu)
+    _, i2s, _ = oracle.degree_sort(R[:, 2], ni)
+    for key, src in (("R_sorted_ids", R), ("T_sorted_ids", I[name + ".T"].reshape(-1, 3))):
+        want = G[f"{name}.{key}"].reshape(-1, 3)
+        assert np.array_equal(src[:, 0], want[:, 0])
+        assert np.array_equal(u2s[src[:, 1]], want[:, 1]) and np.array_equal(i2s[src[:, 2]], want[:, 2])
+    # the scattered binary16 arenas: row of id e at its sorted position, rounded to nearest even
+    k = int(meta[1])
+    for key, src, o2s_ in (("P_arena", I[name + ".P"].reshape(nu, k), u2s), ("Q_arena", I[name + ".Q"].reshape(ni, k), i2s)):
+        want = G[f"{name}.{key}"].reshape(-1, k)
+        got = np.empty_like(src)
+        got[o2s_] = oracle.h2f(oracle.f2h(src))
+        assert_bit_equal(got, want, key)
+
+
 def test_group_error_formula(oracle):
     rng = np.random.default_rng(9)
     k, groups = 64, 7
