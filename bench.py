@@ -1,23 +1,28 @@
 """Benchmark of the MASCOT training hot path: rating updates per second at k=128.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c4]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c4|c5|c1|c2|c3]
 
-A "step" is one training epoch = one pass of the update kernel over the whole rating stream of
-the workload (default: the 100M-rating configuration, 480,189 x 17,770, 100,480,507 ratings,
-MASCOT variant, k=128, with its g-switching check epochs).  Synthetic, seeded data.
+A "step" is one training epoch = one pass of the update kernels over the whole rating stream of the
+workload (default c4: 480,189 x 17,770, 100,480,507 ratings, MASCOT variant, k=128, with its g-switching
+check epochs; c5: 1,000,990 x 624,961, 252,800,275 ratings, the configuration whose factors exceed L2).
+Synthetic, seeded data with the shapes and distributions of the benchmark configurations.
 
-`value`  : updates/s with the rating stream resident in HBM, timed with CUDA events on the
-           engine's stream over exactly K epochs (update kernel + statistics + precision switching).
-`e2e`    : the same metric through the C ABI from HOST buffers: every step copies the step's
-           rating stream from pinned host memory to the device (mascot_reload_train), trains the
-           epoch and reads the test RMSE back.
-`--impl reference` times the CPU restatement of the reference's update rule (the reference itself
+`value`  : updates/s with the rating stream resident in HBM, timed with CUDA events on the engine's
+           stream over exactly K epochs (update kernels + statistics + precision switching).  The line
+           also gives the value of each precision phase (before / after the first promotion).
+`e2e`    : the same metric through the C ABI from HOST buffers: every step copies the step's rating
+           stream from pinned host memory to the device, trains the epoch and reads the test RMSE back.
+N > 1    : one process per GPU; the whole multi-GPU epoch (block schedule, NCCL hand-overs, statistics
+           all-reduce) runs inside libmascot (mascot_shard_*); torch.distributed only carries the 128-byte
+           group id and the barriers of the measurement.
+`--impl reference` times the host-core loop of the same update rule (oracle/host_loop.cpp; the reference
 is CUDA-only and has no CPU path) on all host cores, on a bounded sample of the same workload.
 """
 import argparse
 import importlib.util
 import json
 import os
+import re
 import statistics
 import subprocess
 import sys
@@ -106,8 +111,9 @@ class ClockSampler(threading.Thread):
 
 
 # The reference's own CUDA build (oracle/_ref/quantized_mf, sm_100) on the same synthetic data and one
-# B200, measured with oracle/run_reference_gpu.py; quoted beside the engine's numbers, not re-run here.
-REFERENCE_CUDA_BUILD = {
+# B200, measured earlier with oracle/run_reference_gpu.py at full size.  A FALLBACK, labelled as such:
+# the bench measures the build itself on a scaled copy of the workload when the binary is present.
+REFERENCE_CUDA_BUILD_EARLIER_RUNS = {
     "c1": {"updates_per_s": 2.90e9, "wg": 2048, "final_rmse": 1.03972, "epochs": 20},
     "c2": {"updates_per_s": 1.53e9, "wg": 2048, "final_rmse": 0.618434, "epochs": 50},
     "c3": {"updates_per_s": 2.55e9, "wg": 2304, "final_rmse": 0.638323, "epochs": 50},
@@ -125,6 +131,15 @@ def measured_peak():
     return 6650.0, "fallback"
 
 
+def host_threads():
+    """Cores this process may use.  torch.distributed.run exports OMP_NUM_THREADS=1, which says nothing
+    about the machine; the affinity mask does."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except Exception:
+        return max(1, os.cpu_count() or 1)
+
+
 def engine_config(M, cfg, **extra):
     hy = dict(cfg["hyper"])
     kw = dict(version=cfg["version"], k=cfg["k"], **hy)
@@ -132,244 +147,173 @@ def engine_config(M, cfg, **extra):
     return M.default_config(**kw)
 
 
-def run_reference(args, S, cfg):
-    """CPU arm: the oracle's Hogwild epoch (a port of the reference update rule; the reference has
-    no CPU implementation) on all host cores, each step over a bounded sample of the stream."""
+def traffic_table(workload):
+    """Per-update byte counts of the dominant kernel from the committed ncu summaries (profiles/)."""
+    path = os.path.join(ROOT, "profiles", "train_kernel_traffic.json")
+    try:
+        data = json.load(open(path))
+        return data.get(workload) if isinstance(data.get(workload), dict) else (data if data.get("workload") == workload else None)
+    except Exception:
+        return None
+
+
+# ---------------------------------------------------------------------------------------------
+# host-core baseline
+# ---------------------------------------------------------------------------------------------
+def host_loop_model(S, cfg, seed, n_sample):
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import oracle as O
-    threads = O.max_threads()
-    sample_n = min(cfg["n_train"], args.cpu_sample)
-    small = dict(cfg, n_train=sample_n, n_test=1000)
-    # same shapes and distributions; only the number of ratings per step is bounded
-    train, _ = S.generate(small, seed=args.seed)
+    small = dict(cfg, n_train=n_sample, n_test=1000)
+    train, _ = S.generate(small, seed=seed)          # same shapes and distributions; only the count is bounded
     k = cfg["k"]
-    rng = np.random.default_rng(args.seed)
+    rng = np.random.default_rng(seed)
     P = (rng.standard_normal((cfg["users"], k)) * 0.01).astype(np.float32)
     Q = (rng.standard_normal((cfg["items"], k)) * 0.01).astype(np.float32)
-    rules = O.rules_reference()
+    model = O.HostLoopModel(k, P, Q, half=(cfg["version"] == 1))
+    return O, model, train
+
+
+def run_reference(args, S, cfg):
+    """CPU arm: the host-core loop of the update rule (a port: the reference has no CPU implementation)
+    on all host cores, each step over a bounded sample of the stream."""
+    threads = host_threads()
+    sample_n = min(cfg["n_train"], 4_000_000)
+    O, model, train = host_loop_model(S, cfg, args.seed, sample_n)
     lrs = O.lr_schedule(cfg["hyper"]["learning_rate"], cfg["hyper"]["decay"], args.steps + args.warmup + 1)
     lam = cfg["hyper"]["lam"]
-    if cfg["version"] == 1:
-        model = O.MascotModel(k, P, Q, np.zeros(cfg["users"], np.uint32), np.zeros(cfg["items"], np.uint32),
-                              np.zeros(1, np.uint8), np.zeros(1, np.uint8))
-        step = lambda e: O.mascot_epoch_hogwild(model, train, float(lrs[e]), lam, threads, rules)
-    else:
-        step = lambda e: O.sgd_epoch_hogwild(k, train, P, Q, float(lrs[e]), lam, threads, rules)
     for e in range(args.warmup):
-        step(e)
+        model.epoch(train, float(lrs[e]), lam, threads)
     t0 = time.perf_counter()
     for e in range(args.steps):
-        step(args.warmup + e)
+        model.epoch(train, float(lrs[args.warmup + e]), lam, threads)
     dt = time.perf_counter() - t0
     value = sample_n * args.steps / dt
+    rule = "binary16 rows and arithmetic (MASCOT, no group promoted)" if cfg["version"] == 1 else "fp32 SGD"
     line = {
         "impl": "reference", "metric": "rating updates/sec (k=128)", "value": value, "unit": "updates/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16+f32", "data": "synthetic",
         "config": {"workload": args.workload_desc, "sample": f"{sample_n} ratings per step"},
         "cpu_baseline": {"value": value, "unit": "updates/s", "cores": threads, "kind": "port",
-                         "sample": f"first {sample_n} ratings of the workload per step, {threads} host threads, Hogwild"},
+                         "sample": f"first {sample_n} ratings of the workload per step, {threads} host threads, Hogwild, "
+                                   f"AVX2+F16C loop of the as-built rule: {rule}"},
         "e2e": {"value": value, "unit": "updates/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
 
 
-def cpu_baseline_sample(S, cfg, seed, budget_s=15.0):
+def cpu_baseline_sample(S, cfg, seed, budget_s=12.0):
     """Bounded CPU-baseline leg of the default run (rank 0, N=1)."""
-    sys.path.insert(0, os.path.join(ROOT, "oracle"))
-    import oracle as O
-    threads = O.max_threads()
-    k = cfg["k"]
+    threads = host_threads()
     n = 2_000_000
-    small = dict(cfg, n_train=n, n_test=1000)
-    train, _ = S.generate(small, seed=seed)
-    rng = np.random.default_rng(seed)
-    P = (rng.standard_normal((cfg["users"], k)) * 0.01).astype(np.float32)
-    Q = (rng.standard_normal((cfg["items"], k)) * 0.01).astype(np.float32)
-    rules = O.rules_reference()
+    O, model, train = host_loop_model(S, cfg, seed, n)
     lam, lr = cfg["hyper"]["lam"], cfg["hyper"]["learning_rate"]
-    if cfg["version"] == 1:
-        model = O.MascotModel(k, P, Q, np.zeros(cfg["users"], np.uint32), np.zeros(cfg["items"], np.uint32),
-                              np.zeros(1, np.uint8), np.zeros(1, np.uint8))
-        step = lambda: O.mascot_epoch_hogwild(model, train, lr, lam, threads, rules)
-    else:
-        step = lambda: O.sgd_epoch_hogwild(k, train, P, Q, lr, lam, threads, rules)
-    step()
+    model.epoch(train, lr, lam, threads)
     t0 = time.perf_counter()
     reps = 0
     while True:
-        step()
+        model.epoch(train, lr, lam, threads)
         reps += 1
-        if time.perf_counter() - t0 > budget_s or reps >= 20:
+        if time.perf_counter() - t0 > budget_s or reps >= 200:
             break
     dt = time.perf_counter() - t0
+    rule = "binary16 rows and arithmetic (MASCOT, no group promoted)" if cfg["version"] == 1 else "fp32 SGD"
     return {"value": n * reps / dt, "unit": "updates/s", "cores": threads, "kind": "port",
-            "sample": f"{reps} passes over the first {n} ratings of the workload, {threads} host threads, Hogwild"}
+            "sample": f"{reps} passes over the first {n} ratings of the workload, {threads} host threads, Hogwild, "
+                      f"AVX2+F16C loop of the as-built rule: {rule} (oracle/host_loop.cpp; the bit-exact oracle is ~25x slower)"}
 
 
-def sharded_e2e(args, MU, dist, shard, rank, world, dev, epoch, n_train):
-    """End to end at N GPUs: every step uploads each rank's ratings from pinned host memory again,
-    trains the epoch (all sub-epochs and hand-overs) and reads the global test RMSE back."""
+# ---------------------------------------------------------------------------------------------
+# the reference's CUDA build, measured here
+# ---------------------------------------------------------------------------------------------
+def reference_cuda_leg(S, M, cfg, workload, seed, scale=0.1, epochs=6):
+    """Times oracle/_ref/quantized_mf (the reference's own sources compiled for sm_100) on a scaled copy
+    of the workload, written as the TSV the reference reads.  Returns None when the binary is absent."""
+    exe = os.path.join(ROOT, "oracle", "_ref", "quantized_mf")
+    conv = os.path.join(PKG, "bin", "convert_ratings")
+    if not (os.path.exists(exe) and os.path.exists(conv)):
+        return None
+    import tempfile
+    sc = S.scaled(cfg, scale)
+    train_t, test_t = S.generate_cuda(sc, seed=seed)
+    tmp = tempfile.mkdtemp(prefix="mascot_ref_")
+    try:
+        tr_bin, te_bin = os.path.join(tmp, "train.bin"), os.path.join(tmp, "test.bin")
+        tr_txt, te_txt = os.path.join(tmp, "ratings_train.tsv"), os.path.join(tmp, "ratings_test.tsv")
+        M.write_binary_ratings(tr_bin, train_t.numpy().view(np.uint32).reshape(-1, 3), sc["users"], sc["items"])
+        M.write_binary_ratings(te_bin, test_t.numpy().view(np.uint32).reshape(-1, 3), sc["users"], sc["items"])
+        subprocess.check_call([conv, tr_bin, tr_txt, "tsv"]); subprocess.check_call([conv, te_bin, te_txt, "tsv"])
+        hy = cfg["hyper"]
+        wg = 2048
+        cmd = [exe, "-i", tr_txt, "-y", te_txt, "-k", str(cfg["k"]), "-l", str(epochs), "-a", str(hy["learning_rate"]), "-d", str(hy["decay"]),
+               "-b", str(hy["lam"]), "-wg", str(wg), "-bl", "128", "-v", str(cfg["version"]), "-ug", "50", "-ig", "50",
+               "-s", str(hy.get("sample_ratio", 0.01)), "-it", str(hy.get("interval", 1)), "-e", str(hy.get("error_threshold", 0.001))]
+        t0 = time.time()
+        p = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+        wall = time.time() - t0
+        m = re.search(r"(?:Parameters update per epoch|Execution time\(avg per epoch\))\s*:\s*([0-9.eE+]+)", p.stdout)
+        n = int(train_t.shape[0])
+        updates = wg * int(np.ceil(n / (wg * 128))) * 128
+        if p.returncode != 0 or not m:
+            return {"measured": False, "why": f"rc {p.returncode}: {p.stderr[-200:]}"}
+        us = float(m.group(1))
+        return {"measured": True, "updates_per_s": updates / (us * 1e-6), "kernel_us_per_epoch": us, "wg": wg, "epochs": epochs,
+                "workload": f"{workload} scaled by {scale}: {sc['users']}x{sc['items']}, {n} ratings (ug=ig=50)", "wall_s": wall}
+    finally:
+        import shutil
+        shutil.rmtree(tmp, ignore_errors=True)
+
+
+# ---------------------------------------------------------------------------------------------
+# shared pieces of both GPU arms
+# ---------------------------------------------------------------------------------------------
+def phase_report(n_train, steps):
+    """steps: list of (total_ms, kernel_ms, check flag, groups promoted in that epoch).  Splits the window
+    at the first promotion: before it every row is binary16, after it some groups are fp32."""
+    out, promoted_so_far = {}, False
+    phases = {"fp16": [], "promoted": []}
+    for total, kern, chk, prom in steps:
+        phases["promoted" if promoted_so_far else "fp16"].append((total, kern, chk))
+        if prom:
+            promoted_so_far = True
+    for name, rows in phases.items():
+        if not rows:
+            continue
+        plain = [k for _, k, c in rows if not c]
+        check = [k for _, k, c in rows if c]
+        out[name] = {"epochs": len(rows), "updates_per_s": n_train * len(rows) / (sum(t for t, _, _ in rows) * 1e-3),
+                     "plain_kernel_ms": statistics.median(plain) if plain else None,
+                     "check_kernel_ms": statistics.median(check) if check else None}
+    return out
+
+
+def time_to_rmse(rmse, cum_ms, targets):
+    out = {}
+    for t in targets:
+        hit = next((j for j, v in enumerate(rmse) if v <= t), None)
+        out[f"{t:.6g}"] = None if hit is None else {"epoch": hit + 1, "ms": round(cum_ms[hit], 2)}
+    return out
+
+
+def rmse_targets(workload):
+    ref = REFERENCE_CUDA_BUILD_EARLIER_RUNS.get(workload)
+    base = {"c4": [0.65, 0.62, 0.61], "c5": [1.40, 1.36, 1.34]}.get(workload, [])
+    return base + ([ref["final_rmse"]] if ref else [])
+
+
+def run_single(args, S, M, cfg, local_rank):
     import torch
-    host = torch.from_numpy(np.ascontiguousarray(shard.local_ratings).view(np.int32).reshape(-1, 3)).pin_memory()
-    e2e_steps = max(2, min(args.steps, 5))
-    dist.barrier(); shard.sync(); torch.cuda.synchronize()
-    t1 = time.perf_counter()
-    for _ in range(e2e_steps):
-        shard.engine.reload_train_raw(host.data_ptr(), shard.n_local)          # H2D of this step's inputs
-        MU.train_epoch(dist, shard, rank, world, epoch, comm_device=dev); epoch += 1
-        MU.gather_item_factors(dist, shard, world)
-        MU.global_rmse(dist, shard, world, comm_device=dev)                     # D2H of the step's result
-    shard.sync(); torch.cuda.synchronize()
-    te = torch.tensor([time.perf_counter() - t1], dtype=torch.float64, device=dev)
-    dist.all_reduce(te, op=dist.ReduceOp.MAX)
-    e2e_s = float(te.item())
-    return {"value": n_train * e2e_steps / e2e_s, "unit": "updates/s", "h2d_bytes_per_step": int(12 * n_train),
-            "d2h_bytes_per_step": int(16 * world), "steps": e2e_steps, "ms_per_step": 1e3 * e2e_s / e2e_steps,
-            "timing": "wall clock between barriers, max over ranks (the upload is a host call)"}
-
-
-def run_sharded(args, S, M, cfg, rank, world, local_rank):
-    """N > 1: one process per GPU, users pinned per rank, item blocks rotating (multi.py)."""
-    import torch
-    import torch.distributed as dist
-    MU = _load("mascot_multi", os.path.join(PKG, "multi.py"))
-    dev = torch.device("cuda", local_rank)
-    dist.init_process_group("nccl", device_id=dev)
-    train_t, test_t = S.generate_cuda(cfg, seed=args.seed, device=f"cuda:{local_rank}")     # same seed: same data on every rank
-    torch.cuda.synchronize(); torch.cuda.empty_cache()
-    train = train_t.numpy().view(np.uint32).reshape(-1, 3).view(M.RATING).reshape(-1)
-    test = test_t.numpy().view(np.uint32).reshape(-1, 3).view(M.RATING).reshape(-1)
-    n_train = int(train.size)
-    plan = MU.make_plan(train["u"], train["i"], cfg["users"], cfg["items"], world)
-    workers = args.workers if args.workers else MU.workers_per_rank(n_train, world)
-    ecfg = engine_config(M, cfg, device=local_rank, seed=args.seed, num_workers=workers)
-    shard = MU.EngineShard(M, ecfg, plan, rank, train, test, cfg["users"], cfg["items"])
-    shard.engine.init_factors()                        # same seed: identical factors on every rank
-    del train, test, train_t, test_t
-    epoch = 0
-    for _ in range(args.warmup):
-        MU.train_epoch(dist, shard, rank, world, epoch, comm_device=dev); epoch += 1
-    MU.gather_item_factors(dist, shard, world)
-    rmse_before = MU.global_rmse(dist, shard, world, comm_device=dev)
-    sampler = ClockSampler(list(range(world)))      # rank 0 watches every GPU of the job
-    if rank == 0:
-        sampler.start()
-    # device time: CUDA events on the engine's stream, which also orders the block transfers
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    dist.barrier(); shard.sync(); torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    ev0.record(shard.stream)
-    sent = 0
-    marks = []
-    for _ in range(args.steps):
-        chk = 1 if shard.is_check_epoch(epoch) else 0
-        b, _pr = MU.train_epoch(dist, shard, rank, world, epoch, comm_device=dev); epoch += 1
-        sent += b
-        ev = torch.cuda.Event(enable_timing=True); ev.record(shard.stream)
-        marks.append((ev, chk, int(_pr[0]) + int(_pr[1])))
-    ev1.record(shard.stream)
-    shard.sync(); torch.cuda.synchronize()
-    wall_ms = (time.perf_counter() - t0) * 1e3
-    mine_ms = ev0.elapsed_time(ev1)
-    per_step, prev = [], ev0
-    for ev, chk, promoted in marks:
-        per_step.append([round(prev.elapsed_time(ev), 3), chk, promoted]); prev = ev
-    dist.barrier()
-    t = torch.tensor([mine_ms], dtype=torch.float64, device=dev)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms = float(t.item())
-    loc = torch.tensor([float(shard.n_local)], dtype=torch.float64, device=dev)
-    mx = loc.clone(); dist.all_reduce(mx, op=dist.ReduceOp.MAX)
-    MU.gather_item_factors(dist, shard, world)
-    rmse_after = MU.global_rmse(dist, shard, world, comm_device=dev)
-    # ---- end to end: every step uploads each rank's ratings from pinned host memory again, trains the
-    # epoch (all sub-epochs and hand-overs) and reads the global test RMSE back ----
-    e2e = None
-    if not args.no_e2e:
-        e2e = sharded_e2e(args, MU, dist, shard, rank, world, dev, epoch, n_train)
-    sampler.stop_flag.set()
-    if rank == 0:
-        sampler.join(timeout=3)
-    if rank == 0:
-        peak, peak_kind = measured_peak()
-        value = n_train * args.steps / (total_ms * 1e-3)
-        achieved = value * 2 * cfg["k"] * 4 / 1e9            # all-fp16 rows: 2*k*(2+2) bytes per update
-        line = {
-            "metric": "rating updates/sec (k=128)", "value": value, "unit": "updates/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "f16+f32", "data": "synthetic",
-            "config": {"workload": args.workload_desc, "parallelism": f"users pinned on {world} GPUs, {world} interleaved item blocks rotating by NCCL send/recv",
-                       "l2": "inputs larger than L2", "rmse_before": rmse_before, "rmse_after": rmse_after,
-                       "item_blocks": "row r of the degree-sorted item index belongs to block r mod N", "max_ratings_on_one_rank": int(mx.item()),
-                       "nvlink_bytes_sent_per_rank_per_step": sent / max(args.steps, 1), "workers_per_gpu": workers, "rank0_ms_check_flag_promoted_groups_per_step": per_step,
-                       "timing": "CUDA events on the engine's stream around the K steps, max over ranks", "wall_ms_per_step_rank0": wall_ms / max(args.steps, 1)},
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak * world, "unit": "GB/s", "frac": achieved / (peak * world),
-                         "traffic": None, "peak_kind": f"of {peak_kind} (x{world} GPUs)"},
-            "clocks": sampler.summary(), "gpu_launches": args.steps * world * world, "e2e": e2e,
-        }
-        print(json.dumps(line), flush=True)
-    shard.close()
-    dist.destroy_process_group()
-    return 0
-
-
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c4")
-    ap.add_argument("--scale", type=float, default=1.0, help="shrink the workload (debugging only)")
-    ap.add_argument("--seed", type=int, default=4)
-    ap.add_argument("--cpu-sample", type=int, default=4_000_000)
-    ap.add_argument("--item-zipf", type=float, default=None, help="experiment knob: override the item popularity exponent")
-    ap.add_argument("--workers", type=int, default=0, help="concurrent sequential workers (-wg); 0 = the engine's automatic choice")
-    ap.add_argument("--sample-ratio", type=float, default=None, help="experiment knob: override -s")
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-e2e", action="store_true")
-    args = ap.parse_args()
-    args.warmup = max(args.warmup, 0)
-
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-
-    S = _load("mascot_synth", os.path.join(PKG, "synth.py"))
-    cfg = S.CONFIGS[args.workload]
-    if args.scale != 1.0:
-        cfg = S.scaled(cfg, args.scale)
-    if args.item_zipf is not None:
-        cfg = dict(cfg, item_deg=("zipf", args.item_zipf))
-    args.workload_desc = (f"{args.workload}: MASCOT -v {cfg['version']} k={cfg['k']}, {cfg['users']}x{cfg['items']}, "
-                          f"{cfg['n_train']} train ratings, ug=ig=100 s=0.05 it=2 e=20")
-
-    if args.impl == "reference":
-        if rank == 0:
-            run_reference(args, S, cfg)
-        return 0
-
-    import torch
-    M = _load("mascot_binding", os.path.join(PKG, "mascot.py"))
-    M.load()   # fails loudly when the CUDA library is missing
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: libmascot has no CPU path")
-    torch.cuda.set_device(local_rank)
-    if world > 1:
-        return run_sharded(args, S, M, cfg, rank, world, local_rank)
     train_t, test_t = S.generate_cuda(cfg, seed=args.seed, device=f"cuda:{local_rank}")
     torch.cuda.synchronize()
     torch.cuda.empty_cache()
     n_train, n_test = train_t.shape[0], test_t.shape[0]
-
     extra = {"num_workers": args.workers} if args.workers else {}
-    if args.sample_ratio is not None:
-        extra["sample_ratio"] = args.sample_ratio
     ecfg = engine_config(M, cfg, device=local_rank, seed=args.seed, **extra)
     eng = M.Engine(ecfg)
+    t_setup = time.perf_counter()
     eng.set_ratings_raw(train_t.data_ptr(), n_train, test_t.data_ptr(), n_test, cfg["users"], cfg["items"])
+    setup_ms = (time.perf_counter() - t_setup) * 1e3
     eng.init_factors()
 
     sampler = ClockSampler(local_rank)
@@ -386,8 +330,8 @@ def main():
     dev_ms = kern_ms = 0.0
     launches = 0
     alg_bytes = 0
-    checks = 0
-    per_epoch = []
+    steps = []
+    st = None
     for _ in range(args.steps):
         st = eng.train_epoch(epoch)
         epoch += 1
@@ -395,21 +339,18 @@ def main():
         kern_ms += st.kernel_ms
         launches += st.kernel_launches
         alg_bytes += st.algorithmic_bytes
-        checks += st.error_check
-        per_epoch.append((round(st.kernel_ms, 2), int(st.error_check)))
+        steps.append((st.total_ms, st.kernel_ms, int(st.error_check), int(st.promoted_user_groups + st.promoted_item_groups)))
     torch.cuda.synchronize()
     wall_ms = (time.perf_counter() - t0) * 1e3
     rmse_after = eng.eval_rmse()
-    updates = n_train * args.steps
-    value = updates / (dev_ms * 1e-3)
+    value = n_train * args.steps / (dev_ms * 1e-3)
+    phases = phase_report(n_train, steps)
 
     # ---- timed region 2: end to end from host buffers ----
     e2e = None
     if not args.no_e2e:
-        for _ in range(1):
-            eng.reload_train_raw(train_t.data_ptr(), n_train)
-            eng.train_epoch(epoch); epoch += 1
-            eng.eval_rmse()
+        eng.train_epoch_streamed_raw(epoch, train_t.data_ptr(), n_train); epoch += 1      # untimed: allocates the staging buffers
+        eng.eval_rmse()
         torch.cuda.synchronize()
         t1 = time.perf_counter()
         e2e_steps = max(2, min(args.steps, 5))
@@ -424,43 +365,271 @@ def main():
                "ms_per_step": 1e3 * e2e_s / e2e_steps}
     sampler.stop_flag.set()
     sampler.join(timeout=3)
+    workers = int(st.workers) if st else 0
+    eng.close()
 
-    peak, peak_kind = measured_peak()
-    achieved = (alg_bytes / args.steps) / (kern_ms / args.steps * 1e-3) / 1e9
-    # DRAM bytes per launch from the committed ncu capture of this very workload (the figure is
-    # not transferable to other sizes: it depends on how much of the factors L2 holds)
-    traffic = None
-    tpath = os.path.join(ROOT, "profiles", "train_kernel_traffic.json")
-    if os.path.exists(tpath) and args.workload == "c4" and args.scale == 1.0:
+    # ---- time to a target RMSE: a fresh run of the configured number of epochs, test RMSE after each ----
+    convergence = None
+    if not args.no_convergence:
+        eng2 = M.Engine(ecfg)
+        eng2.set_ratings_raw(train_t.data_ptr(), n_train, test_t.data_ptr(), n_test, cfg["users"], cfg["items"])
+        eng2.init_factors()
+        rm, cum, acc = [], [], 0.0
+        for e in range(int(cfg["hyper"]["epoch"])):
+            s2 = eng2.train_epoch(e)
+            acc += s2.total_ms
+            rm.append(eng2.eval_rmse()); cum.append(acc)
+        eng2.close()
+        convergence = {"epochs": len(rm), "final_rmse": rm[-1], "train_ms_total": acc,
+                       "updates_per_s_whole_run": n_train * len(rm) / (acc * 1e-3),
+                       "time_to_rmse": time_to_rmse(rm, cum, rmse_targets(args.workload)),
+                       "rmse_every_5_epochs": [round(v, 5) for v in rm[4::5]]}
+
+    # ---- roofline of the dominant kernel (the all-binary16 update kernel of a plain epoch) ----
+    hbm_peak, peak_kind = measured_peak()
+    fp16 = phases.get("fp16") or phases.get("promoted")
+    plain_ms = fp16["plain_kernel_ms"] or (kern_ms / args.steps)
+    bytes_per_update_alg = 2 * cfg["k"] * 4 if cfg["version"] in (1, 7, 8) else 2 * cfg["k"] * 8
+    alg_gbs = bytes_per_update_alg * n_train / (plain_ms * 1e-3) / 1e9
+    tt = traffic_table(args.workload) if args.scale == 1.0 else None
+    dram_per_launch = tt["dram_bytes_per_update"] * n_train if tt and tt.get("dram_bytes_per_update") else None
+    factor_bytes = (cfg["users"] + cfg["items"]) * cfg["k"] * 2
+    if factor_bytes < 126e6:
+        # factors fit in L2: the kernel's traffic is L2 <-> SM traffic, judged against a measured L2 read bandwidth
+        l2_peak = M.probe_read_bandwidth(32 << 20, passes=40, device=local_rank)
+        l2_per_update = tt["l2_bytes_per_update"] if tt and tt.get("l2_bytes_per_update") else None
+        achieved = (l2_per_update * n_train / (plain_ms * 1e-3) / 1e9) if l2_per_update else alg_gbs
+        roofline = {"bound": "l2", "achieved": achieved, "peak": l2_peak, "unit": "GB/s", "frac": achieved / l2_peak,
+                    "traffic": dram_per_launch,
+                    "peak_kind": "measured in this run: 128-bit L2-only loads over a 32 MiB L2-resident buffer (mascot_probe_read_bandwidth)",
+                    "achieved_kind": ("L2<->SM bytes per update from the committed ncu capture x updates / event-timed plain-epoch kernel"
+                                      if l2_per_update else "algorithmic bytes (no ncu figure for this workload)"),
+                    "frac_hbm": (dram_per_launch / (plain_ms * 1e-3) / 1e9 / hbm_peak) if dram_per_launch else None,
+                    "hbm_peak": hbm_peak, "hbm_peak_kind": f"of {peak_kind}",
+                    "algorithmic_gbs": alg_gbs, "algorithmic_bytes_per_update": bytes_per_update_alg,
+                    "note": "factors are L2-resident on this workload (item side entirely, user side mostly): the kernel is bound by "
+                            "L2 traffic and issue slots, not by HBM; algorithmic bytes / HBM peak is not a roofline here and is not reported as frac"}
+    else:
+        roofline = {"bound": "hbm", "achieved": alg_gbs, "peak": hbm_peak, "unit": "GB/s", "frac": alg_gbs / hbm_peak,
+                    "traffic": dram_per_launch, "peak_kind": f"of {peak_kind}",
+                    "frac_dram_traffic": (dram_per_launch / (plain_ms * 1e-3) / 1e9 / hbm_peak) if dram_per_launch else None,
+                    "algorithmic_bytes_per_update": bytes_per_update_alg,
+                    "note": "achieved = algorithmic row bytes 2*k*(b_user+b_item) per update x updates / event-timed plain-epoch kernel; "
+                            "factors exceed L2 on this workload"}
+
+    ref_cuda = None
+    if not args.no_reference_cuda and args.scale == 1.0:
         try:
-            traffic = json.load(open(tpath))["dram_bytes_per_update"] * n_train
-        except Exception:
-            traffic = None
+            ref_cuda = reference_cuda_leg(S, M, cfg, args.workload, args.seed)
+        except Exception as ex:      # the leg is a courtesy measurement: never lose the bench line over it
+            ref_cuda = {"measured": False, "why": repr(ex)[:200]}
+    if not ref_cuda or not ref_cuda.get("measured"):
+        earlier = REFERENCE_CUDA_BUILD_EARLIER_RUNS.get(args.workload)
+        ref_cuda = dict(ref_cuda or {}, measured=False, fallback_from_an_earlier_full_size_run=earlier)
+
     line = {
         "metric": "rating updates/sec (k=128)", "value": value, "unit": "updates/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f16+f32", "data": "synthetic",
-        "config": {"workload": args.workload_desc, "l2": "inputs larger than L2 (1.2 GB rating stream + 123 MB user factors per epoch)",
-                   "check_epochs_in_timed_region": checks, "kernel_ms_per_step": kern_ms / args.steps,
-                   "wall_ms_per_step": wall_ms / args.steps, "rmse_before": rmse_before, "rmse_after": rmse_after,
-                   "kernel_ms_and_check_flag_per_step": per_epoch, "workers": int(st.workers),
-                   "reference_cuda_build": REFERENCE_CUDA_BUILD.get(args.workload) if args.scale == 1.0 else None},
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": traffic, "peak_kind": f"of {peak_kind}",
-                     "algorithmic_bytes_per_launch": alg_bytes / args.steps,
-                     "note": "achieved = algorithmic row bytes 2*k*(b_user+b_item) per update / kernel time; the 126 MB L2 "
-                             "serves most of them (item factors resident, user rows reused), so frac can exceed 1; "
-                             "traffic = DRAM bytes per launch from ncu"},
+        "config": {"workload": args.workload_desc, "l2": "inputs larger than L2 (rating stream read once per epoch)",
+                   "phases": phases, "kernel_ms_per_step": kern_ms / args.steps, "wall_ms_per_step": wall_ms / args.steps,
+                   "rmse_before": rmse_before, "rmse_after": rmse_after, "workers": workers, "setup_ms": setup_ms,
+                   "total_ms_kernel_ms_check_promoted_per_step": [[round(a, 2), round(b, 2), c, d] for a, b, c, d in steps],
+                   "convergence": convergence, "reference_cuda_build": ref_cuda},
+        "roofline": roofline,
         "clocks": sampler.summary(),
         "gpu_launches": launches,
     }
     if e2e:
         line["e2e"] = e2e
-    if not args.no_cpu_baseline and rank == 0:
+    if not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline_sample(S, cfg, args.seed)
-    eng.close()
     print(json.dumps(line), flush=True)
     return 0
+
+
+def run_sharded(args, S, M, cfg, rank, world, local_rank):
+    """N > 1: one process per GPU; users pinned per rank, item blocks travelling (libmascot, csrc/shard.cu)."""
+    import torch
+    import torch.distributed as dist
+    dev = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", device_id=dev)
+    # the group id of libmascot's own communicator: made by rank 0, carried by the launcher's process group
+    idt = torch.zeros(M.COMM_ID_BYTES, dtype=torch.uint8, device=dev)
+    if rank == 0:
+        idt.copy_(torch.frombuffer(bytearray(M.comm_unique_id()), dtype=torch.uint8))
+    dist.broadcast(idt, src=0)
+    comm_id = bytes(idt.cpu().numpy().tobytes())
+    train_t, test_t = S.generate_cuda(cfg, seed=args.seed, device=f"cuda:{local_rank}")     # same seed: same data on every rank
+    torch.cuda.synchronize(); torch.cuda.empty_cache()
+    n_train, n_test = int(train_t.shape[0]), int(test_t.shape[0])
+    extra = {"num_workers": args.workers} if args.workers else {}
+    ecfg = engine_config(M, cfg, device=local_rank, seed=args.seed, **extra)
+    eng = M.Engine(ecfg)
+    eng.shard_init(comm_id, rank, world, args.blocks_per_gpu, timeout_ms=120000)
+    t_setup = time.perf_counter()
+    eng.shard_set_ratings_raw(train_t.data_ptr(), n_train, test_t.data_ptr(), n_test, cfg["users"], cfg["items"])
+    setup_ms = (time.perf_counter() - t_setup) * 1e3
+    eng.init_factors()                                 # same seed: identical factors on every rank
+    n_local = eng.n_train
+    # this rank's own ratings as a pinned host array, for the end-to-end leg (positions in the whole array)
+    local_host = None
+    if not args.no_e2e:
+        order = torch.from_numpy(eng.stream_order().astype(np.int64))
+        local_host = torch.empty(n_local, 3, dtype=torch.int32).pin_memory()
+        torch.index_select(train_t, 0, order, out=local_host)
+    epoch = 0
+    for _ in range(args.warmup):
+        eng.shard_train_epoch(epoch); epoch += 1
+    rmse_before = eng.shard_eval_rmse()
+    sampler = ClockSampler(list(range(world)))      # rank 0 watches every GPU of the job
+    if rank == 0:
+        sampler.start()
+    dist.barrier(); torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    steps, launches, st = [], 0, None
+    for _ in range(args.steps):
+        st = eng.shard_train_epoch(epoch); epoch += 1
+        launches += st.kernel_launches
+        steps.append((st.total_ms, st.kernel_ms, int(st.error_check), int(st.promoted_user_groups + st.promoted_item_groups)))
+    torch.cuda.synchronize()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    mine_ms = sum(s[0] for s in steps)              # CUDA events on the engine's stream, per epoch
+    t = torch.tensor([mine_ms, float(launches)], dtype=torch.float64, device=dev)
+    mx = t.clone(); dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+    sm = t.clone(); dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+    total_ms, all_launches = float(mx[0].item()), int(sm[1].item())
+    loc = torch.tensor([float(n_local)], dtype=torch.float64, device=dev); dist.all_reduce(loc, op=dist.ReduceOp.MAX)
+    rmse_after = eng.shard_eval_rmse()
+    sent = eng.shard_info()["bytes_sent"]
+
+    # ---- end to end: every step each rank uploads its own ratings from pinned host memory again, trains
+    # the epoch (all steps and hand-overs) and reads the global test RMSE back ----
+    e2e = None
+    if not args.no_e2e:
+        eng.reload_train_raw(local_host.data_ptr(), n_local)
+        eng.shard_train_epoch(epoch); epoch += 1
+        eng.shard_eval_rmse()
+        e2e_steps = max(2, min(args.steps, 5))
+        dist.barrier(); torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        for _ in range(e2e_steps):
+            eng.reload_train_raw(local_host.data_ptr(), n_local)          # H2D of this step's inputs
+            eng.shard_train_epoch(epoch); epoch += 1
+            eng.shard_eval_rmse()                                          # D2H of the step's result
+        torch.cuda.synchronize()
+        te = torch.tensor([time.perf_counter() - t1], dtype=torch.float64, device=dev)
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        e2e_s = float(te.item())
+        e2e = {"value": n_train * e2e_steps / e2e_s, "unit": "updates/s", "h2d_bytes_per_step": int(12 * n_train),
+               "d2h_bytes_per_step": int(16 * world + 4 * ((n_test + 511) // 512)), "steps": e2e_steps, "ms_per_step": 1e3 * e2e_s / e2e_steps,
+               "timing": "wall clock between barriers, max over ranks (the upload is a host call)"}
+
+    # ---- time to a target RMSE: fresh factors, the configured number of epochs, global RMSE after each ----
+    convergence = None
+    if not args.no_convergence:
+        eng.close()
+        eng = M.Engine(ecfg)
+        idt2 = torch.zeros(M.COMM_ID_BYTES, dtype=torch.uint8, device=dev)
+        if rank == 0:
+            idt2.copy_(torch.frombuffer(bytearray(M.comm_unique_id()), dtype=torch.uint8))
+        dist.broadcast(idt2, src=0)
+        eng.shard_init(bytes(idt2.cpu().numpy().tobytes()), rank, world, args.blocks_per_gpu, timeout_ms=120000)
+        eng.shard_set_ratings_raw(train_t.data_ptr(), n_train, test_t.data_ptr(), n_test, cfg["users"], cfg["items"])
+        eng.init_factors()
+        rm, cum, acc = [], [], 0.0
+        for e in range(int(cfg["hyper"]["epoch"])):
+            s2 = eng.shard_train_epoch(e)
+            acc += s2.total_ms
+            rm.append(eng.shard_eval_rmse()); cum.append(acc)
+        tc = torch.tensor(cum, dtype=torch.float64, device=dev); dist.all_reduce(tc, op=dist.ReduceOp.MAX)
+        cum = tc.cpu().tolist()
+        convergence = {"epochs": len(rm), "final_rmse": rm[-1], "train_ms_total": cum[-1],
+                       "updates_per_s_whole_run": n_train * len(rm) / (cum[-1] * 1e-3),
+                       "time_to_rmse": time_to_rmse(rm, cum, rmse_targets(args.workload)),
+                       "rmse_every_5_epochs": [round(v, 5) for v in rm[4::5]]}
+    sampler.stop_flag.set()
+    if rank == 0:
+        sampler.join(timeout=3)
+        hbm_peak, peak_kind = measured_peak()
+        value = n_train * args.steps / (total_ms * 1e-3)
+        bytes_per_update_alg = 2 * cfg["k"] * 4 if cfg["version"] in (1, 7, 8) else 2 * cfg["k"] * 8
+        achieved = value * bytes_per_update_alg / 1e9
+        factor_bytes = (cfg["users"] + cfg["items"]) * cfg["k"] * 2
+        phases = phase_report(n_train, steps)
+        line = {
+            "metric": "rating updates/sec (k=128)", "value": value, "unit": "updates/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16+f32", "data": "synthetic",
+            "config": {"workload": args.workload_desc,
+                       "parallelism": f"users pinned on {world} GPUs, {world * args.blocks_per_gpu} item blocks travelling by ncclSend/ncclRecv "
+                                      f"inside libmascot ({args.blocks_per_gpu} per GPU)",
+                       "l2": "inputs larger than L2", "rmse_before": rmse_before, "rmse_after": rmse_after,
+                       "item_blocks": "sorted item index s belongs to block s mod B; a block is one contiguous row range",
+                       "max_ratings_on_one_rank": int(loc.item()), "nvlink_bytes_sent_rank0_per_step": sent / max(args.steps + args.warmup, 1),
+                       "workers_per_gpu": int(st.workers) if st else 0, "setup_ms_rank0": setup_ms, "phases_rank0": phases,
+                       "rank0_total_ms_kernel_ms_check_promoted_per_step": [[round(a, 3), round(b, 3), c, d] for a, b, c, d in steps],
+                       "timing": "CUDA events on each engine's stream around every epoch, summed over the K steps, max over ranks",
+                       "wall_ms_per_step_rank0": wall_ms / max(args.steps, 1), "convergence": convergence},
+            "roofline": {"bound": "hbm" if factor_bytes >= 126e6 else "l2", "achieved": achieved, "peak": hbm_peak * world, "unit": "GB/s",
+                         "frac": achieved / (hbm_peak * world), "traffic": None, "peak_kind": f"HBM copy bandwidth of {peak_kind} (x{world} GPUs)",
+                         "note": "algorithmic row bytes of the whole job against the HBM peak of all GPUs; on workloads whose factors fit "
+                                 "L2 the single-GPU line carries the L2 figures"},
+            "clocks": sampler.summary(), "gpu_launches": all_launches, "e2e": e2e,
+        }
+        print(json.dumps(line), flush=True)
+    eng.close()
+    dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c4")
+    ap.add_argument("--scale", type=float, default=1.0,
+                    help="shrink the workload; used only by the ncu capture recipes in profiles/, which need a small case")
+    ap.add_argument("--seed", type=int, default=4)
+    ap.add_argument("--workers", type=int, default=0, help="concurrent sequential workers (-wg); 0 = the engine's automatic choice")
+    ap.add_argument("--blocks-per-gpu", type=int, default=1, choices=[1, 2],
+                    help="N > 1: item blocks per GPU (2 = hand-overs hidden under the update kernels)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-convergence", action="store_true", help="skip the time-to-RMSE run")
+    ap.add_argument("--no-reference-cuda", action="store_true", help="skip timing the reference's own CUDA build")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 0)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    S = _load("mascot_synth", os.path.join(PKG, "synth.py"))
+    cfg = S.CONFIGS[args.workload]
+    if args.scale != 1.0:
+        cfg = S.scaled(cfg, args.scale)
+    hy = cfg["hyper"]
+    args.workload_desc = (f"{args.workload}: -v {cfg['version']} k={cfg['k']}, {cfg['users']}x{cfg['items']}, {cfg['n_train']} train ratings"
+                          + (f", ug=ig={hy.get('user_group_num')} s={hy.get('sample_ratio')} it={hy.get('interval')} e={hy.get('error_threshold')}"
+                             if cfg["version"] == 1 else ""))
+
+    if args.impl == "reference":
+        if rank == 0:
+            run_reference(args, S, cfg)
+        return 0
+
+    import torch
+    M = _load("mascot_binding", os.path.join(PKG, "mascot.py"))
+    M.load()   # fails loudly when the CUDA library is missing
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: libmascot has no CPU path")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        return run_sharded(args, S, M, cfg, rank, world, local_rank)
+    return run_single(args, S, M, cfg, local_rank)
 
 
 if __name__ == "__main__":

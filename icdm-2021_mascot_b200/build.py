@@ -19,8 +19,8 @@ BIN = os.path.join(HERE, "bin")
 NVCC_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 
-LIB_SOURCES = ["mascot_api.cu", "train_kernels.cu", "eval_kernels.cu", "prep_kernels.cu"]
-CLI_SOURCES = {"quantized_mf": "quantized_mf.cpp", "test_mf": "test_mf.cpp"}
+LIB_SOURCES = ["mascot_api.cu", "setup.cu", "shard.cu", "train_kernels.cu", "eval_kernels.cu", "prep_kernels.cu", "probe.cu"]
+CLI_SOURCES = {"quantized_mf": "quantized_mf.cpp", "test_mf": "test_mf.cpp", "convert_ratings": "convert_ratings.cpp"}
 
 
 def _newer(target, deps):
@@ -49,7 +49,7 @@ def build_library(force=False, verbose=True, ptxas_verbose=False):
             cmd = ["nvcc"] + NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_verbose else []) + ["-c", s, "-o", o]
             _run(cmd, verbose)
         objs.append(o)
-    _run(["nvcc", "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB] + objs + ["-lcudart"], verbose)
+    _run(["nvcc", "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB] + objs + ["-lcudart", "-ldl"], verbose)
     return LIB
 
 
@@ -65,7 +65,7 @@ def build_cli(force=False, verbose=True):
                [os.path.join(CLI, f) for f in os.listdir(CLI) if f.endswith(".h")]
         if force or _newer(exe, deps) or _newer(exe, [LIB]):
             _run(["g++", "-O2", "-std=c++17", "-I", os.path.join(ROOT, "include"), s, "-o", exe,
-                  "-L", HERE, "-lmascot", "-Wl,-rpath," + HERE, "-Wl,-rpath,$ORIGIN/.."], verbose)
+                  "-L", HERE, "-lmascot", "-lpthread", "-Wl,-rpath," + HERE, "-Wl,-rpath,$ORIGIN/.."], verbose)
         out.append(exe)
     return out
 

@@ -17,7 +17,23 @@
 //   model  <out>_reconst.txt  "<n_users> <n_items> <k>\n", P then Q in sorted-index order
 //                             (io_utils.h:305-332)
 //   reconst_<testfile>        the test set in sorted-index space (io_utils.h:374-405)
+//
+// Binary formats beside them (no counterpart in the reference; recognised by their magic, so every
+// flag that takes a file accepts either kind):
+//   ratings  32-byte header {u32 magic "MSCR", u32 version 1, u64 n, u32 n_users, u32 n_items,
+//            u32 flags, u32 0} followed by n records {f32 r, u32 u, u32 i} - the Node of
+//            common_struct.h:8-12.  flags bit 0: ids are already compact (0..n_users-1, 0..n_items-1):
+//            the file is mapped into memory and handed to the library as it is, no pass over the
+//            ratings on the host.  Without the bit the ids are compacted in first-seen order like text.
+//   model    24-byte header {u32 magic "MSCM", u32 version 1, u32 rows_p, u32 rows_q, u32 k, u32 0}
+//            followed by rows_p*k then rows_q*k floats: the same rows in the same order as the text
+//            model of the same run (original-id rows with zero rows for absent ids, or sorted-index rows).
 #pragma once
+#include <fcntl.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
 #include <algorithm>
 #include <cerrno>
 #include <cstdio>
@@ -36,9 +52,52 @@
 
 namespace mascot_io {
 
+constexpr uint32_t kRatingMagic = 0x5243534du;   // "MSCR"
+constexpr uint32_t kModelMagic = 0x4d43534du;    // "MSCM"
+constexpr uint32_t kFlagCompactIds = 1u;
+
+struct RatingFileHeader { uint32_t magic, version; uint64_t n; uint32_t n_users, n_items, flags, reserved; };
+struct ModelFileHeader { uint32_t magic, version, rows_p, rows_q, k, reserved; };
+static_assert(sizeof(RatingFileHeader) == 32 && sizeof(ModelFileHeader) == 24, "file headers are packed");
+
+// A read-only memory mapping of a whole file.
+struct Mapping {
+    const unsigned char* data = nullptr;
+    size_t size = 0;
+    Mapping() = default;
+    Mapping(const Mapping&) = delete;
+    Mapping& operator=(const Mapping&) = delete;
+    ~Mapping() { if (data) munmap(const_cast<unsigned char*>(data), size); }
+    bool open(const std::string& path) {
+        const int fd = ::open(path.c_str(), O_RDONLY);
+        if (fd < 0) return false;
+        struct stat st;
+        if (fstat(fd, &st) != 0 || st.st_size <= 0) { ::close(fd); return false; }
+        void* p = mmap(nullptr, (size_t)st.st_size, PROT_READ, MAP_PRIVATE, fd, 0);
+        ::close(fd);
+        if (p == MAP_FAILED) return false;
+        data = static_cast<const unsigned char*>(p); size = (size_t)st.st_size;
+        return true;
+    }
+};
+
+inline bool has_magic(const std::string& path, uint32_t magic) {
+    FILE* f = std::fopen(path.c_str(), "rb");
+    if (!f) return false;
+    uint32_t m = 0;
+    const bool ok = std::fread(&m, 4, 1, f) == 1 && m == magic;
+    std::fclose(f);
+    return ok;
+}
+
 struct Dataset {
-    std::vector<mascot_rating> train, test;
-    std::vector<uint32_t> user_orig, item_orig;            // compact id -> original id
+    std::vector<mascot_rating> train, test;                // owned copies (text input, or binary input that needs compaction)
+    const mascot_rating* train_ptr = nullptr; uint64_t n_train = 0;   // what to hand to the library: the vectors above
+    const mascot_rating* test_ptr = nullptr; uint64_t n_test = 0;     // or a mapped binary file with compact ids
+    Mapping train_map, test_map;
+    bool identity_ids = false;                             // compact binary input: compact id == original id
+    uint32_t n_users = 0, n_items = 0;
+    std::vector<uint32_t> user_orig, item_orig;            // compact id -> original id (empty with identity_ids)
     std::unordered_map<uint32_t, uint32_t> user_map, item_map;   // original id -> compact id
     uint64_t missing = 0;                                  // test ratings dropped
 };
@@ -110,7 +169,43 @@ inline uint32_t compact(std::unordered_map<uint32_t, uint32_t>& map, std::vector
 }
 
 // read_training_dataset (io_utils.h:30-120)
+inline bool read_binary_ratings(const std::string& path, Mapping& map, RatingFileHeader& hdr, const mascot_rating** recs) {
+    if (!map.open(path) || map.size < sizeof(RatingFileHeader)) return false;
+    std::memcpy(&hdr, map.data, sizeof hdr);
+    if (hdr.magic != kRatingMagic || hdr.version != 1 || map.size < sizeof hdr + hdr.n * sizeof(mascot_rating)) return false;
+    *recs = reinterpret_cast<const mascot_rating*>(map.data + sizeof hdr);
+    return true;
+}
+
+inline bool write_binary_ratings(const std::string& path, const mascot_rating* recs, uint64_t n, uint32_t n_users, uint32_t n_items, uint32_t flags) {
+    FILE* f = std::fopen(path.c_str(), "wb");
+    if (!f) return false;
+    const RatingFileHeader hdr = {kRatingMagic, 1, n, n_users, n_items, flags, 0};
+    bool ok = std::fwrite(&hdr, sizeof hdr, 1, f) == 1;
+    if (ok && n) ok = std::fwrite(recs, sizeof(mascot_rating), n, f) == n;
+    return std::fclose(f) == 0 && ok;
+}
+
+inline void finish_training(Dataset& d) {
+    if (!d.train_ptr) { d.train_ptr = d.train.data(); d.n_train = d.train.size(); }
+    if (!d.identity_ids) { d.n_users = (uint32_t)d.user_orig.size(); d.n_items = (uint32_t)d.item_orig.size(); }
+}
+
 inline bool read_training(Dataset& d, const std::string& path) {
+    if (has_magic(path, kRatingMagic)) {
+        RatingFileHeader hdr; const mascot_rating* recs = nullptr;
+        if (!read_binary_ratings(path, d.train_map, hdr, &recs)) return false;
+        if (hdr.flags & kFlagCompactIds) {          // mapped and handed over as it is
+            d.identity_ids = true; d.n_users = hdr.n_users; d.n_items = hdr.n_items;
+            d.train_ptr = recs; d.n_train = hdr.n;
+        } else {
+            d.train.reserve(hdr.n);
+            for (uint64_t j = 0; j < hdr.n; j++)
+                d.train.push_back({recs[j].r, compact(d.user_map, d.user_orig, recs[j].u), compact(d.item_map, d.item_orig, recs[j].i)});
+        }
+        finish_training(d);
+        return true;
+    }
     std::string text;
     if (!read_whole(path, text)) return false;
     const bool yahoo = is_yahoo(path);
@@ -138,14 +233,39 @@ inline bool read_training(Dataset& d, const std::string& path) {
             d.train.push_back({tok_float(tb[2], te[2]), user_c, item_c});
         });
     }
+    finish_training(d);
     return true;
 }
 
 // read_test_dataset (io_utils.h:122-240).  The reference keeps the test set in a map per user, so a
 // repeated (user, item) pair keeps its last rating; the result is ordered by (user, item).
 inline bool read_test(Dataset& d, const std::string& path) {
+    d.test_ptr = nullptr; d.n_test = 0;
+    if (has_magic(path, kRatingMagic)) {
+        RatingFileHeader hdr; const mascot_rating* recs = nullptr;
+        if (!read_binary_ratings(path, d.test_map, hdr, &recs)) return false;
+        if ((hdr.flags & kFlagCompactIds) && d.identity_ids) {       // same id space as the training file by construction
+            d.test_ptr = recs; d.n_test = hdr.n;
+            return true;
+        }
+        for (uint64_t j = 0; j < hdr.n; j++) {
+            uint32_t u = recs[j].u, i = recs[j].i;
+            if (d.identity_ids) { if (u >= d.n_users || i >= d.n_items) { d.missing++; continue; } }
+            else {
+                auto iu = d.user_map.find(u); auto it = d.item_map.find(i);
+                if (iu == d.user_map.end() || it == d.item_map.end()) { d.missing++; continue; }
+                u = iu->second; i = it->second;
+            }
+            d.test.push_back({recs[j].r, u, i});
+        }
+        std::cout << "Missing the number of ratings : " << d.missing << std::endl;
+        d.test_ptr = d.test.data(); d.n_test = d.test.size();
+        return true;
+    }
     std::string text;
-    if (!read_whole(path, text)) return false;
+    // a missing test file (the default "None") is an empty test set, like the reference, whose ifstream
+    // simply yields no lines (io_utils.h:131-132)
+    if (!read_whole(path, text)) return true;
     const bool yahoo = is_yahoo(path);
     const int ui = item_first(path) ? 1 : 0, ii = item_first(path) ? 0 : 1;
     std::vector<uint32_t> remove_user, remove_item;
@@ -193,9 +313,10 @@ inline bool read_test(Dataset& d, const std::string& path) {
     for (int which = 0; which < 2; which++) {
         const std::string out = dir + (which == 0 ? "/remove_user.txt" : "/remove_item.txt");
         std::ofstream f(out.c_str(), std::ofstream::out);
-        if (f.fail()) { std::cout << "fail to write file named " << out << std::endl; return true; }
+        if (f.fail()) { std::cout << "fail to write file named " << out << std::endl; break; }
         for (uint32_t v : (which == 0 ? remove_user : remove_item)) f << v << std::endl;
     }
+    d.test_ptr = d.test.data(); d.n_test = d.test.size();
     return true;
 }
 
@@ -215,19 +336,46 @@ inline void write_rows_original_order(std::ofstream& f, const std::vector<uint32
     f << buf.str();
 }
 
+inline std::vector<uint32_t> orig_ids(const std::vector<uint32_t>& orig, uint32_t n, bool identity) {
+    if (!identity) return orig;
+    std::vector<uint32_t> v(n);
+    for (uint32_t e = 0; e < n; e++) v[e] = e;
+    return v;
+}
+
 // save_trained_model (io_utils.h:242-303)
 inline bool save_model(const std::string& outfile, const Dataset& d, const float* P, const float* Q, uint32_t k) {
     std::cout << "Save trained model..." << std::endl;
     const std::string path = outfile + ".txt";
     std::ofstream f(path.c_str());
     if (f.fail()) { std::cout << "fail to write file named " << path << std::endl; std::cerr << "Error: " << std::strerror(errno); return false; }
-    const uint32_t max_user = *std::max_element(d.user_orig.begin(), d.user_orig.end());
-    const uint32_t max_item = *std::max_element(d.item_orig.begin(), d.item_orig.end());
+    const std::vector<uint32_t> uo = orig_ids(d.user_orig, d.n_users, d.identity_ids), io = orig_ids(d.item_orig, d.n_items, d.identity_ids);
+    const uint32_t max_user = *std::max_element(uo.begin(), uo.end());
+    const uint32_t max_item = *std::max_element(io.begin(), io.end());
     f << max_user + 1 << " " << max_item + 1 << " " << k << std::endl;
-    write_rows_original_order(f, d.user_orig, P, k);
+    write_rows_original_order(f, uo, P, k);
     f << std::endl;
-    write_rows_original_order(f, d.item_orig, Q, k);
+    write_rows_original_order(f, io, Q, k);
     return true;
+}
+
+// The binary model beside the text one: same rows, same order (see the head of this file).
+inline bool save_model_binary(const std::string& path, uint32_t rows_p, uint32_t rows_q, const float* P, const float* Q, uint32_t k) {
+    FILE* f = std::fopen(path.c_str(), "wb");
+    if (!f) { std::cout << "fail to write file named " << path << std::endl; return false; }
+    const ModelFileHeader hdr = {kModelMagic, 1, rows_p, rows_q, k, 0};
+    bool ok = std::fwrite(&hdr, sizeof hdr, 1, f) == 1;
+    ok = ok && std::fwrite(P, sizeof(float), (size_t)rows_p * k, f) == (size_t)rows_p * k;
+    ok = ok && std::fwrite(Q, sizeof(float), (size_t)rows_q * k, f) == (size_t)rows_q * k;
+    return std::fclose(f) == 0 && ok;
+}
+
+// Original-id rows with zero rows for absent ids, as save_trained_model lays them out.
+inline void rows_in_original_order(const std::vector<uint32_t>& orig, const float* M, uint32_t k, std::vector<float>& out, uint32_t* rows) {
+    const uint32_t max_id = *std::max_element(orig.begin(), orig.end());
+    out.assign((size_t)(max_id + 1) * k, 0.f);
+    for (uint32_t c = 0; c < orig.size(); c++) std::memcpy(&out[(size_t)orig[c] * k], M + (size_t)c * k, sizeof(float) * k);
+    *rows = max_id + 1;
 }
 
 // save_trained_model_reconst (io_utils.h:305-332)
@@ -272,6 +420,18 @@ struct Model {
 
 // read_trained_model (io_utils.h:334-372): header tokens, then whitespace-separated floats
 inline bool read_model(const std::string& path, Model& m) {
+    if (has_magic(path, kModelMagic)) {
+        Mapping map;
+        ModelFileHeader hdr;
+        if (!map.open(path) || map.size < sizeof hdr) return false;
+        std::memcpy(&hdr, map.data, sizeof hdr);
+        const size_t np = (size_t)hdr.rows_p * hdr.k, nq = (size_t)hdr.rows_q * hdr.k;
+        if (hdr.version != 1 || map.size < sizeof hdr + (np + nq) * sizeof(float)) return false;
+        m.n_users = hdr.rows_p; m.n_items = hdr.rows_q; m.k = hdr.k;
+        const float* v = reinterpret_cast<const float*>(map.data + sizeof hdr);
+        m.P.assign(v, v + np); m.Q.assign(v + np, v + np + nq);
+        return true;
+    }
     std::string text;
     if (!read_whole(path, text)) return false;
     char* p = &text[0];
@@ -288,6 +448,12 @@ inline bool read_model(const std::string& path, Model& m) {
 
 // read_testset_pretrained_model (io_utils.h:407-456): ids are used as they stand in the file
 inline bool read_testset_raw(const std::string& path, std::vector<mascot_rating>& out) {
+    if (has_magic(path, kRatingMagic)) {
+        Mapping map; RatingFileHeader hdr; const mascot_rating* recs = nullptr;
+        if (!read_binary_ratings(path, map, hdr, &recs)) return false;
+        out.assign(recs, recs + hdr.n);
+        return true;
+    }
     std::string text;
     if (!read_whole(path, text)) return false;
     const int ui = item_first(path) ? 1 : 0, ii = item_first(path) ? 0 : 1;

@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 #include <cstdint>
 
+#include "layout.cuh"
+
 namespace mascot {
 
 // Structure-of-arrays rating stream.  u/i carry the row index in bits 0..30 and the storage
@@ -49,6 +51,13 @@ enum RowClass { ROWCLASS_HH = 0,   // binary16 user row, binary16 item row
                 ROWCLASS_FF = 3,   // both fp32
                 ROWCLASS_ANY = 4 };
 
+// Four 8-byte device counters (all zero when handed over) through which the update launches of one
+// stream hand out their chunks in turn, and the number of launches made so far.
+struct WorkCounters {
+    unsigned long long* d_slots = nullptr;
+    unsigned long long launches = 0;
+};
+
 struct LaunchShape {
     int grid = 0;
     int block = 0;
@@ -58,8 +67,8 @@ struct LaunchShape {
 
 // Update kernels.  `stats` == nullptr -> plain epoch.  `workers` = requested number of concurrent
 // sequential workers (1 = fully sequential); `row_class` tells the mixed-precision trainer which
-// precisions the ratings of this range combine (ignored by the other kinds); `work_counter` is 8 bytes of device
-// scratch the launch resets and uses to hand out chunks; `bits` is the width of MuPPET's forward and
+// precisions the ratings of this range combine (ignored by the other kinds); `counters` are the
+// engine's chunk counters (all launches that share them must be queued on one stream); `bits` is the width of MuPPET's forward and
 // backward pass (8, 12, 14, 16 or 32; ignored by the other kinds), `epoch` the epoch index (AFP
 // re-estimates its formats at every rating early in epoch 0).  With `add_user_delta` (ignored for a
 // single worker) user rows are written back as reductions of their change, so that concurrent
@@ -67,7 +76,7 @@ struct LaunchShape {
 // MuPPET statistics use gsum_p[0..K) (sum of the sampled updates, physical order) and nsum_p[0].
 cudaError_t launch_train(int K, TrainKind kind, const Stream& s, Arena P, Arena Q, float lr, float lam,
                          const SampleStats* stats, RowClass row_class, unsigned workers,
-                         unsigned long long* work_counter, int bits, int epoch, bool add_user_delta,
+                         WorkCounters* counters, int bits, int epoch, bool add_user_delta,
                          cudaStream_t st, LaunchShape* shape);
 
 // Folds the private statistic sets of a launch into set 0 (sets are added in index order).
@@ -80,9 +89,14 @@ cudaError_t launch_rmse_plain(int K, const void* d_test_aos, uint64_t n, const f
                               float* block_err, cudaStream_t st);
 
 // Set-up / conversion kernels.
+// Codes n ratings {r,u,i} into the stream arrays: optional seeded permutation + item-sorted windows, ids
+// mapped to arena rows (maps may be null: identity) and tagged with the row's storage flags.  Ids are
+// checked against n_users / n_items first; an id out of range raises *err_flag and is not used as an
+// index (the rating becomes a zero rating of row 0).  item_rows = rows of the item arena (sort key range).
 cudaError_t launch_encode_stream(const void* d_src_aos, uint64_t n, bool shuffle, uint64_t seed,
                                  const uint32_t* user_map, const uint32_t* item_map,
-                                 const uint8_t* uprec_row, const uint8_t* iprec_row, uint32_t n_items,
+                                 const uint8_t* uprec_row, const uint8_t* iprec_row, uint32_t n_users, uint32_t n_items,
+                                 uint32_t item_rows, uint32_t* err_flag,
                                  float* r, uint32_t* u, uint32_t* i, uint32_t* src_out, uint32_t src_base,
                                  cudaStream_t st);
 cudaError_t launch_recode(uint32_t* ids, uint64_t n, const uint8_t* prec_row, cudaStream_t st);
@@ -97,13 +111,14 @@ cudaError_t launch_partition_by_class(const float* r, const uint32_t* u, const u
                                       uint16_t* key_a, uint16_t* key_b, uint32_t* idx_a, uint32_t* idx_b,
                                       void* temp, size_t temp_bytes, unsigned long long* d_first,
                                       float* r2, uint32_t* u2, uint32_t* i2, uint32_t* src2, cudaStream_t st);
-// Sets the "stored in fp32" flag of n per-row bytes (the other flags stay).
-cudaError_t launch_mark_fp32(uint8_t* row_flags, uint32_t n, cudaStream_t st);
 cudaError_t launch_scatter_factors(int K, const float* src, uint32_t rows, const uint32_t* row_map,
                                    bool round_through_half, __half* dst16, float* dst32, cudaStream_t st);
 cudaError_t launch_gather_factors(int K, Arena a, const uint8_t* prec_row, uint32_t rows,
-                                  const uint32_t* row_map, float* dst, cudaStream_t st);
-cudaError_t launch_promote_rows(int K, Arena a, uint32_t row_begin, uint32_t row_end, cudaStream_t st);
+                                  const uint32_t* row_map, const RowLayout& layout, float* dst, cudaStream_t st);
+// Widens the rows of the sorted indices [sorted_begin, sorted_end) from the binary16 into the fp32 arena
+// and sets their "stored in fp32" flag.
+cudaError_t launch_promote_rows(int K, Arena a, uint8_t* row_flags, const RowLayout& layout, uint32_t sorted_begin, uint32_t sorted_end,
+                                cudaStream_t st);
 cudaError_t launch_init_normal(float* dst, uint64_t count, uint64_t seed, uint64_t stream_id, cudaStream_t st);
 
 // Number of SMs of the current device (cached per device).

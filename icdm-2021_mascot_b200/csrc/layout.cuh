@@ -87,4 +87,37 @@ constexpr uint32_t kIdMask = 0x3fffffffu;
 constexpr uint8_t kRowPrec = 1, kRowHot = 2;
 MASCOT_HD inline uint32_t row_flags_to_code(uint8_t b) { return ((b & kRowPrec) ? kPrecBit : 0u) | ((b & kRowHot) ? kHotBit : 0u); }
 
+// Where the row of sorted index s lives in an arena.
+//   parts <= 1          : row s (a single engine).
+//   parts > 1, !snake   : items of a sharded run - `parts` blocks, sorted index s belongs to block
+//                         s % parts and is row s / parts of that block, so every block holds the same mix
+//                         of popular and rare items and is one contiguous range of rows_per_part rows.
+//   parts > 1, snake    : users of a sharded run - dealt to `parts` ranks from the highest degree down,
+//                         reversing direction every round, so that the rating counts of the ranks stay
+//                         close for heavy-tailed degrees; rank p owns rows [p * rows_per_part, ...).
+// The last rows of a part stay unused when n is not a multiple of parts.
+struct RowLayout {
+    uint32_t parts = 1;
+    uint32_t rows_per_part = 0;
+    uint32_t n = 0;
+    uint32_t snake = 0;
+};
+MASCOT_HD inline uint32_t layout_rows(const RowLayout& L) { return L.parts <= 1 ? L.n : L.parts * L.rows_per_part; }
+MASCOT_HD inline uint32_t arena_row(const RowLayout& L, uint32_t s) {
+    if (L.parts <= 1) return s;
+    if (!L.snake) return (s % L.parts) * L.rows_per_part + s / L.parts;
+    const uint32_t pos = L.n - 1 - s, rnd = pos / L.parts, idx = pos % L.parts;
+    return ((rnd & 1) ? L.parts - 1 - idx : idx) * L.rows_per_part + rnd;
+}
+MASCOT_HD inline uint32_t part_of_row(const RowLayout& L, uint32_t row) { return L.parts <= 1 ? 0 : row / L.rows_per_part; }
+// Inverse of arena_row; returns 0xffffffff for an unused (padding) row.
+MASCOT_HD inline uint32_t sorted_of_row(const RowLayout& L, uint32_t row) {
+    if (L.parts <= 1) return row;
+    const uint32_t part = row / L.rows_per_part, within = row % L.rows_per_part;
+    if (!L.snake) { const uint64_t s = (uint64_t)within * L.parts + part; return s < L.n ? (uint32_t)s : 0xffffffffu; }
+    const uint32_t idx = (within & 1) ? L.parts - 1 - part : part;
+    const uint64_t pos = (uint64_t)within * L.parts + idx;
+    return pos < L.n ? (uint32_t)(L.n - 1 - pos) : 0xffffffffu;
+}
+
 }  // namespace mascot

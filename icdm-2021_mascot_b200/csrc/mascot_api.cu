@@ -5,6 +5,7 @@
 // m-quantization set-up (degree sort, grouping, id maps) runs once on the host; everything per
 // epoch runs on the device and only the small group statistics travel back on check epochs.
 #include <algorithm>
+#include <chrono>
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -15,103 +16,28 @@
 #include <cuda_runtime.h>
 
 #include "../../include/mascot.h"
-#include "engine.h"
-#include "layout.cuh"
+#include "handle.h"
 
 using namespace mascot;
-
-struct mascot_handle {
-    mascot_config cfg;
-    int K = 0;
-    TrainKind kind = KIND_MIXED;
-    bool grouped = false;          // m-quantization / g-switching active (MASCOT variant)
-    // MuPPET precision policy (mf_methods.cu:586-601): index into {8, 12, 14, 16, 32} and its history
-    int mup_idx = 0, mup_switched_epoch = -1, mup_violations = 0;
-    float mup_max_diversity = -1.f;
-    std::vector<float> mup_norms_epoch, mup_sums_epoch;
-    std::vector<uint32_t> urow_degree;           // training degree of every user row (row space of the arenas)
-    bool switched_to_fp32 = false;               // whole-model switching trainer: the switch has happened
-    float switch_initial_error = 1.f;            // its error at epoch index 5 (mf_methods.cu:1444, 1530)
-    cudaStream_t stream = nullptr;
-    cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
-    // streamed epochs: a copy stream and two staging buffers, so that the upload of one piece of the
-    // rating array overlaps the encoding and the updates of the piece before it
-    cudaStream_t copy_stream = nullptr;
-    cudaEvent_t ev_copied[2] = {nullptr, nullptr}, ev_free[2] = {nullptr, nullptr};
-    mascot_rating* d_stage[2] = {nullptr, nullptr};
-    uint64_t stage_ratings = 0;
-
-    uint32_t n_users = 0, n_items = 0;
-    uint64_t n_train = 0, n_test = 0;
-    bool have_ratings = false, have_factors = false;
-
-    // device
-    float* tr_r = nullptr; uint32_t* tr_u = nullptr; uint32_t* tr_i = nullptr;
-    uint32_t* tr_src = nullptr;     // source position of each stream entry (when n_train < 2^32)
-    float* te_r = nullptr; uint32_t* te_u = nullptr; uint32_t* te_i = nullptr;
-    Arena P, Q;
-    uint8_t* d_uprec_row = nullptr; uint8_t* d_iprec_row = nullptr;
-    uint16_t* d_ugroup = nullptr; uint16_t* d_igroup = nullptr;
-    uint32_t* d_umap = nullptr; uint32_t* d_imap = nullptr;
-    float* d_stats = nullptr;       // stats_copies sets of: gsum_p | gsum_q | nsum_p | nsum_q
-    int stats_copies = 1; size_t stats_stride = 0;
-    float* d_block_err = nullptr;
-    unsigned long long* d_work_counter = nullptr;
-    // grow-only device scratch shared by mascot_reload_train (staging of the uploaded array) and by the
-    // partition of the stream by precision class; released by mascot_release_scratch / mascot_destroy
-    void* d_scratch = nullptr; size_t scratch_bytes = 0;
-    // Mixed-precision trainer, several workers: once a group has been promoted the stream is kept
-    // partitioned, inside every segment, into the four precision classes (see RowClass); cls_off holds
-    // five stream positions per segment: the starts of the classes and the end of the segment.
-    bool partitioned = false;
-    std::vector<uint64_t> cls_off;
-
-    // host
-    std::vector<uint32_t> user2sorted, item2sorted, uend, iend;
-    std::vector<uint8_t> uprec, iprec;
-    std::vector<float> uerr, ierr, init_uerr, init_ierr;
-    std::vector<float> lr;
-    std::vector<float> h_stats;     // same layout as d_stats, gsum in LOGICAL element order
-    std::vector<float> h_block_err;
-    std::vector<uint64_t> udeg_sum, ideg_sum;   // ratings per group (training set), for byte accounting
-    std::vector<uint64_t> seg_off;              // training stream segments: [seg_off[s], seg_off[s+1])
-    uint64_t n_train_accounted = 0;
-    std::string err;
-};
 
 namespace {
 
 thread_local std::string g_create_error;
-constexpr int kStatCopies = 256;   // private accumulator sets of the sampled statistics
 
 }  // namespace
 
 void mascot::set_global_error(const char* msg) { g_create_error = msg ? msg : ""; }
 
-namespace {
+double mascot::now_us() {
+    return std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now().time_since_epoch()).count();
+}
 
-int fail(mascot_handle* h, int code, const std::string& msg) {
+int mascot::fail(mascot_handle* h, int code, const std::string& msg) {
     if (h) h->err = msg; else g_create_error = msg;
     return code;
 }
 
-#define CU(h, call)                                                                               \
-    do {                                                                                          \
-        cudaError_t e_ = (call);                                                                  \
-        if (e_ != cudaSuccess) {                                                                  \
-            char buf_[512];                                                                       \
-            snprintf(buf_, sizeof buf_, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, __LINE__); \
-            return fail(h, e_ == cudaErrorMemoryAllocation ? MASCOT_ERR_OOM : MASCOT_ERR_CUDA, buf_); \
-        }                                                                                         \
-    } while (0)
-
-template <typename T>
-cudaError_t dev_alloc(T** p, size_t count) {
-    return cudaMalloc(reinterpret_cast<void**>(p), sizeof(T) * (count ? count : 1));
-}
-
-template <typename T>
-void dev_free(T*& p) { if (p) { cudaFree(p); p = nullptr; } }
+namespace mascot {
 
 void free_ratings(mascot_handle* h) {
     dev_free(h->tr_r); dev_free(h->tr_u); dev_free(h->tr_i); dev_free(h->tr_src);
@@ -123,6 +49,7 @@ void free_ratings(mascot_handle* h) {
 }
 
 // mf_methods.cu:94-97: evaluated in double, stored as float.
+
 float lr_at(const mascot_config& c, uint32_t e) {
     return (float)((double)c.learning_rate / (1.0 + ((double)c.decay * std::pow((double)e, 1.5))));
 }
@@ -132,26 +59,6 @@ bool is_check_epoch(const mascot_config& c, uint32_t e) {
     const uint32_t start_idx = 5;
     const uint32_t it = c.interval ? c.interval : 1;
     return e >= start_idx && (e % it == start_idx % it) && (c.epoch - 1 != e);
-}
-
-// user_item_rating_histogram (preprocess_utils.h:54-99): degree histogram, then ascending sort by
-// degree, ties in ascending id order.  Returns sorted2orig and the sorted degree list.  A shard of a
-// larger data set passes the global degrees so that every shard builds the same index space.
-void degree_sort(const mascot_rating* R, uint64_t n, bool users, uint32_t n_entities, const uint32_t* given_degree,
-                 std::vector<uint32_t>& sorted2orig, std::vector<uint32_t>& orig2sorted, std::vector<uint32_t>& cnt_sorted) {
-    std::vector<uint32_t> cnt(n_entities, 0);
-    if (given_degree) cnt.assign(given_degree, given_degree + n_entities);   // degrees of the whole data set (sharded runs)
-    else for (uint64_t j = 0; j < n; j++) cnt[users ? R[j].u : R[j].i]++;
-    uint32_t maxc = 0;
-    for (uint32_t e = 0; e < n_entities; e++) maxc = std::max(maxc, cnt[e]);
-    std::vector<uint64_t> start((size_t)maxc + 2, 0);
-    for (uint32_t e = 0; e < n_entities; e++) start[cnt[e] + 1]++;
-    for (uint32_t c = 0; c <= maxc; c++) start[c + 1] += start[c];
-    sorted2orig.resize(n_entities); orig2sorted.resize(n_entities); cnt_sorted.resize(n_entities);
-    for (uint32_t e = 0; e < n_entities; e++) {
-        const uint64_t pos = start[cnt[e]]++;
-        sorted2orig[pos] = e; orig2sorted[e] = (uint32_t)pos; cnt_sorted[pos] = cnt[e];
-    }
 }
 
 // split_group_based_equal_size_not_strict_ret_end_idx (preprocess_utils.h:101-213): target size
@@ -205,36 +112,6 @@ size_t stats_floats(const mascot_handle* h) {
     return (size_t)(h->uend.size() + h->iend.size()) * (h->K + 1);
 }
 
-unsigned worker_count(const mascot_handle* h, uint64_t n);
-
-int upload_side_tables(mascot_handle* h, bool users) {
-    const uint32_t n = users ? h->n_users : h->n_items;
-    const std::vector<uint32_t>& end = users ? h->uend : h->iend;
-    const std::vector<uint8_t>& prec = users ? h->uprec : h->iprec;
-    std::vector<uint16_t> group(n);
-    std::vector<uint8_t> prow(n);
-    uint32_t s = 0;
-    for (size_t g = 0; g < end.size(); g++)
-        for (; s <= end[g] && s < n; s++) { group[s] = (uint16_t)g; prow[s] = prec[g] ? kRowPrec : 0; }
-    if (users) {
-        // A user whose ratings are so many that several workers hold its row at any time keeps the plain
-        // store: adding up the changes of many concurrent, equally stale updates multiplies the step and
-        // can diverge, while a plain store lets one of them win.  Expected number of workers inside their
-        // read-to-write span of a row: workers x 4 ratings x degree / n.  Measured: 23 still converges
-        // as well as the reference (20M-rating configuration), 82 diverges (252M-rating one); marked above 32.
-        const uint64_t w_est = std::min<uint64_t>(worker_count(h, h->n_train), 16384);
-        for (uint32_t r = 0; r < n && r < h->urow_degree.size(); r++)
-            if ((uint64_t)h->urow_degree[r] * w_est > 8 * h->n_train) prow[r] |= kRowHot;
-    }
-    uint16_t** dg = users ? &h->d_ugroup : &h->d_igroup;
-    uint8_t** dp = users ? &h->d_uprec_row : &h->d_iprec_row;
-    CU(h, dev_alloc(dg, n)); CU(h, dev_alloc(dp, n));
-    CU(h, cudaMemcpyAsync(*dg, group.data(), sizeof(uint16_t) * n, cudaMemcpyHostToDevice, h->stream));
-    CU(h, cudaMemcpyAsync(*dp, prow.data(), sizeof(uint8_t) * n, cudaMemcpyHostToDevice, h->stream));
-    CU(h, cudaStreamSynchronize(h->stream));
-    return MASCOT_OK;
-}
-
 // Encodes an uploaded rating array into the structure-of-arrays stream, segment by segment: the
 // seeded permutation and the item-sorted windows never cross a segment boundary.
 cudaError_t encode_segments(mascot_handle* h, const mascot_rating* d_src, const std::vector<uint64_t>& seg, bool shuffle,
@@ -242,26 +119,11 @@ cudaError_t encode_segments(mascot_handle* h, const mascot_rating* d_src, const 
     for (size_t sgm = 0; sgm + 1 < seg.size(); sgm++) {
         const uint64_t off = seg[sgm], n = seg[sgm + 1] - off;
         cudaError_t e = launch_encode_stream(d_src + off, n, shuffle, h->cfg.seed + 0x9e3779b97f4a7c15ull * sgm, h->d_umap, h->d_imap,
-                                             h->d_uprec_row, h->d_iprec_row, h->n_items, r + off, u + off, i + off,
-                                             src_idx ? src_idx + off : nullptr, (uint32_t)off, h->stream);
+                                             h->d_uprec_row, h->d_iprec_row, h->n_users, h->n_items, h->irows, h->d_err_flag,
+                                             r + off, u + off, i + off, src_idx ? src_idx + off : nullptr, (uint32_t)off, h->stream);
         if (e != cudaSuccess) return e;
     }
     return cudaSuccess;
-}
-
-int upload_and_encode(mascot_handle* h, const mascot_rating* src, uint64_t n, const std::vector<uint64_t>& seg, bool shuffle,
-                      float** r, uint32_t** u, uint32_t** i, uint32_t** src_idx) {
-    CU(h, dev_alloc(r, n)); CU(h, dev_alloc(u, n)); CU(h, dev_alloc(i, n));
-    if (src_idx && n < (1ull << 32)) CU(h, dev_alloc(src_idx, n));
-    if (!n) return MASCOT_OK;
-    mascot_rating* tmp = nullptr;
-    CU(h, dev_alloc(&tmp, n));
-    cudaError_t e = cudaMemcpyAsync(tmp, src, sizeof(mascot_rating) * n, cudaMemcpyHostToDevice, h->stream);
-    if (e == cudaSuccess) e = encode_segments(h, tmp, seg, shuffle, *r, *u, *i, src_idx ? *src_idx : nullptr);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
-    cudaFree(tmp);
-    CU(h, e);
-    return MASCOT_OK;
 }
 
 // One group fp16 -> fp32 (precision_switching.h:12-27): widen its rows into the fp32 arena and flip
@@ -271,8 +133,7 @@ int promote_group(mascot_handle* h, bool users, size_t g) {
     std::vector<uint8_t>& prec = users ? h->uprec : h->iprec;
     uint8_t* prow = users ? h->d_uprec_row : h->d_iprec_row;
     const uint32_t b = g ? end[g - 1] + 1 : 0, e = end[g] + 1;
-    CU(h, launch_promote_rows(h->K, users ? h->P : h->Q, b, e, h->stream));
-    CU(h, launch_mark_fp32(prow + b, e - b, h->stream));
+    CU(h, launch_promote_rows(h->K, users ? h->P : h->Q, prow, users ? h->ulay : h->ilay, b, e, h->stream));
     prec[g] = 1;
     return MASCOT_OK;
 }
@@ -448,7 +309,8 @@ int mascot_create(const mascot_config* cfg, mascot_handle** out) {
     cudaError_t e = cudaSetDevice(cfg->device);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking);
     for (int j = 0; j < 4 && e == cudaSuccess; j++) e = cudaEventCreate(&h->ev[j]);
-    if (e == cudaSuccess) e = dev_alloc(&h->d_work_counter, 1);
+    if (e == cudaSuccess) e = dev_alloc(&h->counters.d_slots, 4);
+    if (e == cudaSuccess) e = cudaMemset(h->counters.d_slots, 0, 4 * sizeof(unsigned long long));
     if (e != cudaSuccess) {
         std::string msg = std::string("CUDA set-up failed: ") + cudaGetErrorString(e);
         mascot_destroy(h);
@@ -462,7 +324,8 @@ int mascot_destroy(mascot_handle* h) {
     if (!h) return MASCOT_OK;
     cudaSetDevice(h->cfg.device);
     free_ratings(h);
-    dev_free(h->d_scratch); dev_free(h->d_work_counter);
+    shard_destroy(h);
+    dev_free(h->d_scratch); dev_free(h->counters.d_slots); dev_free(h->d_err_flag);
     for (auto& ev : h->ev) if (ev) cudaEventDestroy(ev);
     for (int b = 0; b < 2; b++) {
         if (h->ev_copied[b]) cudaEventDestroy(h->ev_copied[b]);
@@ -485,105 +348,24 @@ int mascot_set_ratings_sharded(mascot_handle* h, const mascot_rating* train, uin
                                const mascot_rating* test, uint64_t n_test, uint32_t n_users, uint32_t n_items,
                                const uint32_t* user_degree, const uint32_t* item_degree) {
     if (!h) return MASCOT_ERR_BAD_ARG;
-    if ((!train && n_train) || (!test && n_test)) return fail(h, MASCOT_ERR_BAD_ARG, "null rating array");
-    if (!n_users || !n_items || n_users > kIdMask || n_items > kIdMask) return fail(h, MASCOT_ERR_BAD_ARG, "user/item count out of range");
-    if (n_train >= (1ull << 40)) return fail(h, MASCOT_ERR_BAD_ARG, "too many ratings");
-    if (n_segments == 0 || (n_segments > 1 && !segment_offsets)) return fail(h, MASCOT_ERR_BAD_ARG, "bad segment table");
-    if ((user_degree == nullptr) != (item_degree == nullptr)) return fail(h, MASCOT_ERR_BAD_ARG, "give both degree tables or none");
-    std::vector<uint64_t> seg(n_segments + 1);
-    if (segment_offsets) {
-        for (uint32_t j = 0; j <= n_segments; j++) seg[j] = segment_offsets[j];
-        if (seg[0] != 0 || seg[n_segments] != n_train) return fail(h, MASCOT_ERR_BAD_ARG, "segment offsets must run from 0 to n_train");
-        for (uint32_t j = 0; j < n_segments; j++) if (seg[j] > seg[j + 1]) return fail(h, MASCOT_ERR_BAD_ARG, "segment offsets must not decrease");
-    } else { seg[0] = 0; seg[1] = n_train; }
-    for (uint64_t j = 0; j < n_train; j++)
-        if (train[j].u >= n_users || train[j].i >= n_items) return fail(h, MASCOT_ERR_BAD_ARG, "training rating with id out of range");
-    for (uint64_t j = 0; j < n_test; j++)
-        if (test[j].u >= n_users || test[j].i >= n_items) return fail(h, MASCOT_ERR_BAD_ARG, "test rating with id out of range");
-    CU(h, cudaSetDevice(h->cfg.device));
-    free_ratings(h);
-    h->n_users = n_users; h->n_items = n_items; h->n_train = n_train; h->n_test = n_test;
-    h->seg_off = seg;
-    h->cls_off.clear(); h->partitioned = false;
-
-    // --- m-quantization set-up on the host (one-off) ---
-    if (h->grouped) {
-        std::vector<uint32_t> s2o, cnt;
-        degree_sort(train, n_train, true, n_users, user_degree, s2o, h->user2sorted, cnt);
-        h->urow_degree = cnt;                      // sorted position -> degree
-        make_groups(cnt, h->cfg.user_group_num, h->uend);
-        degree_sort(train, n_train, false, n_items, item_degree, s2o, h->item2sorted, cnt);
-        make_groups(cnt, h->cfg.item_group_num, h->iend);
-        if (h->uend.size() > 65535 || h->iend.size() > 65535) return fail(h, MASCOT_ERR_BAD_ARG, "more than 65535 groups");
-        h->uprec.assign(h->uend.size(), 0); h->iprec.assign(h->iend.size(), 0);
-        // ratings of THIS engine's stream per group (byte accounting)
-        std::vector<uint32_t> ug_of(n_users), ig_of(n_items);
-        { uint32_t p = 0; for (size_t g = 0; g < h->uend.size(); g++) for (; p <= h->uend[g] && p < n_users; p++) ug_of[p] = (uint32_t)g; }
-        { uint32_t p = 0; for (size_t g = 0; g < h->iend.size(); g++) for (; p <= h->iend[g] && p < n_items; p++) ig_of[p] = (uint32_t)g; }
-        h->udeg_sum.assign(h->uend.size(), 0); h->ideg_sum.assign(h->iend.size(), 0);
-        for (uint64_t j = 0; j < n_train; j++) {
-            h->udeg_sum[ug_of[h->user2sorted[train[j].u]]]++;
-            h->ideg_sum[ig_of[h->item2sorted[train[j].i]]]++;
-        }
-    } else {
-        h->user2sorted.clear(); h->item2sorted.clear();
-        h->urow_degree.assign(n_users, 0);
-        for (uint64_t j = 0; j < n_train; j++) h->urow_degree[train[j].u]++;
-        h->uend.assign(1, n_users - 1); h->iend.assign(1, n_items - 1);
-        const uint8_t p = (h->kind == KIND_MEMQUANT || h->kind == KIND_SWITCH) ? 0 : 1;
-        h->uprec.assign(1, p); h->iprec.assign(1, p);
-        h->udeg_sum.assign(1, n_train); h->ideg_sum.assign(1, n_train);
-    }
-    h->n_train_accounted = n_train;
-    h->uerr.assign(h->uend.size(), 0.f); h->ierr.assign(h->iend.size(), 0.f);
-    h->init_uerr.assign(h->uend.size(), 1.f); h->init_ierr.assign(h->iend.size(), 1.f);   // mf_methods.cu:150-151
-
-    int rc;
-    if ((rc = upload_side_tables(h, true)) != MASCOT_OK) return rc;
-    if ((rc = upload_side_tables(h, false)) != MASCOT_OK) return rc;
-    if (h->grouped) {
-        CU(h, dev_alloc(&h->d_umap, n_users)); CU(h, dev_alloc(&h->d_imap, n_items));
-        CU(h, cudaMemcpy(h->d_umap, h->user2sorted.data(), sizeof(uint32_t) * n_users, cudaMemcpyHostToDevice));
-        CU(h, cudaMemcpy(h->d_imap, h->item2sorted.data(), sizeof(uint32_t) * n_items, cudaMemcpyHostToDevice));
-    }
-
-    // --- rating streams ---
-    if ((rc = upload_and_encode(h, train, n_train, seg, h->cfg.shuffle != 0, &h->tr_r, &h->tr_u, &h->tr_i, &h->tr_src)) != MASCOT_OK) return rc;
-    {
-        // test_set_preprocess (preprocess_utils.h:38-52) leaves the test set ordered by (user, item)
-        std::vector<mascot_rating> t(test, test + n_test);
-        std::stable_sort(t.begin(), t.end(), [](const mascot_rating& a, const mascot_rating& b) {
-            return a.u != b.u ? a.u < b.u : a.i < b.i;
-        });
-        const std::vector<uint64_t> whole = {0, n_test};
-        if ((rc = upload_and_encode(h, t.data(), n_test, whole, false, &h->te_r, &h->te_u, &h->te_i, nullptr)) != MASCOT_OK) return rc;
-    }
-
-    // --- factor arenas and statistics ---
-    const size_t pu = (size_t)n_users * h->K, qi = (size_t)n_items * h->K;
-    if (h->kind == KIND_MIXED || h->kind == KIND_MEMQUANT || h->kind == KIND_SWITCH) { CU(h, dev_alloc(&h->P.f16, pu)); CU(h, dev_alloc(&h->Q.f16, qi)); }
-    if (h->kind != KIND_MEMQUANT) { CU(h, dev_alloc(&h->P.f32, pu)); CU(h, dev_alloc(&h->Q.f32, qi)); }
-    h->stats_copies = h->cfg.deterministic ? 1 : kStatCopies;
-    h->stats_stride = (stats_floats(h) + 63) / 64 * 64;
-    CU(h, dev_alloc(&h->d_stats, h->stats_stride * h->stats_copies));
-    CU(h, cudaMemset(h->d_stats, 0, sizeof(float) * h->stats_stride * h->stats_copies));
-    h->h_stats.assign(stats_floats(h), 0.f);
-    const size_t blocks = (size_t)((n_test + 511) / 512);
-    CU(h, dev_alloc(&h->d_block_err, blocks));
-    h->h_block_err.assign(blocks, 0.f);
-    h->have_ratings = true;
-    return MASCOT_OK;
+    if (h->shard) return fail(h, MASCOT_ERR_STATE, "this engine belongs to a sharded group: use mascot_shard_set_ratings");
+    SetupRequest rq;
+    rq.train = train; rq.n_train = n_train; rq.segment_offsets = segment_offsets; rq.n_segments = n_segments;
+    rq.test = test; rq.n_test = n_test; rq.n_users = n_users; rq.n_items = n_items;
+    rq.user_degree = user_degree; rq.item_degree = item_degree;
+    return setup_ratings(h, rq);
 }
 
 int mascot_reload_train(mascot_handle* h, const mascot_rating* train, uint64_t n_train) {
     if (!h) return MASCOT_ERR_BAD_ARG;
     if (!train && n_train) return fail(h, MASCOT_ERR_BAD_ARG, "null rating array");
     if (!h->have_ratings) return fail(h, MASCOT_ERR_STATE, "mascot_set_ratings must come first");
+    if (n_train >= (1ull << 32)) return fail(h, MASCOT_ERR_BAD_ARG, "too many ratings (limit 2^32 - 1 per engine)");
     CU(h, cudaSetDevice(h->cfg.device));
     if (n_train != h->n_train) {
         dev_free(h->tr_r); dev_free(h->tr_u); dev_free(h->tr_i); dev_free(h->tr_src);
         CU(h, dev_alloc(&h->tr_r, n_train)); CU(h, dev_alloc(&h->tr_u, n_train)); CU(h, dev_alloc(&h->tr_i, n_train));
-        if (n_train < (1ull << 32)) CU(h, dev_alloc(&h->tr_src, n_train));
+        CU(h, dev_alloc(&h->tr_src, n_train));
         h->n_train = n_train;
         h->seg_off.assign({0, n_train});           // a stream of another length is one segment
         h->cls_off.clear(); h->partitioned = false;
@@ -592,20 +374,26 @@ int mascot_reload_train(mascot_handle* h, const mascot_rating* train, uint64_t n
     const size_t bytes = sizeof(mascot_rating) * n_train;
     int rc = need_scratch(h, bytes);
     if (rc != MASCOT_OK) return rc;
+    CU(h, cudaMemsetAsync(h->d_err_flag, 0, sizeof(uint32_t), h->stream));
     CU(h, cudaMemcpyAsync(h->d_scratch, train, bytes, cudaMemcpyHostToDevice, h->stream));
     CU(h, encode_segments(h, static_cast<const mascot_rating*>(h->d_scratch), h->seg_off, h->cfg.shuffle != 0,
                           h->tr_r, h->tr_u, h->tr_i, h->tr_src));
+    uint32_t bad = 0;
+    CU(h, cudaMemcpyAsync(&bad, h->d_err_flag, sizeof(uint32_t), cudaMemcpyDeviceToHost, h->stream));
     h->cls_off.clear();
     if ((rc = partition_all(h)) != MASCOT_OK) return rc;      // the new stream carries the current precisions
     CU(h, cudaStreamSynchronize(h->stream));
+    if (bad) return fail(h, MASCOT_ERR_BAD_ARG, "training rating with id out of range (replaced by zero ratings of row 0; reload a valid array)");
     return MASCOT_OK;
 }
 
 static int scatter_from_device(mascot_handle* h, const float* dP, const float* dQ) {
+    const double t0 = now_us();
     const bool through_half = (h->kind == KIND_MPT);   // MPT masters start from fp16 values (mf_methods.cu:730-733)
     CU(h, launch_scatter_factors(h->K, dP, h->n_users, h->d_umap, through_half, h->P.f16, h->P.f32, h->stream));
     CU(h, launch_scatter_factors(h->K, dQ, h->n_items, h->d_imap, through_half, h->Q.f16, h->Q.f32, h->stream));
     CU(h, cudaStreamSynchronize(h->stream));
+    h->timings.copy_to_grouped_us += now_us() - t0;
     h->have_factors = true;
     return MASCOT_OK;
 }
@@ -647,7 +435,7 @@ int mascot_init_factors(mascot_handle* h) {
 
 }  // extern "C"
 
-namespace {
+namespace mascot {
 
 unsigned worker_count(const mascot_handle* h, uint64_t n) {
     // -wg 0 = automatic: one worker per 8192 ratings keeps the sequential depth per worker - and with
@@ -657,6 +445,7 @@ unsigned worker_count(const mascot_handle* h, uint64_t n) {
     // configuration: final RMSE still below the reference's, three times the throughput of 512 workers).
     if (h->cfg.deterministic) return 1u;
     if (h->cfg.num_workers) return h->cfg.num_workers;
+    if (h->shard) return shard_worker_count(h);
     if (n < 1500000) return (unsigned)std::min<uint64_t>(std::max<uint64_t>(n / 512, 512), 1536);
     return (unsigned)std::min<uint64_t>(std::max<uint64_t>(n / 8192, 512), 1u << 20);
 }
@@ -752,14 +541,14 @@ int train_span(mascot_handle* h, float lr, uint32_t epoch, uint64_t begin, uint6
     if (head > 0) {
         Stream sa = s; sa.n = head;
         CU(h, launch_train(h->K, kind, sa, h->P, h->Q, lr, h->cfg.lambda, nullptr, cls, workers,
-                           h->d_work_counter, muppet_bits(h), (int)epoch, h->cfg.plain_user_stores == 0, h->stream, shape));
+                           &h->counters, muppet_bits(h), (int)epoch, h->cfg.plain_user_stores == 0, h->stream, shape));
         (*launches)++;
     }
     if (head < n) {
         Stream sb; sb.r = s.r + head; sb.u = s.u + head; sb.i = s.i + head; sb.n = n - head;
         const SampleStats st = stats_view(h);
         CU(h, launch_train(h->K, kind, sb, h->P, h->Q, lr, h->cfg.lambda, &st, cls, workers,
-                           h->d_work_counter, muppet_bits(h), (int)epoch, h->cfg.plain_user_stores == 0, h->stream, shape));
+                           &h->counters, muppet_bits(h), (int)epoch, h->cfg.plain_user_stores == 0, h->stream, shape));
         (*launches)++;
     }
     return MASCOT_OK;
@@ -769,7 +558,7 @@ int train_span(mascot_handle* h, float lr, uint32_t epoch, uint64_t begin, uint6
 // mode, which reads each id's precision bit), else one launch per non-empty precision class.  On a
 // check epoch every launched range contributes its own sampled tail.
 int train_range(mascot_handle* h, float lr, uint32_t epoch, size_t segment, bool collect, LaunchShape* shape, uint32_t* launches,
-                uint64_t policy_n = 0) {
+                uint64_t policy_n) {
     const uint64_t begin = h->seg_off[segment], end = h->seg_off[segment + 1];
     if (!policy_n) policy_n = end - begin;
     if (!h->partitioned)
@@ -785,6 +574,7 @@ int train_range(mascot_handle* h, float lr, uint32_t epoch, size_t segment, bool
 // Folds the private accumulator sets and brings the sums to the host in LOGICAL element order.
 int fetch_stats(mascot_handle* h, uint32_t* launches) {
     const int ug = (int)h->uend.size(), ig = (int)h->iend.size(), K = h->K;
+    const double t0 = now_us();
     if (h->stats_copies > 1) {
         CU(h, launch_reduce_stats(h->d_stats, h->stats_copies, h->stats_stride, stats_floats(h), h->stream));
         if (launches) (*launches)++;
@@ -795,6 +585,7 @@ int fetch_stats(mascot_handle* h, uint32_t* launches) {
     for (size_t g = 0; g < (size_t)(ug + ig); g++)
         for (int p = 0; p < K; p++) h->h_stats[g * K + logical_of_phys(K, p)] = raw[g * K + p];
     std::copy(raw.begin() + (size_t)(ug + ig) * K, raw.end(), h->h_stats.begin() + (size_t)(ug + ig) * K);
+    h->timings.error_computation_us += now_us() - t0;
     return MASCOT_OK;
 }
 
@@ -802,6 +593,7 @@ int fetch_stats(mascot_handle* h, uint32_t* launches) {
 // precision_switching.h:8-51).
 int apply_stats(mascot_handle* h, uint32_t epoch, uint32_t* promoted_u, uint32_t* promoted_i, uint32_t* launches) {
     const int ug = (int)h->uend.size(), ig = (int)h->iend.size(), K = h->K;
+    const double t_err = now_us();
     auto errors = [&](int groups, const float* gsum, const float* nsum, const std::vector<uint8_t>& prec,
                       const std::vector<float>& initial, std::vector<float>& err) {
         for (int g = 0; g < groups; g++) {
@@ -817,8 +609,10 @@ int apply_stats(mascot_handle* h, uint32_t epoch, uint32_t* promoted_u, uint32_t
     errors(ug, gs_p, ns_p, h->uprec, h->init_uerr, h->uerr);
     errors(ig, gs_q, ns_q, h->iprec, h->init_ierr, h->ierr);
     if (epoch == 5) { h->init_uerr = h->uerr; h->init_ierr = h->ierr; }   // mf_methods.cu:381-388
+    h->timings.error_computation_us += now_us() - t_err;
     if (epoch > 5) {
         int rc;
+        const double t_sw = now_us();
         for (int side = 0; side < 2; side++) {
             const bool users = side == 0;
             const std::vector<uint8_t>& prec = users ? h->uprec : h->iprec;
@@ -837,7 +631,9 @@ int apply_stats(mascot_handle* h, uint32_t epoch, uint32_t* promoted_u, uint32_t
         if (*promoted_u + *promoted_i) {
             if ((rc = partition_all(h)) != MASCOT_OK) return rc;
             if (launches && h->partitioned) (*launches) += 4;
+            CU(h, cudaStreamSynchronize(h->stream));
         }
+        h->timings.precision_switching_us += now_us() - t_sw;
     }
     return MASCOT_OK;
 }
@@ -911,6 +707,7 @@ int mascot_stats_apply(mascot_handle* h, uint32_t epoch, const float* grad_sum_p
 
 int mascot_train_epoch(mascot_handle* h, uint32_t epoch, mascot_epoch_stats* out) {
     if (!h) return MASCOT_ERR_BAD_ARG;
+    if (h->shard) return fail(h, MASCOT_ERR_STATE, "this engine belongs to a sharded group: use mascot_shard_train_epoch");
     if (!h->have_ratings || !h->have_factors) return fail(h, MASCOT_ERR_STATE, "ratings and factors must be set before training");
     CU(h, cudaSetDevice(h->cfg.device));
     const float lr = epoch < h->lr.size() ? h->lr[epoch] : lr_at(h->cfg, epoch);
@@ -954,6 +751,7 @@ int mascot_train_epoch(mascot_handle* h, uint32_t epoch, mascot_epoch_stats* out
         cudaEventElapsedTime(&out->kernel_ms, h->ev[1], h->ev[2]);
         cudaEventElapsedTime(&out->total_ms, h->ev[0], h->ev[3]);
     }
+    { float kms = 0.f; if (cudaEventElapsedTime(&kms, h->ev[1], h->ev[2]) == cudaSuccess) h->timings.update_us += 1e3 * kms; }
     return MASCOT_OK;
 }
 
@@ -961,6 +759,7 @@ int mascot_train_epoch_streamed(mascot_handle* h, uint32_t epoch, const mascot_r
     if (!h || (!train && n_train)) return MASCOT_ERR_BAD_ARG;
     if (!h->have_ratings || !h->have_factors) return fail(h, MASCOT_ERR_STATE, "ratings and factors must be set before training");
     if (h->kind == KIND_AFP) return fail(h, MASCOT_ERR_UNSUPPORTED, "the AFP trainer keeps its per-worker state for a whole epoch: use mascot_train_epoch");
+    if (h->shard) return fail(h, MASCOT_ERR_STATE, "this engine belongs to a sharded group: use mascot_shard_train_epoch");
     CU(h, cudaSetDevice(h->cfg.device));
     constexpr uint64_t kPiece = 8ull << 20;           // ratings per piece (96 MiB of input)
     if (!h->copy_stream) {
@@ -980,9 +779,10 @@ int mascot_train_epoch_streamed(mascot_handle* h, uint32_t epoch, const mascot_r
     if (n_train != h->n_train) {
         dev_free(h->tr_r); dev_free(h->tr_u); dev_free(h->tr_i); dev_free(h->tr_src);
         CU(h, dev_alloc(&h->tr_r, n_train)); CU(h, dev_alloc(&h->tr_u, n_train)); CU(h, dev_alloc(&h->tr_i, n_train));
-        if (n_train < (1ull << 32)) CU(h, dev_alloc(&h->tr_src, n_train));
+        CU(h, dev_alloc(&h->tr_src, n_train));
         h->n_train = n_train;
     }
+    CU(h, cudaMemsetAsync(h->d_err_flag, 0, sizeof(uint32_t), h->stream));
     // the pieces become the segments of the resident stream (seeded permutation inside each piece)
     h->seg_off.clear();
     for (uint64_t off = 0; off < n_train; off += piece) h->seg_off.push_back(off);
@@ -1011,8 +811,8 @@ int mascot_train_epoch_streamed(mascot_handle* h, uint32_t epoch, const mascot_r
         CU(h, cudaEventRecord(h->ev_copied[b], h->copy_stream));
         CU(h, cudaStreamWaitEvent(h->stream, h->ev_copied[b], 0));
         CU(h, launch_encode_stream(h->d_stage[b], len, h->cfg.shuffle != 0, h->cfg.seed + 0x9e3779b97f4a7c15ull * c, h->d_umap, h->d_imap,
-                                   h->d_uprec_row, h->d_iprec_row, h->n_items, h->tr_r + off, h->tr_u + off, h->tr_i + off,
-                                   h->tr_src ? h->tr_src + off : nullptr, (uint32_t)off, h->stream));
+                                   h->d_uprec_row, h->d_iprec_row, h->n_users, h->n_items, h->irows, h->d_err_flag,
+                                   h->tr_r + off, h->tr_u + off, h->tr_i + off, h->tr_src ? h->tr_src + off : nullptr, (uint32_t)off, h->stream));
         launches++;
         CU(h, cudaEventRecord(h->ev_free[b], h->stream));
         if (partition_pieces) {
@@ -1038,8 +838,11 @@ int mascot_train_epoch_streamed(mascot_handle* h, uint32_t epoch, const mascot_r
         else if (switch_only) { if ((rc = switch_only_policy(h, epoch, &promoted_u, &promoted_i)) != MASCOT_OK) return rc; }
         else if ((rc = apply_stats(h, epoch, &promoted_u, &promoted_i, &launches)) != MASCOT_OK) return rc;
     }
+    uint32_t bad = 0;
+    CU(h, cudaMemcpyAsync(&bad, h->d_err_flag, sizeof(uint32_t), cudaMemcpyDeviceToHost, h->stream));
     CU(h, cudaEventRecord(h->ev[3], h->stream));
     CU(h, cudaEventSynchronize(h->ev[3]));
+    if (bad) return fail(h, MASCOT_ERR_BAD_ARG, "training rating with id out of range (it was trained as a zero rating of row 0)");
     if (out) {
         std::memset(out, 0, sizeof(*out));
         out->updates = n_train; out->lr = lr; out->error_check = check ? 1 : 0; out->pass_bits = (uint32_t)bits_this_epoch;
@@ -1049,6 +852,7 @@ int mascot_train_epoch_streamed(mascot_handle* h, uint32_t epoch, const mascot_r
         cudaEventElapsedTime(&out->kernel_ms, h->ev[1], h->ev[2]);
         cudaEventElapsedTime(&out->total_ms, h->ev[0], h->ev[3]);
     }
+    { float kms = 0.f; if (cudaEventElapsedTime(&kms, h->ev[1], h->ev[2]) == cudaSuccess) h->timings.update_us += 1e3 * kms; }
     return MASCOT_OK;
 }
 
@@ -1057,11 +861,33 @@ int mascot_item_rows(mascot_handle* h, uint32_t row_begin, uint32_t row_end, voi
     if (!h || row_end < row_begin) return MASCOT_ERR_BAD_ARG;
     if (!h->have_ratings) return fail(h, MASCOT_ERR_STATE, "mascot_set_ratings must come first");
     if (row_end > h->n_items) return fail(h, MASCOT_ERR_BAD_ARG, "item row range out of bounds");
+    if (h->ilay.parts > 1) return fail(h, MASCOT_ERR_UNSUPPORTED, "the items of a sharded engine are laid out block by block, not by sorted index");
     const size_t b = (size_t)row_begin * h->K, n = (size_t)(row_end - row_begin) * h->K;
     if (f16_ptr) *f16_ptr = h->Q.f16 ? (void*)(h->Q.f16 + b) : nullptr;
     if (f16_bytes) *f16_bytes = h->Q.f16 ? n * sizeof(__half) : 0;
     if (f32_ptr) *f32_ptr = h->Q.f32 ? (void*)(h->Q.f32 + b) : nullptr;
     if (f32_bytes) *f32_bytes = h->Q.f32 ? n * sizeof(float) : 0;
+    return MASCOT_OK;
+}
+
+int mascot_get_timings(mascot_handle* h, mascot_timings* out) {
+    if (!h || !out) return MASCOT_ERR_BAD_ARG;
+    *out = h->timings;
+    return MASCOT_OK;
+}
+
+int mascot_get_worker_count(mascot_handle* h, uint32_t* workers) {
+    if (!h || !workers) return MASCOT_ERR_BAD_ARG;
+    if (!h->have_ratings) return fail(h, MASCOT_ERR_STATE, "mascot_set_ratings must come first");
+    *workers = worker_count(h, h->n_train);
+    return MASCOT_OK;
+}
+
+int mascot_release_scratch(mascot_handle* h) {
+    if (!h) return MASCOT_ERR_BAD_ARG;
+    CU(h, cudaSetDevice(h->cfg.device));
+    CU(h, cudaStreamSynchronize(h->stream));
+    dev_free(h->d_scratch); h->scratch_bytes = 0;
     return MASCOT_OK;
 }
 
@@ -1112,20 +938,20 @@ int mascot_get_factors(mascot_handle* h, float* P, float* Q, int order) {
     if (!h->have_factors) return fail(h, MASCOT_ERR_STATE, "no factors yet");
     if (order != 0 && order != 1) return fail(h, MASCOT_ERR_BAD_ARG, "order must be 0 or 1");
     CU(h, cudaSetDevice(h->cfg.device));
-    auto one = [&](float* dst, Arena a, const uint8_t* prow, uint32_t rows, const uint32_t* map) -> int {
+    auto one = [&](float* dst, Arena a, const uint8_t* prow, uint32_t rows, const uint32_t* map, const RowLayout& lay) -> int {
         if (!dst) return MASCOT_OK;
         float* d = nullptr;
         CU(h, dev_alloc(&d, (size_t)rows * h->K));
-        cudaError_t e = launch_gather_factors(h->K, a, prow, rows, order == 0 ? map : nullptr, d, h->stream);
+        cudaError_t e = launch_gather_factors(h->K, a, prow, rows, order == 0 ? map : nullptr, lay, d, h->stream);
         if (e == cudaSuccess) e = cudaMemcpyAsync(dst, d, sizeof(float) * (size_t)rows * h->K, cudaMemcpyDeviceToHost, h->stream);
         if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
         cudaFree(d);
         CU(h, e);
         return MASCOT_OK;
     };
-    int rc = one(P, h->P, h->d_uprec_row, h->n_users, h->d_umap);
+    int rc = one(P, h->P, h->d_uprec_row, h->n_users, h->d_umap, h->ulay);
     if (rc != MASCOT_OK) return rc;
-    return one(Q, h->Q, h->d_iprec_row, h->n_items, h->d_imap);
+    return one(Q, h->Q, h->d_iprec_row, h->n_items, h->d_imap, h->ilay);
 }
 
 int mascot_get_group_info(mascot_handle* h, int side, uint32_t* n_groups, uint32_t* end_idx, uint8_t* precision, float* error) {
@@ -1145,11 +971,11 @@ int mascot_get_index_maps(mascot_handle* h, uint32_t* user2sorted, uint32_t* ite
     if (!h) return MASCOT_ERR_BAD_ARG;
     if (!h->have_ratings) return fail(h, MASCOT_ERR_STATE, "mascot_set_ratings must come first");
     if (user2sorted) {
-        if (h->grouped) std::copy(h->user2sorted.begin(), h->user2sorted.end(), user2sorted);
+        if (h->sorted_space) std::copy(h->user2sorted.begin(), h->user2sorted.end(), user2sorted);
         else for (uint32_t e = 0; e < h->n_users; e++) user2sorted[e] = e;
     }
     if (item2sorted) {
-        if (h->grouped) std::copy(h->item2sorted.begin(), h->item2sorted.end(), item2sorted);
+        if (h->sorted_space) std::copy(h->item2sorted.begin(), h->item2sorted.end(), item2sorted);
         else for (uint32_t e = 0; e < h->n_items; e++) item2sorted[e] = e;
     }
     return MASCOT_OK;
@@ -1195,13 +1021,14 @@ int mascot_get_test_ratings(mascot_handle* h, mascot_rating* out, int order) {
     CU(h, cudaMemcpy(u.data(), h->te_u, sizeof(uint32_t) * n, cudaMemcpyDeviceToHost));
     CU(h, cudaMemcpy(i.data(), h->te_i, sizeof(uint32_t) * n, cudaMemcpyDeviceToHost));
     std::vector<uint32_t> s2u, s2i;
-    if (order == 0 && h->grouped) {
+    if (order == 0 && h->sorted_space) {
         s2u.resize(h->n_users); s2i.resize(h->n_items);
         for (uint32_t e = 0; e < h->n_users; e++) s2u[h->user2sorted[e]] = e;
         for (uint32_t e = 0; e < h->n_items; e++) s2i[h->item2sorted[e]] = e;
     }
     for (uint64_t j = 0; j < n; j++) {
-        uint32_t uu = u[j] & kIdMask, ii = i[j] & kIdMask;
+        // the stream holds arena rows: back to sorted indices, then (order 0) to the caller's ids
+        uint32_t uu = sorted_of_row(h->ulay, u[j] & kIdMask), ii = sorted_of_row(h->ilay, i[j] & kIdMask);
         if (!s2u.empty()) { uu = s2u[uu]; ii = s2i[ii]; }
         out[j].r = r[j]; out[j].u = uu; out[j].i = ii;
     }

@@ -25,13 +25,20 @@ inline int grid_for(uint64_t n, int block) {
 // Replaces the host random_shuffle (mf_methods.cu:38-39) and the id remap
 // matrix_reconst_gpu_triplet (preprocess_utils.h:28-36): stream position j takes source rating
 // permute_index(j), ids are mapped to sorted indices and tagged with the row's storage precision.
+// An id outside [0, n_users) x [0, n_items) is never used as an index: the rating is replaced by a
+// no-op record on row 0 (r = 0 would still train, so the host reports the raised flag as an error).
+__device__ __forceinline__ NodeAos checked(NodeAos nd, uint32_t n_users, uint32_t n_items, uint32_t* err) {
+    if (nd.u >= n_users || nd.i >= n_items) { atomicOr(err, 1u); nd.u = 0; nd.i = 0; nd.r = 0.f; }
+    return nd;
+}
+
 __global__ void encode_kernel(const NodeAos* src, uint64_t n, int shuffle, uint64_t seed,
                               const uint32_t* umap, const uint32_t* imap,
-                              const uint8_t* uprec, const uint8_t* iprec,
+                              const uint8_t* uprec, const uint8_t* iprec, uint32_t n_users, uint32_t n_items, uint32_t* err,
                               float* r, uint32_t* u, uint32_t* i, uint32_t* src_out, uint32_t src_base) {
     for (uint64_t j = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; j < n; j += (uint64_t)gridDim.x * blockDim.x) {
         const uint64_t s = shuffle ? permute_index(j, n, seed) : j;
-        const NodeAos nd = src[s];
+        const NodeAos nd = checked(src[s], n_users, n_items, err);
         uint32_t uu = umap ? umap[nd.u] : nd.u;
         uint32_t ii = imap ? imap[nd.i] : nd.i;
         uu |= row_flags_to_code(uprec[uu]);
@@ -54,7 +61,7 @@ constexpr int kWindow = kSortThreads * kSortItemsPerThread;
 
 __global__ void __launch_bounds__(kSortThreads) encode_sorted_kernel(
         const NodeAos* src, uint64_t n, uint64_t seed, const uint32_t* umap, const uint32_t* imap,
-        const uint8_t* uprec, const uint8_t* iprec, int key_bits,
+        const uint8_t* uprec, const uint8_t* iprec, uint32_t n_users, uint32_t n_items, uint32_t* err, int key_bits,
         float* r, uint32_t* u, uint32_t* i, uint32_t* src_out, uint32_t src_base) {
     typedef cub::BlockRadixSort<uint32_t, kSortThreads, kSortItemsPerThread, uint32_t> Sort;
     __shared__ typename Sort::TempStorage temp;
@@ -68,7 +75,8 @@ __global__ void __launch_bounds__(kSortThreads) encode_sorted_kernel(
             const uint64_t pos = base + local;
             uint32_t key = 0xffffffffu >> (32 - key_bits);      // padding sorts last
             if (pos < n) {
-                const uint32_t it = src[permute_index(pos, n, seed)].i;
+                uint32_t it = src[permute_index(pos, n, seed)].i;
+                if (it >= n_items) it = 0;                      // reported when the record is read below
                 key = imap ? imap[it] : it;
             }
             keys[t] = key;
@@ -81,9 +89,9 @@ __global__ void __launch_bounds__(kSortThreads) encode_sorted_kernel(
             const uint64_t out = base + threadIdx.x * kSortItemsPerThread + t;
             if (out < n) {
                 const uint64_t s = permute_index(base + vals[t], n, seed);
-                const NodeAos nd = src[s];
+                const NodeAos nd = checked(src[s], n_users, n_items, err);
                 uint32_t uu = umap ? umap[nd.u] : nd.u;
-                uint32_t ii = keys[t];
+                uint32_t ii = (imap ? imap[nd.i] : nd.i);        // equals keys[t] unless the record was replaced
                 uu |= row_flags_to_code(uprec[uu]);
                 ii |= row_flags_to_code(iprec[ii]);
                 r[out] = nd.r; u[out] = uu; i[out] = ii;
@@ -118,23 +126,32 @@ __global__ void scatter_kernel(const float* src, uint32_t rows, const uint32_t* 
     }
 }
 
+// Output row e is the arena row row_map[e] (caller's id order) or, without a map, the arena row of
+// sorted index e (sorted-index order).
 template <int K>
 __global__ void gather_kernel(const __half* a16, const float* a32, const uint8_t* prec_row, uint32_t rows,
-                              const uint32_t* row_map, float* dst) {
+                              const uint32_t* row_map, RowLayout layout, float* dst) {
     const uint64_t total = (uint64_t)rows * K;
     for (uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (uint64_t)gridDim.x * blockDim.x) {
         const uint32_t e = (uint32_t)(t / K);
         const int d = (int)(t % K);
-        const uint32_t row = row_map ? row_map[e] : e;
+        const uint32_t row = row_map ? row_map[e] : arena_row(layout, e);
         const size_t o = (size_t)row * K + phys_of_logical(K, d);
         dst[t] = (prec_row[row] & kRowPrec) ? a32[o] : __half2float(a16[o]);
     }
 }
 
-// mem_cpy_fp162fp32 (precision_switching.h:1-6) without the re-allocation around it.
-__global__ void promote_kernel(const __half* a16, float* a32, uint64_t begin, uint64_t end) {
-    for (uint64_t t = begin + (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; t < end; t += (uint64_t)gridDim.x * blockDim.x)
-        a32[t] = __half2float(a16[t]);
+// mem_cpy_fp162fp32 (precision_switching.h:1-6) without the re-allocation around it: widens the rows of
+// the sorted indices [begin, end) - one group - wherever the layout put them, and marks them fp32.
+template <int K>
+__global__ void promote_kernel(const __half* a16, float* a32, uint8_t* row_flags, RowLayout layout, uint32_t begin, uint32_t end) {
+    const uint64_t total = (uint64_t)(end - begin) * K;
+    for (uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t row = arena_row(layout, begin + (uint32_t)(t / K));
+        const size_t o = (size_t)row * K + (size_t)(t % K);
+        a32[o] = __half2float(a16[o]);
+        if (t % K == 0) row_flags[row] |= kRowPrec;
+    }
 }
 
 __device__ __forceinline__ uint64_t splitmix64(uint64_t x) {
@@ -209,32 +226,24 @@ __global__ void init_normal_kernel(float* dst, uint64_t count, uint64_t seed, ui
 
 cudaError_t launch_encode_stream(const void* d_src_aos, uint64_t n, bool shuffle, uint64_t seed,
                                  const uint32_t* user_map, const uint32_t* item_map,
-                                 const uint8_t* uprec_row, const uint8_t* iprec_row, uint32_t n_items,
+                                 const uint8_t* uprec_row, const uint8_t* iprec_row, uint32_t n_users, uint32_t n_items,
+                                 uint32_t item_rows, uint32_t* err_flag,
                                  float* r, uint32_t* u, uint32_t* i, uint32_t* src_out, uint32_t src_base,
                                  cudaStream_t st) {
     if (n == 0) return cudaSuccess;
     const NodeAos* src = static_cast<const NodeAos*>(d_src_aos);
     if (shuffle) {
         int key_bits = 1;
-        while (key_bits < 31 && (1ull << key_bits) < (uint64_t)n_items + 1) key_bits++;
+        while (key_bits < 31 && (1ull << key_bits) < (uint64_t)item_rows + 1) key_bits++;
         const uint64_t windows = (n + kWindow - 1) / kWindow;
         const uint64_t cap = (uint64_t)sm_count() * 8;
         const int grid = (int)(windows < cap ? windows : cap);
         encode_sorted_kernel<<<grid, kSortThreads, 0, st>>>(src, n, seed, user_map, item_map, uprec_row, iprec_row,
-                                                             key_bits, r, u, i, src_out, src_base);
+                                                             n_users, n_items, err_flag, key_bits, r, u, i, src_out, src_base);
     } else {
         encode_kernel<<<grid_for(n, 256), 256, 0, st>>>(src, n, 0, seed, user_map, item_map, uprec_row, iprec_row,
-                                                         r, u, i, src_out, src_base);
+                                                         n_users, n_items, err_flag, r, u, i, src_out, src_base);
     }
-    return cudaGetLastError();
-}
-
-__global__ void mark_fp32_kernel(uint8_t* flags, uint32_t n) {
-    for (uint32_t j = blockIdx.x * blockDim.x + threadIdx.x; j < n; j += gridDim.x * blockDim.x) flags[j] |= kRowPrec;
-}
-cudaError_t launch_mark_fp32(uint8_t* row_flags, uint32_t n, cudaStream_t st) {
-    if (n == 0) return cudaSuccess;
-    mark_fp32_kernel<<<grid_for(n, 256), 256, 0, st>>>(row_flags, n);
     return cudaGetLastError();
 }
 
@@ -307,19 +316,22 @@ cudaError_t launch_scatter_factors(int K, const float* src, uint32_t rows, const
 }
 
 cudaError_t launch_gather_factors(int K, Arena a, const uint8_t* prec_row, uint32_t rows,
-                                  const uint32_t* row_map, float* dst, cudaStream_t st) {
+                                  const uint32_t* row_map, const RowLayout& layout, float* dst, cudaStream_t st) {
     if (rows == 0) return cudaSuccess;
     const int g = grid_for((uint64_t)rows * K, 256);
-    if (K == 128) gather_kernel<128><<<g, 256, 0, st>>>(a.f16, a.f32, prec_row, rows, row_map, dst);
-    else if (K == 64) gather_kernel<64><<<g, 256, 0, st>>>(a.f16, a.f32, prec_row, rows, row_map, dst);
+    if (K == 128) gather_kernel<128><<<g, 256, 0, st>>>(a.f16, a.f32, prec_row, rows, row_map, layout, dst);
+    else if (K == 64) gather_kernel<64><<<g, 256, 0, st>>>(a.f16, a.f32, prec_row, rows, row_map, layout, dst);
     else return cudaErrorInvalidValue;
     return cudaGetLastError();
 }
 
-cudaError_t launch_promote_rows(int K, Arena a, uint32_t row_begin, uint32_t row_end, cudaStream_t st) {
-    if (row_end <= row_begin) return cudaSuccess;
-    const uint64_t b = (uint64_t)row_begin * K, e = (uint64_t)row_end * K;
-    promote_kernel<<<grid_for(e - b, 256), 256, 0, st>>>(a.f16, a.f32, b, e);
+cudaError_t launch_promote_rows(int K, Arena a, uint8_t* row_flags, const RowLayout& layout, uint32_t sorted_begin, uint32_t sorted_end,
+                                cudaStream_t st) {
+    if (sorted_end <= sorted_begin) return cudaSuccess;
+    const int g = grid_for((uint64_t)(sorted_end - sorted_begin) * K, 256);
+    if (K == 128) promote_kernel<128><<<g, 256, 0, st>>>(a.f16, a.f32, row_flags, layout, sorted_begin, sorted_end);
+    else if (K == 64) promote_kernel<64><<<g, 256, 0, st>>>(a.f16, a.f32, row_flags, layout, sorted_begin, sorted_end);
+    else return cudaErrorInvalidValue;
     return cudaGetLastError();
 }
 

@@ -17,7 +17,8 @@
 //     for an old load also waits for every younger load on the same scoreboard);
 //   * the row of an item that repeats (the stream is item-sorted inside shuffle windows) stays in
 //     registers for the whole run and is written back once;
-//   * chunks are handed out in spans of eight through one atomic ticket per span.
+//   * chunks are handed out in runs of up to eight through one atomic ticket per run; the runs shrink
+//     to single chunks near the end of the stream, so that all workers finish together.
 //   * user rows are written back as vector reductions of their change whenever several workers run,
 //     so racing updates of one user add up instead of overwriting each other (add_row_delta).
 // The item lead is short on purpose.  Between the request of an item row and its write-back (a plain
@@ -271,9 +272,10 @@ struct KernelArgs {
     int epoch;                    // AFP: epoch index
     int add_user_delta;           // user rows are written back as reductions of the change (concurrent launches)
     unsigned workers;             // concurrent sequential workers actually launched
-    unsigned long long* next_chunk;   // work counter, zero at launch: chunks beyond the first two per
+    unsigned long long* next_chunk;   // work counter, zero at launch: chunks beyond the first two runs per
                                       // worker are handed out dynamically, so the launch never depends on
                                       // every block being resident at the same time
+    unsigned long long* zero_counter; // another counter, which this launch resets for a later launch
 };
 
 // ---- MuPPET (muppet/muppet_sgd_kernel.h:7-48, 121-264; _k64.h) -------------------------------
@@ -631,7 +633,7 @@ constexpr uint32_t F_UDUP = 2u;     // its user also occurs among the NS ratings
 constexpr uint32_t F_RS = 4u;       // its item differs from the item of the rating before it (a run starts)
 constexpr uint32_t F_IDUP = 8u;     // run start whose item also occurs among the NS ratings before it
 
-constexpr int kSpan = 8;            // consecutive chunks handed out together (one ticket per span)
+constexpr int kSpan = 8;            // consecutive chunks handed out together (the longest run of one ticket)
 
 // Shared memory of one worker: two chunks of records, then the user ring, then the item ring.  A ring
 // slot is as large as the widest row its side can hold in this launch.
@@ -660,7 +662,6 @@ __global__ void __launch_bounds__(256, (UM == ROWS_HALF && IM == ROWS_HALF && !S
     const uint64_t worker = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) / TS;
     const uint64_t W = a.workers;
     const uint64_t nchunks = (a.s.n + TS - 1) / TS;
-    const uint64_t nspans = (nchunks + kSpan - 1) / kSpan;
 
     unsigned char* const mine = smem_raw + (size_t)(threadIdx.x / TS) * SM::kBytes;
     uint4* const recs = reinterpret_cast<uint4*>(mine);                  // [2][TS]
@@ -683,21 +684,35 @@ __global__ void __launch_bounds__(256, (UM == ROWS_HALF && IM == ROWS_HALF && !S
     if (worker >= W) return;
 
     // ---- which chunks this worker processes ----
-    // Spans of kSpan consecutive chunks: span `worker`, span `worker + W`, then spans 2W + ticket from
-    // the shared counter.  A ticket is requested one span before it is needed and stays in lane 0
-    // until then, so the launch neither waits for the counter nor depends on all blocks being resident.
-    uint64_t span_cur = worker, span_next = worker + W;
-    int kin = 0;
-    unsigned long long ticket = (m == 0) ? atomicAdd(a.next_chunk, 1ull) : 0ull;
+    // Runs of consecutive chunks: first the static runs [worker*kSpan, +kSpan) and [(worker+W)*kSpan,
+    // +kSpan), then runs handed out by the shared counter, which counts chunks beyond the static part.
+    // A dynamic run is kSpan chunks long while plenty of work is left and shrinks to a single chunk as
+    // the counter nears the end (its length is what is left, as seen at the previous ticket, divided by
+    // twice the number of workers), so that the workers finish within about one chunk of each other.  A
+    // ticket is requested one run before it is needed and stays in lane 0 until then, so the launch
+    // neither waits for the counter nor depends on all blocks being resident.
+    const uint64_t static_chunks = 2 * W * kSpan;
+    const uint64_t dyn_chunks = nchunks > static_chunks ? nchunks - static_chunks : 0;
+    auto run_length = [&](unsigned long long seen) -> unsigned {
+        const uint64_t left = dyn_chunks > seen ? dyn_chunks - seen : 0;
+        const uint64_t g = left / (2 * W);
+        return g >= (uint64_t)kSpan ? (unsigned)kSpan : (g < 1 ? 1u : (unsigned)g);
+    };
+    uint64_t run_cur = worker * kSpan, run_next = (worker + W) * kSpan;
+    unsigned len_cur = kSpan, len_next = kSpan, kin = 0;
+    unsigned tlen = run_length(0);
+    unsigned long long ticket = (m == 0) ? atomicAdd(a.next_chunk, (unsigned long long)tlen) : 0ull;
+    if (blockIdx.x == 0 && threadIdx.x == 0) *a.zero_counter = 0ull;      // the counter of the launch after next
     auto next_chunk_id = [&]() -> uint64_t {
-        if (span_cur >= nspans) return ~0ull;
-        const uint64_t ci = span_cur * kSpan + kin;
-        if (++kin == kSpan) {
+        if (run_cur >= nchunks) return ~0ull;
+        const uint64_t ci = run_cur + kin;
+        if (++kin == len_cur) {
             kin = 0;
-            span_cur = span_next;
+            run_cur = run_next; len_cur = len_next;
             const unsigned lo = __shfl_sync(wmask, (unsigned)ticket, 0, TS), hi = __shfl_sync(wmask, (unsigned)(ticket >> 32), 0, TS);
-            span_next = 2 * W + (((uint64_t)hi << 32) | lo);
-            ticket = (m == 0) ? atomicAdd(a.next_chunk, 1ull) : 0ull;
+            len_next = __shfl_sync(wmask, tlen, 0, TS);
+            run_next = static_chunks + (((uint64_t)hi << 32) | lo);
+            if (m == 0) { tlen = run_length(ticket); ticket = atomicAdd(a.next_chunk, (unsigned long long)tlen); }
         }
         return ci < nchunks ? ci : ~0ull;
     };
@@ -1006,15 +1021,19 @@ int sm_count() {
 }
 
 cudaError_t launch_train(int K, TrainKind kind, const Stream& s, Arena P, Arena Q, float lr, float lam,
-                         const SampleStats* stats, RowClass row_class, unsigned workers, unsigned long long* work_counter,
+                         const SampleStats* stats, RowClass row_class, unsigned workers, WorkCounters* counters,
                          int bits, int epoch, bool add_user_delta, cudaStream_t st, LaunchShape* shape) {
     KernelArgs a;
     a.add_user_delta = add_user_delta ? 1 : 0;
-    a.s = s; a.P = P; a.Q = Q; a.lr = lr; a.lam = lam; a.workers = workers; a.next_chunk = work_counter; a.bits = bits; a.epoch = epoch;
+    a.s = s; a.P = P; a.Q = Q; a.lr = lr; a.lam = lam; a.workers = workers; a.bits = bits; a.epoch = epoch;
     if (stats) a.st = *stats;
     if (s.n == 0) { if (shape) *shape = LaunchShape(); return cudaSuccess; }
-    cudaError_t e0 = cudaMemsetAsync(work_counter, 0, sizeof(unsigned long long), st);
-    if (e0 != cudaSuccess) return e0;
+    // Launches of one engine run one after the other on its stream.  Launch number L hands out chunks
+    // through counter L mod 4 and resets counter (L + 2) mod 4, which the launch after next will use and
+    // which no launch in flight touches; all four start at zero.
+    a.next_chunk = counters->d_slots + (counters->launches & 3);
+    a.zero_counter = counters->d_slots + ((counters->launches + 2) & 3);
+    counters->launches++;
     if (K == 128) return launch_k<128>(kind, a, stats != nullptr, row_class, workers, st, shape);
     if (K == 64) return launch_k<64>(kind, a, stats != nullptr, row_class, workers, st, shape);
     return cudaErrorInvalidValue;

@@ -26,7 +26,11 @@ EXPORTS = [
     "mascot_get_test_ratings", "mascot_promote_group", "mascot_reload_train", "mascot_stream_source_index", "mascot_get_stream_order", "mascot_rmse_host", "mascot_rmse_device", "mascot_rmse_device_noalloc",
     "mascot_set_ratings_sharded", "mascot_is_check_epoch", "mascot_stats_begin", "mascot_train_segment", "mascot_stats_fetch",
     "mascot_stats_apply", "mascot_item_rows", "mascot_sync", "mascot_get_stream", "mascot_eval_sq_error", "mascot_train_epoch_streamed",
+    "mascot_release_scratch", "mascot_comm_unique_id", "mascot_shard_init", "mascot_shard_set_ratings", "mascot_shard_train_epoch",
+    "mascot_shard_eval_rmse", "mascot_shard_gather_factors", "mascot_shard_info", "mascot_shard_schedule", "mascot_probe_read_bandwidth", "mascot_get_timings", "mascot_get_worker_count",
 ]
+
+COMM_ID_BYTES = 128
 
 
 class Config(C.Structure):
@@ -225,6 +229,44 @@ class Engine:
         train = as_ratings(train)
         self.reload_train_raw(train.ctypes.data, train.size)
 
+    # ---- sharded training inside the library (one engine per GPU, NCCL between them) ----
+    def shard_init(self, comm_id, rank, world, blocks_per_gpu=1, timeout_ms=0):
+        """Join the group identified by the 128 bytes `comm_id` (see comm_unique_id)."""
+        buf = (C.c_ubyte * COMM_ID_BYTES).from_buffer_copy(bytes(comm_id))
+        self._check(self._lib.mascot_shard_init(self._h, buf, C.c_uint32(rank), C.c_uint32(world), C.c_uint32(blocks_per_gpu),
+                                                C.c_uint32(timeout_ms)))
+
+    def shard_set_ratings(self, train, test, n_users, n_items):
+        train, test = as_ratings(train), as_ratings(test)
+        self.shard_set_ratings_raw(train.ctypes.data, train.size, test.ctypes.data, test.size, n_users, n_items)
+
+    def shard_set_ratings_raw(self, train_ptr, n_train, test_ptr, n_test, n_users, n_items):
+        self._check(self._lib.mascot_shard_set_ratings(self._h, C.c_void_p(train_ptr), C.c_uint64(n_train), C.c_void_p(test_ptr),
+                                                       C.c_uint64(n_test), C.c_uint32(n_users), C.c_uint32(n_items)))
+        info = self.shard_info()
+        self.n_users, self.n_items, self.n_train, self.n_test = n_users, n_items, info["local_ratings"], info["local_test_ratings"]
+
+    def shard_train_epoch(self, epoch):
+        st = EpochStats()
+        self._check(self._lib.mascot_shard_train_epoch(self._h, C.c_uint32(epoch), C.byref(st)))
+        return st
+
+    def shard_eval_rmse(self):
+        v = C.c_double()
+        self._check(self._lib.mascot_shard_eval_rmse(self._h, C.byref(v)))
+        return v.value
+
+    def shard_gather_factors(self):
+        self._check(self._lib.mascot_shard_gather_factors(self._h))
+
+    def shard_info(self):
+        r, w, b, n, nt, sent = C.c_uint32(), C.c_uint32(), C.c_uint32(), C.c_uint64(), C.c_uint64(), C.c_uint64()
+        self._check(self._lib.mascot_shard_info(self._h, C.byref(r), C.byref(w), C.byref(b), C.byref(n), C.byref(nt), C.byref(sent)))
+        return dict(rank=r.value, world=w.value, blocks=b.value, local_ratings=n.value, local_test_ratings=nt.value, bytes_sent=sent.value)
+
+    def release_scratch(self):
+        self._check(self._lib.mascot_release_scratch(self._h))
+
     def init_factors(self):
         self._check(self._lib.mascot_init_factors(self._h))
 
@@ -291,6 +333,47 @@ class Engine:
         v = C.c_uint64()
         self._check(self._lib.mascot_stream_source_index(self._h, C.c_uint64(pos), C.byref(v)))
         return v.value
+
+
+def write_binary_ratings(path, records, n_users, n_items):
+    """Write the binary rating file of the command-line tools (cli/io_formats.h): `records` is an (n, 3)
+    uint32 view or a RATING array with compact ids."""
+    recs = as_ratings(records)
+    header = np.zeros(1, np.dtype([("magic", "<u4"), ("version", "<u4"), ("n", "<u8"), ("n_users", "<u4"), ("n_items", "<u4"),
+                                   ("flags", "<u4"), ("reserved", "<u4")]))
+    header["magic"], header["version"], header["n"] = 0x5243534d, 1, recs.size
+    header["n_users"], header["n_items"], header["flags"] = n_users, n_items, 1
+    with open(path, "wb") as f:
+        f.write(header.tobytes())
+        recs.tofile(f)
+
+
+def comm_unique_id():
+    """128 opaque bytes naming a new group of sharded engines (made by one rank, carried to the others)."""
+    buf = (C.c_ubyte * COMM_ID_BYTES)()
+    rc = load().mascot_comm_unique_id(buf)
+    if rc != OK:
+        raise MascotError(rc, load().mascot_last_error(None).decode())
+    return bytes(buf)
+
+
+def shard_schedule(world, blocks_per_gpu, rank, step):
+    """(block trained, rank it is sent to, block that arrives, rank it comes from) - needs no device."""
+    out = [C.c_uint32() for _ in range(4)]
+    rc = load().mascot_shard_schedule(C.c_uint32(world), C.c_uint32(blocks_per_gpu), C.c_uint32(rank), C.c_uint32(step),
+                                      *[C.byref(o) for o in out])
+    if rc != OK:
+        raise MascotError(rc, "bad schedule arguments")
+    return tuple(o.value for o in out)
+
+
+def probe_read_bandwidth(nbytes, passes=20, device=0):
+    """GB/s of 128-bit L2-only loads over a buffer of `nbytes` (L2-resident when small, HBM when large)."""
+    v = C.c_double()
+    rc = load().mascot_probe_read_bandwidth(C.c_int(device), C.c_uint64(nbytes), C.c_uint32(passes), C.byref(v))
+    if rc != OK:
+        raise MascotError(rc, load().mascot_last_error(None).decode())
+    return v.value
 
 
 def rmse_host(P, Q, test, k, device=0):

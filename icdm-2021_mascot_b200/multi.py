@@ -1,4 +1,8 @@
-"""Sharded (multi-GPU) training on top of the libmascot building blocks: one process per GPU.
+"""Host-side model of sharded (multi-GPU) training, kept as a TEST DRIVER: the product path is the C++
+implementation inside libmascot (csrc/shard.cu, mascot_shard_* in include/mascot.h).  This module
+restates its partition plan and its block rotation in Python, so that CPU tests can run the schedule
+with gloo ranks and a CPU stand-in for the engine, and so that GPU tests have an independent replay to
+compare the library against.
 
 Scheme (the reference is single-GPU; this has no counterpart there): the users are dealt to the
 ranks so that every rank gets the same mix of degrees, and with them their ratings and their rows of
@@ -12,8 +16,10 @@ races between GPUs, and after `world` sub-epochs every block is back home.  The 
 communication is that block hand-over (point-to-point, NCCL send/recv through torch.distributed on
 GPUs); the small g-switching statistics and the RMSE partial sums are all-reduced.
 
-The schedule and the exchange are written against a tiny shard interface, so the same code drives
-libmascot engines on GPUs and a CPU stand-in in the tests.
+With `blocks` = 2 x world the library's overlapped variant is modelled: rank g trains block
+(2 g + t) mod blocks in step t and a block is trained by its receiver two steps after it was sent.
+
+The schedule and the exchange are written against a tiny shard interface (see tests/test_multi_cpu.py).
 """
 import numpy as np
 
@@ -21,8 +27,9 @@ import numpy as np
 class Plan:
     """Who owns which user and which item block an item belongs to."""
 
-    def __init__(self, world, user_rank, item_block, user_degree, item_degree, item_sorted_index):
+    def __init__(self, world, user_rank, item_block, user_degree, item_degree, item_sorted_index, blocks=None):
         self.world = world
+        self.blocks = blocks or world             # item blocks in all (world x blocks per GPU)
         self.user_rank = user_rank                # [n_users] compact id -> rank
         self.item_block = item_block              # [n_items] compact id -> block (= sorted index mod world)
         self.user_degree = user_degree
@@ -30,8 +37,9 @@ class Plan:
         self.item_sorted_index = item_sorted_index
 
 
-def make_plan(train_u, train_i, n_users, n_items, world):
+def make_plan(train_u, train_i, n_users, n_items, world, blocks=None):
     """Degree tables of the whole training set, user dealing and item blocks."""
+    blocks = blocks or world
     user_degree = np.bincount(train_u, minlength=n_users).astype(np.uint32)
     item_degree = np.bincount(train_i, minlength=n_items).astype(np.uint32)
     # same order as the engine's set-up: ascending degree, ties by ascending id
@@ -45,8 +53,8 @@ def make_plan(train_u, train_i, n_users, n_items, world):
     user_rank[user_sorted[::-1]] = np.where(rnd % 2 == 0, idx, world - 1 - idx)
     item_sorted_index = np.empty(n_items, np.uint32)
     item_sorted_index[item_sorted] = np.arange(n_items, dtype=np.uint32)
-    item_block = (item_sorted_index % np.uint32(world)).astype(np.int32)
-    return Plan(world, user_rank, item_block, user_degree, item_degree, item_sorted_index)
+    item_block = (item_sorted_index % np.uint32(blocks)).astype(np.int32)
+    return Plan(world, user_rank, item_block, user_degree, item_degree, item_sorted_index, blocks)
 
 
 def shard_ratings(plan, rank, train, test):
@@ -55,8 +63,8 @@ def shard_ratings(plan, rank, train, test):
     blk = plan.item_block[mine["i"]]
     order = np.argsort(blk, kind="stable")
     mine = np.ascontiguousarray(mine[order])
-    counts = np.bincount(blk, minlength=plan.world)
-    seg = np.zeros(plan.world + 1, np.uint64)
+    counts = np.bincount(blk, minlength=plan.blocks)
+    seg = np.zeros(plan.blocks + 1, np.uint64)
     seg[1:] = np.cumsum(counts)
     my_test = np.ascontiguousarray(test[plan.user_rank[test["u"]] == rank])
     return mine, seg, my_test
@@ -103,19 +111,24 @@ def exchange_block(dist, shard, send_block, recv_block, dst, src):
     return nbytes
 
 
-def train_epoch(dist, shard, rank, world, epoch, comm_device="cpu"):
-    """One epoch = `world` sub-epochs with a block rotation after each.  Returns bytes sent."""
+def train_epoch(dist, shard, rank, world, epoch, comm_device="cpu", schedule=None):
+    """One epoch = `blocks` steps with a block hand-over after each.  `schedule(rank, step)` returns
+    (block trained, rank it goes to, block that arrives, rank it comes from); default: one block per
+    rank.  Returns bytes sent."""
     import torch
     check = shard.is_check_epoch(epoch)
     sent = 0
+    steps = getattr(getattr(shard, "plan", None), "blocks", world) if schedule else world
+    if schedule is None:
+        schedule = lambda r, s: ((r + s) % world, (r - 1) % world, (r + s + 1) % world, (r + 1) % world)
     with shard.device_order():
         if check:
             shard.stats_begin()
-        for s in range(world):
-            b = (rank + s) % world
+        for s in range(steps):
+            b, dst, incoming, src = schedule(rank, s)
             shard.train_segment(epoch, b, collect_stats=check)
             if world > 1:
-                sent += exchange_block(dist, shard, b, (rank + s + 1) % world, (rank - 1) % world, (rank + 1) % world)
+                sent += exchange_block(dist, shard, b, incoming, dst, src)
         promoted = (0, 0)
         if check:
             parts = shard.stats_fetch()
@@ -134,11 +147,13 @@ def gather_item_factors(dist, shard, world):
     """After an epoch every rank holds only its home block fresh; make all of Q fresh everywhere."""
     if world == 1:
         return
+    blocks = getattr(getattr(shard, "plan", None), "blocks", world)
+    per_rank = blocks // world
     with shard.device_order():
-        for b in range(world):
+        for b in range(blocks):
             for t in shard.block_tensors(b):
                 buf = t.contiguous()
-                dist.broadcast(buf, src=b)
+                dist.broadcast(buf, src=b // per_rank)     # the home of block b
                 t.copy_(buf)
     shard.sync()
 
@@ -150,83 +165,3 @@ def global_rmse(dist, shard, world, comm_device="cpu"):
     if world > 1:
         dist.all_reduce(t)
     return float(torch.sqrt(t[0] / t[1]).item()) if t[1] > 0 else float("nan")
-
-
-class _DeviceBytes:
-    """Raw device memory exposed through the CUDA array interface, so torch can wrap it without a copy."""
-
-    def __init__(self, ptr, nbytes):
-        self.__cuda_array_interface__ = {"shape": (int(nbytes),), "typestr": "|u1", "data": (int(ptr), False), "version": 2}
-
-
-class EngineShard:
-    """A libmascot engine holding one rank's shard."""
-
-    def __init__(self, M, cfg, plan, rank, train, test, n_users, n_items):
-        import torch
-        self.M, self.plan, self.rank = M, plan, rank
-        mine, seg, my_test = shard_ratings(plan, rank, train, test)
-        self.n_local = int(mine.size)
-        self.local_ratings = mine                   # host copy of this rank's ratings, in segment order
-        self.n_items = int(n_items)
-        self.engine = M.Engine(cfg)
-        self.engine.set_ratings_sharded(mine, seg, my_test, n_users, n_items, plan.user_degree, plan.item_degree)
-        self.device = torch.device("cuda", int(cfg.device))
-        self.stream = torch.cuda.ExternalStream(self.engine.stream_handle(), device=self.device)
-        self._views = {}
-        self._live = None
-
-    def device_order(self):
-        """Context in which torch's current stream is the engine's stream."""
-        import torch
-        return torch.cuda.stream(self.stream)
-
-    def _live_arenas(self):
-        """(binary16 arena holds live item rows, fp32 arena holds live item rows): an item row lives in
-        exactly one of them, by its group's precision, so an arena without live rows need not travel.
-        Every rank reaches the same answer, because all take the same switching decisions."""
-        if self._live is None:
-            prec = self.engine.group_info(1)[1]
-            self._live = (bool((prec == 0).any()), bool((prec != 0).any()))
-        return self._live
-
-    def block_tensors(self, b):
-        """Strided byte views [rows of block b, bytes per row] of the item arenas that hold live rows."""
-        import torch
-        if b not in self._views:
-            views = []
-            for live, (ptr, nbytes) in zip(self._live_arenas(), self.engine.item_rows(0, self.n_items)):
-                if live and ptr and nbytes:
-                    whole = torch.as_tensor(_DeviceBytes(ptr, nbytes), device=self.device).view(self.n_items, nbytes // self.n_items)
-                    views.append(whole[b::self.plan.world])
-            self._views[b] = views
-        return self._views[b]
-
-    def is_check_epoch(self, epoch):
-        return self.engine.is_check_epoch(epoch)
-
-    def stats_begin(self):
-        self.engine.stats_begin()
-
-    def train_segment(self, epoch, b, collect_stats=False):
-        self.engine.train_segment(epoch, b, collect_stats, wait=False)
-
-    def sync(self):
-        self.engine.sync()
-
-    def stats_fetch(self):
-        return self.engine.stats_fetch()
-
-    def stats_apply(self, epoch, *sums):
-        promoted = self.engine.stats_apply(epoch, *sums)
-        if promoted[1]:
-            self._live = None                     # item groups changed precision: re-derive which arenas travel
-            self._views.clear()
-        return promoted
-
-    def eval_sq_error(self):
-        return self.engine.eval_sq_error()
-
-    def close(self):
-        self._views.clear()
-        self.engine.close()

@@ -38,7 +38,7 @@ enum {
     MASCOT_ERR_OOM = -3,          /* host or device allocation failed */
     MASCOT_ERR_STATE = -4,        /* call order violated (e.g. training before ratings were set) */
     MASCOT_ERR_NO_DEVICE = -5,    /* no CUDA device / requested device absent */
-    MASCOT_ERR_TIMEOUT = -6,      /* a bounded wait (multi-GPU exchange) ran out */
+    MASCOT_ERR_TIMEOUT = -6,      /* a bounded wait on another rank of a sharded group ran out */
     MASCOT_ERR_UNSUPPORTED = -7,  /* valid request the engine does not implement */
     MASCOT_ERR_COMM = -8          /* NCCL / peer communication failure */
 };
@@ -119,6 +119,19 @@ typedef struct mascot_epoch_stats {
                                     item element), 2 for fp16 storage and 4 for fp32            */
 } mascot_epoch_stats;
 
+/* The phases of the reference's timing report (mf_methods.cu:401-418), in microseconds: host clock
+ * around phases that end with a synchronisation, CUDA events for the update kernels. */
+typedef struct mascot_timings {
+    double rating_histogram_us;    /* upload, id check, degree histogram and degree sort (user_item_rating_histogram) */
+    double grouping_us;            /* grouping walk, group / map / flag tables (split_group_based_equal_size_...) */
+    double reconstruction_us;      /* id remap, shuffle, coding of the stream and the test set (matrix_reconstruction) */
+    double copy_to_grouped_us;     /* factors scattered into the arenas (cpy2grouped_parameters_gpu_...) */
+    double additional_init_us;     /* arenas, statistics buffers (mf_methods.cu:93-166) */
+    double precision_switching_us; /* total: widening of promoted groups, re-tagging and re-partition of the stream */
+    double error_computation_us;   /* total: folding and read-back of the statistics, group errors */
+    double update_us;              /* total time of the update kernels */
+} mascot_timings;
+
 typedef struct mascot_handle mascot_handle;
 
 /* ABI self-description for bindings: version and the byte sizes of the two public structs. */
@@ -139,14 +152,19 @@ MASCOT_API const char* mascot_status_string(int status);
  * [0,n_items), the id space produced by read_training_dataset, io_utils.h:93-106).  Uploads them,
  * and for MASCOT_V_MASCOT runs the m-quantization set-up: degree histogram, ascending sort,
  * grouping, id -> sorted-index remap (user_item_rating_histogram / split_group_... /
- * matrix_reconstruction, preprocess_utils.h:54-255; host shuffle mf_methods.cu:38-42). */
+ * matrix_reconstruction, preprocess_utils.h:54-255; host shuffle mf_methods.cu:38-42).  The whole
+ * set-up runs on the device after one host->device copy of each array; the host only walks per-entity
+ * tables.  At most 2^32 - 1 ratings per engine. */
 MASCOT_API int mascot_set_ratings(mascot_handle* h, const mascot_rating* train, uint64_t n_train,
                        const mascot_rating* test, uint64_t n_test, uint32_t n_users, uint32_t n_items);
 
 /* Extension: replace the training stream by `train` (host memory, same id space and same
  * n_users / n_items as the last mascot_set_ratings) without redoing the set-up: one host->device
  * copy plus the encode kernel.  This is the per-step input path of an out-of-core / end-to-end
- * epoch.  The ids are not validated again. */
+ * epoch.  Ids are checked on the device while the stream is coded: an id out of range is never used as
+ * an index and makes the call return MASCOT_ERR_BAD_ARG (the stream then holds zero ratings of row 0 in
+ * its place and should be reloaded).  If groups have been promoted the new stream is partitioned by
+ * precision class like the one it replaces. */
 MASCOT_API int mascot_reload_train(mascot_handle* h, const mascot_rating* train, uint64_t n_train);
 
 /* N(0, 0.01^2) factors from a counter-based generator seeded with cfg.seed (init_model_single /
@@ -159,7 +177,17 @@ MASCOT_API int mascot_set_factors(mascot_handle* h, const float* P, const float*
 /* One epoch = one pass of the update kernel over the training stream with lr_schedule[epoch]; for
  * MASCOT_V_MASCOT also the sampled group-error statistics on check epochs and the precision
  * switching that follows (epoch body of mf_methods.cu:168-397; precision_switching.h:8-51).
- * `stats` may be NULL. */
+ * `stats` may be NULL.
+ * Sampling rule: on a check epoch every launched range of the stream - a segment, or, once groups have
+ * been promoted and several workers run, each precision class inside a segment - passes its last
+ * sample_ratio through the statistics kernel.  With one segment and no promoted group this is the
+ * reference's "last sample_ratio of the stream" (mf_methods.cu:102-103).  Segments are what the last
+ * mascot_set_ratings_sharded / mascot_train_epoch_streamed left (one segment after mascot_set_ratings).
+ * Per-worker state of the AFP trainer starts afresh with every launched range.
+ * After a promotion, and with more than one worker, the stream is stably re-ordered inside each segment
+ * by (user precision, item precision), so that every class runs a kernel instantiation without
+ * per-rating precision tests; mascot_stream_source_index / mascot_get_stream_order follow the new order.
+ * The deterministic mode never re-orders. */
 MASCOT_API int mascot_train_epoch(mascot_handle* h, uint32_t epoch, mascot_epoch_stats* stats);
 
 /* Test RMSE of the current factors, reduced exactly like gpu_test_rmse (rmse.h:168-189): fp32 dot
@@ -225,8 +253,9 @@ MASCOT_API int mascot_set_ratings_sharded(mascot_handle* h, const mascot_rating*
  * encoded and trained, so the epoch costs max(upload, updates) instead of their sum.  The seeded
  * permutation and the item-sorted windows stay inside a piece; afterwards the pieces are the
  * segments of the resident stream, as after mascot_reload_train.  Ids must be those given to
- * mascot_set_ratings (same users/items); the statistics of a check epoch come from the last
- * sample_ratio of the whole array.  No reference counterpart (the reference uploads once,
+ * mascot_set_ratings (same users/items; checked on the device, MASCOT_ERR_BAD_ARG as for
+ * mascot_reload_train); on a check epoch every piece contributes its own sampled tail (see
+ * mascot_train_epoch).  No reference counterpart (the reference uploads once,
  * mf_methods.cu:41-42).  AFP is not supported here (its per-worker state spans a whole epoch). */
 MASCOT_API int mascot_train_epoch_streamed(mascot_handle* h, uint32_t epoch, const mascot_rating* train, uint64_t n_train,
                                 mascot_epoch_stats* stats);
@@ -257,6 +286,66 @@ MASCOT_API int mascot_sync(mascot_handle* h);
 MASCOT_API int mascot_get_stream(mascot_handle* h, void** stream);
 /* Sum of squared test errors and number of test ratings of this engine (for an RMSE over shards). */
 MASCOT_API int mascot_eval_sq_error(mascot_handle* h, double* sum_sq, uint64_t* count);
+
+/* Accumulated phase times of this engine since mascot_create. */
+MASCOT_API int mascot_get_timings(mascot_handle* h, mascot_timings* out);
+/* Number of concurrent sequential workers the update launches of this engine ask for (the value of -wg, or
+ * the automatic choice for the current stream when cfg.num_workers == 0). */
+MASCOT_API int mascot_get_worker_count(mascot_handle* h, uint32_t* workers);
+
+/* Release the engine's grow-only device scratch (staging buffer of mascot_reload_train, sort buffers of
+ * the set-up and of the stream partition).  It is allocated again when next needed. */
+MASCOT_API int mascot_release_scratch(mascot_handle* h);
+
+/* ---- sharded training inside the library: one engine per GPU, one host thread or process per engine,
+ * NCCL between them.  No counterpart in the reference (single-GPU).  Users are pinned to a GPU with their
+ * ratings and their rows of P; the item factors are cut into world x blocks_per_gpu blocks that travel
+ * from GPU to GPU during an epoch, so that no two GPUs ever update the same row at once.  Every call of
+ * this section is collective: all engines of the group make it, in the same order.  Waits on other
+ * ranks are bounded by the group's timeout: MASCOT_ERR_TIMEOUT / MASCOT_ERR_COMM dissolve the group
+ * (the engine can still be read out and destroyed).  AFP is not sharded. ---- */
+
+#define MASCOT_COMM_ID_BYTES 128
+/* 128 opaque bytes that identify a group (an NCCL unique id).  One rank makes them; the caller carries
+ * them to the other ranks by any means it has (shared memory between threads, a file, a socket, MPI). */
+MASCOT_API int mascot_comm_unique_id(void* id_out);
+/* Join the engine (on its cfg.device) to the group `id` as rank `rank` of `world`.  blocks_per_gpu: 1 =
+ * a block is passed on when its training ends and the receiver waits for it; 2 = a block travels while
+ * its receiver trains another one (transfers hidden under the update kernels; the workers of a GPU then
+ * share half as many item rows at a time, which costs some convergence per epoch).  timeout_ms bounds
+ * every wait on another rank (0 = 60 s). */
+MASCOT_API int mascot_shard_init(mascot_handle* h, const void* id, uint32_t rank, uint32_t world, uint32_t blocks_per_gpu,
+                                 uint32_t timeout_ms);
+/* Like mascot_set_ratings, called by every rank with the WHOLE data set (same arrays on all ranks): the
+ * engine builds the common index space from the global degrees, keeps the ratings of the users dealt to
+ * its rank and orders them by the step of the block schedule at which their item block is on this GPU. */
+MASCOT_API int mascot_shard_set_ratings(mascot_handle* h, const mascot_rating* train, uint64_t n_train,
+                                        const mascot_rating* test, uint64_t n_test, uint32_t n_users, uint32_t n_items);
+/* One epoch over this rank's ratings: world x blocks_per_gpu update launches with the block hand-overs
+ * between them (ncclSend / ncclRecv on a transfer stream), on check epochs the all-reduce of the sampled
+ * statistics and the same precision switching on every rank.  `stats` reports this rank's share. */
+MASCOT_API int mascot_shard_train_epoch(mascot_handle* h, uint32_t epoch, mascot_epoch_stats* stats);
+/* Test RMSE over all ranks (double accumulation of the ranks' block sums): all-gathers the item blocks,
+ * evaluates this rank's test ratings, all-reduces (sum of squared errors, count). */
+MASCOT_API int mascot_shard_eval_rmse(mascot_handle* h, double* rmse);
+/* All-gather both factor matrices, after which mascot_get_factors on any rank returns the whole model. */
+MASCOT_API int mascot_shard_gather_factors(mascot_handle* h);
+/* Rank, world size, number of item blocks, this rank's training and test ratings, item-block bytes sent
+ * so far.  Any pointer may be NULL. */
+MASCOT_API int mascot_shard_info(mascot_handle* h, uint32_t* rank, uint32_t* world, uint32_t* blocks,
+                                 uint64_t* local_ratings, uint64_t* local_test_ratings, uint64_t* bytes_sent);
+/* The block schedule as a pure function (no device needed): in step `step` (0 <= step < world x
+ * blocks_per_gpu) rank `rank` trains block *train_block, then sends it to *send_to while *recv_block -
+ * trained by *recv_from in the same step - arrives; the arriving block is trained blocks_per_gpu steps
+ * later.  Any output pointer may be NULL. */
+MASCOT_API int mascot_shard_schedule(uint32_t world, uint32_t blocks_per_gpu, uint32_t rank, uint32_t step,
+                                     uint32_t* train_block, uint32_t* send_to, uint32_t* recv_block, uint32_t* recv_from);
+
+/* Measurement utility (no counterpart in the reference): GB/s at which all SMs of `device` read a buffer
+ * of `bytes` with 128-bit L2-only loads, `passes` times after a warm-up pass.  A buffer that fits in L2
+ * gives the L2 -> SM bandwidth the update kernel is judged against while the factors are L2-resident,
+ * one far larger than L2 the HBM read bandwidth.  Allocates and frees the buffer. */
+MASCOT_API int mascot_probe_read_bandwidth(int device, uint64_t bytes, uint32_t passes, double* gb_per_s);
 
 /* ---- handle-free evaluation: the `gpu_test_rmse` used by test_mf (test_mf/test.cu:56-72) ---- */
 

@@ -291,6 +291,52 @@ def mascot_epoch_hogwild(model, R, lr, lam, threads, rules):
                                   C.c_float(lr), C.c_float(lam), C.c_int(threads), C.byref(rules))
 
 
+# ---- the fast host-core baseline (oracle/host_loop.cpp): measured by bench.py, checked by RMSE only ----
+_HL = None
+
+
+def host_loop():
+    """ctypes handle of libhostloop.so; raises when the CPU lacks AVX2 / F16C / FMA."""
+    global _HL
+    if _HL is None:
+        path = os.path.join(_HERE, "libhostloop.so")
+        if not os.path.exists(path):
+            subprocess.check_call(["make", "-s", "-C", _HERE, "libhostloop.so"])
+        L = C.CDLL(path)
+        L.hl_max_threads.restype = C.c_int
+        L.hl_supported.restype = C.c_int
+        if not L.hl_supported():
+            raise OSError("this CPU lacks AVX2 / F16C / FMA: the fast host loop cannot run here")
+        _HL = L
+    return _HL
+
+
+class HostLoopModel:
+    """Factors of the fast host loop: binary16 rows (MASCOT, all groups still binary16) or fp32 rows (SGD)."""
+
+    def __init__(self, k, P, Q, half):
+        self.k, self.half = int(k), bool(half)
+        L = host_loop()
+        P = np.ascontiguousarray(P, np.float32); Q = np.ascontiguousarray(Q, np.float32)
+        if half:
+            self.P = np.empty(P.shape, np.uint16); self.Q = np.empty(Q.shape, np.uint16)
+            L.hl_to_half(_p(P), _p(self.P), C.c_uint64(P.size)); L.hl_to_half(_p(Q), _p(self.Q), C.c_uint64(Q.size))
+        else:
+            self.P, self.Q = P.copy(), Q.copy()
+
+    def epoch(self, R, lr, lam, threads):
+        R = as_nodes(R)
+        fn = host_loop().hl_mascot_half_epoch if self.half else host_loop().hl_sgd_epoch
+        fn(C.c_int(self.k), _p(R), C.c_uint64(R.shape[0]), _p(self.P), _p(self.Q), C.c_float(lr), C.c_float(lam), C.c_int(threads))
+
+    def factors(self):
+        if not self.half:
+            return self.P, self.Q
+        P = np.empty(self.P.shape, np.float32); Q = np.empty(self.Q.shape, np.float32)
+        host_loop().hl_to_float(_p(self.P), _p(P), C.c_uint64(P.size)); host_loop().hl_to_float(_p(self.Q), _p(Q), C.c_uint64(Q.size))
+        return P, Q
+
+
 def chunk_sequence(starts, vec, nnz):
     """Order in which one reference warp visits the rating array: for every drawn start, `vec`
     consecutive positions modulo nnz (sgd/sgd_kernel.h:21-33)."""

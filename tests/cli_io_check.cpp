@@ -46,5 +46,17 @@ int main(int argc, char** argv) {
         std::printf("max_err %.3g gap %.3g\n", err, gap);
         return 0;
     }
+    if (mode == "binmodel" && argc >= 3) {   // binary model: write, read back, compare bit for bit
+        const uint32_t k = 64, nu = 7, ni = 5;
+        std::vector<float> P((size_t)nu * k), Q((size_t)ni * k);
+        for (size_t j = 0; j < P.size(); j++) P[j] = 1.0f / (float)(j + 3);
+        for (size_t j = 0; j < Q.size(); j++) Q[j] = -2.5f / (float)(j + 7);
+        if (!mascot_io::save_model_binary(argv[2], nu, ni, P.data(), Q.data(), k)) return 4;
+        mascot_io::Model m;
+        if (!mascot_io::read_model(argv[2], m)) return 5;
+        const bool same = m.n_users == nu && m.n_items == ni && m.k == k && m.P == P && m.Q == Q;
+        std::printf("binmodel %s\n", same ? "identical" : "DIFFERENT");
+        return same ? 0 : 6;
+    }
     return 2;
 }

@@ -1,51 +1,60 @@
-"""Worker of tests/test_gpu_multi.py: one rank of a 2-GPU deterministic sharded run.  Launched with
-torch.distributed.run; writes this rank's factors for the parent test to compare with the replay."""
+"""Worker of tests/test_gpu_multi.py: one rank of a deterministic sharded run through the library's own
+multi-GPU path (mascot_shard_*: C++ schedule, NCCL hand-overs).  Started as a plain process per rank;
+the 128-byte group id travels through a file.  Writes this rank's results for the parent test.
+
+    python multi_gpu_worker.py <out_dir> <rank> <world> <blocks_per_gpu>
+"""
+import importlib.util
 import os
 import sys
+import time
 
 import numpy as np
-import torch
-import torch.distributed as dist
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 sys.path.insert(0, os.path.join(ROOT, "oracle"))
-from test_multi_cpu import HYPER, dataset, load_multi  # noqa: E402
+from test_multi_cpu import HYPER, dataset  # noqa: E402
 
 
 def main():
-    import importlib.util
-    out_dir = sys.argv[1]
-    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    out_dir, rank, world, per_gpu = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4])
     spec = importlib.util.spec_from_file_location("mascot_binding", os.path.join(ROOT, "icdm-2021_mascot_b200", "mascot.py"))
     M = importlib.util.module_from_spec(spec); sys.modules["mascot_binding"] = M; spec.loader.exec_module(M)
-    multi = load_multi()
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-    dist.init_process_group("nccl", device_id=dev)
-    try:
-        R, test, P, Q, n_users, n_items = dataset()
-        plan = multi.make_plan(R["u"], R["i"], n_users, n_items, world)
-        cfg = M.default_config(version=M.V_MASCOT, k=HYPER["k"], deterministic=1, shuffle=0, epoch=HYPER["epochs"],
-                               learning_rate=HYPER["lr"], decay=HYPER["decay"], lam=HYPER["lam"], user_group_num=HYPER["ug"],
-                               item_group_num=HYPER["ig"], sample_ratio=HYPER["sample_ratio"], interval=HYPER["interval"],
-                               error_threshold=HYPER["threshold"], device=local)
-        shard = multi.EngineShard(M, cfg, plan, rank, R, test, n_users, n_items)
-        shard.engine.set_factors(P, Q)
-        rm, promoted = [], []
-        for e in range(8):
-            _, pr = multi.train_epoch(dist, shard, rank, world, e, comm_device=dev)
-            multi.gather_item_factors(dist, shard, world)
-            rm.append(multi.global_rmse(dist, shard, world, comm_device=dev))
-            promoted.append(pr)
-        Pm, Qm = shard.engine.get_factors(1)
-        uprec, iprec = shard.engine.group_info(0)[1], shard.engine.group_info(1)[1]
-        np.savez(os.path.join(out_dir, f"gpu_rank{rank}.npz"), P=Pm, Q=Qm, rmse=np.array(rm), promoted=np.array(promoted),
-                 uprec=uprec, iprec=iprec)
-        shard.close()
-    finally:
-        dist.destroy_process_group()
+    id_path = os.path.join(out_dir, "group.id")
+    if rank == 0:
+        with open(id_path + ".tmp", "wb") as f:
+            f.write(M.comm_unique_id())
+        os.replace(id_path + ".tmp", id_path)
+    deadline = time.time() + 120
+    while not os.path.exists(id_path):
+        if time.time() > deadline:
+            raise SystemExit("no group id within two minutes")
+        time.sleep(0.05)
+    comm_id = open(id_path, "rb").read()
+    R, test, P, Q, n_users, n_items = dataset()
+    cfg = M.default_config(version=M.V_MASCOT, k=HYPER["k"], deterministic=1, shuffle=0, epoch=HYPER["epochs"],
+                           learning_rate=HYPER["lr"], decay=HYPER["decay"], lam=HYPER["lam"], user_group_num=HYPER["ug"],
+                           item_group_num=HYPER["ig"], sample_ratio=HYPER["sample_ratio"], interval=HYPER["interval"],
+                           error_threshold=HYPER["threshold"], device=rank)
+    eng = M.Engine(cfg)
+    eng.shard_init(comm_id, rank, world, per_gpu, timeout_ms=60000)
+    eng.shard_set_ratings(R, test, n_users, n_items)
+    eng.set_factors(P, Q)
+    rm, promoted = [], []
+    for e in range(8):
+        st = eng.shard_train_epoch(e)
+        rm.append(eng.shard_eval_rmse())
+        promoted.append([st.promoted_user_groups, st.promoted_item_groups])
+    info = eng.shard_info()
+    eng.shard_gather_factors()
+    Pm, Qm = eng.get_factors(1)
+    uprec, iprec = eng.group_info(0)[1], eng.group_info(1)[1]
+    u2s, i2s = eng.index_maps()
+    np.savez(os.path.join(out_dir, f"gpu_rank{rank}.npz"), P=Pm, Q=Qm, rmse=np.array(rm), promoted=np.array(promoted),
+             uprec=uprec, iprec=iprec, u2s=u2s, i2s=i2s, local=info["local_ratings"], sent=info["bytes_sent"],
+             test_ratings=eng.test_ratings(1))
+    eng.close()
 
 
 if __name__ == "__main__":

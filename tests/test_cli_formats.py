@@ -91,6 +91,60 @@ def test_model_files_round_trip(io_check, tmp_path):
     assert body[1].endswith(" ")
 
 
+def test_binary_rating_files_and_the_converter(io_check, tmp_path):
+    """convert_ratings: text -> binary -> the three text layouts, and the binary file parses to the same
+    ratings as the text it came from (ids compacted in first-seen order, then stored compact)."""
+    conv = os.path.join(BIN, "convert_ratings")
+    if not os.path.exists(conv):
+        pytest.skip("command-line tools not built")
+    rng = np.random.default_rng(4)
+    n = 500
+    users, items = rng.integers(1, 80, n), rng.integers(1, 50, n)
+    ratings = rng.choice(np.arange(0, 101, 10), n)
+    y = tmp_path / "Yahoo_src"; y.mkdir()
+    order = np.argsort(users, kind="stable")
+    with open(y / "train.txt", "w") as f:
+        for u in np.unique(users):
+            rows = order[users[order] == u]
+            f.write(f"{u}|{rows.size}\n")
+            for j in rows:
+                f.write(f"{items[j]}\t{ratings[j]}\n")
+    (y / "test.txt").write_text("")
+    ref = run([io_check, "parse", str(y / "train.txt"), str(y / "test.txt")]).stdout.splitlines()
+    ref_T = [l for l in ref if l.startswith("T ")]
+    assert len(ref_T) == n
+    b = tmp_path / "ratings.bin"
+    assert run([conv, str(y / "train.txt"), str(b), "bin"]).returncode == 0
+    assert os.path.getsize(b) == 32 + 12 * n
+    hdr = np.fromfile(b, np.uint32, 8)
+    assert hdr[0] == 0x5243534d and hdr[1] == 1 and hdr[2] == n and hdr[6] == 1       # magic, version, n, compact ids
+    recs = np.fromfile(b, np.dtype([("r", "<f4"), ("u", "<u4"), ("i", "<u4")]), offset=32)
+    want = np.array([[float(l.split()[3]), int(l.split()[1]), int(l.split()[2])] for l in ref_T])
+    assert np.array_equal(recs["u"], want[:, 1].astype(np.uint32)) and np.array_equal(recs["i"], want[:, 2].astype(np.uint32))
+    assert np.array_equal(recs["r"], want[:, 0].astype(np.float32))
+    # binary -> yahoo text -> parse: the same multiset of (user, item, rating) in compact ids of the binary file
+    y2 = tmp_path / "Yahoo_out"; y2.mkdir()
+    assert run([conv, str(b), str(y2 / "train.txt"), "yahoo"]).returncode == 0
+    back = run([io_check, "parse", str(y2 / "train.txt"), str(y / "test.txt")]).stdout.splitlines()
+    trip = lambda lines: sorted((int(l.split()[4]), int(l.split()[5]), float(l.split()[3])) for l in lines if l.startswith("T "))
+    assert trip(back) == sorted((int(u), int(i), float(r)) for r, u, i in want)
+    # tsv and item-first layouts
+    t = tmp_path / "plain"; t.mkdir()
+    assert run([conv, str(b), str(t / "train.tsv"), "tsv"]).returncode == 0
+    rows = [l.split("\t") for l in open(t / "train.tsv").read().splitlines()]
+    assert len(rows) == n and [int(r[0]) for r in rows] == recs["u"].tolist()
+    assert np.array_equal(np.array([r[2] for r in rows], np.float32), recs["r"]), "ratings survive the text form exactly"
+    nf = tmp_path / "netflix_out"; nf.mkdir()
+    assert run([conv, str(b), str(nf / "train.tsv"), "item_first"]).returncode == 0
+    rows = [l.split("\t") for l in open(nf / "train.tsv").read().splitlines()]
+    assert [int(r[0]) for r in rows] == recs["i"].tolist() and [int(r[1]) for r in rows] == recs["u"].tolist()
+
+
+def test_binary_model_round_trip(io_check, tmp_path):
+    out = run([io_check, "binmodel", str(tmp_path / "m.bin")])
+    assert out.returncode == 0 and "binmodel identical" in out.stdout
+
+
 def test_tools_fail_loudly_without_a_gpu(tmp_path):
     import torch
     if torch.cuda.is_available():

@@ -1,6 +1,7 @@
-"""GPU test of the sharded path on 2 GPUs (skipped on a single-GPU box): two libmascot engines in
-deterministic mode, item blocks exchanged with NCCL send/recv, must equal the sequential CPU replay
-of the same block order bit for bit."""
+"""GPU tests of the library's sharded path (mascot_shard_*, csrc/shard.cu): engines in deterministic
+mode, item blocks handed over by the C++ schedule with NCCL, must equal the sequential CPU replay of the
+same block order bit for bit.  The one-GPU case runs everywhere; the two-GPU cases are skipped on a
+single-GPU box."""
 import os
 import subprocess
 import sys
@@ -12,49 +13,67 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def test_two_gpus_equal_the_sequential_replay(tmp_path, oracle):
+def run_ranks(tmp_path, world, per_gpu):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "multi_gpu_worker.py"), str(tmp_path), str(r), str(world), str(per_gpu)],
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env) for r in range(world)]
+    outs = []
+    for p in procs:
+        try:
+            out, _ = p.communicate(timeout=600)
+        except subprocess.TimeoutExpired:
+            for q in procs:
+                q.kill()
+            raise
+        outs.append(out)
+    for r, p in enumerate(procs):
+        assert p.returncode == 0, f"rank {r}:\n" + outs[r][-3000:]
+    return [np.load(os.path.join(tmp_path, f"gpu_rank{r}.npz")) for r in range(world)]
+
+
+def check_against_replay(oracle, got, world, per_gpu):
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from test_multi_cpu import dataset, load_multi, sequential_replay
+    multi = load_multi()
+    shards, plan, rm = sequential_replay(oracle, multi, world, per_gpu)
+    R, test, P, Q, n_users, n_items = dataset()
+    assert sum(int(g["local"]) for g in got) == R.size, "every rating belongs to exactly one rank"
+    for r in range(world):
+        assert np.array_equal(got[r]["u2s"], shards[r].u2s) and np.array_equal(got[r]["i2s"], shards[r].i2s)
+        assert int(got[r]["local"]) == int((plan.user_rank[R["u"]] == r).sum()), "the library deals the users like the plan"
+        Pm, Qm = shards[r].model.factors()
+        # after the gather every rank holds the whole model: each user's rows from the rank that owns it
+        for owner in range(world):
+            rows = shards[owner].u2s[np.flatnonzero(plan.user_rank == owner)]
+            Po, _ = shards[owner].model.factors()
+            assert (got[r]["P"][rows].view(np.uint32) == Po[rows].view(np.uint32)).all(), f"rank {r}: user rows of rank {owner}"
+        assert (got[r]["Q"].view(np.uint32) == Qm.view(np.uint32)).all(), f"rank {r} item factors"
+        assert (got[r]["uprec"] == shards[r].model.uprec).all() and (got[r]["iprec"] == shards[r].model.iprec).all()
+        # the engine sums float32 block partials, the replay float64 squared errors: 1e-6 relative
+        assert np.allclose(got[r]["rmse"], rm, rtol=1e-6), (got[r]["rmse"], rm)
+        want_t = shards[r].T
+        key = lambda a: np.lexsort((a["r"].view(np.uint32), a["i"], a["u"]))
+        assert np.array_equal(got[r]["test_ratings"][key(got[r]["test_ratings"])], want_t[key(want_t)])
+    assert got[0]["promoted"].sum() > 0, "the case is meant to exercise switching"
+    assert got[0]["rmse"][-1] < got[0]["rmse"][0]
+    if world > 1:
+        assert all(int(g["sent"]) > 0 for g in got)
+
+
+@pytest.mark.parametrize("per_gpu", [1, 2])
+def test_group_of_one_equals_the_sequential_replay(tmp_path, oracle, per_gpu):
+    """world = 1: the set-up selection, the block-contiguous item layout (two blocks when per_gpu = 2), the
+    step loop and the statistics path of the sharded code, without a second GPU."""
+    got = run_ranks(tmp_path, 1, per_gpu)
+    check_against_replay(oracle, got, 1, per_gpu)
+
+
+@pytest.mark.parametrize("per_gpu", [1, 2])
+def test_two_gpus_equal_the_sequential_replay(tmp_path, oracle, per_gpu):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
-    from test_multi_cpu import OracleShard, dataset, load_multi
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", "29731", os.path.join(ROOT, "tests", "multi_gpu_worker.py"), str(tmp_path)]
-    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
-    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
-    got = [np.load(os.path.join(tmp_path, f"gpu_rank{r}.npz")) for r in range(2)]
-    multi = load_multi()
-    world = 2
-    R, test, P, Q, n_users, n_items = dataset()
-    plan = multi.make_plan(R["u"], R["i"], n_users, n_items, world)
-    shards = [OracleShard(oracle, multi, plan, r, R, test, P, Q, n_users, n_items) for r in range(world)]
-
-    def copy_block(src, dst, b):
-        for a, c in zip(src.block_tensors(b), dst.block_tensors(b)):
-            c.copy_(a)
-    for e in range(8):
-        check = shards[0].is_check_epoch(e)
-        if check:
-            for sh in shards:
-                sh.stats_begin()
-        for s in range(world):
-            for r in range(world):
-                shards[r].train_segment(e, (r + s) % world, collect_stats=check)
-            for r in range(world):
-                copy_block(shards[r], shards[(r - 1) % world], (r + s) % world)
-        if check:
-            sums = [sum(sh.stats_fetch()[j] for sh in shards) for j in range(4)]
-            for sh in shards:
-                sh.stats_apply(e, *sums)
-        for b in range(world):
-            for r in range(world):
-                if r != b:
-                    copy_block(shards[b], shards[r], b)
-    for r in range(world):
-        Pm, Qm = shards[r].model.factors()
-        rows = shards[r].u2s[np.flatnonzero(plan.user_rank == r)]
-        assert (got[r]["P"][rows].view(np.uint32) == Pm[rows].view(np.uint32)).all(), f"rank {r} user factors"
-        assert (got[r]["Q"].view(np.uint32) == Qm.view(np.uint32)).all(), f"rank {r} item factors"
-        assert (got[r]["uprec"] == shards[r].model.uprec).all() and (got[r]["iprec"] == shards[r].model.iprec).all()
-    assert got[0]["promoted"].sum() > 0
+    got = run_ranks(tmp_path, 2, per_gpu)
+    check_against_replay(oracle, got, 2, per_gpu)
+    assert (got[0]["Q"].view(np.uint32) == got[1]["Q"].view(np.uint32)).all()
+    assert (got[0]["P"].view(np.uint32) == got[1]["P"].view(np.uint32)).all()

@@ -99,7 +99,7 @@ def test_partitioned_stream_on_conflict_free_ratings_bit_exact(mascot, oracle, k
     order = eng.stream_order()
     assert np.array_equal(np.sort(order), np.arange(n)), "still every rating exactly once"
     # inside each segment the classes are contiguous, in the order hh, hf, fh, ff
-    up, ip = model.uprec_row()[u2s[R["u"][order]]], model.iprec_row()[i2s[R["i"][order]]]
+    up, ip = model.uprec_row[u2s[R["u"][order]]], model.iprec_row[i2s[R["i"][order]]]
     cls = 2 * (up != 0) + (ip != 0)
     assert (np.isin(order[:n // 3], np.arange(n // 3))).all(), "segments keep their ratings"
     for lo, hi in ((0, n // 3), (n // 3, n)):

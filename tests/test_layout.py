@@ -83,3 +83,18 @@ def test_launch_cache_raises_the_shared_memory_limit_once_and_never_lowers_it(tm
     # a failing raise is reported, and tried again by the next launch
     out = subprocess.run([exe, "57344", "7", "0:224:50176", "0:224:50176"], capture_output=True, text=True, check=True).stdout
     assert out.count("raise dev=0") == 2 and out.count("rc=7") == 2
+
+
+def test_bounded_wait_returns_ok_error_or_timeout(tmp_path):
+    """csrc/bounded_wait.h, the wait behind every cross-rank dependency of the sharded path: finished
+    work ends it with 0, a failing poll with that failure, and work that never finishes with
+    MASCOT_ERR_TIMEOUT (-6) once the limit has passed - never later than a little after the limit."""
+    exe = str(tmp_path / "bounded_wait_check")
+    subprocess.check_call(["g++", "-O1", "-std=c++17", "-I", CSRC, os.path.join(ROOT, "tests", "bounded_wait_check.cpp"), "-o", exe])
+    run = lambda *a: subprocess.run([exe] + [str(x) for x in a], capture_output=True, text=True, check=True).stdout.split()
+    rc, ms, polls = run(5, 2000, 0)
+    assert rc == "0" and int(polls) == 6 and float(ms) < 500
+    rc, ms, polls = run(-1, 200, 0)                  # never ready
+    assert rc == "-6" and 200 <= float(ms) < 1500
+    rc, ms, polls = run(-1, 5000, -8)                # the poll reports a communication failure
+    assert rc == "-8" and int(polls) == 3 and float(ms) < 1000

@@ -68,7 +68,7 @@ class OracleShard:
     def block_tensors(self, b):
         # strided views of raw bytes [rows of the block, bytes per row], like the device views of the real
         # engine; as there, an arena travels only while it holds live rows (a row lives in exactly one)
-        n, w = self.model.Q16.shape[0], self.plan.world
+        n, w = self.model.Q16.shape[0], self.plan.blocks
         views = []
         if (self.model.iprec == 0).any():
             views.append(torch.from_numpy(self.model.Q16.view(np.uint8).reshape(n, -1))[b::w])
@@ -125,17 +125,32 @@ class OracleShard:
         return float(((self.T["r"] - pred) ** 2).sum()), int(self.T.size)
 
 
-def _worker(rank, world, port, out_dir):
+def load_binding():
+    """ctypes binding of libmascot (used here only for the device-free schedule function)."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("mascot_binding", os.path.join(ROOT, "icdm-2021_mascot_b200", "mascot.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def library_schedule(world, per_gpu):
+    """The library's own block schedule (mascot_shard_schedule), as the callable multi.train_epoch takes."""
+    M = load_binding()
+    return lambda rank, step: M.shard_schedule(world, per_gpu, rank, step)
+
+
+def _worker(rank, world, port, out_dir, per_gpu=1):
     import oracle as O
     multi = load_multi()
     dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
     try:
         R, test, P, Q, n_users, n_items = dataset()
-        plan = multi.make_plan(R["u"], R["i"], n_users, n_items, world)
+        plan = multi.make_plan(R["u"], R["i"], n_users, n_items, world, world * per_gpu)
         shard = OracleShard(O, multi, plan, rank, R, test, P, Q, n_users, n_items)
         rm, promoted = [], []
         for e in range(8):
-            _, pr = multi.train_epoch(dist, shard, rank, world, e)
+            _, pr = multi.train_epoch(dist, shard, rank, world, e, schedule=library_schedule(world, per_gpu))
             multi.gather_item_factors(dist, shard, world)
             rm.append(multi.global_rmse(dist, shard, world))
             promoted.append(pr)
@@ -211,42 +226,53 @@ def test_plan_is_a_partition_with_balanced_users():
         assert per_rank.max() <= 1.25 * per_rank.mean() + plan.user_degree.max()
 
 
-def test_two_ranks_equal_the_sequential_replay_bit_for_bit(tmp_path):
-    import oracle as O
-    multi = load_multi()
-    world = 2
-    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
-    got = [np.load(os.path.join(tmp_path, f"rank{r}.npz")) for r in range(world)]
+def sequential_replay(O, multi, world, per_gpu, epochs=8):
+    """The sharded run in ONE process: `world` stand-in shards, the library's block order, the hand-overs
+    emulated by copying blocks between the shards.  Returns (shards, plan, rmse per epoch)."""
     R, test, P, Q, n_users, n_items = dataset()
-    assert sum(int(g["processed"]) for g in got) == 8 * R.size, "every rating exactly once per epoch"
-    # sequential replay of the same block order in ONE process
-    plan = multi.make_plan(R["u"], R["i"], n_users, n_items, world)
+    blocks = world * per_gpu
+    plan = multi.make_plan(R["u"], R["i"], n_users, n_items, world, blocks)
     shards = [OracleShard(O, multi, plan, r, R, test, P, Q, n_users, n_items) for r in range(world)]
-    # the stand-ins share nothing, so emulate the exchange by copying blocks between them
+
     def copy_block(src, dst, b):
         for a, c in zip(src.block_tensors(b), dst.block_tensors(b)):
             c.copy_(a)
     rm = []
-    for e in range(8):
+    for e in range(epochs):
         check = shards[0].is_check_epoch(e)
         if check:
             for sh in shards:
                 sh.stats_begin()
-        for s in range(world):
+        for s in range(blocks):
             for r in range(world):
-                shards[r].train_segment(e, (r + s) % world, collect_stats=check)
+                shards[r].train_segment(e, (per_gpu * r + s) % blocks, collect_stats=check)
             for r in range(world):
-                copy_block(shards[r], shards[(r - 1) % world], (r + s) % world)
+                if world > 1:
+                    copy_block(shards[r], shards[(r - 1) % world], (per_gpu * r + s) % blocks)
         if check:
             sums = [sum(sh.stats_fetch()[j] for sh in shards) for j in range(4)]
             for sh in shards:
                 sh.stats_apply(e, *sums)
-        for b in range(world):
+        for b in range(blocks):
             for r in range(world):
-                if r != b:
-                    copy_block(shards[b], shards[r], b)
+                if r != b // per_gpu:
+                    copy_block(shards[b // per_gpu], shards[r], b)
         parts = [sh.eval_sq_error() for sh in shards]
         rm.append(np.sqrt(sum(p[0] for p in parts) / sum(p[1] for p in parts)))
+    return shards, plan, rm
+
+
+@pytest.mark.parametrize("per_gpu", [1, 2])
+def test_two_ranks_equal_the_sequential_replay_bit_for_bit(tmp_path, per_gpu):
+    import oracle as O
+    multi = load_multi()
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path), per_gpu), nprocs=world, join=True)
+    got = [np.load(os.path.join(tmp_path, f"rank{r}.npz")) for r in range(world)]
+    R, test, P, Q, n_users, n_items = dataset()
+    assert sum(int(g["processed"]) for g in got) == 8 * R.size, "every rating exactly once per epoch"
+    # sequential replay of the same block order in ONE process
+    shards, plan, rm = sequential_replay(O, multi, world, per_gpu)
     for r in range(world):
         Pm, Qm = shards[r].model.factors()
         mine_rows = shards[r].u2s[np.flatnonzero(plan.user_rank == r)]
@@ -257,3 +283,66 @@ def test_two_ranks_equal_the_sequential_replay_bit_for_bit(tmp_path):
     assert (got[0]["Q"].view(np.uint32) == got[1]["Q"].view(np.uint32)).all(), "Q is identical on both ranks after the gather"
     assert got[0]["promoted"].sum() > 0, "the case is meant to exercise switching across ranks"
     assert got[0]["rmse"][-1] < got[0]["rmse"][0]
+
+
+@pytest.mark.parametrize("world,per_gpu", [(1, 1), (1, 2), (2, 1), (2, 2), (3, 1), (4, 2), (8, 1), (8, 2)])
+def test_library_schedule_is_conflict_free_and_complete(world, per_gpu):
+    """mascot_shard_schedule (pure host function of libmascot): in every step the ranks train distinct
+    blocks; over an epoch every rank trains every block exactly once; a block is sent to rank-1 and the
+    block that arrives is the one rank+1 trained in the same step and is trained here `per_gpu` steps
+    later, so with two blocks per GPU a block in flight is never the one being trained."""
+    M = load_binding()
+    blocks = world * per_gpu
+    seen = {r: [] for r in range(world)}
+    for step in range(blocks):
+        row = [M.shard_schedule(world, per_gpu, r, step) for r in range(world)]
+        trained = [x[0] for x in row]
+        assert len(set(trained)) == world, "no two ranks hold the same block"
+        for r, (b, dst, incoming, src) in enumerate(row):
+            assert dst == (r - 1) % world and src == (r + 1) % world
+            assert incoming == row[src][0], "what arrives is what the neighbour has just trained"
+            later = M.shard_schedule(world, per_gpu, r, (step + per_gpu) % blocks)[0]
+            assert later == incoming
+            if per_gpu == 2 and world > 1:
+                assert M.shard_schedule(world, per_gpu, r, (step + 1) % blocks)[0] not in (incoming, b)
+            seen[r].append(b)
+    for r in range(world):
+        assert sorted(seen[r]) == list(range(blocks))
+    with pytest.raises(M.MascotError):
+        M.shard_schedule(world, per_gpu, world, 0)
+
+
+def _timeout_worker(rank, world, port, out_dir):
+    """Rank 1 leaves before the hand-over of the first step; rank 0's bounded wait must end with the
+    timeout status instead of blocking."""
+    import datetime
+    multi = load_multi()
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=3))
+    status = 0
+    try:
+        data = torch.zeros(8, 4)
+
+        class Toy:
+            def block_tensors(self, b):
+                return [data[4 * b:4 * b + 4]]
+        if rank == 0:
+            try:
+                multi.exchange_block(dist, Toy(), 0, 1, 1, 1)          # its partner never sends
+            except Exception:
+                status = -6                                            # MASCOT_ERR_TIMEOUT
+        with open(os.path.join(out_dir, f"status{rank}.txt"), "w") as f:
+            f.write(str(status))
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def test_missing_rank_ends_in_the_timeout_status(tmp_path):
+    """Host-made failure: a rank that skips its send.  The waiting rank gives up after the group's limit
+    and reports MASCOT_ERR_TIMEOUT (-6); nothing hangs."""
+    mp.spawn(_timeout_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    assert open(os.path.join(tmp_path, "status0.txt")).read() == "-6"
+    assert open(os.path.join(tmp_path, "status1.txt")).read() == "0"
