@@ -16,6 +16,7 @@
 #include <chrono>
 #include <cmath>
 #include <iostream>
+#include <sstream>
 #include <string>
 #include <sys/stat.h>
 #include <thread>
@@ -133,17 +134,13 @@ bool save_outputs(const Run& run, mascot_handle* h) {
     return true;
 }
 
-int train_single(Run& run) {
+int train_single(Run& run, mascot_handle* h) {
     mascot_config& cfg = run.cfg;
-    mascot_handle* h = nullptr;
-    if (mascot_create(&cfg, &h) != MASCOT_OK) { std::cerr << "libmascot: " << mascot_last_error(nullptr) << std::endl; return 1; }
     auto die = [&](const char* what) {
         std::cerr << "libmascot: " << what << ": " << mascot_last_error(h) << std::endl;
         mascot_destroy(h);
         return 1;
     };
-    if (mascot_set_ratings(h, run.data.train_ptr, run.data.n_train, run.data.test_ptr, run.data.n_test, run.data.n_users, run.data.n_items) != MASCOT_OK)
-        return die("set_ratings");
     if (cfg.version == MASCOT_V_MASCOT || cfg.version == MASCOT_V_NAIVE) print_groups(h);
     if (mascot_init_factors(h) != MASCOT_OK) return die("init_factors");
     for (uint32_t e = 0; e < cfg.epoch; e++) {
@@ -250,17 +247,25 @@ int main(int argc, const char* argv[]) {
     if (!run.wg_given) cfg.num_workers = 0;
     cfg.is_yahoo = mascot_io::is_yahoo(run.infile) ? 1u : 0u;
 
-    // The data is read before the banner is printed (the automatic worker count depends on the number of
-    // ratings); the order of the output lines is the reference's.
+    // The data is read - and, on one GPU, handed to the engine - before the banner is printed: the automatic
+    // worker count depends on the data.  The order of the output lines is the reference's.
     if (!mascot_io::read_training(run.data, run.infile)) { std::cout << "cannot read " << run.infile << std::endl; return 1; }
+    std::ostringstream test_log;                  // what read_test prints belongs below the banner
+    { std::streambuf* old = std::cout.rdbuf(test_log.rdbuf());
+      const bool ok = mascot_io::read_test(run.data, run.testfile);
+      std::cout.rdbuf(old);
+      if (!ok) { std::cout << "cannot read " << run.testfile << std::endl; return 1; } }
     uint32_t shown_workers = cfg.num_workers;
-    if (!run.wg_given) {
-        // the engine's automatic choice (mascot_config.num_workers), restated for the banner
-        const uint64_t n = run.data.n_train;
-        if (cfg.deterministic) shown_workers = 1;
-        else if (run.gpus > 1) shown_workers = (uint32_t)std::max<uint64_t>(std::max<uint64_t>(3 * n / 16384, 512) / run.gpus, 64);
-        else if (n < 1500000) shown_workers = (uint32_t)std::min<uint64_t>(std::max<uint64_t>(n / 512, 512), 1536);
-        else shown_workers = (uint32_t)std::min<uint64_t>(std::max<uint64_t>(n / 8192, 512), 1u << 20);
+    mascot_handle* single = nullptr;
+    std::string early_error;
+    if (run.gpus == 1) {
+        if (mascot_create(&cfg, &single) != MASCOT_OK) early_error = mascot_last_error(nullptr);
+        else if (mascot_set_ratings(single, run.data.train_ptr, run.data.n_train, run.data.test_ptr, run.data.n_test, run.data.n_users,
+                                    run.data.n_items) != MASCOT_OK) early_error = std::string("set_ratings: ") + mascot_last_error(single);
+        else mascot_get_worker_count(single, &shown_workers);
+    } else if (!run.wg_given) {
+        // the sharded engines' automatic choice (see mascot_shard_init), restated for the banner
+        shown_workers = cfg.deterministic ? 1u : (uint32_t)std::max<uint64_t>(std::max<uint64_t>(3 * run.data.n_train / 16384, 512) / run.gpus, 64);
     }
     std::cout << std::endl;
     std::cout << "Input file                  : " << run.infile << std::endl;
@@ -277,11 +282,12 @@ int main(int argc, const char* argv[]) {
     std::cout << "Error threshold             : " << cfg.error_threshold << std::endl;
     std::cout << "Interval                    : " << cfg.interval << std::endl;
 
-    if (!mascot_io::read_test(run.data, run.testfile)) { std::cout << "cannot read " << run.testfile << std::endl; return 1; }
+    std::cout << test_log.str();
     std::cout << "The number of nonzeros      : " << run.data.n_train << std::endl;
     std::cout << "The number of users         : " << run.data.n_users << std::endl;
     std::cout << "The number of items         : " << run.data.n_items << std::endl;
     std::cout << "The number of test nonzeros : " << run.data.n_test << std::endl;
 
-    return run.gpus > 1 ? train_sharded(run) : train_single(run);
+    if (!early_error.empty()) { std::cerr << "libmascot: " << early_error << std::endl; mascot_destroy(single); return 1; }
+    return run.gpus > 1 ? train_sharded(run) : train_single(run, single);
 }

@@ -38,8 +38,8 @@ __device__ __forceinline__ float block_tree_512(float* tmp) {
 __device__ __forceinline__ void load8(const Arena& A, uint32_t code, int K, int tl, float* x) {
     const uint32_t row = code & kIdMask;
     if (code & kPrecBit) {
-        const float4* p = reinterpret_cast<const float4*>(A.f32 + (size_t)row * K) + 2 * tl;
-        const float4 v = __ldcg(p), w = __ldcg(p + 1);
+        const float4* p = reinterpret_cast<const float4*>(A.f32 + (size_t)row * K) + tl;      // two half-rows (layout.cuh)
+        const float4 v = __ldcg(p), w = __ldcg(p + K / 8);
         x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w; x[4] = w.x; x[5] = w.y; x[6] = w.z; x[7] = w.w;
     } else {
         const uint4 v = __ldcg(reinterpret_cast<const uint4*>(A.f16 + (size_t)row * K) + tl);

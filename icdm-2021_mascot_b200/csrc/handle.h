@@ -80,6 +80,8 @@ struct mascot_handle {
     uint32_t* d_err_flag = nullptr; // set by kernels that met an id out of range
     mascot::ShardCtx* shard = nullptr;   // group membership of a sharded engine (shard.cu)
     mascot_timings timings = {};         // accumulated phase times (mascot_get_timings)
+    bool l2_window_set = false;          // a persisting access-policy window is installed on `stream`
+    size_t l2_limit_before = 0;          // the process's persisting-L2 limit before this engine changed it
 };
 
 namespace mascot {
@@ -141,6 +143,16 @@ struct SetupRequest {
     uint32_t blocks = 1, blocks_per_rank = 1;
 };
 int setup_ratings(mascot_handle* h, const SetupRequest& rq);
+
+// Installs / removes the persisting-L2 window over the item arena (cfg.l2_item_window).
+int l2_window_install(mascot_handle* h);
+void l2_window_remove(mascot_handle* h);
+
+// NVTX range for the lifetime of the object (a no-op unless a profiler is attached).
+struct NvtxRange {
+    explicit NvtxRange(const char* name);
+    ~NvtxRange();
+};
 
 // ---- shard.cu ----
 void shard_destroy(mascot_handle* h);

@@ -50,6 +50,13 @@ MASCOT_HD inline int logical_of_phys(int K, int p) {
     return m + 8 * (s >> 2) + 16 * ((s >> 1) & 1) + 32 * (s & 1);
 }
 
+// The fp32 arena stores a row as two halves of K/2 floats: lane m's first four values (positions
+// 8m..8m+3 of the binary16 order) at floats 4m..4m+3 of the first half, its last four at 4m..4m+3 of the
+// second half.  A worker then reads or writes a row with two 128-bit accesses per lane, each of which
+// covers a CONTIGUOUS quarter kilobyte across the worker's lanes (whole 32-byte sectors), instead of two
+// interleaved accesses that each touch half of every sector.
+MASCOT_HD inline int f32_pos_of_phys(int K, int p) { return ((p & 4) ? K / 2 : 0) + 4 * (p >> 3) + (p & 3); }
+
 // Seeded bijection of [0, n): a 4-round Feistel network over the next even power-of-two domain,
 // cycle-walked back into range.  Integer-only, so host and device agree exactly.
 MASCOT_HD inline uint32_t mix32(uint32_t x) {

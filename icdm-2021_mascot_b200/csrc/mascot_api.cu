@@ -14,6 +14,7 @@
 #include <vector>
 
 #include <cuda_runtime.h>
+#include <nvtx3/nvToolsExt.h>
 
 #include "../../include/mascot.h"
 #include "handle.h"
@@ -27,6 +28,47 @@ thread_local std::string g_create_error;
 }  // namespace
 
 void mascot::set_global_error(const char* msg) { g_create_error = msg ? msg : ""; }
+
+mascot::NvtxRange::NvtxRange(const char* name) { nvtxRangePushA(name); }
+mascot::NvtxRange::~NvtxRange() { nvtxRangePop(); }
+
+// L2 residency for the item factors (north of L2-sized models the item side is what every rating of a
+// run re-reads): a persisting access-policy window on the engine's stream over the arena that holds the
+// binary16 item rows (or the fp32 one for fp32 variants).  The carve-out is a per-process limit of the
+// device, not a GPU setting: it is restored when the engine goes away.
+int mascot::l2_window_install(mascot_handle* h) {
+    if (!h->cfg.l2_item_window || h->l2_window_set) return MASCOT_OK;
+    int dev = h->cfg.device, max_persist = 0, max_window = 0;
+    CU(h, cudaDeviceGetAttribute(&max_persist, cudaDevAttrMaxPersistingL2CacheSize, dev));
+    CU(h, cudaDeviceGetAttribute(&max_window, cudaDevAttrMaxAccessPolicyWindowSize, dev));
+    void* base = h->Q.f16 ? (void*)h->Q.f16 : (void*)h->Q.f32;
+    const size_t bytes = (size_t)h->irows * h->K * (h->Q.f16 ? sizeof(__half) : sizeof(float));
+    if (!base || !bytes || max_persist <= 0 || max_window <= 0) return MASCOT_OK;
+    CU(h, cudaDeviceGetLimit(&h->l2_limit_before, cudaLimitPersistingL2CacheSize));
+    const size_t carve = std::min<size_t>((size_t)max_persist, bytes);
+    CU(h, cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, carve));
+    cudaStreamAttrValue attr;
+    std::memset(&attr, 0, sizeof attr);
+    attr.accessPolicyWindow.base_ptr = base;
+    attr.accessPolicyWindow.num_bytes = std::min<size_t>(bytes, (size_t)max_window);
+    attr.accessPolicyWindow.hitRatio = (float)std::min(1.0, (double)carve / (double)attr.accessPolicyWindow.num_bytes);
+    attr.accessPolicyWindow.hitProp = cudaAccessPropertyPersisting;
+    attr.accessPolicyWindow.missProp = cudaAccessPropertyStreaming;
+    CU(h, cudaStreamSetAttribute(h->stream, cudaStreamAttributeAccessPolicyWindow, &attr));
+    h->l2_window_set = true;
+    return MASCOT_OK;
+}
+
+void mascot::l2_window_remove(mascot_handle* h) {
+    if (!h->l2_window_set) return;
+    cudaStreamAttrValue attr;
+    std::memset(&attr, 0, sizeof attr);
+    attr.accessPolicyWindow.num_bytes = 0;            // an empty window switches the policy off
+    cudaStreamSetAttribute(h->stream, cudaStreamAttributeAccessPolicyWindow, &attr);
+    cudaCtxResetPersistingL2Cache();
+    cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, h->l2_limit_before);
+    h->l2_window_set = false;
+}
 
 double mascot::now_us() {
     return std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now().time_since_epoch()).count();
@@ -219,9 +261,23 @@ int partition_segments(mascot_handle* h, size_t seg_first, size_t seg_count) {
 
 // The stream is partitioned when that pays: mixed-precision trainer, more than one worker, at least
 // one promoted group, and sizes the 16-bit sort key and the 32-bit permutation can express.
+// Do the binary16 factors of this engine fit in the device's L2?
+bool factors_fit_l2(const mascot_handle* h) {
+    int l2 = 0;
+    if (cudaDeviceGetAttribute(&l2, cudaDevAttrL2CacheSize, h->cfg.device) != cudaSuccess || l2 <= 0) return true;
+    return ((size_t)h->n_users + h->n_items) * h->K * sizeof(__half) <= (size_t)l2 + (size_t)l2 / 2;
+}
+
 bool wants_partition(const mascot_handle* h) {
-    return h->grouped && !h->cfg.deterministic && any_fp32_group(h) && h->n_train < (1ull << 32) &&
-           (h->seg_off.size() - 1) * 4 <= 65536;
+    if (!(h->grouped && !h->cfg.deterministic && any_fp32_group(h) && h->n_train < (1ull << 32) && (h->seg_off.size() - 1) * 4 <= 65536)) return false;
+    if (h->cfg.no_class_partition == 1) return false;
+    if (h->cfg.no_class_partition == 2) return true;
+    // Automatic: measured on one B200 with the popular groups promoted - 100M-rating set (factors fit L2): one
+    // launch per class 14.0 ms per epoch, per-rating precision bits 15.2 ms; 252M-rating set (factors 416 MB, rows
+    // stream from HBM): 47 ms against 30.7 ms at half size - a class launch puts every worker on the popular fp32
+    // rows at once, and what bounds that set is traffic to those rows.  So the stream is partitioned only while
+    // the factors fit L2.
+    return factors_fit_l2(h);
 }
 
 int partition_all(mascot_handle* h) {
@@ -323,6 +379,7 @@ int mascot_create(const mascot_config* cfg, mascot_handle** out) {
 int mascot_destroy(mascot_handle* h) {
     if (!h) return MASCOT_OK;
     cudaSetDevice(h->cfg.device);
+    l2_window_remove(h);
     free_ratings(h);
     shard_destroy(h);
     dev_free(h->d_scratch); dev_free(h->counters.d_slots); dev_free(h->d_err_flag);
@@ -395,7 +452,7 @@ static int scatter_from_device(mascot_handle* h, const float* dP, const float* d
     CU(h, cudaStreamSynchronize(h->stream));
     h->timings.copy_to_grouped_us += now_us() - t0;
     h->have_factors = true;
-    return MASCOT_OK;
+    return l2_window_install(h);
 }
 
 int mascot_set_factors(mascot_handle* h, const float* P, const float* Q) {
@@ -447,7 +504,12 @@ unsigned worker_count(const mascot_handle* h, uint64_t n) {
     if (h->cfg.num_workers) return h->cfg.num_workers;
     if (h->shard) return shard_worker_count(h);
     if (n < 1500000) return (unsigned)std::min<uint64_t>(std::max<uint64_t>(n / 512, 512), 1536);
-    return (unsigned)std::min<uint64_t>(std::max<uint64_t>(n / 8192, 512), 1u << 20);
+    uint64_t w = std::min<uint64_t>(std::max<uint64_t>(n / 8192, 512), 1u << 20);
+    // Factors beyond L2: the rows stream from HBM and 16 warps per SM saturate it; more workers only add
+    // contention on the popular rows (252M-rating set, all rows binary16: 45.4 ms per epoch with 4,736 workers,
+    // 52.8 with 7,104, 53.3 with 9,472; 53.7 with 2,368).
+    if (!factors_fit_l2(h)) w = std::min<uint64_t>(w, (uint64_t)sm_count() * 16 * (32 / (h->K / 8)));
+    return (unsigned)w;
 }
 
 // Width of MuPPET's forward and backward pass this epoch (mf_methods.cu:597, 623-624).
@@ -526,10 +588,9 @@ SampleStats stats_view(mascot_handle* h) {
 // statistics.  `policy_n` (0 = the range's own length) is the stream length the automatic worker
 // count is taken from.
 int train_span(mascot_handle* h, float lr, uint32_t epoch, uint64_t begin, uint64_t end, RowClass cls, bool collect,
-               LaunchShape* shape, uint32_t* launches, uint64_t policy_n) {
+               LaunchShape* shape, uint32_t* launches, unsigned workers, cudaStream_t stream, WorkCounters* counters) {
     if (end <= begin) return MASCOT_OK;
     const uint64_t n = end - begin;
-    const unsigned workers = worker_count(h, policy_n ? policy_n : n);
     // after its switch the whole-model switching trainer is the plain fp32 trainer (sgd_kernel.h:296-326)
     const TrainKind kind = (h->kind == KIND_SWITCH && h->switched_to_fp32) ? KIND_FP32 : h->kind;
     Stream s; s.r = h->tr_r + begin; s.u = h->tr_u + begin; s.i = h->tr_i + begin; s.n = n;
@@ -541,31 +602,35 @@ int train_span(mascot_handle* h, float lr, uint32_t epoch, uint64_t begin, uint6
     if (head > 0) {
         Stream sa = s; sa.n = head;
         CU(h, launch_train(h->K, kind, sa, h->P, h->Q, lr, h->cfg.lambda, nullptr, cls, workers,
-                           &h->counters, muppet_bits(h), (int)epoch, h->cfg.plain_user_stores == 0, h->stream, shape));
+                           counters, muppet_bits(h), (int)epoch, h->cfg.plain_user_stores == 0, stream, shape));
         (*launches)++;
     }
     if (head < n) {
         Stream sb; sb.r = s.r + head; sb.u = s.u + head; sb.i = s.i + head; sb.n = n - head;
         const SampleStats st = stats_view(h);
         CU(h, launch_train(h->K, kind, sb, h->P, h->Q, lr, h->cfg.lambda, &st, cls, workers,
-                           &h->counters, muppet_bits(h), (int)epoch, h->cfg.plain_user_stores == 0, h->stream, shape));
+                           counters, muppet_bits(h), (int)epoch, h->cfg.plain_user_stores == 0, stream, shape));
         (*launches)++;
     }
     return MASCOT_OK;
 }
 
-// One segment of the stream: a single launch while every row is binary16 (or in the single-worker
-// mode, which reads each id's precision bit), else one launch per non-empty precision class.  On a
-// check epoch every launched range contributes its own sampled tail.
+// One segment of the stream: a single launch while every row is binary16 (or when the stream is not
+// partitioned: the launch then reads each id's precision bit), else one launch per non-empty precision
+// class, one after the other.  (Running the classes side by side on streams of their own, each with a
+// share of the workers, was measured too: 15.7 ms per promoted epoch on the 100M-rating set against 14.0 ms
+// one after the other.)  On a check epoch every launched range contributes its own sampled tail.
 int train_range(mascot_handle* h, float lr, uint32_t epoch, size_t segment, bool collect, LaunchShape* shape, uint32_t* launches,
                 uint64_t policy_n) {
     const uint64_t begin = h->seg_off[segment], end = h->seg_off[segment + 1];
     if (!policy_n) policy_n = end - begin;
+    const unsigned workers = worker_count(h, policy_n);
     if (!h->partitioned)
-        return train_span(h, lr, epoch, begin, end, any_fp32_group(h) ? ROWCLASS_ANY : ROWCLASS_HH, collect, shape, launches, policy_n);
+        return train_span(h, lr, epoch, begin, end, any_fp32_group(h) ? ROWCLASS_ANY : ROWCLASS_HH, collect, shape, launches, workers,
+                          h->stream, &h->counters);
     const uint64_t* off = &h->cls_off[segment * 5];
     for (int c = 0; c < 4; c++) {
-        const int rc = train_span(h, lr, epoch, off[c], off[c + 1], (RowClass)c, collect, shape, launches, policy_n);
+        const int rc = train_span(h, lr, epoch, off[c], off[c + 1], (RowClass)c, collect, shape, launches, workers, h->stream, &h->counters);
         if (rc != MASCOT_OK) return rc;
     }
     return MASCOT_OK;
@@ -592,6 +657,7 @@ int fetch_stats(mascot_handle* h, uint32_t* launches) {
 // Group errors from the sums in h->h_stats and the switching that follows (mf_methods.cu:325-393,
 // precision_switching.h:8-51).
 int apply_stats(mascot_handle* h, uint32_t epoch, uint32_t* promoted_u, uint32_t* promoted_i, uint32_t* launches) {
+    NvtxRange range("mascot: group errors and precision switching");
     const int ug = (int)h->uend.size(), ig = (int)h->iend.size(), K = h->K;
     const double t_err = now_us();
     auto errors = [&](int groups, const float* gsum, const float* nsum, const std::vector<uint8_t>& prec,
@@ -709,6 +775,7 @@ int mascot_train_epoch(mascot_handle* h, uint32_t epoch, mascot_epoch_stats* out
     if (!h) return MASCOT_ERR_BAD_ARG;
     if (h->shard) return fail(h, MASCOT_ERR_STATE, "this engine belongs to a sharded group: use mascot_shard_train_epoch");
     if (!h->have_ratings || !h->have_factors) return fail(h, MASCOT_ERR_STATE, "ratings and factors must be set before training");
+    NvtxRange range("mascot_train_epoch");
     CU(h, cudaSetDevice(h->cfg.device));
     const float lr = epoch < h->lr.size() ? h->lr[epoch] : lr_at(h->cfg, epoch);
     const bool muppet = h->kind == KIND_MUPPET;
@@ -787,9 +854,11 @@ int mascot_train_epoch_streamed(mascot_handle* h, uint32_t epoch, const mascot_r
     h->seg_off.clear();
     for (uint64_t off = 0; off < n_train; off += piece) h->seg_off.push_back(off);
     h->seg_off.push_back(n_train);
+    // The pieces are not partitioned by precision class: finding the class boundaries needs a read-back,
+    // i.e. a host wait per piece, which would stall the upload pipeline.  With promoted groups every piece
+    // runs the instantiation that reads each id's precision bit; its extra cost hides behind the upload.
     h->cls_off.clear();
     h->partitioned = false;
-    const bool partition_pieces = wants_partition(h);
 
     const float lr = epoch < h->lr.size() ? h->lr[epoch] : lr_at(h->cfg, epoch);
     const bool muppet = h->kind == KIND_MUPPET;
@@ -815,12 +884,6 @@ int mascot_train_epoch_streamed(mascot_handle* h, uint32_t epoch, const mascot_r
                                    h->tr_r + off, h->tr_u + off, h->tr_i + off, h->tr_src ? h->tr_src + off : nullptr, (uint32_t)off, h->stream));
         launches++;
         CU(h, cudaEventRecord(h->ev_free[b], h->stream));
-        if (partition_pieces) {
-            // the piece was encoded with the current precisions: bring its classes together before training it
-            if ((rc = partition_segments(h, c, 1)) != MASCOT_OK) return rc;
-            h->partitioned = true;
-            launches += 4;
-        }
         if ((rc = train_range(h, lr, epoch, c, check, &shape, &launches, n_train)) != MASCOT_OK) return rc;
     }
     if (check && h->stats_copies > 1) {

@@ -118,11 +118,11 @@ __global__ void scatter_kernel(const float* src, uint32_t rows, const uint32_t* 
         const uint32_t e = (uint32_t)(t / K);
         const int d = (int)(t % K);
         const uint32_t row = row_map ? row_map[e] : e;
-        const size_t o = (size_t)row * K + phys_of_logical(K, d);
+        const int ph = phys_of_logical(K, d);
         const float v = src[t];
         const __half h = __float2half_rn(v);
-        if (dst16) dst16[o] = h;
-        if (dst32) dst32[o] = through_half ? __half2float(h) : v;
+        if (dst16) dst16[(size_t)row * K + ph] = h;
+        if (dst32) dst32[(size_t)row * K + f32_pos_of_phys(K, ph)] = through_half ? __half2float(h) : v;
     }
 }
 
@@ -136,8 +136,8 @@ __global__ void gather_kernel(const __half* a16, const float* a32, const uint8_t
         const uint32_t e = (uint32_t)(t / K);
         const int d = (int)(t % K);
         const uint32_t row = row_map ? row_map[e] : arena_row(layout, e);
-        const size_t o = (size_t)row * K + phys_of_logical(K, d);
-        dst[t] = (prec_row[row] & kRowPrec) ? a32[o] : __half2float(a16[o]);
+        const int ph = phys_of_logical(K, d);
+        dst[t] = (prec_row[row] & kRowPrec) ? a32[(size_t)row * K + f32_pos_of_phys(K, ph)] : __half2float(a16[(size_t)row * K + ph]);
     }
 }
 
@@ -148,9 +148,9 @@ __global__ void promote_kernel(const __half* a16, float* a32, uint8_t* row_flags
     const uint64_t total = (uint64_t)(end - begin) * K;
     for (uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (uint64_t)gridDim.x * blockDim.x) {
         const uint32_t row = arena_row(layout, begin + (uint32_t)(t / K));
-        const size_t o = (size_t)row * K + (size_t)(t % K);
-        a32[o] = __half2float(a16[o]);
-        if (t % K == 0) row_flags[row] |= kRowPrec;
+        const int ph = (int)(t % K);
+        a32[(size_t)row * K + f32_pos_of_phys(K, ph)] = __half2float(a16[(size_t)row * K + ph]);
+        if (ph == 0) row_flags[row] |= kRowPrec;
     }
 }
 

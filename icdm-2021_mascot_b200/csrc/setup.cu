@@ -197,7 +197,9 @@ int setup_ratings(mascot_handle* h, const SetupRequest& rq) {
         if (seg[0] != 0 || seg[rq.n_segments] != rq.n_train) return fail(h, MASCOT_ERR_BAD_ARG, "segment offsets must run from 0 to n_train");
         for (uint32_t j = 0; j < rq.n_segments; j++) if (seg[j] > seg[j + 1]) return fail(h, MASCOT_ERR_BAD_ARG, "segment offsets must not decrease");
     } else { seg[0] = 0; seg[1] = rq.n_train; }
+    NvtxRange range("mascot: rating set-up");
     CU(h, cudaSetDevice(h->cfg.device));
+    l2_window_remove(h);
     free_ratings(h);
     h->n_users = n_users; h->n_items = n_items; h->n_test = 0; h->n_train = 0;
     h->cls_off.clear(); h->partitioned = false;

@@ -302,6 +302,7 @@ int mascot_shard_train_epoch(mascot_handle* h, uint32_t epoch, mascot_epoch_stat
     if (rc != MASCOT_OK) return rc;
     if (!h->have_ratings || !h->have_factors) return fail(h, MASCOT_ERR_STATE, "ratings and factors must be set before training");
     ShardCtx* S = h->shard;
+    NvtxRange range("mascot_shard_train_epoch");
     CU(h, cudaSetDevice(h->cfg.device));
     const float lr = epoch < h->lr.size() ? h->lr[epoch] : lr_at(h->cfg, epoch);
     const bool check = h->grouped && is_check_epoch(h->cfg, epoch);

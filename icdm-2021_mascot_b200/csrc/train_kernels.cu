@@ -122,9 +122,9 @@ __device__ __forceinline__ Raw<MODE> ld_row(const Arena& A, uint32_t code, int m
     const uint32_t row = code & kIdMask;
     Raw<MODE> r;
     if (is_f32<MODE>(code)) {
-        const uint4* p = reinterpret_cast<const uint4*>(A.f32 + (size_t)row * K) + 2 * m;
+        const uint4* p = reinterpret_cast<const uint4*>(A.f32 + (size_t)row * K) + m;     // first half; second half K/8 uint4 on
         r.a = __ldcg(p);
-        if constexpr (MODE != ROWS_HALF) r.b = __ldcg(p + 1);
+        if constexpr (MODE != ROWS_HALF) r.b = __ldcg(p + K / 8);
     } else {
         r.a = __ldcg(reinterpret_cast<const uint4*>(A.f16 + (size_t)row * K) + m);
     }
@@ -134,9 +134,9 @@ template <int K, int MODE>
 __device__ __forceinline__ void st_row(const Arena& A, uint32_t code, int m, const Raw<MODE>& r) {
     const uint32_t row = code & kIdMask;
     if (is_f32<MODE>(code)) {
-        uint4* p = reinterpret_cast<uint4*>(A.f32 + (size_t)row * K) + 2 * m;
+        uint4* p = reinterpret_cast<uint4*>(A.f32 + (size_t)row * K) + m;
         __stcg(p, r.a);
-        if constexpr (MODE != ROWS_HALF) __stcg(p + 1, r.b);
+        if constexpr (MODE != ROWS_HALF) __stcg(p + K / 8, r.b);
     } else {
         __stcg(reinterpret_cast<uint4*>(A.f16 + (size_t)row * K) + m, r.a);
     }
@@ -152,10 +152,10 @@ __device__ __forceinline__ void add_row_delta(const Arena& A, uint32_t code, int
     const uint32_t row = code & kIdMask;
     if (is_f32<MODE>(code)) {
         if constexpr (MODE != ROWS_HALF) {
-            float4* p = reinterpret_cast<float4*>(A.f32 + (size_t)row * K) + 2 * m;
+            float4* p = reinterpret_cast<float4*>(A.f32 + (size_t)row * K) + m;
             const V8f n = v8f_of(now.a, now.b), o = v8f_of(before.a, before.b);
             atomicAdd(p, make_float4(__fsub_rn(n.x[0], o.x[0]), __fsub_rn(n.x[1], o.x[1]), __fsub_rn(n.x[2], o.x[2]), __fsub_rn(n.x[3], o.x[3])));
-            atomicAdd(p + 1, make_float4(__fsub_rn(n.x[4], o.x[4]), __fsub_rn(n.x[5], o.x[5]), __fsub_rn(n.x[6], o.x[6]), __fsub_rn(n.x[7], o.x[7])));
+            atomicAdd(p + K / 8, make_float4(__fsub_rn(n.x[4], o.x[4]), __fsub_rn(n.x[5], o.x[5]), __fsub_rn(n.x[6], o.x[6]), __fsub_rn(n.x[7], o.x[7])));
         }
     } else {
         const V8h n = v8h_of(now.a), o = v8h_of(before.a);
@@ -171,12 +171,18 @@ __device__ __forceinline__ void add_row_delta(const Arena& A, uint32_t code, int
 // A lane's elements e0..e7 sit at positions 0 2 4 6 1 3 5 7 (layout.cuh), i.e. as the binary16 pairs
 // (e0,e4) (e1,e5) (e2,e6) (e3,e7).  Lane partial: (f_0 + f_1) + (f_2 + f_3) with
 // f_j = fma(e_2j, e'_2j, e_2j+1 * e'_2j+1).
+// fp32 arithmetic runs on the packed two-lane instructions of sm_100 (fma / mul / add .f32x2): each lane
+// is rounded on its own, exactly like the scalar instruction, and a row slice needs half as many issue
+// slots - which is what bounds this kernel.
+__device__ __forceinline__ float2 pr(const V8f& v, int j) { return make_float2(v.x[2 * j], v.x[2 * j + 1]); }
+__device__ __forceinline__ void set_pr(V8f& v, int j, float2 t) { v.x[2 * j] = t.x; v.x[2 * j + 1] = t.y; }
+
 __device__ __forceinline__ float pair_partial(const V8f& a, const V8f& b) {
-    const float f0 = __fmaf_rn(a.x[0], b.x[0], __fmul_rn(a.x[2], b.x[2]));
-    const float f1 = __fmaf_rn(a.x[4], b.x[4], __fmul_rn(a.x[6], b.x[6]));
-    const float f2 = __fmaf_rn(a.x[1], b.x[1], __fmul_rn(a.x[3], b.x[3]));
-    const float f3 = __fmaf_rn(a.x[5], b.x[5], __fmul_rn(a.x[7], b.x[7]));
-    return __fadd_rn(__fadd_rn(f0, f1), __fadd_rn(f2, f3));
+    // (f0, f2) = (a0 b0 + a2 b2, a1 b1 + a3 b3), (f1, f3) likewise from positions 4..7
+    const float2 f02 = __ffma2_rn(pr(a, 0), pr(b, 0), __fmul2_rn(pr(a, 1), pr(b, 1)));
+    const float2 f13 = __ffma2_rn(pr(a, 2), pr(b, 2), __fmul2_rn(pr(a, 3), pr(b, 3)));
+    const float2 t = __fadd2_rn(f02, f13);                                     // (f0+f1, f2+f3)
+    return __fadd_rn(t.x, t.y);
 }
 __device__ __forceinline__ __half pair_partial(const V8h& p, const V8h& q) {
     const __half2 f02 = __hfma2(p.v[0], q.v[0], __hmul2_rn(p.v[1], q.v[1]));   // (f_0, f_2)
@@ -214,8 +220,9 @@ __device__ __forceinline__ __half worker_sum(__half x, unsigned wmask) {
 // t = fma(e, y, -(lam*x)) and x' = fma(lr, t, x), element-wise
 __device__ __forceinline__ V8f grad(float e, const V8f& y, float lam, const V8f& x) {
     V8f g;
+    const float2 e2 = make_float2(e, e), nlam2 = make_float2(-lam, -lam);      // (-lam) * x == -(lam * x), bit for bit
 #pragma unroll
-    for (int s = 0; s < 8; s++) g.x[s] = __fmaf_rn(e, y.x[s], -__fmul_rn(lam, x.x[s]));
+    for (int j = 0; j < 4; j++) set_pr(g, j, __ffma2_rn(e2, pr(y, j), __fmul2_rn(nlam2, pr(x, j))));
     return g;
 }
 __device__ __forceinline__ V8h grad(__half2 e, const V8h& y, __half2 lam, const V8h& x) {
@@ -226,8 +233,9 @@ __device__ __forceinline__ V8h grad(__half2 e, const V8h& y, __half2 lam, const 
 }
 __device__ __forceinline__ V8f step(float lr, const V8f& g, const V8f& x) {
     V8f o;
+    const float2 lr2 = make_float2(lr, lr);
 #pragma unroll
-    for (int s = 0; s < 8; s++) o.x[s] = __fmaf_rn(lr, g.x[s], x.x[s]);
+    for (int j = 0; j < 4; j++) set_pr(o, j, __ffma2_rn(lr2, pr(g, j), pr(x, j)));
     return o;
 }
 __device__ __forceinline__ V8h step(__half2 lr, const V8h& g, const V8h& x) {
@@ -544,10 +552,11 @@ __device__ __forceinline__ void update_one(const Consts& c, float r, uint32_t uc
         const __half2 e = __half2half2(__hmul_rn(c.mpt_scale, __hsub_rn(__float2half_rn(r), dot)));
         const V8f gp = widen(grad(e, qh, c.mpt_lam, ph)), gq = widen(grad(e, ph, c.mpt_lam, qh));
         V8f po, qo;
+        const float2 lr2 = make_float2(c.lr, c.lr), rev2 = make_float2(c.mpt_rev, c.mpt_rev);
 #pragma unroll
-        for (int s = 0; s < 8; s++) {
-            po.x[s] = __fmaf_rn(c.lr, __fmul_rn(c.mpt_rev, gp.x[s]), p.x[s]);
-            qo.x[s] = __fmaf_rn(c.lr, __fmul_rn(c.mpt_rev, gq.x[s]), q.x[s]);
+        for (int j = 0; j < 4; j++) {
+            set_pr(po, j, __ffma2_rn(lr2, __fmul2_rn(rev2, pr(gp, j)), pr(p, j)));
+            set_pr(qo, j, __ffma2_rn(lr2, __fmul2_rn(rev2, pr(gq, j)), pr(q, j)));
         }
         put(p_raw, po); put(q_raw, qo);
     } else if constexpr (KIND == KIND_MUPPET) {
@@ -604,15 +613,16 @@ __device__ __forceinline__ void cp16(void* smem_dst, const void* gsrc) {
 __device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// Slot layout: the first 16 bytes of every lane, then (fp32 rows) the second 16 bytes of every lane,
-// so that 128-bit shared-memory accesses of neighbouring lanes never collide on a bank.
+// Slot layout = row layout: the first 16 bytes of every lane, then (fp32 rows) the second 16 bytes of
+// every lane (layout.cuh), so that neither the 128-bit shared-memory accesses of neighbouring lanes collide
+// on a bank nor the global accesses of a worker touch partial sectors.
 template <int K, int MODE>
 __device__ __forceinline__ void cp_row(unsigned char* slot, const Arena& A, uint32_t code, int m) {
     const uint32_t row = code & kIdMask;
     if (is_f32<MODE>(code)) {
-        const unsigned char* g = reinterpret_cast<const unsigned char*>(A.f32 + (size_t)row * K) + 32 * m;
+        const unsigned char* g = reinterpret_cast<const unsigned char*>(A.f32 + (size_t)row * K) + 16 * m;
         cp16(slot + 16 * m, g);
-        if constexpr (MODE != ROWS_HALF) cp16(slot + 2 * K + 16 * m, g + 16);
+        if constexpr (MODE != ROWS_HALF) cp16(slot + 2 * K + 16 * m, g + 2 * K);       // second half of the row
     } else {
         cp16(slot + 16 * m, reinterpret_cast<const unsigned char*>(A.f16 + (size_t)row * K) + 16 * m);
     }
@@ -650,7 +660,7 @@ template <int K, int UM, int IM, int NS, int NSI> struct WorkerSmem {
 // worker updates between the request and the write-back loses that update, and the chance of that
 // grows with the lead.
 template <int K, int KIND, int UM, int IM, bool STATS, int NS, int NSI, int D, int DI>
-__global__ void __launch_bounds__(256, (UM == ROWS_HALF && IM == ROWS_HALF && !STATS) ? 4 : 3) train_kernel(const KernelArgs a) {
+__global__ void __launch_bounds__(256, (UM == ROWS_HALF && IM == ROWS_HALF && !STATS) ? 4 : ((UM == ROWS_DYN || STATS) ? 2 : 3)) train_kernel(const KernelArgs a) {
     using SM = WorkerSmem<K, UM, IM, NS, NSI>;
     constexpr int TS = SM::TS;                     // lanes per worker = ratings per chunk
     static_assert(TS % NS == 0, "the ring must divide the chunk");

@@ -80,8 +80,9 @@ typedef struct mascot_config {
                                        fewer workers lose fewer updates of popular rows to races and
                                        converge faster per epoch, more workers run faster; rounded up
                                        to fill every SM evenly; 0 = automatic (one per 8192 training
-                                       ratings, at least 512, at most what the GPU keeps resident;
-                                       sets under 1.5M ratings: one per 512 ratings, at most 1536)
+                                       ratings, at least 512, at most what the GPU keeps resident - or 16 warps
+                                       per SM when the binary16 factors exceed the GPU's L2, where more workers
+                                       run slower; sets under 1.5M ratings: one per 512 ratings, at most 1536)
                                                                                    default 2048        */
     uint32_t epoch;              /* -l   number of epochs          default 50                  */
     uint32_t thread_block_size;  /* -bl  accepted for CLI parity, not used (blocks are sized per SM) */
@@ -100,7 +101,15 @@ typedef struct mascot_config {
     uint32_t plain_user_stores;  /* extension: 0 (default) = with more than one worker, user rows are written back as
                                     reductions of their change, so racing updates of one user are not lost;
                                     1 = plain stores like the reference (racing updates overwrite each other) */
-    uint32_t reserved[5];
+    uint32_t l2_item_window;     /* extension: 1 = ask the GPU to keep the item factors in L2 (a persisting access-policy
+                                    window of the engine's stream over the item arena, sized to what the device allows);
+                                    for data sets whose factors exceed L2.  Sets this process's persisting-L2 limit on
+                                    the device for the life of the engine; mascot_destroy puts the old limit back. */
+    uint32_t no_class_partition; /* extension: 0 (default) = automatic: after a promotion the stream is re-ordered by precision
+                                    class (see mascot_train_epoch) while the binary16 factors fit the GPU's L2; larger
+                                    models keep their order and every launch reads each id's precision bit (measured
+                                    faster there); 1 = never re-order; 2 = always re-order */
+    uint32_t reserved[3];
 } mascot_config;
 
 typedef struct mascot_epoch_stats {
@@ -186,7 +195,8 @@ MASCOT_API int mascot_set_factors(mascot_handle* h, const float* P, const float*
  * Per-worker state of the AFP trainer starts afresh with every launched range.
  * After a promotion, and with more than one worker, the stream is stably re-ordered inside each segment
  * by (user precision, item precision), so that every class runs a kernel instantiation without
- * per-rating precision tests; mascot_stream_source_index / mascot_get_stream_order follow the new order.
+ * per-rating precision tests (one launch per class, one after the other; models larger than the GPU's L2 keep
+ * their order, see mascot_config.no_class_partition); mascot_stream_source_index / mascot_get_stream_order follow the new order.
  * The deterministic mode never re-orders. */
 MASCOT_API int mascot_train_epoch(mascot_handle* h, uint32_t epoch, mascot_epoch_stats* stats);
 
@@ -255,7 +265,8 @@ MASCOT_API int mascot_set_ratings_sharded(mascot_handle* h, const mascot_rating*
  * segments of the resident stream, as after mascot_reload_train.  Ids must be those given to
  * mascot_set_ratings (same users/items; checked on the device, MASCOT_ERR_BAD_ARG as for
  * mascot_reload_train); on a check epoch every piece contributes its own sampled tail (see
- * mascot_train_epoch).  No reference counterpart (the reference uploads once,
+ * mascot_train_epoch).  The pieces are never re-ordered by precision class (that would need a host wait
+ * per piece); once groups have been promoted each piece runs the kernel that reads every id's precision bit.  No reference counterpart (the reference uploads once,
  * mf_methods.cu:41-42).  AFP is not supported here (its per-worker state spans a whole epoch). */
 MASCOT_API int mascot_train_epoch_streamed(mascot_handle* h, uint32_t epoch, const mascot_rating* train, uint64_t n_train,
                                 mascot_epoch_stats* stats);
@@ -365,7 +376,9 @@ MASCOT_API int mascot_rmse_device(const float* d_P, const float* d_Q, uint32_t k
  *   - limit: at most 33,554,432 test ratings per call (65,536 blocks of 512); larger sets are
  *     rejected with MASCOT_ERR_BAD_ARG and a message naming the limit;
  *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress, with
- *     that device current); make that first call before any stream capture begins;
+ *     that device current); make that first call before any stream capture begins.  "No allocation"
+ *     holds from the second call on a device: the first one also makes the CUDA runtime load this
+ *     kernel's module onto the device, which allocates driver-side memory once;
  *   - all calls share the one array (and one host staging buffer) and it keeps the previous call's
  *     contents; each call overwrites every entry it reads, so nothing needs clearing, but two calls
  *     that overlap in time - from different threads or on different streams of one GPU - race;
