@@ -101,14 +101,16 @@ cudaError_t launch_encode_stream(const void* d_src_aos, uint64_t n, bool shuffle
                                  cudaStream_t st);
 cudaError_t launch_recode(uint32_t* ids, uint64_t n, const uint8_t* prec_row, cudaStream_t st);
 // Stable partition of a coded stream by precision class inside every segment: rating j goes to the
-// position given by the stable order of (segment, class), class = 2 * (user row fp32) + (item row fp32).
-// Inputs r/u/i/src (src may be null) stay untouched; the result goes to r2/u2/i2/src2.  key_* (n u16),
+// position given by the stable order of (segment, class), class = 2 * (user row fp32) + (item row fp32);
+// with run_window_log2 >= 16 the classes with fp32 item rows are also sorted by item inside windows of
+// 2^run_window_log2 positions (0: they keep their order like the others).
+// Inputs r/u/i/src (src may be null) stay untouched; the result goes to r2/u2/i2/src2.  key_* (n u64),
 // idx_* (n u32) and temp (partition_temp_bytes) are scratch; d_first receives, for every key
 // segment * 4 + class, the first position holding it (all ones when the key does not occur).
-size_t partition_temp_bytes(uint64_t n, int key_bits);
+size_t partition_temp_bytes(uint64_t n, int key_bits, int run_window_log2);
 cudaError_t launch_partition_by_class(const float* r, const uint32_t* u, const uint32_t* i, const uint32_t* src, uint64_t n,
-                                      const uint64_t* d_seg_off, int nseg, int key_bits,
-                                      uint16_t* key_a, uint16_t* key_b, uint32_t* idx_a, uint32_t* idx_b,
+                                      const uint64_t* d_seg_off, int nseg, int key_bits, int run_window_log2,
+                                      uint64_t* key_a, uint64_t* key_b, uint32_t* idx_a, uint32_t* idx_b,
                                       void* temp, size_t temp_bytes, unsigned long long* d_first,
                                       float* r2, uint32_t* u2, uint32_t* i2, uint32_t* src2, cudaStream_t st);
 cudaError_t launch_scatter_factors(int K, const float* src, uint32_t rows, const uint32_t* row_map,

@@ -220,15 +220,18 @@ int partition_segments(mascot_handle* h, size_t seg_first, size_t seg_count) {
     int key_bits = 2;
     while ((1ull << key_bits) < seg_count * 4) key_bits++;
     auto up = [](size_t b) { return (b + 255) / 256 * 256; };
-    const size_t temp_bytes = partition_temp_bytes(n, key_bits);
-    const size_t b_key = up(sizeof(uint16_t) * n), b_idx = up(sizeof(uint32_t) * n), b_seg = up(sizeof(uint64_t) * (seg_count + 1));
+    int run_window_log2 = 0;
+    if (const char* e = getenv("MASCOT_EXP_HOTWIN")) run_window_log2 = atoi(e);
+    if (run_window_log2 && run_window_log2 < 16) run_window_log2 = 16;
+    const size_t temp_bytes = partition_temp_bytes(n, key_bits, run_window_log2);
+    const size_t b_key = up(sizeof(uint64_t) * n), b_idx = up(sizeof(uint32_t) * n), b_seg = up(sizeof(uint64_t) * (seg_count + 1));
     const size_t b_first = up(sizeof(unsigned long long) * seg_count * 4);
     const size_t total = 2 * b_key + 2 * b_idx + 4 * b_idx + b_seg + b_first + up(temp_bytes);
     int rc = need_scratch(h, total);
     if (rc != MASCOT_OK) return rc;
     unsigned char* base = static_cast<unsigned char*>(h->d_scratch);
-    uint16_t* key_a = reinterpret_cast<uint16_t*>(base); base += b_key;
-    uint16_t* key_b = reinterpret_cast<uint16_t*>(base); base += b_key;
+    uint64_t* key_a = reinterpret_cast<uint64_t*>(base); base += b_key;
+    uint64_t* key_b = reinterpret_cast<uint64_t*>(base); base += b_key;
     uint32_t* idx_a = reinterpret_cast<uint32_t*>(base); base += b_idx;
     uint32_t* idx_b = reinterpret_cast<uint32_t*>(base); base += b_idx;
     float* r2 = reinterpret_cast<float*>(base); base += b_idx;
@@ -242,7 +245,7 @@ int partition_segments(mascot_handle* h, size_t seg_first, size_t seg_count) {
     for (size_t j = 0; j <= seg_count; j++) rel[j] = h->seg_off[seg_first + j] - begin;
     CU(h, cudaMemcpyAsync(d_seg, rel.data(), sizeof(uint64_t) * rel.size(), cudaMemcpyHostToDevice, h->stream));
     uint32_t* src = h->tr_src ? h->tr_src + begin : nullptr;
-    CU(h, launch_partition_by_class(h->tr_r + begin, h->tr_u + begin, h->tr_i + begin, src, n, d_seg, (int)seg_count, key_bits,
+    CU(h, launch_partition_by_class(h->tr_r + begin, h->tr_u + begin, h->tr_i + begin, src, n, d_seg, (int)seg_count, key_bits, run_window_log2,
                                     key_a, key_b, idx_a, idx_b, temp, temp_bytes, d_first, r2, u2, i2, s2, h->stream));
     CU(h, cudaMemcpyAsync(h->tr_r + begin, r2, sizeof(float) * n, cudaMemcpyDeviceToDevice, h->stream));
     CU(h, cudaMemcpyAsync(h->tr_u + begin, u2, sizeof(uint32_t) * n, cudaMemcpyDeviceToDevice, h->stream));
@@ -265,7 +268,10 @@ int partition_segments(mascot_handle* h, size_t seg_first, size_t seg_count) {
 bool factors_fit_l2(const mascot_handle* h) {
     int l2 = 0;
     if (cudaDeviceGetAttribute(&l2, cudaDevAttrL2CacheSize, h->cfg.device) != cudaSuccess || l2 <= 0) return true;
-    return ((size_t)h->n_users + h->n_items) * h->K * sizeof(__half) <= (size_t)l2 + (size_t)l2 / 2;
+    // an engine of a sharded group works on its own users and one item block at a time
+    const size_t users = h->ulay.parts > 1 ? h->ulay.rows_per_part : h->n_users;
+    const size_t items = h->ilay.parts > 1 ? h->ilay.rows_per_part : h->n_items;
+    return (users + items) * h->K * sizeof(__half) <= (size_t)l2 + (size_t)l2 / 2;
 }
 
 bool wants_partition(const mascot_handle* h) {
@@ -507,8 +513,9 @@ unsigned worker_count(const mascot_handle* h, uint64_t n) {
     uint64_t w = std::min<uint64_t>(std::max<uint64_t>(n / 8192, 512), 1u << 20);
     // Factors beyond L2: the rows stream from HBM and 16 warps per SM saturate it; more workers only add
     // contention on the popular rows (252M-rating set, all rows binary16: 45.4 ms per epoch with 4,736 workers,
-    // 52.8 with 7,104, 53.3 with 9,472; 53.7 with 2,368).
-    if (!factors_fit_l2(h)) w = std::min<uint64_t>(w, (uint64_t)sm_count() * 16 * (32 / (h->K / 8)));
+    // 52.8 with 7,104, 53.3 with 9,472; 53.7 with 2,368).  The AFP trainer is bound by its own arithmetic
+    // (fixed-point conversion of every element in both passes), not by memory: it keeps the full count.
+    if (!factors_fit_l2(h) && h->kind != KIND_AFP) w = std::min<uint64_t>(w, (uint64_t)sm_count() * 16 * (32 / (h->K / 8)));
     return (unsigned)w;
 }
 
@@ -608,8 +615,9 @@ int train_span(mascot_handle* h, float lr, uint32_t epoch, uint64_t begin, uint6
     if (head < n) {
         Stream sb; sb.r = s.r + head; sb.u = s.u + head; sb.i = s.i + head; sb.n = n - head;
         const SampleStats st = stats_view(h);
+        LaunchShape tail_shape;            // the caller is told the shape of the plain launch when there is one
         CU(h, launch_train(h->K, kind, sb, h->P, h->Q, lr, h->cfg.lambda, &st, cls, workers,
-                           counters, muppet_bits(h), (int)epoch, h->cfg.plain_user_stores == 0, stream, shape));
+                           counters, muppet_bits(h), (int)epoch, h->cfg.plain_user_stores == 0, stream, head > 0 ? &tail_shape : shape));
         (*launches)++;
     }
     return MASCOT_OK;

@@ -254,16 +254,24 @@ cudaError_t launch_recode(uint32_t* ids, uint64_t n, const uint8_t* prec_row, cu
 }
 
 // ---- partition of the stream by precision class ---------------------------------------------
-// key = segment * 4 + class, class = 2 * (user row is fp32) + (item row is fp32).  A stable sort by
-// that key keeps the segments where they are and, inside each, puts the ratings of one class next to
-// each other in their previous order (so runs of equal items stay runs).
+// key = (segment * 4 + class) << 46 | order inside the class, class = 2 * (user row is fp32) + (item row is
+// fp32).  The low part is zero for the classes whose item rows are binary16: a stable sort then keeps the
+// segments where they are and, inside each, puts the ratings of one class next to each other in their
+// previous order (so runs of equal items stay runs).  For the classes with fp32 item rows - the popular
+// items - and run_window_log2 > 0 the low part is (position >> run_window_log2) << 30 | item row: inside
+// windows of that many positions the ratings are sorted by item, which makes the runs of an item
+// (2^run_window_log2 / 4096) times longer, i.e. that many fewer reads and writes of the popular rows.
+constexpr int kClassShift = 46;
 __global__ void class_key_kernel(const uint32_t* u, const uint32_t* i, uint64_t n, const uint64_t* seg_off, int nseg,
-                                 uint16_t* key, uint32_t* idx) {
+                                 int run_window_log2, uint64_t* key, uint32_t* idx) {
     for (uint64_t j = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; j < n; j += (uint64_t)gridDim.x * blockDim.x) {
         int lo = 0, hi = nseg - 1;                    // last segment whose offset is <= j
         while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (seg_off[mid] <= j) lo = mid; else hi = mid - 1; }
-        const uint32_t cls = ((u[j] & kPrecBit) ? 2u : 0u) | ((i[j] & kPrecBit) ? 1u : 0u);
-        key[j] = (uint16_t)(lo * 4 + cls);
+        const uint32_t ic = i[j];
+        const uint64_t cls = ((u[j] & kPrecBit) ? 2u : 0u) | ((ic & kPrecBit) ? 1u : 0u);
+        uint64_t k = ((uint64_t)lo * 4 + cls) << kClassShift;
+        if (run_window_log2 > 0 && (cls & 1u)) k |= ((j >> run_window_log2) << 30) | (ic & kIdMask);
+        key[j] = k;
         idx[j] = (uint32_t)j;
     }
 }
@@ -275,28 +283,38 @@ __global__ void class_gather_kernel(const uint32_t* perm, uint64_t n, const floa
         if (src) src2[j] = src[s];
     }
 }
-// first[k] = smallest position whose key is k (entries of absent keys keep their preset value)
-__global__ void class_first_kernel(const uint16_t* key_sorted, uint64_t n, unsigned long long* first) {
+// first[k] = smallest position whose class key is k (entries of absent keys keep their preset value)
+__global__ void class_first_kernel(const uint64_t* key_sorted, uint64_t n, unsigned long long* first) {
     for (uint64_t j = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; j < n; j += (uint64_t)gridDim.x * blockDim.x)
-        if (j == 0 || key_sorted[j] != key_sorted[j - 1]) first[key_sorted[j]] = j;
+        if (j == 0 || (key_sorted[j] >> kClassShift) != (key_sorted[j - 1] >> kClassShift)) first[key_sorted[j] >> kClassShift] = j;
 }
 
-size_t partition_temp_bytes(uint64_t n, int key_bits) {
+// Bits of the sort key that can differ: without item-sorted windows only the class part.
+static inline void partition_key_range(int key_bits, int run_window_log2, int* begin_bit, int* end_bit) {
+    *begin_bit = run_window_log2 > 0 ? 0 : kClassShift;
+    *end_bit = kClassShift + key_bits;
+}
+
+size_t partition_temp_bytes(uint64_t n, int key_bits, int run_window_log2) {
     size_t bytes = 0;
-    cub::DeviceRadixSort::SortPairs(nullptr, bytes, (const uint16_t*)nullptr, (uint16_t*)nullptr, (const uint32_t*)nullptr,
-                                    (uint32_t*)nullptr, n, 0, key_bits);
+    int b0, b1;
+    partition_key_range(key_bits, run_window_log2, &b0, &b1);
+    cub::DeviceRadixSort::SortPairs(nullptr, bytes, (const uint64_t*)nullptr, (uint64_t*)nullptr, (const uint32_t*)nullptr,
+                                    (uint32_t*)nullptr, n, b0, b1);
     return bytes;
 }
 
 cudaError_t launch_partition_by_class(const float* r, const uint32_t* u, const uint32_t* i, const uint32_t* src, uint64_t n,
-                                      const uint64_t* d_seg_off, int nseg, int key_bits,
-                                      uint16_t* key_a, uint16_t* key_b, uint32_t* idx_a, uint32_t* idx_b,
+                                      const uint64_t* d_seg_off, int nseg, int key_bits, int run_window_log2,
+                                      uint64_t* key_a, uint64_t* key_b, uint32_t* idx_a, uint32_t* idx_b,
                                       void* temp, size_t temp_bytes, unsigned long long* d_first,
                                       float* r2, uint32_t* u2, uint32_t* i2, uint32_t* src2, cudaStream_t st) {
     if (n == 0) return cudaSuccess;
     const int g = grid_for(n, 256);
-    class_key_kernel<<<g, 256, 0, st>>>(u, i, n, d_seg_off, nseg, key_a, idx_a);
-    cudaError_t e = cub::DeviceRadixSort::SortPairs(temp, temp_bytes, key_a, key_b, idx_a, idx_b, n, 0, key_bits, st);
+    int b0, b1;
+    partition_key_range(key_bits, run_window_log2, &b0, &b1);
+    class_key_kernel<<<g, 256, 0, st>>>(u, i, n, d_seg_off, nseg, run_window_log2, key_a, idx_a);
+    cudaError_t e = cub::DeviceRadixSort::SortPairs(temp, temp_bytes, key_a, key_b, idx_a, idx_b, n, b0, b1, st);
     if (e != cudaSuccess) return e;
     class_gather_kernel<<<g, 256, 0, st>>>(idx_b, n, r, u, i, src, r2, u2, i2, src2);
     e = cudaMemsetAsync(d_first, 0xff, sizeof(unsigned long long) * (size_t)nseg * 4, st);

@@ -141,3 +141,36 @@ def test_full_grid_then_single_block_then_full_grid(mascot):
         rm.append(eng.eval_rmse())
         eng.close()
     assert all(np.isfinite(rm))
+
+
+def test_ids_out_of_range_are_reported_and_never_used_as_an_index(mascot):
+    """mascot_set_ratings, mascot_reload_train and mascot_train_epoch_streamed check ids on the device: a bad id
+    gives MASCOT_ERR_BAD_ARG (the rating is replaced by a zero rating of row 0, no out-of-bounds access), and the
+    engine keeps working once a valid array is loaded."""
+    k, nu, ni, n = 64, 500, 400, 20000
+    rng = np.random.default_rng(12)
+    R, P, Q = random_problem(rng, nu, ni, n, k)
+    bad = R.copy(); bad["u"][n // 2] = nu + 7
+    bad_item = R.copy(); bad_item["i"][17] = 0x3fffffff
+    eng = make_engine(mascot, mascot.V_SGD, k, deterministic=0, shuffle=1, num_workers=64)
+    with pytest.raises(mascot.MascotError) as err:
+        eng.set_ratings(bad, R[:100], nu, ni)
+    assert err.value.status == mascot.ERR_BAD_ARG and "out of range" in str(err.value)
+    with pytest.raises(mascot.MascotError) as err:
+        eng.set_ratings(R, bad_item[:100], nu, ni)
+    assert err.value.status == mascot.ERR_BAD_ARG
+    eng.set_ratings(R, R[:100], nu, ni)
+    eng.set_factors(P, Q)
+    for broken in (bad, bad_item):
+        with pytest.raises(mascot.MascotError) as err:
+            eng.reload_train(broken)
+        assert err.value.status == mascot.ERR_BAD_ARG
+        with pytest.raises(mascot.MascotError) as err:
+            eng.train_epoch_streamed(0, broken)
+        assert err.value.status == mascot.ERR_BAD_ARG
+    eng.reload_train(R)
+    r0 = eng.eval_rmse()
+    for e in range(3):
+        eng.train_epoch(e)
+    assert np.isfinite(eng.eval_rmse()) and eng.eval_rmse() < r0
+    eng.close()
