@@ -73,6 +73,8 @@ struct LaunchShape {
 // re-estimates its formats at every rating early in epoch 0).  With `add_user_delta` (ignored for a
 // single worker) user rows are written back as reductions of their change, so that concurrent
 // updates of one user by several workers are not lost.  Returns the launch shape used.
+// With `counters` == nullptr the call is dry: the instantiation the launch would use is loaded and configured
+// (so that the first real launch does not pay for it) and nothing is launched.
 // MuPPET statistics use gsum_p[0..K) (sum of the sampled updates, physical order) and nsum_p[0].
 cudaError_t launch_train(int K, TrainKind kind, const Stream& s, Arena P, Arena Q, float lr, float lam,
                          const SampleStats* stats, RowClass row_class, unsigned workers,
@@ -100,19 +102,19 @@ cudaError_t launch_encode_stream(const void* d_src_aos, uint64_t n, bool shuffle
                                  float* r, uint32_t* u, uint32_t* i, uint32_t* src_out, uint32_t src_base,
                                  cudaStream_t st);
 cudaError_t launch_recode(uint32_t* ids, uint64_t n, const uint8_t* prec_row, cudaStream_t st);
-// Stable partition of a coded stream by precision class inside every segment: rating j goes to the
-// position given by the stable order of (segment, class), class = 2 * (user row fp32) + (item row fp32);
-// with run_window_log2 >= 16 the classes with fp32 item rows are also sorted by item inside windows of
-// 2^run_window_log2 positions (0: they keep their order like the others).
+// Stable re-ordering of a coded stream inside every segment, by precision class (by_class; class = 2 * (user
+// row fp32) + (item row fp32)) and / or by item inside windows of 2^run_window_log2 positions
+// (run_window_log2 > 0; item_rows = rows of the item arena, which bounds the item part of the key).
 // Inputs r/u/i/src (src may be null) stay untouched; the result goes to r2/u2/i2/src2.  key_* (n u64),
-// idx_* (n u32) and temp (partition_temp_bytes) are scratch; d_first receives, for every key
-// segment * 4 + class, the first position holding it (all ones when the key does not occur).
-size_t partition_temp_bytes(uint64_t n, int key_bits, int run_window_log2);
-cudaError_t launch_partition_by_class(const float* r, const uint32_t* u, const uint32_t* i, const uint32_t* src, uint64_t n,
-                                      const uint64_t* d_seg_off, int nseg, int key_bits, int run_window_log2,
-                                      uint64_t* key_a, uint64_t* key_b, uint32_t* idx_a, uint32_t* idx_b,
-                                      void* temp, size_t temp_bytes, unsigned long long* d_first,
-                                      float* r2, uint32_t* u2, uint32_t* i2, uint32_t* src2, cudaStream_t st);
+// idx_* (n u32) and temp (stream_sort_temp_bytes) are scratch; d_first (may be null) receives, for every
+// segment * 4 + class, the first position holding it (all ones when it does not occur).  segclass_bits =
+// bits of the largest segment * 4 + class.
+size_t stream_sort_temp_bytes(uint64_t n, int segclass_bits, bool by_class, int run_window_log2, uint32_t item_rows);
+cudaError_t launch_stream_sort(const float* r, const uint32_t* u, const uint32_t* i, const uint32_t* src, uint64_t n,
+                               const uint64_t* d_seg_off, int nseg, int segclass_bits, bool by_class, int run_window_log2,
+                               uint32_t item_rows, uint64_t* key_a, uint64_t* key_b, uint32_t* idx_a, uint32_t* idx_b,
+                               void* temp, size_t temp_bytes, unsigned long long* d_first,
+                               float* r2, uint32_t* u2, uint32_t* i2, uint32_t* src2, cudaStream_t st);
 cudaError_t launch_scatter_factors(int K, const float* src, uint32_t rows, const uint32_t* row_map,
                                    bool round_through_half, __half* dst16, float* dst32, cudaStream_t st);
 cudaError_t launch_gather_factors(int K, Arena a, const uint8_t* prec_row, uint32_t rows,

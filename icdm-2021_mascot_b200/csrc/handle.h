@@ -116,6 +116,8 @@ void dev_free(T*& p) { if (p) { cudaFree(p); p = nullptr; } }
 void free_ratings(mascot_handle* h);
 int need_scratch(mascot_handle* h, size_t bytes);           // grow-only device scratch of at least `bytes`
 bool any_fp32_group(const mascot_handle* h);
+int warm_kernels(mascot_handle* h);                        // load the update kernels the first epochs will launch
+int sort_run_windows(mascot_handle* h);                    // item-sorted run windows of a freshly encoded resident stream
 int partition_all(mascot_handle* h);                        // (re)partition the stream by precision class when that pays
 bool is_check_epoch(const mascot_config& c, uint32_t e);
 float lr_at(const mascot_config& c, uint32_t e);

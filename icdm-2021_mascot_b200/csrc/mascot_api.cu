@@ -201,14 +201,16 @@ bool any_fp32_group(const mascot_handle* h) {
     return false;
 }
 
-// Re-orders the segments [seg_first, seg_first + seg_count) of the coded stream so that, inside each
-// segment, the ratings of one precision class are contiguous (stable: the order inside a class is the
-// order before), and records the class boundaries.  Called after the precision bits of the ids changed
-// (promotion + recode) or after a stream was encoded while promoted groups exist.  The single-worker
-// deterministic mode keeps the caller's order and never partitions.
-int partition_segments(mascot_handle* h, size_t seg_first, size_t seg_count) {
+// Re-orders the segments [seg_first, seg_first + seg_count) of the coded stream, stably, inside each segment:
+//   by_class: the ratings of one precision class become contiguous (the order inside a class is the order
+//     before) and the class boundaries are recorded.  Called after the precision bits of the ids changed
+//     (promotion + recode) or after a stream was encoded while promoted groups exist.
+//   run_window_log2 > 0: every window of 2^run_window_log2 positions is sorted by item (longer runs of equal
+//     items).  Called once after a stream was encoded.
+// The single-worker deterministic mode keeps the caller's order and does neither.
+int reorder_segments(mascot_handle* h, size_t seg_first, size_t seg_count, bool by_class, int run_window_log2) {
     const size_t nseg_all = h->seg_off.size() - 1;
-    if (h->cls_off.size() != nseg_all * 5) {
+    if (by_class && h->cls_off.size() != nseg_all * 5) {
         h->cls_off.assign(nseg_all * 5, 0);
         for (size_t sg = 0; sg < nseg_all; sg++) {          // everything in the first class
             h->cls_off[sg * 5] = h->seg_off[sg];
@@ -220,10 +222,7 @@ int partition_segments(mascot_handle* h, size_t seg_first, size_t seg_count) {
     int key_bits = 2;
     while ((1ull << key_bits) < seg_count * 4) key_bits++;
     auto up = [](size_t b) { return (b + 255) / 256 * 256; };
-    int run_window_log2 = 0;
-    if (const char* e = getenv("MASCOT_EXP_HOTWIN")) run_window_log2 = atoi(e);
-    if (run_window_log2 && run_window_log2 < 16) run_window_log2 = 16;
-    const size_t temp_bytes = partition_temp_bytes(n, key_bits, run_window_log2);
+    const size_t temp_bytes = stream_sort_temp_bytes(n, key_bits, by_class, run_window_log2, h->irows);
     const size_t b_key = up(sizeof(uint64_t) * n), b_idx = up(sizeof(uint32_t) * n), b_seg = up(sizeof(uint64_t) * (seg_count + 1));
     const size_t b_first = up(sizeof(unsigned long long) * seg_count * 4);
     const size_t total = 2 * b_key + 2 * b_idx + 4 * b_idx + b_seg + b_first + up(temp_bytes);
@@ -245,15 +244,17 @@ int partition_segments(mascot_handle* h, size_t seg_first, size_t seg_count) {
     for (size_t j = 0; j <= seg_count; j++) rel[j] = h->seg_off[seg_first + j] - begin;
     CU(h, cudaMemcpyAsync(d_seg, rel.data(), sizeof(uint64_t) * rel.size(), cudaMemcpyHostToDevice, h->stream));
     uint32_t* src = h->tr_src ? h->tr_src + begin : nullptr;
-    CU(h, launch_partition_by_class(h->tr_r + begin, h->tr_u + begin, h->tr_i + begin, src, n, d_seg, (int)seg_count, key_bits, run_window_log2,
-                                    key_a, key_b, idx_a, idx_b, temp, temp_bytes, d_first, r2, u2, i2, s2, h->stream));
+    CU(h, launch_stream_sort(h->tr_r + begin, h->tr_u + begin, h->tr_i + begin, src, n, d_seg, (int)seg_count, key_bits, by_class,
+                             run_window_log2, h->irows, key_a, key_b, idx_a, idx_b, temp, temp_bytes, by_class ? d_first : nullptr,
+                             r2, u2, i2, s2, h->stream));
     CU(h, cudaMemcpyAsync(h->tr_r + begin, r2, sizeof(float) * n, cudaMemcpyDeviceToDevice, h->stream));
     CU(h, cudaMemcpyAsync(h->tr_u + begin, u2, sizeof(uint32_t) * n, cudaMemcpyDeviceToDevice, h->stream));
     CU(h, cudaMemcpyAsync(h->tr_i + begin, i2, sizeof(uint32_t) * n, cudaMemcpyDeviceToDevice, h->stream));
     if (src) CU(h, cudaMemcpyAsync(src, s2, sizeof(uint32_t) * n, cudaMemcpyDeviceToDevice, h->stream));
     std::vector<unsigned long long> first(seg_count * 4);
-    CU(h, cudaMemcpyAsync(first.data(), d_first, sizeof(unsigned long long) * first.size(), cudaMemcpyDeviceToHost, h->stream));
+    if (by_class) CU(h, cudaMemcpyAsync(first.data(), d_first, sizeof(unsigned long long) * first.size(), cudaMemcpyDeviceToHost, h->stream));
     CU(h, cudaStreamSynchronize(h->stream));          // `rel` and `first` are host buffers of this call
+    if (!by_class) return MASCOT_OK;
     for (size_t j = 0; j < seg_count; j++) {
         uint64_t* off = &h->cls_off[(seg_first + j) * 5];
         off[4] = h->seg_off[seg_first + j + 1];
@@ -289,9 +290,58 @@ bool wants_partition(const mascot_handle* h) {
 int partition_all(mascot_handle* h) {
     h->partitioned = false;
     if (!wants_partition(h)) return MASCOT_OK;
-    const int rc = partition_segments(h, 0, h->seg_off.size() - 1);
+    const int rc = reorder_segments(h, 0, h->seg_off.size() - 1, true, 0);
     if (rc == MASCOT_OK) h->partitioned = true;
     return rc;
+}
+
+// log2 of the item-sorted run windows of the resident stream; 0 = none beyond the encode kernel's own windows.
+// The configured length (default 2^20) is shortened to the largest power of two that keeps two properties:
+//   * a window is no longer than the ratings all workers of a launch hold at one time (workers x 8 chunks of
+//     K/8 ratings): with longer windows every worker is on the same few items at once, and since item rows are
+//     plain stores most of their updates are lost (100M-rating set, 8,288 workers: windows of 2^20 and 2^22
+//     converge like the unsorted stream, 2^24 needs twice the epochs);
+//   * when statistics are sampled, the sampled tail of every launched range (sample_ratio of a segment) spans
+//     at least four windows, so that every item group is met there in proportion.
+int run_window_log2(const mascot_handle* h) {
+    if (h->cfg.deterministic || !h->cfg.shuffle || h->n_train == 0 || h->n_train >= (1ull << 32) || (h->seg_off.size() - 1) * 4 > 65536) return 0;
+    uint32_t w = h->cfg.run_window_log2 ? std::min<uint32_t>(h->cfg.run_window_log2, 32) : 20;
+    uint64_t limit = (uint64_t)worker_count(h, h->n_train) * 8 * (h->K / 8);
+    const bool sampled = h->kind == KIND_MIXED || h->kind == KIND_SWITCH || h->kind == KIND_MUPPET;
+    if (sampled && h->cfg.sample_ratio > 0.f) {
+        uint64_t shortest = ~0ull;
+        for (size_t sg = 0; sg + 1 < h->seg_off.size(); sg++)
+            if (h->seg_off[sg + 1] > h->seg_off[sg]) shortest = std::min<uint64_t>(shortest, h->seg_off[sg + 1] - h->seg_off[sg]);
+        limit = std::min<uint64_t>(limit, (uint64_t)((double)shortest * h->cfg.sample_ratio / 4.0));
+    }
+    while (w > 12 && (1ull << w) > limit) w--;
+    return w <= 12 ? 0 : (int)w;
+}
+
+int muppet_bits(const mascot_handle* h);
+
+// Loads and configures the update-kernel instantiations the first epochs will launch (the CUDA runtime loads
+// a kernel at its first use, which otherwise costs the first epoch a few milliseconds).  The instantiations
+// for promoted rows are left to their first use.
+int warm_kernels(mascot_handle* h) {
+    if (!h->n_train) return MASCOT_OK;
+    Stream s; s.r = h->tr_r; s.u = h->tr_u; s.i = h->tr_i; s.n = h->n_train;
+    const unsigned workers = worker_count(h, h->n_train);
+    const RowClass cls = any_fp32_group(h) ? ROWCLASS_ANY : ROWCLASS_HH;
+    SampleStats st = SampleStats();
+    const bool sampled = h->kind == KIND_MIXED || h->kind == KIND_SWITCH || h->kind == KIND_MUPPET;
+    for (int with_stats = 0; with_stats <= (sampled ? 1 : 0); with_stats++)
+        CU(h, launch_train(h->K, h->kind, s, h->P, h->Q, 0.f, 0.f, with_stats ? &st : nullptr, cls, workers, nullptr, muppet_bits(h), 0,
+                           h->cfg.plain_user_stores == 0, h->stream, nullptr));
+    return MASCOT_OK;
+}
+
+// Sorts the freshly encoded resident stream by item inside its run windows.
+int sort_run_windows(mascot_handle* h) {
+    const int w = run_window_log2(h);
+    if (w == 0 || h->n_train == 0) return MASCOT_OK;
+    NvtxRange range("mascot: item-sorted run windows");
+    return reorder_segments(h, 0, h->seg_off.size() - 1, false, w);
 }
 
 float reference_rmse_from_partials(const std::vector<float>& part, uint64_t n) {
@@ -444,6 +494,7 @@ int mascot_reload_train(mascot_handle* h, const mascot_rating* train, uint64_t n
     uint32_t bad = 0;
     CU(h, cudaMemcpyAsync(&bad, h->d_err_flag, sizeof(uint32_t), cudaMemcpyDeviceToHost, h->stream));
     h->cls_off.clear();
+    if ((rc = sort_run_windows(h)) != MASCOT_OK) return rc;
     if ((rc = partition_all(h)) != MASCOT_OK) return rc;      // the new stream carries the current precisions
     CU(h, cudaStreamSynchronize(h->stream));
     if (bad) return fail(h, MASCOT_ERR_BAD_ARG, "training rating with id out of range (replaced by zero ratings of row 0; reload a valid array)");

@@ -253,24 +253,30 @@ cudaError_t launch_recode(uint32_t* ids, uint64_t n, const uint8_t* prec_row, cu
     return cudaGetLastError();
 }
 
-// ---- partition of the stream by precision class ---------------------------------------------
-// key = (segment * 4 + class) << 46 | order inside the class, class = 2 * (user row is fp32) + (item row is
-// fp32).  The low part is zero for the classes whose item rows are binary16: a stable sort then keeps the
-// segments where they are and, inside each, puts the ratings of one class next to each other in their
-// previous order (so runs of equal items stay runs).  For the classes with fp32 item rows - the popular
-// items - and run_window_log2 > 0 the low part is (position >> run_window_log2) << 30 | item row: inside
-// windows of that many positions the ratings are sorted by item, which makes the runs of an item
-// (2^run_window_log2 / 4096) times longer, i.e. that many fewer reads and writes of the popular rows.
-constexpr int kClassShift = 46;
-__global__ void class_key_kernel(const uint32_t* u, const uint32_t* i, uint64_t n, const uint64_t* seg_off, int nseg,
-                                 int run_window_log2, uint64_t* key, uint32_t* idx) {
+// ---- re-ordering of the coded stream: precision classes and item-sorted run windows --------------
+// One stable radix sort by the key  ((segment * 4 + class) << window_bits | window) << item_bits | item row :
+//   * class = 2 * (user row is fp32) + (item row is fp32) when the sort is by class, else 0;
+//   * window = position inside the sorted range >> run_window_log2, item = the item's arena row, when the
+//     sort is by item windows (window_bits + item_bits > 0), else both absent.
+// By class only, the ratings of one class become contiguous inside every segment and keep their previous
+// order (so runs of equal items stay runs).  By item windows, the ratings of every window of 2^run_window_log2
+// positions are sorted by item: a run of equal items is then as long as the item's share of such a window,
+// not of the 4096 positions the encode kernel sorts, and a worker reads and writes the item's row once per run.
+struct StreamKey {
+    int use_class;           // 1: the class is part of the key
+    int run_window_log2;     // log2 of the window length; only read when window_bits + item_bits > 0
+    int window_bits, item_bits;
+};
+__global__ void stream_key_kernel(const uint32_t* u, const uint32_t* i, uint64_t n, const uint64_t* seg_off, int nseg,
+                                  StreamKey sk, uint64_t* key, uint32_t* idx) {
     for (uint64_t j = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; j < n; j += (uint64_t)gridDim.x * blockDim.x) {
         int lo = 0, hi = nseg - 1;                    // last segment whose offset is <= j
         while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (seg_off[mid] <= j) lo = mid; else hi = mid - 1; }
         const uint32_t ic = i[j];
-        const uint64_t cls = ((u[j] & kPrecBit) ? 2u : 0u) | ((ic & kPrecBit) ? 1u : 0u);
-        uint64_t k = ((uint64_t)lo * 4 + cls) << kClassShift;
-        if (run_window_log2 > 0 && (cls & 1u)) k |= ((j >> run_window_log2) << 30) | (ic & kIdMask);
+        const uint64_t cls = sk.use_class ? (((u[j] & kPrecBit) ? 2u : 0u) | ((ic & kPrecBit) ? 1u : 0u)) : 0u;
+        uint64_t k = (uint64_t)lo * 4 + cls;
+        if (sk.window_bits + sk.item_bits > 0)
+            k = (((k << sk.window_bits) | (j >> sk.run_window_log2)) << sk.item_bits) | (ic & kIdMask);
         key[j] = k;
         idx[j] = (uint32_t)j;
     }
@@ -283,43 +289,49 @@ __global__ void class_gather_kernel(const uint32_t* perm, uint64_t n, const floa
         if (src) src2[j] = src[s];
     }
 }
-// first[k] = smallest position whose class key is k (entries of absent keys keep their preset value)
-__global__ void class_first_kernel(const uint64_t* key_sorted, uint64_t n, unsigned long long* first) {
+// first[k] = smallest position whose (segment, class) part of the key is k (entries of absent keys keep their
+// preset value)
+__global__ void class_first_kernel(const uint64_t* key_sorted, uint64_t n, int low_bits, unsigned long long* first) {
     for (uint64_t j = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; j < n; j += (uint64_t)gridDim.x * blockDim.x)
-        if (j == 0 || (key_sorted[j] >> kClassShift) != (key_sorted[j - 1] >> kClassShift)) first[key_sorted[j] >> kClassShift] = j;
+        if (j == 0 || (key_sorted[j] >> low_bits) != (key_sorted[j - 1] >> low_bits)) first[key_sorted[j] >> low_bits] = j;
 }
 
-// Bits of the sort key that can differ: without item-sorted windows only the class part.
-static inline void partition_key_range(int key_bits, int run_window_log2, int* begin_bit, int* end_bit) {
-    *begin_bit = run_window_log2 > 0 ? 0 : kClassShift;
-    *end_bit = kClassShift + key_bits;
+static StreamKey make_stream_key(uint64_t n, bool by_class, int run_window_log2, uint32_t item_rows) {
+    StreamKey sk{by_class ? 1 : 0, run_window_log2, 0, 0};
+    if (run_window_log2 > 0) {
+        while (((n - 1) >> run_window_log2) >> sk.window_bits) sk.window_bits++;
+        while (sk.item_bits < 30 && (item_rows - 1u) >> sk.item_bits) sk.item_bits++;
+        if (sk.item_bits == 0) sk.item_bits = 1;
+    }
+    return sk;
 }
 
-size_t partition_temp_bytes(uint64_t n, int key_bits, int run_window_log2) {
+size_t stream_sort_temp_bytes(uint64_t n, int segclass_bits, bool by_class, int run_window_log2, uint32_t item_rows) {
     size_t bytes = 0;
-    int b0, b1;
-    partition_key_range(key_bits, run_window_log2, &b0, &b1);
+    const StreamKey sk = make_stream_key(n, by_class, run_window_log2, item_rows);
     cub::DeviceRadixSort::SortPairs(nullptr, bytes, (const uint64_t*)nullptr, (uint64_t*)nullptr, (const uint32_t*)nullptr,
-                                    (uint32_t*)nullptr, n, b0, b1);
+                                    (uint32_t*)nullptr, n, 0, segclass_bits + sk.window_bits + sk.item_bits);
     return bytes;
 }
 
-cudaError_t launch_partition_by_class(const float* r, const uint32_t* u, const uint32_t* i, const uint32_t* src, uint64_t n,
-                                      const uint64_t* d_seg_off, int nseg, int key_bits, int run_window_log2,
-                                      uint64_t* key_a, uint64_t* key_b, uint32_t* idx_a, uint32_t* idx_b,
-                                      void* temp, size_t temp_bytes, unsigned long long* d_first,
-                                      float* r2, uint32_t* u2, uint32_t* i2, uint32_t* src2, cudaStream_t st) {
+cudaError_t launch_stream_sort(const float* r, const uint32_t* u, const uint32_t* i, const uint32_t* src, uint64_t n,
+                               const uint64_t* d_seg_off, int nseg, int segclass_bits, bool by_class, int run_window_log2,
+                               uint32_t item_rows, uint64_t* key_a, uint64_t* key_b, uint32_t* idx_a, uint32_t* idx_b,
+                               void* temp, size_t temp_bytes, unsigned long long* d_first,
+                               float* r2, uint32_t* u2, uint32_t* i2, uint32_t* src2, cudaStream_t st) {
     if (n == 0) return cudaSuccess;
     const int g = grid_for(n, 256);
-    int b0, b1;
-    partition_key_range(key_bits, run_window_log2, &b0, &b1);
-    class_key_kernel<<<g, 256, 0, st>>>(u, i, n, d_seg_off, nseg, run_window_log2, key_a, idx_a);
-    cudaError_t e = cub::DeviceRadixSort::SortPairs(temp, temp_bytes, key_a, key_b, idx_a, idx_b, n, b0, b1, st);
+    const StreamKey sk = make_stream_key(n, by_class, run_window_log2, item_rows);
+    stream_key_kernel<<<g, 256, 0, st>>>(u, i, n, d_seg_off, nseg, sk, key_a, idx_a);
+    cudaError_t e = cub::DeviceRadixSort::SortPairs(temp, temp_bytes, key_a, key_b, idx_a, idx_b, n, 0,
+                                                    segclass_bits + sk.window_bits + sk.item_bits, st);
     if (e != cudaSuccess) return e;
     class_gather_kernel<<<g, 256, 0, st>>>(idx_b, n, r, u, i, src, r2, u2, i2, src2);
-    e = cudaMemsetAsync(d_first, 0xff, sizeof(unsigned long long) * (size_t)nseg * 4, st);
-    if (e != cudaSuccess) return e;
-    class_first_kernel<<<g, 256, 0, st>>>(key_b, n, d_first);
+    if (d_first) {
+        e = cudaMemsetAsync(d_first, 0xff, sizeof(unsigned long long) * (size_t)nseg * 4, st);
+        if (e != cudaSuccess) return e;
+        class_first_kernel<<<g, 256, 0, st>>>(key_b, n, sk.window_bits + sk.item_bits, d_first);
+    }
     return cudaGetLastError();
 }
 

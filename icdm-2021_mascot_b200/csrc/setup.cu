@@ -416,6 +416,11 @@ int setup_ratings(mascot_handle* h, const SetupRequest& rq) {
     CU(h, dev_alloc(&h->d_block_err, blocks));
     h->h_block_err.assign(blocks, 0.f);
     CU(h, cudaStreamSynchronize(h->stream));
+    // the set-up's own use of the scratch buffer is over: the sort below may re-carve it
+    const int rc_sort = sort_run_windows(h);
+    if (rc_sort != MASCOT_OK) return rc_sort;
+    const int rc_warm = warm_kernels(h);
+    if (rc_warm != MASCOT_OK) return rc_warm;
     h->timings.additional_init_us += now_us() - t_phase;
     h->have_ratings = true;
     return MASCOT_OK;

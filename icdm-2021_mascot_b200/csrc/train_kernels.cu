@@ -300,13 +300,28 @@ __device__ __forceinline__ float muppet_scale(int bits, float hi, float lo) {
     const int e = idx > 127.f ? 128 : (int)idx;
     return e >= 128 ? __int_as_float(0x7f800000) : __int_as_float((e + 127) << 23);
 }
-__device__ __forceinline__ float fix_round(float v, float s, float s_rev) { return __fmul_rn(roundf(__fmul_rn(v, s)), s_rev); }
+// roundf (halves away from zero) in three instructions: trunc(x + copysign(largest float below one half, x)).
+// The sum is rounded to nearest-even, which is what makes it exact: x = n + f with f < 1/2 cannot reach n + 1,
+// f >= 1/2 always does.  Equal to roundf for every one of the 2^32 float patterns (checked exhaustively on the
+// host, tests/round_check.c); the library routine costs about three times as much and these trainers call it
+// 34 times per rating and lane.
+__device__ __forceinline__ float round_away(float x) {
+    const float h = __uint_as_float((__float_as_uint(x) & 0x80000000u) | 0x3effffffu);
+    return truncf(__fadd_rn(x, h));
+}
+// 1 / s for a scale that is a power of two: the exponent mirrored around zero, exact while both s and 1 / s are
+// normal numbers; anything else (2^127, infinity) takes the division.
+__device__ __forceinline__ float pow2_rev(float s) {
+    const uint32_t b = __float_as_uint(s);
+    return (b >= 0x00800000u && b < 0x7f000000u && !(b & 0x007fffffu)) ? __uint_as_float(0x7f000000u - b) : __fdiv_rn(1.f, s);
+}
+__device__ __forceinline__ float fix_round(float v, float s, float s_rev) { return __fmul_rn(round_away(__fmul_rn(v, s)), s_rev); }
 __device__ __forceinline__ int sat8(float v) { return v > 127.f ? 127 : (v < -128.f ? -128 : (int)v); }
 __device__ __forceinline__ V8h fix_round_half(const V8f& x, float s, float s_rev) {
     V8h h;
 #pragma unroll
     for (int t = 0; t < 4; t++)
-        h.v[t] = __halves2half2(__float2half_rn(fix_round(x.x[2 * t], s, s_rev)), __float2half_rn(fix_round(x.x[2 * t + 1], s, s_rev)));
+        h.v[t] = __floats2half2_rn(fix_round(x.x[2 * t], s, s_rev), fix_round(x.x[2 * t + 1], s, s_rev));
     return h;
 }
 template <int TS> __device__ __forceinline__ float worker_min(float x, unsigned wmask) {
@@ -340,7 +355,7 @@ template <int TS>
 __device__ __forceinline__ float forward_int8(const V8f& p, const V8f& q, float sp, float sq, unsigned wmask) {
     int acc = 0;
 #pragma unroll
-    for (int t = 0; t < 8; t++) acc += sat8(roundf(__fmul_rn(p.x[t], sp))) * sat8(roundf(__fmul_rn(q.x[t], sq)));
+    for (int t = 0; t < 8; t++) acc += sat8(round_away(__fmul_rn(p.x[t], sp))) * sat8(round_away(__fmul_rn(q.x[t], sq)));
 #pragma unroll
     for (int d = TS / 2; d >= 1; d >>= 1) acc += __shfl_xor_sync(wmask, acc, d);
     return __fdiv_rn((float)acc, __fmul_rn(sp, sq));
@@ -351,7 +366,7 @@ __device__ __forceinline__ float forward_int8(const V8f& p, const V8f& q, float 
 template <int K>
 __device__ __forceinline__ float forward_half(const V8f& p, const V8f& q, float sp, float sq, unsigned wmask) {
     constexpr int TS = K / 8;
-    const V8h ph = fix_round_half(p, sp, __fdiv_rn(1.f, sp)), qh = fix_round_half(q, sq, __fdiv_rn(1.f, sq));
+    const V8h ph = fix_round_half(p, sp, pow2_rev(sp)), qh = fix_round_half(q, sq, pow2_rev(sq));
     __half2 xy;
     if (K == 128) {
         const __half2 xab = __hfma2(ph.v[0], qh.v[0], __hmul2_rn(ph.v[2], qh.v[2]));   // (x of lane m, x of lane m+16)
@@ -372,16 +387,16 @@ __device__ __forceinline__ float forward_half(const V8f& p, const V8f& q, float 
 // backward passes: g_p = q*e + p*(-lam), g_q = p*e + q*(-lam) in int8 or binary16 fixed point
 __device__ __forceinline__ void backward_int8(const V8f& p, const V8f& q, float ruv, float nlam, float sb, V8f& gp, V8f& gq) {
     const float rev2 = __fdiv_rn(1.f, __fmul_rn(sb, sb));
-    const int ei = sat8(roundf(__fmul_rn(ruv, sb))), li = sat8(roundf(__fmul_rn(nlam, sb)));
+    const int ei = sat8(round_away(__fmul_rn(ruv, sb))), li = sat8(round_away(__fmul_rn(nlam, sb)));
 #pragma unroll
     for (int t = 0; t < 8; t++) {
-        const int pi = sat8(roundf(__fmul_rn(p.x[t], sb))), qi = sat8(roundf(__fmul_rn(q.x[t], sb)));
+        const int pi = sat8(round_away(__fmul_rn(p.x[t], sb))), qi = sat8(round_away(__fmul_rn(q.x[t], sb)));
         gp.x[t] = __fmul_rn((float)(qi * ei + pi * li), rev2);
         gq.x[t] = __fmul_rn((float)(pi * ei + qi * li), rev2);
     }
 }
 __device__ __forceinline__ void backward_half(const V8f& p, const V8f& q, float ruv, float nlam, float sb, V8f& gp, V8f& gq) {
-    const float sb_rev = __fdiv_rn(1.f, sb);
+    const float sb_rev = pow2_rev(sb);
     const __half2 e2 = __half2half2(__float2half_rn(fix_round(ruv, sb, sb_rev)));
     const __half2 l2 = __half2half2(__float2half_rn(fix_round(nlam, sb, sb_rev)));
     const V8h ph = fix_round_half(p, sb, sb_rev), qh = fix_round_half(q, sb, sb_rev);
@@ -451,11 +466,11 @@ __device__ __forceinline__ void afp_lane_sums(const float (&v)[G][N], float scal
     float s[G], sq[G];
 #pragma unroll
     for (int g = 0; g < G; g++) {
-        s[g] = fabsf(v[g][0]); sq[g] = fabsf(__fmul_rn(roundf(__fmul_rn(v[g][0], scale)), rev));
+        s[g] = fabsf(v[g][0]); sq[g] = fabsf(__fmul_rn(round_away(__fmul_rn(v[g][0], scale)), rev));
 #pragma unroll
         for (int j = 1; j < N; j++) {
             s[g] = __fadd_rn(s[g], fabsf(v[g][j]));
-            sq[g] = __fadd_rn(sq[g], fabsf(__fmul_rn(roundf(__fmul_rn(v[g][j], scale)), rev)));
+            sq[g] = __fadd_rn(sq[g], fabsf(__fmul_rn(round_away(__fmul_rn(v[g][j], scale)), rev)));
         }
     }
     if (G == 2) { sum = __fadd_rn(s[0], s[1]); sum_q = __fadd_rn(sq[0], sq[1]); }
@@ -923,7 +938,7 @@ __global__ void reduce_stats_kernel(float* sets, int copies, size_t stride, size
 }
 
 template <int K, int KIND, int UM, int IM, bool STATS, int NS, int NSI, int D, int DI>
-cudaError_t launch_ns(KernelArgs a, unsigned warps_per_sm, unsigned workers, cudaStream_t st, LaunchShape* shape) {
+cudaError_t launch_ns(KernelArgs a, unsigned warps_per_sm, unsigned workers, cudaStream_t st, LaunchShape* shape, bool dry) {
     constexpr int TS = K / 8;
     constexpr int kPerWarp = 32 / TS;
     using SM = WorkerSmem<K, UM, IM, NS, NSI>;
@@ -962,13 +977,13 @@ cudaError_t launch_ns(KernelArgs a, unsigned warps_per_sm, unsigned workers, cud
         grid = (int)((unsigned)sm_count() * blocks_per_sm);
         a.workers = (unsigned)grid * warps_per_block * kPerWarp;
     }
-    kern<<<grid, block, smem, st>>>(a);
+    if (!dry) kern<<<grid, block, smem, st>>>(a);      // a dry call stops here: the function is loaded and configured
     if (shape) { shape->grid = grid; shape->block = block; shape->smem = smem; shape->workers = a.workers; }
     return cudaGetLastError();
 }
 
 template <int K, int KIND, int UM, int IM, bool STATS>
-cudaError_t launch_one(const KernelArgs& args, unsigned workers, cudaStream_t st, LaunchShape* shape) {
+cudaError_t launch_one(const KernelArgs& args, unsigned workers, cudaStream_t st, LaunchShape* shape, bool dry) {
     constexpr int TS = K / 8;
     constexpr int kPerWarp = 32 / TS;
     if (workers < 1) workers = 1;
@@ -984,32 +999,32 @@ cudaError_t launch_one(const KernelArgs& args, unsigned workers, cudaStream_t st
     // and the occupancy query trims the number of blocks per SM accordingly.
     // (Requesting fp32 item rows two ratings ahead, into an item ring of four slots, was measured as well and
     // changed nothing either - 13.99 against 14.06 ms per promoted epoch on the 100M-rating configuration.)
-    return launch_ns<K, KIND, UM, IM, STATS, 4, 2, 3, 1>(args, per_sm, workers, st, shape);
+    return launch_ns<K, KIND, UM, IM, STATS, 4, 2, 3, 1>(args, per_sm, workers, st, shape, dry);
 }
 
 template <int K, int KIND, int UM, int IM>
-cudaError_t launch_st(const KernelArgs& a, bool stats, unsigned workers, cudaStream_t st, LaunchShape* sh) {
-    return stats ? launch_one<K, KIND, UM, IM, true>(a, workers, st, sh) : launch_one<K, KIND, UM, IM, false>(a, workers, st, sh);
+cudaError_t launch_st(const KernelArgs& a, bool stats, unsigned workers, cudaStream_t st, LaunchShape* sh, bool dry) {
+    return stats ? launch_one<K, KIND, UM, IM, true>(a, workers, st, sh, dry) : launch_one<K, KIND, UM, IM, false>(a, workers, st, sh, dry);
 }
 
 template <int K>
-cudaError_t launch_k(TrainKind kind, const KernelArgs& a, bool stats, RowClass cls, unsigned workers, cudaStream_t st, LaunchShape* sh) {
+cudaError_t launch_k(TrainKind kind, const KernelArgs& a, bool stats, RowClass cls, unsigned workers, cudaStream_t st, LaunchShape* sh, bool dry) {
     switch (kind) {
         case KIND_MIXED:
             switch (cls) {
-                case ROWCLASS_HH: return launch_st<K, KIND_MIXED, ROWS_HALF, ROWS_HALF>(a, stats, workers, st, sh);
-                case ROWCLASS_HF: return launch_st<K, KIND_MIXED, ROWS_HALF, ROWS_F32>(a, stats, workers, st, sh);
-                case ROWCLASS_FH: return launch_st<K, KIND_MIXED, ROWS_F32, ROWS_HALF>(a, stats, workers, st, sh);
-                case ROWCLASS_FF: return launch_st<K, KIND_MIXED, ROWS_F32, ROWS_F32>(a, stats, workers, st, sh);
-                case ROWCLASS_ANY: return launch_st<K, KIND_MIXED, ROWS_DYN, ROWS_DYN>(a, stats, workers, st, sh);
+                case ROWCLASS_HH: return launch_st<K, KIND_MIXED, ROWS_HALF, ROWS_HALF>(a, stats, workers, st, sh, dry);
+                case ROWCLASS_HF: return launch_st<K, KIND_MIXED, ROWS_HALF, ROWS_F32>(a, stats, workers, st, sh, dry);
+                case ROWCLASS_FH: return launch_st<K, KIND_MIXED, ROWS_F32, ROWS_HALF>(a, stats, workers, st, sh, dry);
+                case ROWCLASS_FF: return launch_st<K, KIND_MIXED, ROWS_F32, ROWS_F32>(a, stats, workers, st, sh, dry);
+                case ROWCLASS_ANY: return launch_st<K, KIND_MIXED, ROWS_DYN, ROWS_DYN>(a, stats, workers, st, sh, dry);
             }
             return cudaErrorInvalidValue;
-        case KIND_FP32: return launch_one<K, KIND_FP32, ROWS_F32, ROWS_F32, false>(a, workers, st, sh);
-        case KIND_MPT: return launch_one<K, KIND_MPT, ROWS_F32, ROWS_F32, false>(a, workers, st, sh);
-        case KIND_MEMQUANT: return launch_one<K, KIND_MEMQUANT, ROWS_HALF, ROWS_HALF, false>(a, workers, st, sh);
-        case KIND_AFP: return launch_one<K, KIND_AFP, ROWS_F32, ROWS_F32, false>(a, workers, st, sh);
-        case KIND_SWITCH: return launch_st<K, KIND_SWITCH, ROWS_HALF, ROWS_HALF>(a, stats, workers, st, sh);
-        case KIND_MUPPET: return launch_st<K, KIND_MUPPET, ROWS_F32, ROWS_F32>(a, stats, workers, st, sh);
+        case KIND_FP32: return launch_one<K, KIND_FP32, ROWS_F32, ROWS_F32, false>(a, workers, st, sh, dry);
+        case KIND_MPT: return launch_one<K, KIND_MPT, ROWS_F32, ROWS_F32, false>(a, workers, st, sh, dry);
+        case KIND_MEMQUANT: return launch_one<K, KIND_MEMQUANT, ROWS_HALF, ROWS_HALF, false>(a, workers, st, sh, dry);
+        case KIND_AFP: return launch_one<K, KIND_AFP, ROWS_F32, ROWS_F32, false>(a, workers, st, sh, dry);
+        case KIND_SWITCH: return launch_st<K, KIND_SWITCH, ROWS_HALF, ROWS_HALF>(a, stats, workers, st, sh, dry);
+        case KIND_MUPPET: return launch_st<K, KIND_MUPPET, ROWS_F32, ROWS_F32>(a, stats, workers, st, sh, dry);
     }
     return cudaErrorInvalidValue;
 }
@@ -1040,14 +1055,20 @@ cudaError_t launch_train(int K, TrainKind kind, const Stream& s, Arena P, Arena 
     a.s = s; a.P = P; a.Q = Q; a.lr = lr; a.lam = lam; a.workers = workers; a.bits = bits; a.epoch = epoch;
     if (stats) a.st = *stats;
     if (s.n == 0) { if (shape) *shape = LaunchShape(); return cudaSuccess; }
+    if (!counters) {
+        // dry call: loads the instantiation this launch would use and sets its shared-memory limit, launches nothing
+        if (K == 128) return launch_k<128>(kind, a, stats != nullptr, row_class, workers, st, shape, true);
+        if (K == 64) return launch_k<64>(kind, a, stats != nullptr, row_class, workers, st, shape, true);
+        return cudaErrorInvalidValue;
+    }
     // Launches of one engine run one after the other on its stream.  Launch number L hands out chunks
     // through counter L mod 4 and resets counter (L + 2) mod 4, which the launch after next will use and
     // which no launch in flight touches; all four start at zero.
     a.next_chunk = counters->d_slots + (counters->launches & 3);
     a.zero_counter = counters->d_slots + ((counters->launches + 2) & 3);
     counters->launches++;
-    if (K == 128) return launch_k<128>(kind, a, stats != nullptr, row_class, workers, st, shape);
-    if (K == 64) return launch_k<64>(kind, a, stats != nullptr, row_class, workers, st, shape);
+    if (K == 128) return launch_k<128>(kind, a, stats != nullptr, row_class, workers, st, shape, false);
+    if (K == 64) return launch_k<64>(kind, a, stats != nullptr, row_class, workers, st, shape, false);
     return cudaErrorInvalidValue;
 }
 

@@ -40,7 +40,7 @@ class Config(C.Structure):
         ("item_group_num", C.c_uint32), ("k", C.c_uint32), ("num_workers", C.c_uint32), ("epoch", C.c_uint32),
         ("thread_block_size", C.c_uint32), ("version", C.c_uint32), ("is_yahoo", C.c_uint32),
         ("deterministic", C.c_uint32), ("shuffle", C.c_uint32), ("seed", C.c_uint64), ("device", C.c_int32),
-        ("muppet_width", C.c_uint32), ("plain_user_stores", C.c_uint32), ("l2_item_window", C.c_uint32), ("no_class_partition", C.c_uint32), ("reserved", C.c_uint32 * 3),
+        ("muppet_width", C.c_uint32), ("plain_user_stores", C.c_uint32), ("l2_item_window", C.c_uint32), ("no_class_partition", C.c_uint32), ("run_window_log2", C.c_uint32), ("reserved", C.c_uint32 * 2),
     ]
 
 

@@ -109,7 +109,14 @@ typedef struct mascot_config {
                                     class (see mascot_train_epoch) while the binary16 factors fit the GPU's L2; larger
                                     models keep their order and every launch reads each id's precision bit (measured
                                     faster there); 1 = never re-order; 2 = always re-order */
-    uint32_t reserved[3];
+    uint32_t run_window_log2;    /* extension: the resident training stream is sorted by item inside windows of 2^run_window_log2
+                                    positions (after the seeded permutation), so that a worker meets an item's ratings in
+                                    one run and reads and writes the item's row once per run.  0 (default) = 20; 1..12 =
+                                    only the 4096-position windows of the encoding step; up to 32.  The engine shortens
+                                    the windows to what all workers of a launch hold at one time and, when statistics
+                                    are sampled, to a quarter of the sampled tail of a segment.  Ignored with
+                                    shuffle = 0 and in deterministic mode (the caller's order is kept) */
+    uint32_t reserved[2];
 } mascot_config;
 
 typedef struct mascot_epoch_stats {

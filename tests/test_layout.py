@@ -98,3 +98,13 @@ def test_bounded_wait_returns_ok_error_or_timeout(tmp_path):
     assert rc == "-6" and 200 <= float(ms) < 1500
     rc, ms, polls = run(-1, 5000, -8)                # the poll reports a communication failure
     assert rc == "-8" and int(polls) == 3 and float(ms) < 1000
+
+
+def test_fast_rounding_and_power_of_two_reciprocal_are_exact(tmp_path):
+    """The fixed-point trainers' kernels replace roundf by trunc(x + copysign(largest float below 1/2, x)) and
+    1 / (power of two) by the mirrored exponent; the host restatement checks the first on all 2^32 float
+    patterns and the second on every power of two it applies to."""
+    exe = str(tmp_path / "round_check")
+    subprocess.check_call(["gcc", "-O2", "-fopenmp", "-ffp-contract=off", os.path.join(ROOT, "tests", "round_check.c"), "-o", exe, "-lm"])
+    out = subprocess.run([exe], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0 and out.stdout.strip() == "ok", out.stdout
