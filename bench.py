@@ -407,8 +407,11 @@ def run_single(args, S, M, cfg, local_rank):
                     "frac_hbm": (dram_per_launch / (plain_ms * 1e-3) / 1e9 / hbm_peak) if dram_per_launch else None,
                     "hbm_peak": hbm_peak, "hbm_peak_kind": f"of {peak_kind}",
                     "algorithmic_gbs": alg_gbs, "algorithmic_bytes_per_update": bytes_per_update_alg,
+                    "warp_instructions_per_update": tt.get("warp_instructions_per_update") if tt else None,
                     "note": "factors are L2-resident on this workload (item side entirely, user side mostly): the kernel is bound by "
-                            "L2 traffic and issue slots, not by HBM; algorithmic bytes / HBM peak is not a roofline here and is not reported as frac"}
+                            "instruction issue and L2 traffic, not by HBM; issue_slots_busy = warp instructions per update (ncu) x updates/s "
+                            "/ (SMs x 4 schedulers x the SM clock sampled in this run); algorithmic bytes / HBM peak is not a roofline "
+                            "here and is not reported as frac"}
     else:
         roofline = {"bound": "hbm", "achieved": alg_gbs, "peak": hbm_peak, "unit": "GB/s", "frac": alg_gbs / hbm_peak,
                     "traffic": dram_per_launch, "peak_kind": f"of {peak_kind}",
@@ -427,6 +430,11 @@ def run_single(args, S, M, cfg, local_rank):
         earlier = REFERENCE_CUDA_BUILD_EARLIER_RUNS.get(args.workload)
         ref_cuda = dict(ref_cuda or {}, measured=False, fallback_from_an_earlier_full_size_run=earlier)
 
+    clocks = sampler.summary()
+    if roofline.get("warp_instructions_per_update") and clocks.get("sm_mhz"):
+        import torch
+        sms = torch.cuda.get_device_properties(local_rank).multi_processor_count
+        roofline["issue_slots_busy"] = (roofline["warp_instructions_per_update"] * n_train / (plain_ms * 1e-3)) / (sms * 4 * clocks["sm_mhz"] * 1e6)
     line = {
         "metric": "rating updates/sec (k=128)", "value": value, "unit": "updates/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True,
@@ -437,7 +445,7 @@ def run_single(args, S, M, cfg, local_rank):
                    "total_ms_kernel_ms_check_promoted_per_step": [[round(a, 2), round(b, 2), c, d] for a, b, c, d in steps],
                    "convergence": convergence, "reference_cuda_build": ref_cuda},
         "roofline": roofline,
-        "clocks": sampler.summary(),
+        "clocks": clocks,
         "gpu_launches": launches,
     }
     if e2e:

@@ -199,7 +199,17 @@ unsigned shard_worker_count(const mascot_handle* h) {
     // times does not; 1.5 times is used.
     const ShardCtx* S = h->shard;
     const uint64_t total = std::max<uint64_t>(3 * S->n_global / 16384, 512);
-    return (unsigned)std::max<uint64_t>(total / (uint64_t)S->world, 64);
+    uint64_t w = std::max<uint64_t>(total / (uint64_t)S->world, 64);
+    // A data set whose binary16 factors exceed one GPU's L2 as a whole: a rank's share of the users and an item
+    // block hold the rows that are popular in the WHOLE set, `world` times as popular inside the rank's share,
+    // and the waits for those rows grow with every further worker.  Measured on two GPUs on the 252M-rating set
+    // at half size (31.6M ratings per step and rank): 8.2 / 8.6 ms per step with 8 warps per SM, 8.4 / 11.5 ms
+    // with 16, 8.8 / 11.6 ms with 32, 10.3 ms with 4.
+    int l2 = 0;
+    if (S->world > 1 && cudaDeviceGetAttribute(&l2, cudaDevAttrL2CacheSize, h->cfg.device) == cudaSuccess && l2 > 0 &&
+        ((size_t)h->n_users + h->n_items) * h->K * sizeof(__half) > (size_t)l2 + (size_t)l2 / 2)
+        w = std::min<uint64_t>(w, (uint64_t)sm_count() * 8 * (32 / (h->K / 8)));
+    return (unsigned)w;
 }
 
 void shard_destroy(mascot_handle* h) {
@@ -294,7 +304,19 @@ int mascot_shard_set_ratings(mascot_handle* h, const mascot_rating* train, uint6
     rq.n_segments = 1;
     rc = setup_ratings(h, rq);
     std::fill(S->arrival_pending.begin(), S->arrival_pending.end(), 0);
-    return rc;
+    if (rc != MASCOT_OK || S->world == 1) return rc;
+    // NCCL opens its connections at the first use of a peer: do that here (one value to the left neighbour, one
+    // from the right one, as the block hand-over will; one sum over all ranks, as the check epochs and the
+    // evaluation will), so that the first epoch does not pay for it (about a second on one node).
+    const int to = (S->rank + S->world - 1) % S->world, from = (S->rank + 1) % S->world;
+    CU(h, cudaMemsetAsync(S->d_pair, 0, 2 * sizeof(double), S->comm_stream));
+    NC(h, S, S->api->GroupStart());
+    NC(h, S, S->api->Send(S->d_pair, 1, ncclDouble, to, S->comm, S->comm_stream));
+    NC(h, S, S->api->Recv(S->d_pair + 1, 1, ncclDouble, from, S->comm, S->comm_stream));
+    NC(h, S, S->api->GroupEnd());
+    if ((rc = wait_stream(h, S->comm_stream, "opening the connections to the neighbours")) != MASCOT_OK) return rc;
+    NC(h, S, S->api->AllReduce(S->d_pair, S->d_pair, 2, ncclDouble, ncclSum, S->comm, h->stream));
+    return wait_stream(h, h->stream, "opening the connections of the group");
 }
 
 int mascot_shard_train_epoch(mascot_handle* h, uint32_t epoch, mascot_epoch_stats* out) {

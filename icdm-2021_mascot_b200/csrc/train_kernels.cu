@@ -449,7 +449,10 @@ struct AfpState { AfpSide user, item, back; long long cur; };
 
 // log2 in double precision, rounded once to float: the CPU restatement computes it the same way, so
 // both take identical re-estimation decisions (it runs only when parameters are re-estimated).
-__device__ __forceinline__ float log2_rounded(float x) { return (float)log2((double)x); }
+// The re-estimation helpers below are deliberately NOT inlined: they run once in many ratings, and inlined -
+// six copies of the double-precision logarithm per update, times the unrolled ring - they made the AFP kernel
+// so large that its warps waited 5 cycles per issued instruction for instruction fetches.
+__device__ __noinline__ float log2_rounded(float x) { return (float)log2((double)x); }
 
 // 2^|ceil(log2(range / (2^(bits-1) - 1)))| (afp_sgd_kernel.h:8-16, 112-118); exponent capped at 126
 __device__ __forceinline__ float afp_scale(int bits, float range) {
@@ -478,7 +481,7 @@ __device__ __forceinline__ void afp_lane_sums(const float (&v)[G][N], float scal
 }
 // QEM / QEM_BP (afp_sgd_kernel.h:31-104): log2(1 + relative loss of the magnitude sum under 8 bits)
 template <int K>
-__device__ __forceinline__ float afp_qem(const V8f& x, float max_val, unsigned wmask) {
+__device__ __noinline__ float afp_qem(V8f x, float max_val, unsigned wmask) {
     constexpr int TS = K / 8;
     const float scale = afp_scale(8, max_val), rev = __fdiv_rn(1.f, scale);
     float sum, sum_q;
@@ -493,7 +496,7 @@ __device__ __forceinline__ float afp_qem(const V8f& x, float max_val, unsigned w
     return log2_rounded(__fadd_rn(fabsf(__fdiv_rn(__fsub_rn(sum, sum_q), sum)), 1.f));
 }
 template <int K>
-__device__ __forceinline__ float afp_qem_back(const V8f& p, const V8f& q, float lam, float ruv, float max_val, unsigned wmask) {
+__device__ __noinline__ float afp_qem_back(V8f p, V8f q, float lam, float ruv, float max_val, unsigned wmask) {
     constexpr int TS = K / 8;
     const float scale = afp_scale(8, max_val), rev = __fdiv_rn(1.f, scale);
     float sum, sum_q;
@@ -510,7 +513,7 @@ __device__ __forceinline__ float afp_qem_back(const V8f& p, const V8f& q, float 
     return log2_rounded(__fadd_rn(fabsf(__fdiv_rn(__fsub_rn(sum, sum_q), sum)), 1.f));
 }
 // QPA (afp_sgd_kernel.h:106-125) and the bookkeeping around each call (196-206)
-__device__ __forceinline__ void afp_requantize(AfpSide& s, float diff, float range, long long cur, int epoch, int init_threshold) {
+__device__ __noinline__ AfpSide afp_requantize(AfpSide s, float diff, float range, long long cur, int epoch, int init_threshold) {
     const float threshold = 0.0005, alpha = 0.04, beta = 0.1, delta = 100, gamma = 2;
     if (cur == 0) s.mov_avg = range;
     const float prev = s.mov_avg;
@@ -521,6 +524,7 @@ __device__ __forceinline__ void afp_requantize(AfpSide& s, float diff, float ran
     int itv = __float2int_rz(__fsub_rn(__fdiv_rn(beta, fmaxf(i1, i2)), gamma));     // saturates; NaN -> 0
     if (epoch == 0 && cur < init_threshold) itv = 1;
     s.next += itv;
+    return s;
 }
 __device__ __forceinline__ float abs_max8(const V8f& x) {
     float m = fabsf(x.x[0]);
@@ -537,14 +541,14 @@ __device__ __forceinline__ void afp_update(const Consts& c, AfpState& st, float 
     const bool need_back = cur == st.back.next;
     if (cur == st.user.next || need_back) pmax = worker_max<TS>(abs_max8(p), wmask);
     if (cur == st.item.next || need_back) qmax = worker_max<TS>(abs_max8(q), wmask);
-    if (cur == st.user.next) afp_requantize(st.user, afp_qem<K>(p, pmax, wmask), pmax, cur, c.afp_epoch, c.afp_init_threshold);
-    if (cur == st.item.next) afp_requantize(st.item, afp_qem<K>(q, qmax, wmask), qmax, cur, c.afp_epoch, c.afp_init_threshold);
+    if (cur == st.user.next) st.user = afp_requantize(st.user, afp_qem<K>(p, pmax, wmask), pmax, cur, c.afp_epoch, c.afp_init_threshold);
+    if (cur == st.item.next) st.item = afp_requantize(st.item, afp_qem<K>(q, qmax, wmask), qmax, cur, c.afp_epoch, c.afp_init_threshold);
     const float pred = (st.user.n == 8 && st.item.n == 8) ? forward_int8<TS>(p, q, st.user.scale, st.item.scale, wmask)
                                                           : forward_half<K>(p, q, st.user.scale, st.item.scale, wmask);
     const float ruv = __fsub_rn(r, pred);
     if (need_back) {
         const float range = fmaxf(fmaxf(fmaxf(pmax, qmax), fabsf(c.lam)), fabsf(ruv));
-        afp_requantize(st.back, afp_qem_back<K>(p, q, c.lam, ruv, range, wmask), range, cur, c.afp_epoch, c.afp_init_threshold);
+        st.back = afp_requantize(st.back, afp_qem_back<K>(p, q, c.lam, ruv, range, wmask), range, cur, c.afp_epoch, c.afp_init_threshold);
     }
     V8f gp, gq;
     if (st.back.n == 8) backward_int8(p, q, ruv, -c.lam, st.back.scale, gp, gq);
@@ -675,7 +679,7 @@ template <int K, int UM, int IM, int NS, int NSI> struct WorkerSmem {
 // worker updates between the request and the write-back loses that update, and the chance of that
 // grows with the lead.
 template <int K, int KIND, int UM, int IM, bool STATS, int NS, int NSI, int D, int DI>
-__global__ void __launch_bounds__(256, (UM == ROWS_HALF && IM == ROWS_HALF && !STATS) ? 4 : ((UM == ROWS_DYN || STATS) ? 2 : 3)) train_kernel(const KernelArgs a) {
+__global__ void __launch_bounds__(256, (UM == ROWS_HALF && IM == ROWS_HALF && !STATS) ? 4 : ((UM == ROWS_DYN || STATS || KIND == KIND_AFP) ? 2 : 3)) train_kernel(const KernelArgs a) {
     using SM = WorkerSmem<K, UM, IM, NS, NSI>;
     constexpr int TS = SM::TS;                     // lanes per worker = ratings per chunk
     static_assert(TS % NS == 0, "the ring must divide the chunk");

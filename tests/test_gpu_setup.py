@@ -174,3 +174,38 @@ def test_ids_out_of_range_are_reported_and_never_used_as_an_index(mascot):
         eng.train_epoch(e)
     assert np.isfinite(eng.eval_rmse()) and eng.eval_rmse() < r0
     eng.close()
+
+
+@pytest.mark.parametrize("window_log2,sorted_inside", [(0, True), (13, True), (12, False)])
+def test_resident_stream_is_sorted_by_item_inside_run_windows(mascot, window_log2, sorted_inside):
+    """Several workers, seeded permutation: the resident stream holds every rating exactly once and, inside
+    windows of 2^13 positions, in ascending order of the item's arena row (mascot_config.run_window_log2:
+    0 = automatic - 2^20 shortened to what 64 workers hold at one time, 64 x 8 chunks x 16 ratings = 2^13 -,
+    13 = asked for, 12 = only the encoding step's windows of 4096 positions, which the check must notice)."""
+    rng = np.random.default_rng(5)
+    nu, ni, n = 3000, 700, 100_000
+    R = np.empty(n, mascot.RATING)
+    R["u"] = rng.integers(0, nu, n); R["i"] = rng.zipf(1.3, n) % ni
+    R["r"] = rng.choice(np.arange(1, 6), n)
+    eng = make_engine(mascot, mascot.V_SGD, 128, deterministic=0, shuffle=1, seed=3, num_workers=64, run_window_log2=window_log2)
+    eng.set_ratings(R, R[:50], nu, ni)
+    order = eng.stream_order()
+    assert np.array_equal(np.sort(order), np.arange(n)), "every rating exactly once"
+    _, i2s = eng.index_maps()
+    rows = i2s[R["i"][order]].astype(np.int64)
+    inside = np.ones(n - 1, bool)
+    inside[np.arange(1, n) % 8192 == 0] = False                   # steps across a window boundary do not count
+    ascending = bool((np.diff(rows)[inside] >= 0).all())
+    assert ascending == sorted_inside
+    # the encoding step's own windows are sorted in every case
+    inside4k = np.ones(n - 1, bool); inside4k[np.arange(1, n) % 4096 == 0] = False
+    assert (np.diff(rows)[inside4k] >= 0).all()
+    # and the order is a permutation of the caller's, not the caller's own
+    assert not np.array_equal(order, np.arange(n))
+    P = (rng.standard_normal((nu, 128)) * 0.1).astype(np.float32); Q = (rng.standard_normal((ni, 128)) * 0.1).astype(np.float32)
+    eng.set_factors(P, Q)
+    before = eng.eval_rmse()
+    for e in range(3):
+        assert eng.train_epoch(e).updates == n
+    assert eng.eval_rmse() < before
+    eng.close()
