@@ -72,13 +72,14 @@ struct LaunchShape {
 // backward pass (8, 12, 14, 16 or 32; ignored by the other kinds), `epoch` the epoch index (AFP
 // re-estimates its formats at every rating early in epoch 0).  With `add_user_delta` (ignored for a
 // single worker) user rows are written back as reductions of their change, so that concurrent
-// updates of one user by several workers are not lost.  Returns the launch shape used.
+// updates of one user by several workers are not lost; of the updates of a user whose id carries the mark in bit 30
+// only one in 2^hot_user_shift is then written back.  Returns the launch shape used.
 // With `counters` == nullptr the call is dry: the instantiation the launch would use is loaded and configured
 // (so that the first real launch does not pay for it) and nothing is launched.
 // MuPPET statistics use gsum_p[0..K) (sum of the sampled updates, physical order) and nsum_p[0].
 cudaError_t launch_train(int K, TrainKind kind, const Stream& s, Arena P, Arena Q, float lr, float lam,
                          const SampleStats* stats, RowClass row_class, unsigned workers,
-                         WorkCounters* counters, int bits, int epoch, bool add_user_delta,
+                         WorkCounters* counters, int bits, int epoch, bool add_user_delta, unsigned hot_user_shift,
                          cudaStream_t st, LaunchShape* shape);
 
 // Folds the private statistic sets of a launch into set 0 (sets are added in index order).

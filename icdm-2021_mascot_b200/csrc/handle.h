@@ -44,6 +44,7 @@ struct mascot_handle {
     float* te_r = nullptr; uint32_t* te_u = nullptr; uint32_t* te_i = nullptr;
     mascot::Arena P, Q;
     uint8_t* d_uprec_row = nullptr; uint8_t* d_iprec_row = nullptr;
+    uint32_t hot_user_shift = 0;    // one in 2^this of the updates of a marked (very popular) user is written back
     uint16_t* d_ugroup = nullptr; uint16_t* d_igroup = nullptr;
     uint32_t* d_umap = nullptr; uint32_t* d_imap = nullptr;
     float* d_stats = nullptr;       // stats_copies sets of: gsum_p | gsum_q | nsum_p | nsum_q

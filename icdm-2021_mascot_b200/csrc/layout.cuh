@@ -86,8 +86,9 @@ MASCOT_HD inline uint64_t permute_index(uint64_t j, uint64_t n, uint64_t seed) {
 }
 
 // Bit 31 of a stream id selects the arena a row lives in: 0 binary16, 1 fp32.  Bit 30 marks a user
-// row that so many workers update at the same time that its write-back stays a plain store (see
-// the update kernel).  The per-row byte tables carry the same two flags in bits 0 and 1.
+// row that so many workers update at the same time that only one in 2^shift of its updates is written
+// back (see the update kernel; the shift is one number per engine).  The per-row byte tables carry the
+// same two flags in bits 0 and 1.
 constexpr uint32_t kPrecBit = 0x80000000u;
 constexpr uint32_t kHotBit = 0x40000000u;
 constexpr uint32_t kIdMask = 0x3fffffffu;

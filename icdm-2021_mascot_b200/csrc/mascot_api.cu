@@ -332,7 +332,7 @@ int warm_kernels(mascot_handle* h) {
     const bool sampled = h->kind == KIND_MIXED || h->kind == KIND_SWITCH || h->kind == KIND_MUPPET;
     for (int with_stats = 0; with_stats <= (sampled ? 1 : 0); with_stats++)
         CU(h, launch_train(h->K, h->kind, s, h->P, h->Q, 0.f, 0.f, with_stats ? &st : nullptr, cls, workers, nullptr, muppet_bits(h), 0,
-                           h->cfg.plain_user_stores == 0, h->stream, nullptr));
+                           h->cfg.plain_user_stores == 0, h->hot_user_shift, h->stream, nullptr));
     return MASCOT_OK;
 }
 
@@ -660,7 +660,7 @@ int train_span(mascot_handle* h, float lr, uint32_t epoch, uint64_t begin, uint6
     if (head > 0) {
         Stream sa = s; sa.n = head;
         CU(h, launch_train(h->K, kind, sa, h->P, h->Q, lr, h->cfg.lambda, nullptr, cls, workers,
-                           counters, muppet_bits(h), (int)epoch, h->cfg.plain_user_stores == 0, stream, shape));
+                           counters, muppet_bits(h), (int)epoch, h->cfg.plain_user_stores == 0, h->hot_user_shift, stream, shape));
         (*launches)++;
     }
     if (head < n) {
@@ -668,7 +668,7 @@ int train_span(mascot_handle* h, float lr, uint32_t epoch, uint64_t begin, uint6
         const SampleStats st = stats_view(h);
         LaunchShape tail_shape;            // the caller is told the shape of the plain launch when there is one
         CU(h, launch_train(h->K, kind, sb, h->P, h->Q, lr, h->cfg.lambda, &st, cls, workers,
-                           counters, muppet_bits(h), (int)epoch, h->cfg.plain_user_stores == 0, stream, head > 0 ? &tail_shape : shape));
+                           counters, muppet_bits(h), (int)epoch, h->cfg.plain_user_stores == 0, h->hot_user_shift, stream, head > 0 ? &tail_shape : shape));
         (*launches)++;
     }
     return MASCOT_OK;

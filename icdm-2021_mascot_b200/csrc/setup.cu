@@ -142,13 +142,18 @@ int build_side(mascot_handle* h, bool users, const std::vector<uint32_t>& s2o, c
     std::vector<uint16_t> group(rows, 0);
     std::vector<uint8_t> flags(rows, 0);
     deg_sum.assign(end.size(), 0);
-    if (users) h->urow_degree.assign(rows, 0);
+    if (users) { h->urow_degree.assign(rows, 0); h->hot_user_shift = 0; }
     uint32_t s = 0;
-    // A user whose ratings are so many that several workers hold its row at any time keeps the plain
-    // store: adding up the changes of many concurrent, equally stale updates multiplies the step and
-    // can diverge, while a plain store lets one of them win.  Expected number of workers inside their
-    // read-to-write span of a row: workers x 4 ratings x degree / n.  Measured: 23 still converges
-    // as well as the reference (20M-rating configuration), 82 diverges (252M-rating one); marked above 32.
+    // A user whose ratings are so many that many workers hold its row at any time: adding up the changes of
+    // that many concurrent, equally stale updates multiplies the step and can diverge.  Expected number of
+    // workers inside their read-to-write span of a row: c = workers x 4 ratings x degree / n.  Measured: 23 still
+    // converges as well as the reference (20M-rating configuration), 82 diverges (252M-rating one).  Above 32 the
+    // row is marked, and only one in 2^shift of the updates of marked rows is written back (as a reduction, like
+    // every other user row), with 2^shift the power of two that brings the c of the most popular user to 32 or
+    // less (one shift per engine: the update kernel gets it as an argument); the other updates of the row are
+    // dropped, which is what a plain store does to all but one of the concurrent holders - without the cost of
+    // plain stores to a line every SM writes (252M-rating set at quarter size: 10.8 ms per epoch with plain stores
+    // for the marked rows, 5.2 ms with reductions for every update, 4.4 ms with no write-back at all).
     const uint64_t w_est = std::min<uint64_t>(worker_count(h, n_local), 16384);
     for (size_t g = 0; g < end.size(); g++) {
         for (; s <= end[g] && s < n; s++) {
@@ -160,7 +165,12 @@ int build_side(mascot_handle* h, bool users, const std::vector<uint32_t>& s2o, c
             deg_sum[g] += deg;
             if (users) {
                 h->urow_degree[row] = deg;
-                if ((uint64_t)deg * w_est > 8 * n_local) flags[row] |= kRowHot;
+                if ((uint64_t)deg * w_est > 8 * n_local) {
+                    uint32_t shift = 1;
+                    while (shift < 24 && (((uint64_t)deg * w_est) >> shift) > 8 * n_local) shift++;
+                    flags[row] |= kRowHot;
+                    h->hot_user_shift = std::max(h->hot_user_shift, shift);
+                }
             }
         }
     }

@@ -284,6 +284,7 @@ struct KernelArgs {
                                       // worker are handed out dynamically, so the launch never depends on
                                       // every block being resident at the same time
     unsigned long long* zero_counter; // another counter, which this launch resets for a later launch
+    unsigned hot_user_shift;          // one in 2^this of the updates of a marked user row is written back
 };
 
 // ---- MuPPET (muppet/muppet_sgd_kernel.h:7-48, 121-264; _k64.h) -------------------------------
@@ -789,6 +790,8 @@ __global__ void __launch_bounds__(256, (UM == ROWS_HALF && IM == ROWS_HALF && !S
     publish(0);
     publish(1);
 
+    unsigned hot_seen = worker;                       // counts the ratings of marked users this worker has met
+    const unsigned hot_mask = (1u << a.hot_user_shift) - 1u;
     // item row of the current run
     uint32_t cur_ic = kNoRow;
     Raw<IM> q;
@@ -915,8 +918,15 @@ __global__ void __launch_bounds__(256, (UM == ROWS_HALF && IM == ROWS_HALF && !S
                 }
                 const Raw<UM> p_before = p;
                 update_one<K, KIND, UM, IM, STATS>(c, r, uc, ic, p, q, sampled, smp, afp, wmask);
-                if (a.add_user_delta && !(uc & kHotBit)) add_row_delta<K, UM>(a.P, uc, m, p, p_before);
-                else st_row<K, UM>(a.P, uc, m, p);
+                if (a.add_user_delta) {
+                    // A marked user (see the set-up): every 2^shift-th update of a marked row that this worker meets
+                    // is written back; the others are dropped.
+                    bool keep = true;
+                    if (uc & kHotBit) keep = ((++hot_seen) & hot_mask) == 0u;
+                    if (keep) add_row_delta<K, UM>(a.P, uc, m, p, p_before);
+                } else {
+                    st_row<K, UM>(a.P, uc, m, p);
+                }
                 if (STATS && sampled) record(smp, uc, ic);
             }
         }
@@ -1053,8 +1063,9 @@ int sm_count() {
 
 cudaError_t launch_train(int K, TrainKind kind, const Stream& s, Arena P, Arena Q, float lr, float lam,
                          const SampleStats* stats, RowClass row_class, unsigned workers, WorkCounters* counters,
-                         int bits, int epoch, bool add_user_delta, cudaStream_t st, LaunchShape* shape) {
+                         int bits, int epoch, bool add_user_delta, unsigned hot_user_shift, cudaStream_t st, LaunchShape* shape) {
     KernelArgs a;
+    a.hot_user_shift = hot_user_shift;
     a.add_user_delta = add_user_delta ? 1 : 0;
     a.s = s; a.P = P; a.Q = Q; a.lr = lr; a.lam = lam; a.workers = workers; a.bits = bits; a.epoch = epoch;
     if (stats) a.st = *stats;
