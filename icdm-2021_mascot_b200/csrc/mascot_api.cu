@@ -264,27 +264,14 @@ int reorder_segments(mascot_handle* h, size_t seg_first, size_t seg_count, bool 
 }
 
 // The stream is partitioned when that pays: mixed-precision trainer, more than one worker, at least
-// one promoted group, and sizes the 16-bit sort key and the 32-bit permutation can express.
-// Do the binary16 factors of this engine fit in the device's L2?
-bool factors_fit_l2(const mascot_handle* h) {
-    int l2 = 0;
-    if (cudaDeviceGetAttribute(&l2, cudaDevAttrL2CacheSize, h->cfg.device) != cudaSuccess || l2 <= 0) return true;
-    // an engine of a sharded group works on its own users and one item block at a time
-    const size_t users = h->ulay.parts > 1 ? h->ulay.rows_per_part : h->n_users;
-    const size_t items = h->ilay.parts > 1 ? h->ilay.rows_per_part : h->n_items;
-    return (users + items) * h->K * sizeof(__half) <= (size_t)l2 + (size_t)l2 / 2;
-}
-
+// one promoted group, and sizes the sort key and the 32-bit permutation can express.
 bool wants_partition(const mascot_handle* h) {
     if (!(h->grouped && !h->cfg.deterministic && any_fp32_group(h) && h->n_train < (1ull << 32) && (h->seg_off.size() - 1) * 4 <= 65536)) return false;
-    if (h->cfg.no_class_partition == 1) return false;
-    if (h->cfg.no_class_partition == 2) return true;
-    // Automatic: measured on one B200 with the popular groups promoted - 100M-rating set (factors fit L2): one
-    // launch per class 14.0 ms per epoch, per-rating precision bits 15.2 ms; 252M-rating set (factors 416 MB, rows
-    // stream from HBM): 47 ms against 30.7 ms at half size - a class launch puts every worker on the popular fp32
-    // rows at once, and what bounds that set is traffic to those rows.  So the stream is partitioned only while
-    // the factors fit L2.
-    return factors_fit_l2(h);
+    // Measured on one B200 with promoted groups: 100M-rating set 7.6 ms per epoch with one launch per class (14.0 ms
+    // before the run windows) against 15.2 ms for one launch that reads each id's precision bit; 252M-rating set,
+    // 40 epochs: 1,126 ms against 1,365 ms (the launch of the all-binary16 class keeps its 32 warps per SM, the
+    // per-rating instantiation runs 16).
+    return h->cfg.no_class_partition != 1;
 }
 
 int partition_all(mascot_handle* h) {
@@ -562,11 +549,6 @@ unsigned worker_count(const mascot_handle* h, uint64_t n) {
     if (h->shard) return shard_worker_count(h);
     if (n < 1500000) return (unsigned)std::min<uint64_t>(std::max<uint64_t>(n / 512, 512), 1536);
     uint64_t w = std::min<uint64_t>(std::max<uint64_t>(n / 8192, 512), 1u << 20);
-    // Factors beyond L2: the rows stream from HBM and 16 warps per SM saturate it; more workers only add
-    // contention on the popular rows (252M-rating set, all rows binary16: 45.4 ms per epoch with 4,736 workers,
-    // 52.8 with 7,104, 53.3 with 9,472; 53.7 with 2,368).  The AFP trainer is bound by its own arithmetic
-    // (fixed-point conversion of every element in both passes), not by memory: it keeps the full count.
-    if (!factors_fit_l2(h) && h->kind != KIND_AFP) w = std::min<uint64_t>(w, (uint64_t)sm_count() * 16 * (32 / (h->K / 8)));
     return (unsigned)w;
 }
 

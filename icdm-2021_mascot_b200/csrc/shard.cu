@@ -199,16 +199,7 @@ unsigned shard_worker_count(const mascot_handle* h) {
     // times does not; 1.5 times is used.
     const ShardCtx* S = h->shard;
     const uint64_t total = std::max<uint64_t>(3 * S->n_global / 16384, 512);
-    uint64_t w = std::max<uint64_t>(total / (uint64_t)S->world, 64);
-    // A data set whose binary16 factors exceed one GPU's L2 as a whole: a rank's share of the users and an item
-    // block hold the rows that are popular in the WHOLE set, `world` times as popular inside the rank's share,
-    // and the waits for those rows grow with every further worker.  Measured on two GPUs on the 252M-rating set
-    // at half size (31.6M ratings per step and rank): 8.2 / 8.6 ms per step with 8 warps per SM, 8.4 / 11.5 ms
-    // with 16, 8.8 / 11.6 ms with 32, 10.3 ms with 4.
-    int l2 = 0;
-    if (S->world > 1 && cudaDeviceGetAttribute(&l2, cudaDevAttrL2CacheSize, h->cfg.device) == cudaSuccess && l2 > 0 &&
-        ((size_t)h->n_users + h->n_items) * h->K * sizeof(__half) > (size_t)l2 + (size_t)l2 / 2)
-        w = std::min<uint64_t>(w, (uint64_t)sm_count() * 8 * (32 / (h->K / 8)));
+    const uint64_t w = std::max<uint64_t>(total / (uint64_t)S->world, 64);
     return (unsigned)w;
 }
 

@@ -105,10 +105,9 @@ typedef struct mascot_config {
                                     window of the engine's stream over the item arena, sized to what the device allows);
                                     for data sets whose factors exceed L2.  Sets this process's persisting-L2 limit on
                                     the device for the life of the engine; mascot_destroy puts the old limit back. */
-    uint32_t no_class_partition; /* extension: 0 (default) = automatic: after a promotion the stream is re-ordered by precision
-                                    class (see mascot_train_epoch) while the binary16 factors fit the GPU's L2; larger
-                                    models keep their order and every launch reads each id's precision bit (measured
-                                    faster there); 1 = never re-order; 2 = always re-order */
+    uint32_t no_class_partition; /* extension: 0 (default) = after a promotion the stream is re-ordered by precision class and
+                                    every class runs the kernel instantiation made for it (see mascot_train_epoch);
+                                    1 = never re-order: every launch reads each id's precision bit */
     uint32_t run_window_log2;    /* extension: the resident training stream is sorted by item inside windows of 2^run_window_log2
                                     positions (after the seeded permutation), so that a worker meets an item's ratings in
                                     one run and reads and writes the item's row once per run.  0 (default) = 20; 1..12 =
