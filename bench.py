@@ -394,8 +394,9 @@ def run_single(args, S, M, cfg, local_rank):
     tt = traffic_table(args.workload) if args.scale == 1.0 else None
     dram_per_launch = tt["dram_bytes_per_update"] * n_train if tt and tt.get("dram_bytes_per_update") else None
     factor_bytes = (cfg["users"] + cfg["items"]) * cfg["k"] * 2
-    if factor_bytes < 1.5 * 126e6:      # item side resident, user side mostly (c4: 127.5 MB against 126 MB of L2)
-        # factors fit in L2: the kernel's traffic is L2 <-> SM traffic, judged against a measured L2 read bandwidth
+    if (tt and tt.get("l2_bytes_per_update")) or factor_bytes < 1.5 * 126e6:
+        # The update kernel is bound by instruction issue and by L2 <-> SM traffic on both listed workloads (ncu: DRAM runs
+        # at a quarter to four tenths of its bandwidth): its traffic is judged against a measured L2 read bandwidth
         l2_peak = max(M.probe_read_bandwidth(32 << 20, passes=60, device=local_rank) for _ in range(5))    # best of five: the clock ramps
         l2_per_update = tt["l2_bytes_per_update"] if tt and tt.get("l2_bytes_per_update") else None
         achieved = (l2_per_update * n_train / (plain_ms * 1e-3) / 1e9) if l2_per_update else alg_gbs
@@ -408,10 +409,11 @@ def run_single(args, S, M, cfg, local_rank):
                     "hbm_peak": hbm_peak, "hbm_peak_kind": f"of {peak_kind}",
                     "algorithmic_gbs": alg_gbs, "algorithmic_bytes_per_update": bytes_per_update_alg,
                     "warp_instructions_per_update": tt.get("warp_instructions_per_update") if tt else None,
-                    "note": "factors are L2-resident on this workload (item side entirely, user side mostly): the kernel is bound by "
-                            "instruction issue and L2 traffic, not by HBM; issue_slots_busy = warp instructions per update (ncu) x updates/s "
-                            "/ (SMs x 4 schedulers x the SM clock sampled in this run); algorithmic bytes / HBM peak is not a roofline "
-                            "here and is not reported as frac"}
+                    "traffic_kind": ("DRAM bytes per update of the committed ncu capture x updates" +
+                                     (f" (captured at scale {tt.get('scale')}: a lower bound for the full size)" if tt and tt.get("scale", 1.0) != 1.0 else "")),
+                    "note": "the kernel is bound by instruction issue and L2 traffic, not by HBM (most row accesses hit L2: popular rows on "
+                            "both sides); issue_slots_busy = warp instructions per update (ncu) x updates/s / (SMs x 4 schedulers x the SM "
+                            "clock sampled in this run); algorithmic bytes / HBM peak is not a roofline here and is not reported as frac"}
     else:
         roofline = {"bound": "hbm", "achieved": alg_gbs, "peak": hbm_peak, "unit": "GB/s", "frac": alg_gbs / hbm_peak,
                     "traffic": dram_per_launch, "peak_kind": f"of {peak_kind}",
