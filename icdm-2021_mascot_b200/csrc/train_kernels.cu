@@ -455,12 +455,38 @@ struct AfpState { AfpSide user, item, back; long long cur; };
 // so large that its warps waited 5 cycles per issued instruction for instruction fetches.
 __device__ __noinline__ float log2_rounded(float x) { return (float)log2((double)x); }
 
+// ceil((float)log2((double)x)) for x > 0 without the logarithm.  x = (1 + M / 2^23) * 2^E: log2(x) lies in
+// [E, E + 1); rounded to float it is E itself when M = 0, or when the fraction is below half the spacing of the
+// floats next to E on the side of E + 1 - the first few M only, the more the larger |E| - and otherwise a value in
+// (E, E + 1], whose ceiling is E + 1.  Equal to the double-precision formula of the CPU restatement for every
+// positive finite float (checked exhaustively on the host, tests/ceil_log2_check.c).  Zero gives a large negative
+// number, as the logarithm would.
+__device__ __forceinline__ int ceil_log2_rounded(float x) {
+    const uint32_t bits = __float_as_uint(x) & 0x7fffffffu;
+    if (bits == 0u) return -100000;
+    int E = (int)(bits >> 23) - 127;
+    uint32_t M = bits & 0x7fffffu;
+    if ((bits >> 23) == 0u) {                      // denormal: normalise
+        const int lz = __clz((int)M) - 9;
+        E = -126 - (lz + 1);
+        M = (M << (lz + 1)) & 0x7fffffu;
+    }
+    if (M == 0u) return E;
+    uint32_t a = (uint32_t)(E < 0 ? -E : E);
+    if (E < 0) a -= 1u;                            // the floats between E and E + 1 are smaller in magnitude than |E|
+    if (E <= 0 && a == 0u) return E + 1;
+    const int j = 31 - __clz((int)a);
+    const uint32_t limit = j <= 1 ? 0u : (j == 2 ? 1u : (j == 3 ? 2u : (j == 4 ? 5u : (j == 5 ? 11u : (j == 6 ? 22u : 44u)))));
+    return M <= limit ? E : E + 1;
+}
+
 // 2^|ceil(log2(range / (2^(bits-1) - 1)))| (afp_sgd_kernel.h:8-16, 112-118); exponent capped at 126
 __device__ __forceinline__ float afp_scale(int bits, float range) {
     if (range == 0.f) return 1.f;
     const float top = bits == 8 ? 127.f : 32767.f;
-    const float e = fabsf(ceilf(log2_rounded(__fdiv_rn(range, top))));
-    const int ei = e > 126.f ? 126 : (int)e;
+    const int c = ceil_log2_rounded(__fdiv_rn(range, top));
+    const int e = c < 0 ? -c : c;
+    const int ei = e > 126 ? 126 : e;
     return __int_as_float((ei + 127) << 23);
 }
 // Sum of magnitudes of the values a reference lane adds, left to right, before and after 8-bit

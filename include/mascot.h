@@ -99,7 +99,11 @@ typedef struct mascot_config {
     uint32_t muppet_width;       /* extension: first pass width of MuPPET, 8/12/14/16/32; 0 = the reference's start
                                     (8, or 12 for Yahoo input; mf_methods.cu:597-601) */
     uint32_t plain_user_stores;  /* extension: 0 (default) = with more than one worker, user rows are written back as
-                                    reductions of their change, so racing updates of one user are not lost;
+                                    reductions of their change, so racing updates of one user are not lost.  A user
+                                    with so many ratings that more than about 32 workers would hold its row at the
+                                    same time has only every 2^s-th of its updates written back (the others are
+                                    dropped, as a plain store drops all but one of the concurrent ones), with s chosen
+                                    so that about 32 concurrent updates of the most popular user remain;
                                     1 = plain stores like the reference (racing updates overwrite each other) */
     uint32_t l2_item_window;     /* extension: 1 = ask the GPU to keep the item factors in L2 (a persisting access-policy
                                     window of the engine's stream over the item arena, sized to what the device allows);

@@ -209,3 +209,35 @@ def test_resident_stream_is_sorted_by_item_inside_run_windows(mascot, window_log
         assert eng.train_epoch(e).updates == n
     assert eng.eval_rmse() < before
     eng.close()
+
+
+def test_very_popular_users_train_with_thinned_reductions(mascot):
+    """Three users own 45 % of the ratings; with 700 workers far more than 32 of them hold such a row at any
+    time, so the engine marks those users and writes back only every 2^s-th of their updates (as reductions).
+    The run must stay finite, learn (test RMSE falls), and end no worse than 5 % above the same run with plain
+    stores for every user (mascot_config.plain_user_stores = 1), which is the reference's behaviour."""
+    rng = np.random.default_rng(11)
+    nu, ni, n, k = 4000, 3000, 600_000, 128
+    Pt = rng.standard_normal((nu, 8)) * 0.5; Qt = rng.standard_normal((ni, 8)) * 0.5
+    u = rng.integers(3, nu, n); hot = rng.random(n) < 0.45
+    u[hot] = rng.integers(0, 3, hot.sum())
+    i = rng.integers(0, ni, n)
+    r = np.clip(np.rint(3.0 + (Pt[u] * Qt[i]).sum(1) + rng.standard_normal(n) * 0.3), 1, 5)
+    R = mascot.make_ratings(u, i, r.astype(np.float32))
+    train, test = R[: n - 20_000], R[n - 20_000:]
+    P0 = (rng.standard_normal((nu, k)) * 0.05).astype(np.float32); Q0 = (rng.standard_normal((ni, k)) * 0.05).astype(np.float32)
+    final = {}
+    for plain in (0, 1):
+        eng = make_engine(mascot, mascot.V_MASCOT, k, deterministic=0, shuffle=1, seed=9, num_workers=700, plain_user_stores=plain,
+                          user_group_num=10, item_group_num=10, sample_ratio=0.05, interval=2, error_threshold=1e9, lam=0.02)
+        eng.set_ratings(train, test, nu, ni)
+        eng.set_factors(P0, Q0)
+        before = eng.eval_rmse()
+        for e in range(8):
+            eng.train_epoch(e)
+        final[plain] = eng.eval_rmse()
+        Pg, Qg = eng.get_factors(1)
+        assert np.isfinite(Pg).all() and np.isfinite(Qg).all()
+        assert final[plain] < 0.9 * before, (before, final[plain])
+        eng.close()
+    assert final[0] <= 1.05 * final[1], final

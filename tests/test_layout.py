@@ -108,3 +108,13 @@ def test_fast_rounding_and_power_of_two_reciprocal_are_exact(tmp_path):
     subprocess.check_call(["gcc", "-O2", "-fopenmp", "-ffp-contract=off", os.path.join(ROOT, "tests", "round_check.c"), "-o", exe, "-lm"])
     out = subprocess.run([exe], capture_output=True, text=True, timeout=600)
     assert out.returncode == 0 and out.stdout.strip() == "ok", out.stdout
+
+
+def test_integer_ceil_log2_equals_the_double_precision_formula(tmp_path):
+    """The AFP trainer's kernel computes ceil((float)log2((double)x)) - the exponent of its fixed-point scale -
+    from the bits of x; the host restatement of that shortcut is compared with the formula on every positive
+    finite float."""
+    exe = str(tmp_path / "ceil_log2_check")
+    subprocess.check_call(["gcc", "-O2", "-fopenmp", os.path.join(ROOT, "tests", "ceil_log2_check.c"), "-o", exe, "-lm"])
+    out = subprocess.run([exe], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0 and out.stdout.strip() == "ok", out.stdout
