@@ -1007,6 +1007,23 @@ cudaError_t launch_ns(KernelArgs a, unsigned warps_per_sm, unsigned workers, cud
         [&](int blk, size_t sm, int* f) { return (int)cudaOccupancyMaxActiveBlocksPerMultiprocessor(f, kern, blk, sm); }, &fit);
     if (rc != 0) return (cudaError_t)rc;
     if (fit < 1) return cudaErrorLaunchOutOfResources;
+    size_t smem_used = smem;
+    if (warps > 8 && blocks_per_sm > (unsigned)fit && warps_per_block < 8) {
+        // The SM cannot hold as many blocks as the even split asked for: blocks of the full eight warps then put
+        // more warps on it (42 warps wanted: six blocks of seven, of which four fit = 28 warps; four blocks of
+        // eight = 32).
+        int fit8 = 0;
+        const size_t smem8 = (size_t)8 * kPerWarp * SM::kBytes;
+        const int rc8 = cache.lookup(
+            dev, 256, smem8, kSmemMax,
+            [&](size_t bytes) { return (int)cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes); },
+            [&](int blk, size_t sm, int* f) { return (int)cudaOccupancyMaxActiveBlocksPerMultiprocessor(f, kern, blk, sm); }, &fit8);
+        if (rc8 != 0) return (cudaError_t)rc8;
+        if (fit8 * 8 > fit * (int)warps_per_block) {
+            warps_per_block = 8; block = 256; smem_used = smem8; fit = fit8;
+            blocks_per_sm = (warps_per_sm + 7) / 8;
+        }
+    }
     if (warps <= 8) {
         // a single block (deterministic runs, tiny worker counts) uses exactly the requested workers
         grid = 1;
@@ -1017,8 +1034,8 @@ cudaError_t launch_ns(KernelArgs a, unsigned warps_per_sm, unsigned workers, cud
         grid = (int)((unsigned)sm_count() * blocks_per_sm);
         a.workers = (unsigned)grid * warps_per_block * kPerWarp;
     }
-    if (!dry) kern<<<grid, block, smem, st>>>(a);      // a dry call stops here: the function is loaded and configured
-    if (shape) { shape->grid = grid; shape->block = block; shape->smem = smem; shape->workers = a.workers; }
+    if (!dry) kern<<<grid, block, smem_used, st>>>(a);      // a dry call stops here: the function is loaded and configured
+    if (shape) { shape->grid = grid; shape->block = block; shape->smem = smem_used; shape->workers = a.workers; }
     return cudaGetLastError();
 }
 
