@@ -6,8 +6,8 @@ TEST / MEASUREMENT INFRASTRUCTURE.  Needs oracle/_ref/quantized_mf (built from t
 `make -C oracle ref`; the binary travels, the reference sources do not), the engine's command-line tools
 (icdm-2021_mascot_b200/bin) and a GPU.
 
-    python oracle/run_reference_gpu.py --workload c2 --epochs 20 --wg 2048,9472 --out gpurun_out/ref_c2.json
-    python oracle/run_reference_gpu.py --workload c5 --scale 0.5 --variants 1,4,3,2 --out gpurun_out/ref_c5.json
+    python oracle/run_reference_gpu.py --workload c2 --epochs 20 --wg 2048,9472 --out ref_c2.json
+    python oracle/run_reference_gpu.py --workload c5 --scale 0.5 --variants 1,4,3,2 --out ref_c5.json
 
 The ratings are generated once, written as the binary rating file of the command-line tools and converted
 (bin/convert_ratings) to the text layout the reference reads: plain TSV, or - for the 252M-rating
