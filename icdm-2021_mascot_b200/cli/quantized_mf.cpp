@@ -265,7 +265,7 @@ int main(int argc, const char* argv[]) {
         else mascot_get_worker_count(single, &shown_workers);
     } else if (!run.wg_given) {
         // the sharded engines' automatic choice (see mascot_shard_init), restated for the banner
-        shown_workers = cfg.deterministic ? 1u : (uint32_t)std::max<uint64_t>(std::max<uint64_t>(3 * run.data.n_train / 16384, 512) / run.gpus, 64);
+        shown_workers = cfg.deterministic ? 1u : (uint32_t)std::max<uint64_t>(std::max<uint64_t>(run.data.n_train / 3584, 512) / run.gpus, 64);
     }
     std::cout << std::endl;
     std::cout << "Input file                  : " << run.infile << std::endl;

@@ -194,11 +194,13 @@ unsigned shard_worker_count(const mascot_handle* h) {
     // What decides the convergence per epoch of these racy updates is how many workers touch one row at
     // the same time.  A rank puts all its workers on 1/world of the items (and of the users), so a row
     // sees `world` times the per-rank count: the total over all ranks has to stay bounded, not the
-    // count per GPU.  Measured on the 100M-rating configuration, a total of about twice the single-GPU
-    // automatic choice (n/8192) still ends within the tolerance of the reference's final RMSE and four
-    // times does not; 1.5 times is used.
+    // count per GPU - which also means that more GPUs shorten an epoch only as far as the total grows.
+    // Measured on the 100M-rating configuration on four GPUs (total / updates per second / epoch and time at
+    // which the reference's final RMSE is reached / RMSE after 50 epochs): 18.9k / 33.8e9 / 33, 99 ms / 0.5998;
+    // 28.4k / 38.0e9 / 38, 100 ms / 0.6003; 37.9k / 38.9e9 / 47, 132 ms / 0.6011.  About 28k (n / 3584, 2.3 times
+    // the single-GPU automatic choice n / 8192) is used: the largest total that costs no time to the target RMSE.
     const ShardCtx* S = h->shard;
-    const uint64_t total = std::max<uint64_t>(3 * S->n_global / 16384, 512);
+    const uint64_t total = std::max<uint64_t>(S->n_global / 3584, 512);
     const uint64_t w = std::max<uint64_t>(total / (uint64_t)S->world, 64);
     return (unsigned)w;
 }

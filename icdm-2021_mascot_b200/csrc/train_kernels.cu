@@ -317,7 +317,14 @@ __device__ __forceinline__ float pow2_rev(float s) {
     return (b >= 0x00800000u && b < 0x7f000000u && !(b & 0x007fffffu)) ? __uint_as_float(0x7f000000u - b) : __fdiv_rn(1.f, s);
 }
 __device__ __forceinline__ float fix_round(float v, float s, float s_rev) { return __fmul_rn(round_away(__fmul_rn(v, s)), s_rev); }
-__device__ __forceinline__ int sat8(float v) { return v > 127.f ? 127 : (v < -128.f ? -128 : (int)v); }
+// Clamp to the int8 range, then to integer.  Every caller passes a value that round_away has already made
+// integral, so the one conversion instruction with saturation (truncating, which changes nothing then) equals
+// v > 127 ? 127 : (v < -128 ? -128 : (int)v).
+__device__ __forceinline__ int sat8(float v) {
+    int r;
+    asm("cvt.rzi.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(v));
+    return r;
+}
 __device__ __forceinline__ V8h fix_round_half(const V8f& x, float s, float s_rev) {
     V8h h;
 #pragma unroll
