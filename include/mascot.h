@@ -250,7 +250,9 @@ MASCOT_API int mascot_get_test_ratings(mascot_handle* h, mascot_rating* out, int
 /* Position in the caller's training array of the rating that the engine processes at stream
  * position `pos` (identity when shuffle == 0).  With shuffle == 1 the stream is the seeded
  * permutation of the caller's array, cut into windows of 4096 positions that are each sorted by
- * item so that equal items are neighbours.  Lets a host replay follow exactly the same order. */
+ * item so that equal items are neighbours; the resident stream of a multi-worker engine is then sorted by item
+ * inside larger windows (mascot_config.run_window_log2) and, after a promotion, re-ordered by precision class
+ * (mascot_train_epoch).  Lets a host replay follow exactly the same order. */
 MASCOT_API int mascot_stream_source_index(const mascot_handle* h, uint64_t pos, uint64_t* src);
 /* The whole order at once: src_out[pos] for pos in [0, n_train). */
 MASCOT_API int mascot_get_stream_order(mascot_handle* h, uint32_t* src_out);
